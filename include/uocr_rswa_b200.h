@@ -1,0 +1,201 @@
+/*
+ * C ABI of the B200-native R-SWA KV-cache path (libuocr_rswa_b200.so).
+ *
+ * Every entry point takes plain pointers and sizes, launches hand-written sm_100a kernels on the
+ * caller's stream and returns an int status (0 = ok).  Nothing here allocates device memory except
+ * the explicit *_create calls; nothing synchronises the stream except the calls documented to do
+ * so.  All launch entry points are safe inside CUDA-graph stream capture.
+ *
+ * Each declaration names the reference interface it stands in for (paths relative to the root of
+ * vaachang/unlimited-ocr.cpp).  Two families exist for every operation:
+ *
+ *   *_f32   -- the reference's own memory layout: contiguous fp32 caches
+ *              [slots][batch_cap][kv_heads*head_dim], argument lists identical to the reference's
+ *              uocr::cuda::rswa_* functions plus a workspace handle where scratch is needed.
+ *   *_paged -- the paged layout this library adds underneath the same semantics: a block pool of
+ *              16-token blocks (bf16 or fp32 payload), a per-slot block table whose row lists the
+ *              (shareable) prefix blocks first and the private ring blocks after them.
+ *
+ * Logical view (what parity is defined on): slot s of a sequence is prefix token s for s < P and
+ * ring slot s - P otherwise; physically, token s < P lives in block table[s / 16] at offset s % 16
+ * and ring slot r in block table[ceil(P / 16) + r / 16] at offset r % 16.
+ */
+#ifndef UOCR_RSWA_B200_H
+#define UOCR_RSWA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define UOCR_B200_API __attribute__((visibility("default")))
+#else
+#define UOCR_B200_API
+#endif
+
+/* A cudaStream_t, spelled without including the CUDA headers. */
+typedef struct CUstream_st* uocr_b200_stream_t;
+
+enum {
+    UOCR_B200_OK = 0,
+    UOCR_B200_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, ...)            */
+    UOCR_B200_ERR_UNSUPPORTED = 2, /* geometry outside what the kernels are built for           */
+    UOCR_B200_ERR_CUDA = 3,        /* a CUDA runtime call or launch failed; see last_error()     */
+    UOCR_B200_ERR_WORKSPACE = 4,   /* workspace too small for this call                          */
+    UOCR_B200_ERR_NO_DEVICE = 5,   /* no usable CUDA device / not an sm_100 part                 */
+    UOCR_B200_ERR_DEVICE_STATUS = 6, /* a kernel recorded a fault (bad block id, wait ran out)  */
+    UOCR_B200_ERR_EXHAUSTED = 7    /* host allocator: pool exhausted                             */
+};
+
+/* KV payload types; numeric values match uocr::DType (include/uocr/common.h:17-26). */
+enum { UOCR_B200_F32 = 0, UOCR_B200_BF16 = 1 };
+
+#define UOCR_B200_BLOCK_TOKENS 16
+
+UOCR_B200_API const char* uocr_b200_status_string(int status);
+/* Message of the most recent failure on the calling thread ("" when none). */
+UOCR_B200_API const char* uocr_b200_last_error(void);
+/* Library / build identification, e.g. "uocr_rswa_b200 0.1 sm_100a". */
+UOCR_B200_API const char* uocr_b200_version(void);
+/* Number of kernels this library has launched in this process (all entry points). */
+UOCR_B200_API uint64_t uocr_b200_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Scratch for split-KV attention.  One workspace serves one stream at a time.
+ * Replaces: nothing (the reference kernels need no scratch: one CTA walks a whole (query, head)
+ * serially, src/kernels/cuda/rswa_attention.cu:82-148).
+ * --------------------------------------------------------------------------------------------- */
+typedef struct uocr_b200_workspace uocr_b200_workspace;
+/* max_rows = largest number of query rows (batch, or packed prefill tokens) of any later call. */
+UOCR_B200_API int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out);
+UOCR_B200_API int uocr_b200_workspace_destroy(uocr_b200_workspace* ws);
+/* Synchronises `stream`, reads and clears the device status word (0 = no kernel reported a fault). */
+UOCR_B200_API int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_stream_t stream,
+                                             int* device_status);
+
+/* ------------------------------------------------------------------------------------------------
+ * Paged KV view of ONE layer.
+ * Replaces: the per-layer buffers `batch_k_[li]`, `batch_v_[li]` + `batch_cap_` addressing
+ * (src/engine/gpu_decoder.cu:904-970; base + slot*batch_cap*stride in
+ * src/kernels/cuda/rswa_attention.cu:98-99,234-235,297-298,332-333).
+ * --------------------------------------------------------------------------------------------- */
+typedef struct {
+    void* k_pool;               /* device, [num_blocks][kv_heads][16][head_dim] of dtype          */
+    void* v_pool;               /* same shape                                                      */
+    const int32_t* block_table; /* device, [slots][table_stride] physical block ids               */
+    int32_t table_stride;
+    int32_t num_blocks;
+    int32_t kv_heads;
+    int32_t head_dim;           /* power of two, 8..256 (bf16) or 4..256 (fp32)                    */
+    int32_t dtype;              /* UOCR_B200_BF16 or UOCR_B200_F32                                 */
+} uocr_b200_paged_kv;
+
+/* ================================================================================================
+ * Append (ring state machine + row write)
+ * ============================================================================================= */
+
+/* Replaces uocr::cuda::rswa_append_decode_batch (include/uocr/cuda_ops.h:95-99;
+ * src/kernels/cuda/rswa_attention.cu:309-338,488-498).  Row b of k/v ([batch][kv_heads*head_dim]
+ * fp32) goes to slot d_slots[b]; d_len / d_ring_pos are that layer's per-slot cursors. */
+UOCR_B200_API int uocr_b200_rswa_append_decode_batch_f32(
+    const float* k, const float* v, float* kcache_base, float* vcache_base, int* d_len,
+    int* d_ring_pos, const int* d_prefill_len, const int* d_slots, int batch, int batch_cap,
+    int window, int kv_heads, int head_dim, uocr_b200_stream_t stream);
+
+/* Replaces uocr::cuda::rswa_append_decode (include/uocr/cuda_ops.h:84-86;
+ * src/kernels/cuda/rswa_attention.cu:458-486): one cache, device cursors. */
+UOCR_B200_API int uocr_b200_rswa_append_decode_f32(
+    const float* k, const float* v, float* kcache, float* vcache, int* d_len, int* d_ring_pos,
+    int prefill_len, int window, int kv_heads, int head_dim, uocr_b200_stream_t stream);
+
+/* Paged form of the batched append: same cursor semantics, the row is rounded to the pool dtype
+ * (bf16: nearest-even on the raw bits, include/uocr/common.h:56-64) and written through the block
+ * table.  `status` may be null; otherwise out-of-range block ids are recorded there. */
+UOCR_B200_API int uocr_b200_rswa_append_decode_batch_paged(
+    const uocr_b200_paged_kv* kv, const float* k, const float* v, int* d_len, int* d_ring_pos,
+    const int* d_prefill_len, const int* d_slots, int batch, int window,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+/* ================================================================================================
+ * Prefill scatter
+ * ============================================================================================= */
+
+/* Replaces uocr::cuda::rswa_write_prefill_ragged (include/uocr/cuda_ops.h:116-119;
+ * src/kernels/cuda/rswa_attention.cu:287-305,445-453): cache[d_slots[t]][d_pos[t]] <- row t. */
+UOCR_B200_API int uocr_b200_rswa_write_prefill_ragged_f32(
+    const float* k, const float* v, float* kcache_base, float* vcache_base, const int* d_slots,
+    const int* d_pos, int total, int batch_cap, int kv_heads, int head_dim,
+    uocr_b200_stream_t stream);
+
+/* Paged form: d_pos[t] is a logical slot of the fixed region (0 <= pos < P of that slot). */
+UOCR_B200_API int uocr_b200_rswa_write_prefill_ragged_paged(
+    const uocr_b200_paged_kv* kv, const float* k, const float* v, const int* d_slots,
+    const int* d_pos, int total, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+/* ================================================================================================
+ * Attention.  q / out are fp32 [rows][heads*head_dim]; scale = 1/sqrt(head_dim); out = 0 for a row
+ * that attends nothing.  All forms run the same split-KV kernels: a plan kernel, a persistent
+ * partial-attention kernel fed by bulk async copies, and a merge kernel.
+ * ============================================================================================= */
+
+/* Replaces uocr::cuda::rswa_attention_batch (include/uocr/cuda_ops.h:104-107;
+ * src/kernels/cuda/rswa_attention.cu:82-148,401-421). */
+UOCR_B200_API int uocr_b200_rswa_attention_batch_f32(
+    const float* q, const float* kcache_base, const float* vcache_base, const int* d_len,
+    const int* d_slots, int batch, int batch_cap, int heads, int kv_heads, int head_dim, float* out,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+UOCR_B200_API int uocr_b200_rswa_attention_batch_paged(
+    const uocr_b200_paged_kv* kv, const float* q, const int* d_len, const int* d_prefill_len,
+    const int* d_slots, int batch, int heads, float* out, uocr_b200_workspace* ws,
+    uocr_b200_stream_t stream);
+
+/* Replaces uocr::cuda::rswa_attention_ragged (include/uocr/cuda_ops.h:120-123;
+ * src/kernels/cuda/rswa_attention.cu:218-284,423-443): packed row t attends rows [0, d_pos[t]] of
+ * slot d_slots[t]. */
+UOCR_B200_API int uocr_b200_rswa_attention_ragged_f32(
+    const float* q, const float* kcache_base, const float* vcache_base, const int* d_slots,
+    const int* d_pos, int total, int batch_cap, int heads, int kv_heads, int head_dim, float* out,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+UOCR_B200_API int uocr_b200_rswa_attention_ragged_paged(
+    const uocr_b200_paged_kv* kv, const float* q, const int* d_prefill_len, const int* d_slots,
+    const int* d_pos, int total, int heads, float* out, uocr_b200_workspace* ws,
+    uocr_b200_stream_t stream);
+
+/* Replaces uocr::cuda::rswa_attention and rswa_attention_decode (include/uocr/cuda_ops.h:61-72;
+ * src/kernels/cuda/rswa_attention.cu:152-214,342-379) and rswa_attention_devlen (:77-80, :381-399)
+ * in one call: one cache, `seq` queries from absolute position q_start; when causal, query s sees
+ * slots [0, min(len, q_start+s+1)).  The length is *d_len when d_len is non-null, else kv_len.
+ * (Unlike the reference's devlen variant, any seq is handled, not just seq == 1.) */
+UOCR_B200_API int uocr_b200_rswa_attention_f32(
+    const float* q, const float* kcache, const float* vcache, int kv_len, const int* d_len, int seq,
+    int q_start, int heads, int kv_heads, int head_dim, int causal, float* out,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+/* Paged form for one slot: length from d_len[slot] when d_len is non-null else kv_len; the fixed
+ * region length from d_prefill_len[slot] when non-null else prefill_len. */
+UOCR_B200_API int uocr_b200_rswa_attention_paged(
+    const uocr_b200_paged_kv* kv, int slot, const float* q, int kv_len, const int* d_len,
+    int prefill_len, const int* d_prefill_len, int seq, int q_start, int heads, int causal,
+    float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+/* ================================================================================================
+ * Block-table gather: paged storage -> the reference's logical view
+ * Replaces: nothing in the reference (it has no block table, include/uocr/block_manager.h:11-13);
+ * reproduces RSWACache::keys(l) / values(l) (include/uocr/kv_cache.h:64-66) for `n` slots:
+ * out[i] is [capacity_rows][kv_heads*head_dim], rows >= len are zero.  out_dtype is F32 (widened)
+ * or the pool dtype (raw copy).
+ * ============================================================================================= */
+UOCR_B200_API int uocr_b200_rswa_gather_paged(
+    const uocr_b200_paged_kv* kv, const int* d_len, const int* d_prefill_len, const int* d_slots,
+    int n, int capacity_rows, void* out_k, void* out_v, int out_dtype, uocr_b200_workspace* ws,
+    uocr_b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UOCR_RSWA_B200_H */

@@ -1,0 +1,247 @@
+"""Python plumbing over the C ABI of libuocr_rswa_b200.so (tests and benchmark only).
+
+The product is the shared library (hand-written sm_100a kernels behind `include/uocr_rswa_b200.h`)
+plus the C++17 host classes under `include/uocr/`.  This module only loads the library with ctypes,
+mirrors the structs of the header, and offers thin wrappers that take torch CUDA tensors (used here
+purely as device-memory handles) and launch on torch's current stream.  There is no fallback: if
+the library is missing or a call fails, an exception is raised.
+
+The directory name is not a Python identifier; load it with
+
+    importlib.util.spec_from_file_location("uocr_b200", "<repo>/unlimited-ocr.cpp_b200/__init__.py")
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+LIB_PATH = os.path.join(HERE, "libuocr_rswa_b200.so")
+
+F32, BF16 = 0, 1
+BLOCK_TOKENS = 16
+STATUS_BAD_BLOCK, STATUS_WAIT_TIMEOUT, STATUS_BAD_SLOT = 1, 2, 4
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
+
+
+def sources():
+    csrc = os.path.join(HERE, "csrc")
+    return sorted(os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cu", ".cpp")))
+
+
+def build(verbose: bool = False) -> str:
+    """Compile every source under csrc/ for sm_100a into libuocr_rswa_b200.so (in-tree)."""
+    cmd = ["nvcc", *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", os.path.join(HERE, "include"),
+           "-I", os.path.join(HERE, "csrc"), "-o", LIB_PATH, *sources()]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return LIB_PATH
+
+
+class PagedKV(C.Structure):
+    """uocr_b200_paged_kv"""
+    _fields_ = [("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("block_table", C.c_void_p),
+                ("table_stride", C.c_int32), ("num_blocks", C.c_int32), ("kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("dtype", C.c_int32)]
+
+
+class Error(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__(f"uocr_b200 status {status}: {msg}")
+        self.status = status
+
+
+_LIB = None
+
+_vp, _i, _i64 = C.c_void_p, C.c_int, C.c_int64
+_SIGS = {
+    "uocr_b200_status_string": (C.c_char_p, [_i]),
+    "uocr_b200_last_error": (C.c_char_p, []),
+    "uocr_b200_version": (C.c_char_p, []),
+    "uocr_b200_launch_count": (C.c_uint64, []),
+    "uocr_b200_workspace_create": (_i, [_i, C.POINTER(_vp)]),
+    "uocr_b200_workspace_destroy": (_i, [_vp]),
+    "uocr_b200_workspace_status": (_i, [_vp, _vp, C.POINTER(_i)]),
+    "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
+    "uocr_b200_rswa_append_decode_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
+    "uocr_b200_rswa_append_decode_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 6 + [_i, _i, _vp, _vp]),
+    "uocr_b200_rswa_write_prefill_ragged_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
+    "uocr_b200_rswa_write_prefill_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _vp, _vp]),
+    "uocr_b200_rswa_attention_batch_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
+    "uocr_b200_rswa_attention_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_attention_ragged_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
+    "uocr_b200_rswa_attention_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_attention_f32": (_i, [_vp] * 3 + [_i, _vp] + [_i] * 6 + [_vp, _vp, _vp]),
+    "uocr_b200_rswa_attention_paged": (_i, [C.POINTER(PagedKV), _i, _vp, _i, _vp, _i, _vp] + [_i] * 4 + [_vp, _vp, _vp]),
+    "uocr_b200_rswa_gather_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 3 + [_i, _i, _vp, _vp, _i, _vp, _vp]),
+}
+
+
+def declared_symbols():
+    """Names of every function declared in include/uocr_rswa_b200.h (parsed from the header)."""
+    import re
+    out = []
+    for name in ("uocr_rswa_b200.h",):
+        text = open(os.path.join(ROOT, "include", name)).read()
+        out += re.findall(r"UOCR_B200_API\s+[\w\s\*]+?\b(uocr_b200_\w+)\s*\(", text)
+    return sorted(set(out))
+
+
+def lib() -> C.CDLL:
+    """Load the shared library (never builds it: a missing library is an error on a GPU box)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(f"{LIB_PATH} is missing: run __graft_entry__.build() first "
+                                    "(there is no Python or CPU fallback for the CUDA path)")
+        L = C.CDLL(LIB_PATH, mode=os.RTLD_LOCAL)
+        for name, (res, args) in _SIGS.items():
+            f = getattr(L, name)
+            f.restype, f.argtypes = res, args
+        _LIB = L
+    return _LIB
+
+
+def check(status: int) -> None:
+    if status != 0:
+        L = lib()
+        raise Error(status, f"{L.uocr_b200_status_string(status).decode()}: {L.uocr_b200_last_error().decode()}")
+
+
+def _p(t):
+    """Device (or host) address of a torch tensor / numpy array / None."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    return t.ctypes.data
+
+
+def stream_handle(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+class Workspace:
+    def __init__(self, max_rows: int):
+        h = _vp()
+        check(lib().uocr_b200_workspace_create(max_rows, C.byref(h)))
+        self.h = h
+
+    def status(self, stream=None) -> int:
+        v = _i(0)
+        check(lib().uocr_b200_workspace_status(self.h, stream_handle(stream), C.byref(v)))
+        return v.value
+
+    def close(self):
+        if self.h:
+            lib().uocr_b200_workspace_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def launch_count() -> int:
+    return int(lib().uocr_b200_launch_count())
+
+
+class PagedLayer:
+    """Device storage of one layer's paged KV plus the descriptor the C ABI takes."""
+
+    def __init__(self, num_blocks, kv_heads, head_dim, dtype, table, device="cuda"):
+        import torch
+        self.dtype = dtype
+        tdt = torch.bfloat16 if dtype == BF16 else torch.float32
+        shape = (num_blocks, kv_heads, BLOCK_TOKENS, head_dim)
+        self.k = torch.zeros(shape, dtype=tdt, device=device)
+        self.v = torch.zeros(shape, dtype=tdt, device=device)
+        self.table = table  # int32 [slots, stride], shared between layers
+        self.desc = PagedKV(self.k.data_ptr(), self.v.data_ptr(), table.data_ptr(), table.shape[1],
+                            num_blocks, kv_heads, head_dim, dtype)
+
+    def ref(self):
+        return C.byref(self.desc)
+
+
+# ---- thin call wrappers (torch tensors in, status checked) ---------------------------------------
+
+def append_decode_batch_paged(layer, k, v, d_len, d_ring, d_prefill, d_slots, batch, window, ws=None, stream=None):
+    check(lib().uocr_b200_rswa_append_decode_batch_paged(layer.ref(), _p(k), _p(v), _p(d_len), _p(d_ring),
+                                                          _p(d_prefill), _p(d_slots), batch, window,
+                                                          ws.h if ws else None, stream_handle(stream)))
+
+
+def attention_batch_paged(layer, q, d_len, d_prefill, d_slots, batch, heads, out, ws, stream=None):
+    check(lib().uocr_b200_rswa_attention_batch_paged(layer.ref(), _p(q), _p(d_len), _p(d_prefill), _p(d_slots),
+                                                      batch, heads, _p(out), ws.h, stream_handle(stream)))
+
+
+def write_prefill_ragged_paged(layer, k, v, d_slots, d_pos, total, ws=None, stream=None):
+    check(lib().uocr_b200_rswa_write_prefill_ragged_paged(layer.ref(), _p(k), _p(v), _p(d_slots), _p(d_pos), total,
+                                                           ws.h if ws else None, stream_handle(stream)))
+
+
+def attention_ragged_paged(layer, q, d_prefill, d_slots, d_pos, total, heads, out, ws, stream=None):
+    check(lib().uocr_b200_rswa_attention_ragged_paged(layer.ref(), _p(q), _p(d_prefill), _p(d_slots), _p(d_pos),
+                                                       total, heads, _p(out), ws.h, stream_handle(stream)))
+
+
+def attention_paged(layer, slot, q, kv_len, d_len, prefill_len, d_prefill, seq, q_start, heads, causal, out, ws,
+                    stream=None):
+    check(lib().uocr_b200_rswa_attention_paged(layer.ref(), slot, _p(q), kv_len, _p(d_len), prefill_len,
+                                                _p(d_prefill), seq, q_start, heads, 1 if causal else 0, _p(out),
+                                                ws.h, stream_handle(stream)))
+
+
+def gather_paged(layer, d_len, d_prefill, d_slots, n, capacity_rows, out_k, out_v, out_dtype, ws=None, stream=None):
+    check(lib().uocr_b200_rswa_gather_paged(layer.ref(), _p(d_len), _p(d_prefill), _p(d_slots), n, capacity_rows,
+                                             _p(out_k), _p(out_v), out_dtype, ws.h if ws else None,
+                                             stream_handle(stream)))
+
+
+def append_decode_batch_f32(k, v, kbase, vbase, d_len, d_ring, d_prefill, d_slots, batch, batch_cap, window,
+                            kv_heads, head_dim, stream=None):
+    check(lib().uocr_b200_rswa_append_decode_batch_f32(_p(k), _p(v), _p(kbase), _p(vbase), _p(d_len), _p(d_ring),
+                                                        _p(d_prefill), _p(d_slots), batch, batch_cap, window,
+                                                        kv_heads, head_dim, stream_handle(stream)))
+
+
+def append_decode_f32(k, v, kcache, vcache, d_len, d_ring, prefill_len, window, kv_heads, head_dim, stream=None):
+    check(lib().uocr_b200_rswa_append_decode_f32(_p(k), _p(v), _p(kcache), _p(vcache), _p(d_len), _p(d_ring),
+                                                  prefill_len, window, kv_heads, head_dim, stream_handle(stream)))
+
+
+def write_prefill_ragged_f32(k, v, kbase, vbase, d_slots, d_pos, total, batch_cap, kv_heads, head_dim, stream=None):
+    check(lib().uocr_b200_rswa_write_prefill_ragged_f32(_p(k), _p(v), _p(kbase), _p(vbase), _p(d_slots), _p(d_pos),
+                                                         total, batch_cap, kv_heads, head_dim, stream_handle(stream)))
+
+
+def attention_batch_f32(q, kbase, vbase, d_len, d_slots, batch, batch_cap, heads, kv_heads, head_dim, out, ws,
+                        stream=None):
+    check(lib().uocr_b200_rswa_attention_batch_f32(_p(q), _p(kbase), _p(vbase), _p(d_len), _p(d_slots), batch,
+                                                    batch_cap, heads, kv_heads, head_dim, _p(out), ws.h,
+                                                    stream_handle(stream)))
+
+
+def attention_ragged_f32(q, kbase, vbase, d_slots, d_pos, total, batch_cap, heads, kv_heads, head_dim, out, ws,
+                         stream=None):
+    check(lib().uocr_b200_rswa_attention_ragged_f32(_p(q), _p(kbase), _p(vbase), _p(d_slots), _p(d_pos), total,
+                                                     batch_cap, heads, kv_heads, head_dim, _p(out), ws.h,
+                                                     stream_handle(stream)))
+
+
+def attention_f32(q, kcache, vcache, kv_len, d_len, seq, q_start, heads, kv_heads, head_dim, causal, out, ws,
+                  stream=None):
+    check(lib().uocr_b200_rswa_attention_f32(_p(q), _p(kcache), _p(vcache), kv_len, _p(d_len), seq, q_start, heads,
+                                              kv_heads, head_dim, 1 if causal else 0, _p(out), ws.h,
+                                              stream_handle(stream)))

@@ -1,0 +1,521 @@
+// extern "C" boundary of libuocr_rswa_b200.so: argument checking, geometry dispatch and kernel
+// launches.  No entry point here allocates (except workspace_create), synchronises (except
+// workspace_status) or falls back to host code.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "rswa_attention.cuh"
+#include "rswa_copy.cuh"
+#include "uocr_rswa_b200.h"
+
+using namespace uocr_b200;
+
+namespace {
+
+thread_local std::string g_last_error;
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(UOCR_B200_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define CHECK_CUDA(expr, what)                             \
+    do {                                                   \
+        cudaError_t e_ = (expr);                           \
+        if (e_ != cudaSuccess) return cuda_fail(e_, what); \
+    } while (0)
+
+int after_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    return UOCR_B200_OK;
+}
+
+struct DeviceInfo {
+    bool known = false;
+    int sms = 0;
+    int smem_optin = 0;
+    int cc_major = 0;
+};
+DeviceInfo g_dev[64];
+
+int device_info(const DeviceInfo** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(UOCR_B200_ERR_NO_DEVICE, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(UOCR_B200_ERR_NO_DEVICE, "device ordinal out of range");
+    DeviceInfo& d = g_dev[dev];
+    if (!d.known) {
+        CHECK_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev), "sm count");
+        CHECK_CUDA(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev), "smem optin");
+        CHECK_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev), "cc major");
+        if (d.cc_major != 10)
+            return fail(UOCR_B200_ERR_NO_DEVICE, "this library only carries sm_100a code (B200)");
+        d.known = true;
+    }
+    *out = &d;
+    return UOCR_B200_OK;
+}
+
+constexpr int kStages = 2;
+constexpr int kMaxWarpsPerCta = 16;
+constexpr int kMaxHeadDim = 256;
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool head_dim_ok(int hd, int dtype) {
+    if (hd < (dtype == UOCR_B200_BF16 ? 8 : 4) || hd > kMaxHeadDim) return false;
+    return (hd & (hd - 1)) == 0;
+}
+
+}  // namespace
+
+// =================================================================================================
+// workspace
+// =================================================================================================
+struct uocr_b200_workspace {
+    int device = 0;
+    int max_rows = 0;
+    int total_warps_max = 0;
+    uint8_t* base = nullptr;
+    size_t bytes = 0;
+    int* status = nullptr;
+    int* rs = nullptr;
+    RowInfo* info = nullptr;
+    float* part_acc = nullptr;
+    float* part_ml = nullptr;
+};
+
+extern "C" {
+
+const char* uocr_b200_status_string(int s) {
+    switch (s) {
+        case UOCR_B200_OK: return "ok";
+        case UOCR_B200_ERR_INVALID: return "invalid argument";
+        case UOCR_B200_ERR_UNSUPPORTED: return "unsupported geometry";
+        case UOCR_B200_ERR_CUDA: return "CUDA error";
+        case UOCR_B200_ERR_WORKSPACE: return "workspace too small";
+        case UOCR_B200_ERR_NO_DEVICE: return "no usable sm_100 device";
+        case UOCR_B200_ERR_DEVICE_STATUS: return "device-side fault recorded";
+        case UOCR_B200_ERR_EXHAUSTED: return "pool exhausted";
+        default: return "unknown status";
+    }
+}
+
+const char* uocr_b200_last_error(void) { return g_last_error.c_str(); }
+const char* uocr_b200_version(void) { return "uocr_rswa_b200 0.1 sm_100a"; }
+uint64_t uocr_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
+    if (!out || max_rows <= 0) return fail(UOCR_B200_ERR_INVALID, "workspace_create: bad arguments");
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+    auto* ws = new uocr_b200_workspace;
+    cudaGetDevice(&ws->device);
+    ws->max_rows = max_rows;
+    ws->total_warps_max = di->sms * kMaxWarpsPerCta;
+    auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+    const size_t o_status = 0;
+    const size_t o_rs = up(256);
+    const size_t o_info = o_rs + up(sizeof(int) * (size_t)(max_rows + 1));
+    const size_t o_acc = o_info + up(sizeof(RowInfo) * (size_t)max_rows);
+    const size_t o_ml = o_acc + up(sizeof(float) * 2 * (size_t)ws->total_warps_max * kMaxHeadDim);
+    ws->bytes = o_ml + up(sizeof(float) * 4 * (size_t)ws->total_warps_max);
+    cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
+    if (e != cudaSuccess) {
+        delete ws;
+        return cuda_fail(e, "workspace cudaMalloc");
+    }
+    e = cudaMemset(ws->base, 0, ws->bytes);
+    if (e != cudaSuccess) {
+        cudaFree(ws->base);
+        delete ws;
+        return cuda_fail(e, "workspace cudaMemset");
+    }
+    ws->status = reinterpret_cast<int*>(ws->base + o_status);
+    ws->rs = reinterpret_cast<int*>(ws->base + o_rs);
+    ws->info = reinterpret_cast<RowInfo*>(ws->base + o_info);
+    ws->part_acc = reinterpret_cast<float*>(ws->base + o_acc);
+    ws->part_ml = reinterpret_cast<float*>(ws->base + o_ml);
+    *out = ws;
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_destroy(uocr_b200_workspace* ws) {
+    if (!ws) return UOCR_B200_OK;
+    if (ws->base) cudaFree(ws->base);
+    delete ws;
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_stream_t stream, int* device_status) {
+    if (!ws || !device_status) return fail(UOCR_B200_ERR_INVALID, "workspace_status: null argument");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int v = 0;
+    CHECK_CUDA(cudaMemcpyAsync(&v, ws->status, sizeof(int), cudaMemcpyDeviceToHost, st), "status D2H");
+    CHECK_CUDA(cudaMemsetAsync(ws->status, 0, sizeof(int), st), "status clear");
+    CHECK_CUDA(cudaStreamSynchronize(st), "status sync");
+    *device_status = v;
+    return UOCR_B200_OK;
+}
+
+}  // extern "C"
+
+// =================================================================================================
+// attention dispatch
+// =================================================================================================
+namespace {
+
+struct AttnCall {
+    // layout
+    bool paged = false;
+    int dtype = UOCR_B200_F32;
+    const void* k_base = nullptr;
+    const void* v_base = nullptr;
+    const int32_t* table = nullptr;
+    int table_stride = 0, num_blocks = 0;
+    long long slot_stride_elems = 0;
+    // geometry
+    int rows = 0, heads = 0, kv_heads = 0, head_dim = 0;
+    const float* q = nullptr;
+    float* out = nullptr;
+    PlanParams plan{};
+};
+
+template <typename KV, int HD, bool PAGED>
+int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, cudaStream_t st, bool dry) {
+    using M = TileMap<KV, HD>;
+    constexpr int per_warp = kStages * 2 * M::kTileBytes;
+    const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024;
+    int warps = budget / per_warp;
+    if (warps > kMaxWarpsPerCta) warps = kMaxWarpsPerCta;
+    if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
+    *warps_used = warps;
+    if (dry) return UOCR_B200_OK;
+    const int bar_bytes = (warps * kStages * 2 * 8 + 127) & ~127;
+    const int smem = bar_bytes + warps * per_warp;
+    auto kern = rswa_attn_partial_kernel<KV, HD, PAGED, kStages>;
+    static int configured_smem[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_smem[dev] < smem) {
+        CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "smem attribute");
+        configured_smem[dev] = smem;
+    }
+    kern<<<di.sms, warps * 32, smem, st>>>(ap);
+    return after_launch("attention partial kernel");
+}
+
+template <typename KV, bool PAGED>
+int dispatch_hd(int hd, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry) {
+    switch (hd) {
+        case 8: return launch_partial<KV, 8, PAGED>(ap, di, warps, st, dry);
+        case 16: return launch_partial<KV, 16, PAGED>(ap, di, warps, st, dry);
+        case 32: return launch_partial<KV, 32, PAGED>(ap, di, warps, st, dry);
+        case 64: return launch_partial<KV, 64, PAGED>(ap, di, warps, st, dry);
+        case 128: return launch_partial<KV, 128, PAGED>(ap, di, warps, st, dry);
+        case 256: return launch_partial<KV, 256, PAGED>(ap, di, warps, st, dry);
+        case 4:
+            if constexpr (KV::kBytes == 4) return launch_partial<KV, 4, PAGED>(ap, di, warps, st, dry);
+            [[fallthrough]];
+        default: return fail(UOCR_B200_ERR_UNSUPPORTED, "head_dim must be a power of two in [8,256] (bf16) or [4,256] (fp32)");
+    }
+}
+
+int dispatch_partial(const AttnCall& c, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry) {
+    if (c.paged) {
+        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true>(c.head_dim, ap, di, warps, st, dry);
+        return dispatch_hd<F32, true>(c.head_dim, ap, di, warps, st, dry);
+    }
+    return dispatch_hd<F32, false>(c.head_dim, ap, di, warps, st, dry);
+}
+
+int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
+    if (c.rows <= 0) return UOCR_B200_OK;  // the reference wrappers return early on empty batches
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "attention: workspace is null");
+    if (!c.q || !c.out || !c.k_base || !c.v_base) return fail(UOCR_B200_ERR_INVALID, "attention: null pointer");
+    if (c.heads <= 0 || c.kv_heads <= 0 || c.heads % c.kv_heads != 0)
+        return fail(UOCR_B200_ERR_INVALID, "attention: heads must be a positive multiple of kv_heads");
+    if (!head_dim_ok(c.head_dim, c.dtype)) return fail(UOCR_B200_ERR_UNSUPPORTED, "attention: unsupported head_dim");
+    if (!aligned16(c.q) || !aligned16(c.out) || !aligned16(c.k_base) || !aligned16(c.v_base))
+        return fail(UOCR_B200_ERR_INVALID, "attention: q/out/cache pointers must be 16-byte aligned");
+    if (c.rows > ws->max_rows) return fail(UOCR_B200_ERR_WORKSPACE, "attention: more rows than the workspace was created for");
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+
+    AttnParams ap{};
+    ap.q = c.q;
+    ap.out = c.out;
+    ap.k_base = static_cast<const uint8_t*>(c.k_base);
+    ap.v_base = static_cast<const uint8_t*>(c.v_base);
+    ap.table = c.table;
+    ap.table_stride = c.table_stride;
+    ap.num_blocks = c.num_blocks;
+    ap.slot_stride_bytes = c.slot_stride_elems * 4;
+    ap.row_stride_bytes = c.kv_heads * c.head_dim * 4;
+    ap.rows = c.rows;
+    ap.heads = c.heads;
+    ap.kv_heads = c.kv_heads;
+    ap.group = c.heads / c.kv_heads;
+    ap.scale_log2e = (1.0f / std::sqrt(static_cast<float>(c.head_dim))) * 1.4426950408889634f;
+    ap.rs = ws->rs;
+    ap.info = ws->info;
+    ap.part_acc = ws->part_acc;
+    ap.part_ml = ws->part_ml;
+    ap.status = ws->status;
+
+    int warps = 0;
+    if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/true)) return rc;
+    ap.total_warps = di->sms * warps;
+    if (ap.total_warps > ws->total_warps_max) return fail(UOCR_B200_ERR_WORKSPACE, "attention: workspace built for a smaller device");
+
+    c.plan.rows = c.rows;
+    c.plan.heads = c.heads;
+    c.plan.paged = c.paged ? 1 : 0;
+    c.plan.rs = ws->rs;
+    c.plan.info = ws->info;
+    int pthreads = c.rows < 1024 ? ((c.rows + 31) & ~31) : 1024;
+    rswa_plan_kernel<<<1, pthreads, 0, st>>>(c.plan);
+    if (int rc = after_launch("plan kernel")) return rc;
+
+    if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/false)) return rc;
+
+    const int items = c.rows * c.heads;
+    rswa_attn_merge_kernel<<<(items + 7) / 8, 256, 0, st>>>(ap, c.head_dim);
+    return after_launch("merge kernel");
+}
+
+int fill_paged(AttnCall& c, const uocr_b200_paged_kv* kv) {
+    if (!kv) return fail(UOCR_B200_ERR_INVALID, "paged view is null");
+    if (kv->dtype != UOCR_B200_BF16 && kv->dtype != UOCR_B200_F32) return fail(UOCR_B200_ERR_UNSUPPORTED, "paged dtype must be bf16 or fp32");
+    if (!kv->block_table || kv->table_stride <= 0 || kv->num_blocks <= 0) return fail(UOCR_B200_ERR_INVALID, "paged view: bad block table");
+    c.paged = true;
+    c.dtype = kv->dtype;
+    c.k_base = kv->k_pool;
+    c.v_base = kv->v_pool;
+    c.table = kv->block_table;
+    c.table_stride = kv->table_stride;
+    c.num_blocks = kv->num_blocks;
+    c.kv_heads = kv->kv_heads;
+    c.head_dim = kv->head_dim;
+    return UOCR_B200_OK;
+}
+
+int paged_view(const uocr_b200_paged_kv* kv, PagedView* pv) {
+    if (!kv || !kv->k_pool || !kv->v_pool || !kv->block_table) return fail(UOCR_B200_ERR_INVALID, "paged view: null pointer");
+    if (kv->dtype != UOCR_B200_BF16 && kv->dtype != UOCR_B200_F32) return fail(UOCR_B200_ERR_UNSUPPORTED, "paged dtype must be bf16 or fp32");
+    if (!head_dim_ok(kv->head_dim, kv->dtype) || kv->kv_heads <= 0) return fail(UOCR_B200_ERR_UNSUPPORTED, "paged view: unsupported head geometry");
+    if (!aligned16(kv->k_pool) || !aligned16(kv->v_pool)) return fail(UOCR_B200_ERR_INVALID, "paged view: pools must be 16-byte aligned");
+    pv->k_pool = static_cast<uint8_t*>(kv->k_pool);
+    pv->v_pool = static_cast<uint8_t*>(kv->v_pool);
+    pv->table = kv->block_table;
+    pv->table_stride = kv->table_stride;
+    pv->num_blocks = kv->num_blocks;
+    pv->kv_heads = kv->kv_heads;
+    pv->head_dim = kv->head_dim;
+    return UOCR_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- append ---------------------------------------------------------------------------------------
+int uocr_b200_rswa_append_decode_batch_f32(const float* k, const float* v, float* kbase, float* vbase,
+                                           int* d_len, int* d_ring_pos, const int* d_prefill_len,
+                                           const int* d_slots, int batch, int batch_cap, int window,
+                                           int kv_heads, int head_dim, uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    if (!k || !v || !kbase || !vbase || !d_len || !d_ring_pos || !d_prefill_len || !d_slots)
+        return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_f32: null pointer");
+    if (window <= 0 || kv_heads <= 0 || head_dim <= 0 || batch_cap <= 0) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_f32: bad geometry");
+    int stride = kv_heads * head_dim;
+    const bool vec = (stride % 4 == 0) && aligned16(k) && aligned16(v) && aligned16(kbase) && aligned16(vbase);
+    rswa_append_f32_kernel<<<batch, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        k, v, kbase, vbase, d_len, d_ring_pos, d_prefill_len, d_slots, 0, batch_cap, window,
+        vec ? stride : -stride);
+    return after_launch("append (fp32, batched)");
+}
+
+int uocr_b200_rswa_append_decode_f32(const float* k, const float* v, float* kcache, float* vcache,
+                                     int* d_len, int* d_ring_pos, int prefill_len, int window,
+                                     int kv_heads, int head_dim, uocr_b200_stream_t stream) {
+    if (!k || !v || !kcache || !vcache || !d_len || !d_ring_pos) return fail(UOCR_B200_ERR_INVALID, "append_decode_f32: null pointer");
+    if (window <= 0 || kv_heads <= 0 || head_dim <= 0 || prefill_len < 0) return fail(UOCR_B200_ERR_INVALID, "append_decode_f32: bad geometry");
+    int stride = kv_heads * head_dim;
+    const bool vec = (stride % 4 == 0) && aligned16(k) && aligned16(v) && aligned16(kcache) && aligned16(vcache);
+    rswa_append_f32_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        k, v, kcache, vcache, d_len, d_ring_pos, nullptr, nullptr, prefill_len, 0, window,
+        vec ? stride : -stride);
+    return after_launch("append (fp32, single)");
+}
+
+int uocr_b200_rswa_append_decode_batch_paged(const uocr_b200_paged_kv* kv, const float* k, const float* v,
+                                             int* d_len, int* d_ring_pos, const int* d_prefill_len,
+                                             const int* d_slots, int batch, int window,
+                                             uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!k || !v || !d_len || !d_ring_pos || !d_prefill_len || !d_slots) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_paged: null pointer");
+    if (!aligned16(k) || !aligned16(v)) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_paged: k/v must be 16-byte aligned");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_paged: window must be positive");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_append_paged_kernel<BF16><<<batch, 256, 0, st>>>(pv, k, v, d_len, d_ring_pos, d_prefill_len, d_slots, window, status);
+    else
+        rswa_append_paged_kernel<F32><<<batch, 256, 0, st>>>(pv, k, v, d_len, d_ring_pos, d_prefill_len, d_slots, window, status);
+    return after_launch("append (paged)");
+}
+
+// ---- prefill scatter --------------------------------------------------------------------------------
+int uocr_b200_rswa_write_prefill_ragged_f32(const float* k, const float* v, float* kbase, float* vbase,
+                                            const int* d_slots, const int* d_pos, int total, int batch_cap,
+                                            int kv_heads, int head_dim, uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    if (!k || !v || !kbase || !vbase || !d_slots || !d_pos) return fail(UOCR_B200_ERR_INVALID, "write_prefill_ragged_f32: null pointer");
+    if (kv_heads <= 0 || head_dim <= 0 || batch_cap <= 0) return fail(UOCR_B200_ERR_INVALID, "write_prefill_ragged_f32: bad geometry");
+    int stride = kv_heads * head_dim;
+    const bool vec = (stride % 4 == 0) && aligned16(k) && aligned16(v) && aligned16(kbase) && aligned16(vbase);
+    rswa_scatter_f32_kernel<<<total, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        k, v, kbase, vbase, d_slots, d_pos, batch_cap, vec ? stride : -stride);
+    return after_launch("prefill scatter (fp32)");
+}
+
+int uocr_b200_rswa_write_prefill_ragged_paged(const uocr_b200_paged_kv* kv, const float* k, const float* v,
+                                              const int* d_slots, const int* d_pos, int total,
+                                              uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!k || !v || !d_slots || !d_pos) return fail(UOCR_B200_ERR_INVALID, "write_prefill_ragged_paged: null pointer");
+    if (!aligned16(k) || !aligned16(v)) return fail(UOCR_B200_ERR_INVALID, "write_prefill_ragged_paged: k/v must be 16-byte aligned");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_scatter_paged_kernel<BF16><<<total, 256, 0, st>>>(pv, k, v, d_slots, d_pos, status);
+    else
+        rswa_scatter_paged_kernel<F32><<<total, 256, 0, st>>>(pv, k, v, d_slots, d_pos, status);
+    return after_launch("prefill scatter (paged)");
+}
+
+// ---- attention ----------------------------------------------------------------------------------------
+int uocr_b200_rswa_attention_batch_f32(const float* q, const float* kbase, const float* vbase, const int* d_len,
+                                       const int* d_slots, int batch, int batch_cap, int heads, int kv_heads,
+                                       int head_dim, float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    if (!d_len || !d_slots) return fail(UOCR_B200_ERR_INVALID, "attention_batch_f32: null index array");
+    AttnCall c;
+    c.k_base = kbase; c.v_base = vbase;
+    c.slot_stride_elems = (long long)batch_cap * kv_heads * head_dim;
+    c.rows = batch; c.heads = heads; c.kv_heads = kv_heads; c.head_dim = head_dim;
+    c.q = q; c.out = out;
+    c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uocr_b200_rswa_attention_batch_paged(const uocr_b200_paged_kv* kv, const float* q, const int* d_len,
+                                         const int* d_prefill_len, const int* d_slots, int batch, int heads,
+                                         float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    if (!d_len || !d_slots || !d_prefill_len) return fail(UOCR_B200_ERR_INVALID, "attention_batch_paged: null index array");
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.rows = batch; c.heads = heads; c.q = q; c.out = out;
+    c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_prefill_len = d_prefill_len;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uocr_b200_rswa_attention_ragged_f32(const float* q, const float* kbase, const float* vbase, const int* d_slots,
+                                        const int* d_pos, int total, int batch_cap, int heads, int kv_heads,
+                                        int head_dim, float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    if (!d_slots || !d_pos) return fail(UOCR_B200_ERR_INVALID, "attention_ragged_f32: null index array");
+    AttnCall c;
+    c.k_base = kbase; c.v_base = vbase;
+    c.slot_stride_elems = (long long)batch_cap * kv_heads * head_dim;
+    c.rows = total; c.heads = heads; c.kv_heads = kv_heads; c.head_dim = head_dim;
+    c.q = q; c.out = out;
+    c.plan.mode = kPlanRagged; c.plan.d_slots = d_slots; c.plan.d_pos = d_pos;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uocr_b200_rswa_attention_ragged_paged(const uocr_b200_paged_kv* kv, const float* q, const int* d_prefill_len,
+                                          const int* d_slots, const int* d_pos, int total, int heads, float* out,
+                                          uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    if (!d_slots || !d_pos || !d_prefill_len) return fail(UOCR_B200_ERR_INVALID, "attention_ragged_paged: null index array");
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.rows = total; c.heads = heads; c.q = q; c.out = out;
+    c.plan.mode = kPlanRagged; c.plan.d_slots = d_slots; c.plan.d_pos = d_pos; c.plan.d_prefill_len = d_prefill_len;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uocr_b200_rswa_attention_f32(const float* q, const float* kcache, const float* vcache, int kv_len, const int* d_len,
+                                 int seq, int q_start, int heads, int kv_heads, int head_dim, int causal, float* out,
+                                 uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (seq <= 0) return UOCR_B200_OK;
+    AttnCall c;
+    c.k_base = kcache; c.v_base = vcache;
+    c.slot_stride_elems = 0;
+    c.rows = seq; c.heads = heads; c.kv_heads = kv_heads; c.head_dim = head_dim;
+    c.q = q; c.out = out;
+    c.plan.mode = kPlanSingle; c.plan.fixed_slot = 0; c.plan.kv_len = kv_len; c.plan.d_len = d_len;
+    c.plan.q_start = q_start; c.plan.causal = causal ? 1 : 0;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uocr_b200_rswa_attention_paged(const uocr_b200_paged_kv* kv, int slot, const float* q, int kv_len, const int* d_len,
+                                   int prefill_len, const int* d_prefill_len, int seq, int q_start, int heads, int causal,
+                                   float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (seq <= 0) return UOCR_B200_OK;
+    if (slot < 0) return fail(UOCR_B200_ERR_INVALID, "attention_paged: negative slot");
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.rows = seq; c.heads = heads; c.q = q; c.out = out;
+    c.plan.mode = kPlanSingle; c.plan.fixed_slot = slot; c.plan.kv_len = kv_len; c.plan.d_len = d_len;
+    c.plan.prefill_len = prefill_len; c.plan.d_prefill_len = d_prefill_len;
+    c.plan.q_start = q_start; c.plan.causal = causal ? 1 : 0;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---- gather ---------------------------------------------------------------------------------------------
+int uocr_b200_rswa_gather_paged(const uocr_b200_paged_kv* kv, const int* d_len, const int* d_prefill_len,
+                                const int* d_slots, int n, int capacity_rows, void* out_k, void* out_v,
+                                int out_dtype, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (n <= 0 || capacity_rows <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!d_len || !d_prefill_len || !d_slots || !out_k || !out_v) return fail(UOCR_B200_ERR_INVALID, "gather_paged: null pointer");
+    if (!aligned16(out_k) || !aligned16(out_v)) return fail(UOCR_B200_ERR_INVALID, "gather_paged: outputs must be 16-byte aligned");
+    if (out_dtype != UOCR_B200_F32 && out_dtype != kv->dtype) return fail(UOCR_B200_ERR_UNSUPPORTED, "gather_paged: out_dtype must be fp32 or the pool dtype");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    dim3 grid(capacity_rows, n);
+    uint8_t* ok = static_cast<uint8_t*>(out_k);
+    uint8_t* ov = static_cast<uint8_t*>(out_v);
+    if (kv->dtype == UOCR_B200_BF16) {
+        if (out_dtype == UOCR_B200_F32)
+            rswa_gather_paged_kernel<BF16, true><<<grid, 160, 0, st>>>(pv, d_len, d_prefill_len, d_slots, capacity_rows, ok, ov, status);
+        else
+            rswa_gather_paged_kernel<BF16, false><<<grid, 160, 0, st>>>(pv, d_len, d_prefill_len, d_slots, capacity_rows, ok, ov, status);
+    } else {
+        rswa_gather_paged_kernel<F32, false><<<grid, 160, 0, st>>>(pv, d_len, d_prefill_len, d_slots, capacity_rows, ok, ov, status);
+    }
+    return after_launch("gather (paged)");
+}
+
+}  // extern "C"

@@ -1,0 +1,232 @@
+// Memory-movement kernels of the R-SWA path: ring append (state machine + row write), ragged
+// prefill scatter, and the block-table gather back to the reference's logical view.
+// All are pure HBM traffic: 16-byte vector accesses, one cache row (or row chunk) per thread group.
+#pragma once
+
+#include "rswa_device.cuh"
+
+namespace uocr_b200 {
+
+// The ring state machine of RSWACache::append_decode (src/scheduler/kv_cache.cpp:54-82) on device
+// cursors, as in rswa_append_batch_kernel (src/kernels/cuda/rswa_attention.cu:309-338) -- except
+// that exactly one thread reads and updates the cursors (the reference lets every thread of the
+// CTA do both without a barrier in between).  Returns the logical slot to write.
+__device__ __forceinline__ int ring_advance(int* len_p, int* ring_p, int prefill_len, int window) {
+    const int len = *len_p;
+    int row;
+    if (len < prefill_len + window) {
+        row = len;
+        *len_p = len + 1;
+        if (len + 1 >= prefill_len + window) *ring_p = 0;
+    } else {
+        const int rp = *ring_p;
+        row = prefill_len + rp;
+        *ring_p = (rp + 1) % window;
+    }
+    return row;
+}
+
+// ---- contiguous fp32 caches (the reference's own layout) ----------------------------------------
+__global__ void __launch_bounds__(256) rswa_append_f32_kernel(
+    const float* __restrict__ k, const float* __restrict__ v, float* __restrict__ kbase,
+    float* __restrict__ vbase, int* __restrict__ d_len, int* __restrict__ d_ring_pos,
+    const int* __restrict__ d_prefill_len, const int* __restrict__ d_slots, int fixed_prefill,
+    int batch_cap, int window, int signed_stride) {
+    // signed_stride > 0: rows and bases are 16-byte aligned, copy with float4; < 0: scalar copy
+    const bool vec = signed_stride > 0;
+    const int stride = vec ? signed_stride : -signed_stride;
+    __shared__ int s_row, s_slot;
+    const int b = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int slot = d_slots ? d_slots[b] : 0;
+        const int pfx = d_prefill_len ? d_prefill_len[slot] : fixed_prefill;
+        s_row = ring_advance(d_len + slot, d_ring_pos + slot, pfx, window);
+        s_slot = slot;
+    }
+    __syncthreads();
+    const size_t dst = ((size_t)s_slot * batch_cap + s_row) * stride;
+    const size_t src = (size_t)b * stride;
+    if (vec) {
+        const float4* k4 = reinterpret_cast<const float4*>(k + src);
+        const float4* v4 = reinterpret_cast<const float4*>(v + src);
+        float4* kd = reinterpret_cast<float4*>(kbase + dst);
+        float4* vd = reinterpret_cast<float4*>(vbase + dst);
+        for (int i = threadIdx.x; i < stride / 4; i += blockDim.x) {
+            kd[i] = __ldg(k4 + i);
+            vd[i] = __ldg(v4 + i);
+        }
+    } else {
+        for (int i = threadIdx.x; i < stride; i += blockDim.x) {
+            kbase[dst + i] = k[src + i];
+            vbase[dst + i] = v[src + i];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) rswa_scatter_f32_kernel(
+    const float* __restrict__ k, const float* __restrict__ v, float* __restrict__ kbase,
+    float* __restrict__ vbase, const int* __restrict__ d_slots, const int* __restrict__ d_pos,
+    int batch_cap, int signed_stride) {
+    const bool vec = signed_stride > 0;
+    const int stride = vec ? signed_stride : -signed_stride;
+    const int t = blockIdx.x;
+    const size_t dst = ((size_t)d_slots[t] * batch_cap + d_pos[t]) * stride;
+    const size_t src = (size_t)t * stride;
+    if (vec) {
+        const float4* k4 = reinterpret_cast<const float4*>(k + src);
+        const float4* v4 = reinterpret_cast<const float4*>(v + src);
+        float4* kd = reinterpret_cast<float4*>(kbase + dst);
+        float4* vd = reinterpret_cast<float4*>(vbase + dst);
+        for (int i = threadIdx.x; i < stride / 4; i += blockDim.x) {
+            kd[i] = __ldg(k4 + i);
+            vd[i] = __ldg(v4 + i);
+        }
+    } else {
+        for (int i = threadIdx.x; i < stride; i += blockDim.x) {
+            kbase[dst + i] = k[src + i];
+            vbase[dst + i] = v[src + i];
+        }
+    }
+}
+
+// ---- paged pool: [block][kv_head][16][head_dim] ---------------------------------------------------
+struct PagedView {
+    uint8_t* k_pool;
+    uint8_t* v_pool;
+    const int32_t* table;
+    int table_stride, num_blocks, kv_heads, head_dim;
+};
+
+// Writes one fp32 row (kv_heads*head_dim) into (block, offset) of the pool, rounding to KV.
+// One thread per 16-byte destination chunk.
+template <typename KV>
+__device__ __forceinline__ void store_row_paged(const PagedView& pv, int blk, int off,
+                                                const float* __restrict__ ksrc,
+                                                const float* __restrict__ vsrc) {
+    constexpr int EPC = KV::kPerChunk;
+    const int hd = pv.head_dim;
+    const int chunks = pv.kv_heads * hd / EPC;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const int e0 = c * EPC;
+        const int head = e0 / hd, d = e0 - head * hd;
+        const size_t dst = ((((size_t)blk * pv.kv_heads + head) * kBlockTokens + off) * hd + d) * KV::kBytes;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(ksrc + e0));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(vsrc + e0));
+        if constexpr (EPC == 8) {
+            const float4 a2 = __ldg(reinterpret_cast<const float4*>(ksrc + e0 + 4));
+            const float4 b2 = __ldg(reinterpret_cast<const float4*>(vsrc + e0 + 4));
+            *reinterpret_cast<uint4*>(pv.k_pool + dst) =
+                make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(a2.x, a2.y),
+                           pack_bf16x2(a2.z, a2.w));
+            *reinterpret_cast<uint4*>(pv.v_pool + dst) =
+                make_uint4(pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w), pack_bf16x2(b2.x, b2.y),
+                           pack_bf16x2(b2.z, b2.w));
+        } else {
+            *reinterpret_cast<float4*>(pv.k_pool + dst) = a;
+            *reinterpret_cast<float4*>(pv.v_pool + dst) = b;
+        }
+    }
+}
+
+template <typename KV>
+__global__ void __launch_bounds__(256) rswa_append_paged_kernel(
+    PagedView pv, const float* __restrict__ k, const float* __restrict__ v, int* __restrict__ d_len,
+    int* __restrict__ d_ring_pos, const int* __restrict__ d_prefill_len,
+    const int* __restrict__ d_slots, int window, int* __restrict__ status) {
+    __shared__ int s_blk, s_off;
+    const int b = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int slot = d_slots[b];
+        const int pfx = d_prefill_len[slot];
+        const int row = ring_advance(d_len + slot, d_ring_pos + slot, pfx, window);
+        const int r = row - pfx;
+        const int idx = (pfx + kBlockTokens - 1) / kBlockTokens + r / kBlockTokens;
+        int blk = -1;
+        if (r >= 0 && idx < pv.table_stride) blk = pv.table[(size_t)slot * pv.table_stride + idx];
+        else if (status) atomicOr(status, kStatusBadSlot);
+        if (blk < 0 || blk >= pv.num_blocks) {
+            if (status) atomicOr(status, kStatusBadBlock);
+            blk = -1;
+        }
+        s_blk = blk;
+        s_off = r & (kBlockTokens - 1);
+    }
+    __syncthreads();
+    if (s_blk < 0) return;
+    const size_t src = (size_t)b * pv.kv_heads * pv.head_dim;
+    store_row_paged<KV>(pv, s_blk, s_off, k + src, v + src);
+}
+
+template <typename KV>
+__global__ void __launch_bounds__(256) rswa_scatter_paged_kernel(
+    PagedView pv, const float* __restrict__ k, const float* __restrict__ v,
+    const int* __restrict__ d_slots, const int* __restrict__ d_pos, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int slot = d_slots[t], pos = d_pos[t];
+    const int idx = pos / kBlockTokens;
+    int blk = -1;
+    if (pos >= 0 && idx < pv.table_stride) blk = pv.table[(size_t)slot * pv.table_stride + idx];
+    if (blk < 0 || blk >= pv.num_blocks) {
+        if (threadIdx.x == 0 && status) atomicOr(status, pos >= 0 && idx < pv.table_stride ? kStatusBadBlock : kStatusBadSlot);
+        return;
+    }
+    const size_t src = (size_t)t * pv.kv_heads * pv.head_dim;
+    store_row_paged<KV>(pv, blk, pos & (kBlockTokens - 1), k + src, v + src);
+}
+
+// Gather: logical row s of slot d_slots[i] -> out[i][s][:]; rows >= len are zero-filled.
+// grid = (capacity_rows, n); one thread per 16-byte pool chunk.
+template <typename KV, bool WIDEN>
+__global__ void __launch_bounds__(256) rswa_gather_paged_kernel(
+    PagedView pv, const int* __restrict__ d_len, const int* __restrict__ d_prefill_len,
+    const int* __restrict__ d_slots, int capacity_rows, uint8_t* __restrict__ out_k,
+    uint8_t* __restrict__ out_v, int* __restrict__ status) {
+    constexpr int EPC = KV::kPerChunk;
+    constexpr int OUT_B = WIDEN ? 4 : KV::kBytes;
+    const int s = blockIdx.x, i = blockIdx.y;
+    const int slot = d_slots[i];
+    const int len = d_len[slot], pfx = d_prefill_len[slot];
+    const int hd = pv.head_dim, row_elems = pv.kv_heads * hd;
+    const size_t out_row = ((size_t)i * capacity_rows + s) * row_elems * OUT_B;
+    const int chunks = row_elems / EPC;
+    int blk = -1, off = 0;
+    if (s < len) {
+        int idx;
+        if (s < pfx) {
+            idx = s / kBlockTokens;
+            off = s & (kBlockTokens - 1);
+        } else {
+            const int r = s - pfx;
+            idx = (pfx + kBlockTokens - 1) / kBlockTokens + r / kBlockTokens;
+            off = r & (kBlockTokens - 1);
+        }
+        if (idx < pv.table_stride) blk = pv.table[(size_t)slot * pv.table_stride + idx];
+        if (blk < 0 || blk >= pv.num_blocks) {
+            if (threadIdx.x == 0 && status) atomicOr(status, kStatusBadBlock);
+            blk = -1;
+        }
+    }
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const int e0 = c * EPC;
+        uint4 kw = make_uint4(0, 0, 0, 0), vw = kw;
+        if (blk >= 0) {
+            const int head = e0 / hd, d = e0 - head * hd;
+            const size_t src = ((((size_t)blk * pv.kv_heads + head) * kBlockTokens + off) * hd + d) * KV::kBytes;
+            kw = *reinterpret_cast<const uint4*>(pv.k_pool + src);
+            vw = *reinterpret_cast<const uint4*>(pv.v_pool + src);
+        }
+        if constexpr (WIDEN && EPC == 8) {
+            float4* ko = reinterpret_cast<float4*>(out_k + out_row + (size_t)e0 * 4);
+            float4* vo = reinterpret_cast<float4*>(out_v + out_row + (size_t)e0 * 4);
+            ko[0] = make_float4(bf16_lo(kw.x), bf16_hi(kw.x), bf16_lo(kw.y), bf16_hi(kw.y));
+            ko[1] = make_float4(bf16_lo(kw.z), bf16_hi(kw.z), bf16_lo(kw.w), bf16_hi(kw.w));
+            vo[0] = make_float4(bf16_lo(vw.x), bf16_hi(vw.x), bf16_lo(vw.y), bf16_hi(vw.y));
+            vo[1] = make_float4(bf16_lo(vw.z), bf16_hi(vw.z), bf16_lo(vw.w), bf16_hi(vw.w));
+        } else {
+            *reinterpret_cast<uint4*>(out_k + out_row + (size_t)e0 * OUT_B) = kw;
+            *reinterpret_cast<uint4*>(out_v + out_row + (size_t)e0 * OUT_B) = vw;
+        }
+    }
+}
+
+}  // namespace uocr_b200
