@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the R-SWA KV-cache hot path: batched decode (ring append + decode attention).
+
+Workload ("cfg2", the configuration the headline metric is quoted on): 64 sequences, 12 layers,
+10 heads x 128, bf16 KV in paged blocks of 16 tokens, one 256-token vision prefix shared by all 64
+sequences (refcount 64), ring window W = 1024, current text positions uniform in [1, 4096]; a step
+appends one token per sequence per layer and runs decode attention; values N(0,1), synthetic.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  Under torchrun every rank owns one GPU and an independent replica
+of the workload (sequences shard by request; no collective on the data path); the timed region is
+bracketed by a barrier + synchronize, timed on the device, max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+
+CFG = dict(seqs=64, layers=12, heads=10, kv_heads=10, head_dim=128, window=1024, prefix=256,
+           pos_lo=1, pos_hi=4096, block_tokens=16, seed=1234)
+METRIC = "rswa_decode_tokens_per_s"
+UNIT = "tokens/s"
+NOMINAL_HBM_GBS = 8000.0
+
+
+def load_pkg():
+    import importlib.util
+    if "uocr_b200" in sys.modules:
+        return sys.modules["uocr_b200"]
+    spec = importlib.util.spec_from_file_location("uocr_b200", os.path.join(ROOT, "unlimited-ocr.cpp_b200", "__init__.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["uocr_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def draw_positions(rank: int):
+    import synth
+    return synth.integers(CFG["seed"], 77 + rank, CFG["pos_lo"], CFG["pos_hi"], (CFG["seqs"],)).astype(np.int64)
+
+
+def algorithmic_bytes_per_layer(pos_after_append: np.ndarray) -> float:
+    """Unique bytes one layer of one decode step must move: window tokens read + the shared prefix
+    once + appended rows written (bf16 K+V = 5120 B per token), plus q read, out written and new
+    k, v read in fp32."""
+    row = CFG["kv_heads"] * CFG["head_dim"]
+    kv_tok = row * 2 * 2
+    n = np.minimum(pos_after_append, CFG["window"])
+    B = len(pos_after_append)
+    return float(kv_tok * (n.sum() + CFG["prefix"] + B) + B * row * 4 * 4)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+class DecodeWorkload:
+    """Device state of the cfg2 workload on the current GPU, driven through the C ABI."""
+
+    def __init__(self, pkg, rank: int):
+        import torch
+        self.pkg, self.torch = pkg, torch
+        c = CFG
+        B, L, W, P, bt = c["seqs"], c["layers"], c["window"], c["prefix"], c["block_tokens"]
+        self.B, self.L = B, L
+        self.row = c["kv_heads"] * c["head_dim"]
+        pb, rb = P // bt, W // bt
+        self.num_blocks = pb + B * rb
+        table = np.zeros((B, pb + rb), np.int32)
+        table[:, :pb] = np.arange(pb)  # one physical prefix, shared by every sequence
+        for s in range(B):
+            table[s, pb:] = pb + s * rb + np.arange(rb)
+        self.table = torch.from_numpy(table).cuda()
+        g = torch.Generator(device="cuda")
+        g.manual_seed(c["seed"] + rank)
+        self.layers = []
+        for _ in range(L):
+            lay = pkg.PagedLayer(self.num_blocks, c["kv_heads"], c["head_dim"], pkg.BF16, self.table)
+            lay.k.copy_(torch.randn(lay.k.shape, generator=g, device="cuda", dtype=torch.float32))
+            lay.v.copy_(torch.randn(lay.v.shape, generator=g, device="cuda", dtype=torch.float32))
+            self.layers.append(lay)
+        self.pos0 = draw_positions(rank)
+        self.d_prefill = torch.full((B,), P, dtype=torch.int32, device="cuda")
+        self.d_slots = torch.arange(B, dtype=torch.int32, device="cuda")
+        self.d_len = torch.zeros((L, B), dtype=torch.int32, device="cuda")
+        self.d_ring = torch.zeros((L, B), dtype=torch.int32, device="cuda")
+        self.set_positions(self.pos0)
+        self.q = torch.randn((L, B, self.row), generator=g, device="cuda")
+        self.k = torch.randn((L, B, self.row), generator=g, device="cuda")
+        self.v = torch.randn((L, B, self.row), generator=g, device="cuda")
+        self.out = torch.zeros((L, B, self.row), device="cuda")
+        self.ws = pkg.Workspace(B)
+        self.graph = None
+        self.launches_per_step = 0
+        self.steps_done = 0
+
+    def set_positions(self, pos):
+        """Cursor state after `pos` appends (closed form of the ring state machine)."""
+        torch = self.torch
+        W, P = CFG["window"], CFG["prefix"]
+        ln = P + np.minimum(pos, W)
+        rp = np.where(pos < W, 0, (pos - W) % W)
+        self.d_len.copy_(torch.from_numpy(np.tile(ln.astype(np.int32), (self.L, 1))))
+        self.d_ring.copy_(torch.from_numpy(np.tile(rp.astype(np.int32), (self.L, 1))))
+
+    def step_plain(self, per_layer_hook=None):
+        p = self.pkg
+        for l in range(self.L):
+            p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                        self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
+            p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots, self.B,
+                                    CFG["heads"], self.out[l], self.ws)
+            if per_layer_hook:
+                per_layer_hook(l)
+
+    def capture(self):
+        torch = self.torch
+        before = self.pkg.launch_count()
+        self.step_plain()  # also sets kernel attributes outside capture
+        self.launches_per_step = self.pkg.launch_count() - before
+        self.steps_done += 1
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step_plain()
+
+    def step(self):
+        self.graph.replay()
+        self.steps_done += 1
+
+
+def run_ours(args, rank, world):
+    import torch
+    pkg = load_pkg()
+    pkg.lib()  # fails loudly when the CUDA library is missing
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    wl = DecodeWorkload(pkg, rank)
+    wl.capture()
+    for _ in range(max(args.warmup - 1, 0)):
+        wl.step()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: K whole steps (12 layers x (append + attention)), one graph launch each ----
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    steps_before = wl.steps_done
+    e0.record(stream)
+    for _ in range(args.steps):
+        wl.step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if dist:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    dev_status = wl.ws.status()
+    assert dev_status == 0, f"device status {dev_status}"
+
+    # ---- roofline of the dominant kernel: per-launch duration of the partial-attention kernel ------
+    pos_mid = wl.pos0 + steps_before + np.arange(args.steps)[:, None] + 1  # after each timed append
+    bytes_layer = float(np.mean([algorithmic_bytes_per_layer(p) for p in pos_mid]))
+    wl.ws.set_timing(True)
+    kms = []
+    wl.step_plain(lambda l: kms.append(wl.ws.last_kernel_ms()))
+    kms = []
+    for _ in range(min(args.steps, 10)):
+        wl.step_plain(lambda l: kms.append(wl.ws.last_kernel_ms()))
+        wl.steps_done += 1
+    wl.ws.set_timing(False)
+    k_ms = float(np.mean(kms))
+    peak, peak_kind = measured_peaks()
+    achieved = bytes_layer / (k_ms * 1e-3) / 1e9
+
+    # ---- e2e: same step from HOST buffers (pinned), H2D of q/k/v and D2H of out inside the timing --
+    hq, hk, hv = (torch.randn(wl.q.shape).pin_memory() for _ in range(3))
+    hout = torch.empty(wl.out.shape).pin_memory()
+    for _ in range(2):
+        wl.q.copy_(hq, non_blocking=True); wl.k.copy_(hk, non_blocking=True); wl.v.copy_(hv, non_blocking=True)
+        wl.step(); hout.copy_(wl.out, non_blocking=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        wl.q.copy_(hq, non_blocking=True); wl.k.copy_(hk, non_blocking=True); wl.v.copy_(hv, non_blocking=True)
+        wl.step()
+        hout.copy_(wl.out, non_blocking=True)
+        stream.synchronize()  # the caller reads the step's result before the next step
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0])
+    h2d = int(hq.numel() * 4 * 3)
+    d2h = int(hout.numel() * 4)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(sample_seqs=16, steps=4)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    tokens = CFG["seqs"] * world * args.steps
+    line = {
+        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg2: batched decode, 64 seqs/GPU x 12 layers, 10 heads x 128, bf16 paged KV "
+                               "(16-token blocks), shared 256-token prefix, W=1024, pos~U[1,4096]",
+                   "seqs_per_gpu": CFG["seqs"], "layers": CFG["layers"], "window": CFG["window"],
+                   "prefix": CFG["prefix"], "kv_resident_gb": round(wl.num_blocks * 81920 * CFG["layers"] / 1e9, 2),
+                   "l2_policy": "inputs larger than L2 (KV pool 4 GB vs 126 MB L2)", "step": "cuda graph of 12 x (append + attention)",
+                   "parallelism": f"replicas x{world} (sequences shard by request, no collective)"},
+        "roofline": {"bound": "hbm", "kernel": "rswa_attn_partial_kernel<BF16,128,paged>", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": k_ms,
+                     "algorithmic_bytes_per_launch": bytes_layer, "traffic": None,
+                     "step_gbs": bytes_layer * CFG["layers"] / (ms / args.steps * 1e-3) / 1e9},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": wl.launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's own RSWACache (compiled, unmodified) or the oracle port
+# ---------------------------------------------------------------------------------------------
+def cpu_baseline(sample_seqs: int, steps: int, threads: int = 0):
+    from oracle import oracle
+    kind = "reference" if oracle.available("ref") else "port"
+    o = oracle.load("ref" if kind == "reference" else "orc")
+    pos = draw_positions(0)[:sample_seqs]
+    pl = np.full(sample_seqs, CFG["prefix"], np.int32)
+    sec, used, _ = o.run_decode_bench(pl, pos, CFG["layers"], CFG["kv_heads"], CFG["head_dim"], CFG["window"],
+                                      steps, threads=threads, seed=CFG["seed"])
+    return {"value": sample_seqs * steps / sec, "unit": UNIT, "cores": used, "kind": kind,
+            "sample": f"first {sample_seqs} of the 64 sequences, all 12 layers, {steps} decode steps, fp32 KV "
+                      f"holding the bf16-rounded values; OpenMP over (sequence, layer) in the harness",
+            "seconds": sec}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    seqs = 16
+    steps = max(args.steps, 1)
+    # warm-up steps are part of the same call (state set-up dominates); time K steps
+    cpu = cpu_baseline(sample_seqs=seqs, steps=steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": world,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": cpu["seconds"] / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2 sample on host cores: " + cpu["sample"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="profiling aid only: fewer layers so an ncu capture holds < 1 GB (not a bench number)")
+    args = ap.parse_args()
+    if args.layers:
+        CFG["layers"] = args.layers
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -76,6 +76,12 @@ UOCR_B200_API int uocr_b200_workspace_destroy(uocr_b200_workspace* ws);
 UOCR_B200_API int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_stream_t stream,
                                              int* device_status);
 
+/* Measurement aid: when enabled, every attention call records a CUDA event pair around its
+ * partial-attention kernel on the launching stream; last_kernel_ms synchronises on the second
+ * event and returns the elapsed time of the most recent call.  Keep it off inside graph capture. */
+UOCR_B200_API int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled);
+UOCR_B200_API int uocr_b200_workspace_last_kernel_ms(uocr_b200_workspace* ws, float* ms);
+
 /* ------------------------------------------------------------------------------------------------
  * Paged KV view of ONE layer.
  * Replaces: the per-layer buffers `batch_k_[li]`, `batch_v_[li]` + `batch_cap_` addressing

@@ -67,6 +67,8 @@ _SIGS = {
     "uocr_b200_workspace_create": (_i, [_i, C.POINTER(_vp)]),
     "uocr_b200_workspace_destroy": (_i, [_vp]),
     "uocr_b200_workspace_status": (_i, [_vp, _vp, C.POINTER(_i)]),
+    "uocr_b200_workspace_set_timing": (_i, [_vp, _i]),
+    "uocr_b200_workspace_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
     "uocr_b200_rswa_append_decode_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "uocr_b200_rswa_append_decode_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 6 + [_i, _i, _vp, _vp]),
@@ -137,6 +139,14 @@ class Workspace:
     def status(self, stream=None) -> int:
         v = _i(0)
         check(lib().uocr_b200_workspace_status(self.h, stream_handle(stream), C.byref(v)))
+        return v.value
+
+    def set_timing(self, enabled: bool) -> None:
+        check(lib().uocr_b200_workspace_set_timing(self.h, 1 if enabled else 0))
+
+    def last_kernel_ms(self) -> float:
+        v = C.c_float(0)
+        check(lib().uocr_b200_workspace_last_kernel_ms(self.h, C.byref(v)))
         return v.value
 
     def close(self):

@@ -95,6 +95,8 @@ struct uocr_b200_workspace {
     RowInfo* info = nullptr;
     float* part_acc = nullptr;
     float* part_ml = nullptr;
+    bool timing = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
 
 extern "C" {
@@ -155,7 +157,26 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
 int uocr_b200_workspace_destroy(uocr_b200_workspace* ws) {
     if (!ws) return UOCR_B200_OK;
     if (ws->base) cudaFree(ws->base);
+    if (ws->ev0) cudaEventDestroy(ws->ev0);
+    if (ws->ev1) cudaEventDestroy(ws->ev1);
     delete ws;
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled) {
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_set_timing: null workspace");
+    if (enabled && !ws->ev0) {
+        CHECK_CUDA(cudaEventCreate(&ws->ev0), "event create");
+        CHECK_CUDA(cudaEventCreate(&ws->ev1), "event create");
+    }
+    ws->timing = enabled != 0;
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_last_kernel_ms(uocr_b200_workspace* ws, float* ms) {
+    if (!ws || !ms || !ws->ev0) return fail(UOCR_B200_ERR_INVALID, "workspace_last_kernel_ms: timing was never enabled");
+    CHECK_CUDA(cudaEventSynchronize(ws->ev1), "event sync");
+    CHECK_CUDA(cudaEventElapsedTime(ms, ws->ev0, ws->ev1), "event elapsed");
     return UOCR_B200_OK;
 }
 
@@ -289,7 +310,9 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     rswa_plan_kernel<<<1, pthreads, 0, st>>>(c.plan);
     if (int rc = after_launch("plan kernel")) return rc;
 
+    if (ws->timing) CHECK_CUDA(cudaEventRecord(ws->ev0, st), "event record");
     if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/false)) return rc;
+    if (ws->timing) CHECK_CUDA(cudaEventRecord(ws->ev1, st), "event record");
 
     const int items = c.rows * c.heads;
     rswa_attn_merge_kernel<<<(items + 7) / 8, 256, 0, st>>>(ap, c.head_dim);
