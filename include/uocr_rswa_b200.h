@@ -189,6 +189,28 @@ UOCR_B200_API int uocr_b200_rswa_attention_paged(
     int prefill_len, const int* d_prefill_len, int seq, int q_start, int heads, int causal,
     float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* Batched paged decode attention for callers that must not allocate.  It has no counterpart in the
+ * reference.  Some hosts of this library cannot call cudaMalloc at all: an engine that hands the
+ * whole GPU to its own arena at start-up (a later driver allocation fails or fragments it), a plugin
+ * slot whose contract forbids allocations, or a serving loop that cannot afford the device-wide
+ * synchronisation cudaMalloc/cudaFree imply.  Such a caller cannot create a uocr_b200_workspace, so
+ * this variant of uocr_b200_rswa_attention_batch_paged keeps the split-KV scratch in a fixed
+ * array that is part of the library image (about 2.7 MB of device memory on every GPU that loads
+ * the library, held until the process exits) and allocates nothing, ever.
+ *
+ * Limits, checked on every call (status UOCR_B200_ERR_WORKSPACE with a message otherwise):
+ * batch <= 1024 rows, head_dim <= 128, and a device of at most 160 SMs.
+ *
+ * The first call on a device looks up the device address of that array (a host-side query, no
+ * allocation); make that first call before any stream capture begins.  All calls on one device
+ * share the array: it still holds the previous call's contents when the next one starts (the call
+ * clears the one word that has to start at zero itself), and two calls that overlap on the GPU --
+ * different streams, or different host threads -- race on it.  Issue them on one stream, or
+ * serialise them yourself.  Results are identical to the workspace-based entry point. */
+UOCR_B200_API int uocr_b200_rswa_attention_batch_paged_noalloc(
+    const uocr_b200_paged_kv* kv, const float* q, const int* d_len, const int* d_prefill_len,
+    const int* d_slots, int batch, int heads, float* out, uocr_b200_stream_t stream);
+
 /* ================================================================================================
  * Block-table gather: paged storage -> the reference's logical view
  * Replaces: nothing in the reference (it has no block table, include/uocr/block_manager.h:11-13);

@@ -76,6 +76,7 @@ _SIGS = {
     "uocr_b200_rswa_write_prefill_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_attention_batch_paged_noalloc": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_attention_ragged_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_attention_f32": (_i, [_vp] * 3 + [_i, _vp] + [_i] * 6 + [_vp, _vp, _vp]),
@@ -194,6 +195,13 @@ def append_decode_batch_paged(layer, k, v, d_len, d_ring, d_prefill, d_slots, ba
 def attention_batch_paged(layer, q, d_len, d_prefill, d_slots, batch, heads, out, ws, stream=None):
     check(lib().uocr_b200_rswa_attention_batch_paged(layer.ref(), _p(q), _p(d_len), _p(d_prefill), _p(d_slots),
                                                       batch, heads, _p(out), ws.h, stream_handle(stream)))
+
+
+def attention_batch_paged_noalloc(layer, q, d_len, d_prefill, d_slots, batch, heads, out, stream=None):
+    """Same result as attention_batch_paged, scratch in the library's built-in device array."""
+    check(lib().uocr_b200_rswa_attention_batch_paged_noalloc(layer.ref(), _p(q), _p(d_len), _p(d_prefill),
+                                                              _p(d_slots), batch, heads, _p(out),
+                                                              stream_handle(stream)))
 
 
 def write_prefill_ragged_paged(layer, k, v, d_slots, d_pos, total, ws=None, stream=None):

@@ -542,3 +542,79 @@ int uocr_b200_rswa_gather_paged(const uocr_b200_paged_kv* kv, const int* d_len, 
 }
 
 }  // extern "C"
+
+// =================================================================================================
+// Allocation-free batched decode attention.
+//
+// For hosts that cannot allocate device memory (the GPU is owned by their own arena, a plugin
+// contract forbids it, or the implicit device synchronisation of cudaMalloc is unaffordable), the
+// split-KV scratch lives in a file-scope device array instead of a uocr_b200_workspace.  The name
+// `g_noalloc_scratch` is only a host-side handle in host code: the device address is looked up once
+// per device with cudaGetSymbolAddress (with that device current) and that pointer is what the
+// kernels receive.
+// =================================================================================================
+namespace {
+
+constexpr int kNoAllocMaxRows = 1024;
+constexpr int kNoAllocMaxHeadDim = 128;
+constexpr int kNoAllocMaxSms = 160;
+constexpr int kNoAllocMaxWarps = kNoAllocMaxSms * kMaxWarpsPerCta;
+constexpr size_t na_up(size_t x) { return (x + 255) & ~size_t(255); }
+constexpr size_t kNaStatus = 0;
+constexpr size_t kNaRs = na_up(256);
+constexpr size_t kNaInfo = kNaRs + na_up(sizeof(int) * (kNoAllocMaxRows + 1));
+constexpr size_t kNaAcc = kNaInfo + na_up(sizeof(RowInfo) * kNoAllocMaxRows);
+constexpr size_t kNaMl = kNaAcc + na_up(sizeof(float) * 2 * size_t(kNoAllocMaxWarps) * kNoAllocMaxHeadDim);
+constexpr size_t kNoAllocBytes = kNaMl + na_up(sizeof(float) * 4 * size_t(kNoAllocMaxWarps));
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+unsigned char* g_noalloc_ptr[64] = {nullptr};  // device address of the array, per device ordinal
+
+}  // namespace
+
+extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
+    const uocr_b200_paged_kv* kv, const float* q, const int* d_len, const int* d_prefill_len,
+    const int* d_slots, int batch, int heads, float* out, uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    if (!d_len || !d_slots || !d_prefill_len) return fail(UOCR_B200_ERR_INVALID, "attention_batch_paged_noalloc: null index array");
+    if (batch > kNoAllocMaxRows)
+        return fail(UOCR_B200_ERR_WORKSPACE, "attention_batch_paged_noalloc: batch exceeds the built-in scratch (max 1024 rows)");
+    if (kv && kv->head_dim > kNoAllocMaxHeadDim)
+        return fail(UOCR_B200_ERR_WORKSPACE, "attention_batch_paged_noalloc: head_dim exceeds the built-in scratch (max 128)");
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+    if (di->sms > kNoAllocMaxSms)
+        return fail(UOCR_B200_ERR_WORKSPACE, "attention_batch_paged_noalloc: device has more SMs than the built-in scratch covers (max 160)");
+
+    // one-time set-up per device: resolve the device address of the static array
+    int dev = 0;
+    CHECK_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        CHECK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
+        g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = g_noalloc_ptr[dev];
+
+    uocr_b200_workspace view;  // a view over the static array; owns nothing
+    view.device = dev;
+    view.max_rows = kNoAllocMaxRows;
+    view.total_warps_max = kNoAllocMaxWarps;
+    view.status = reinterpret_cast<int*>(base + kNaStatus);
+    view.rs = reinterpret_cast<int*>(base + kNaRs);
+    view.info = reinterpret_cast<RowInfo*>(base + kNaInfo);
+    view.part_acc = reinterpret_cast<float*>(base + kNaAcc);
+    view.part_ml = reinterpret_cast<float*>(base + kNaMl);
+
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // the status word is the only part of the scratch that must start at zero; everything else is
+    // rewritten by the plan and partial kernels before it is read
+    CHECK_CUDA(cudaMemsetAsync(view.status, 0, sizeof(int), st), "scratch status clear");
+
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.rows = batch; c.heads = heads; c.q = q; c.out = out;
+    c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_prefill_len = d_prefill_len;
+    return run_attention(c, &view, st);
+}
