@@ -129,9 +129,10 @@ class ClockSampler:
 class DecodeWorkload:
     """Device state of the cfg2 workload on the current GPU, driven through the C ABI."""
 
-    def __init__(self, pkg, rank: int):
+    def __init__(self, pkg, rank: int, fused: bool = True):
         import torch
         self.pkg, self.torch = pkg, torch
+        self.fused = fused
         c = CFG
         B, L, W, P, bt = c["seqs"], c["layers"], c["window"], c["prefix"], c["block_tokens"]
         self.B, self.L = B, L
@@ -178,10 +179,15 @@ class DecodeWorkload:
     def step_plain(self, per_layer_hook=None):
         p = self.pkg
         for l in range(self.L):
-            p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
-                                        self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
-            p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots, self.B,
-                                    CFG["heads"], self.out[l], self.ws)
+            if self.fused:
+                p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                    self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
+                                    self.ws)
+            else:
+                p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                            self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
+                p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots,
+                                        self.B, CFG["heads"], self.out[l], self.ws)
             if per_layer_hook:
                 per_layer_hook(l)
 
@@ -211,7 +217,7 @@ def run_ours(args, rank, world):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    wl = DecodeWorkload(pkg, rank)
+    wl = DecodeWorkload(pkg, rank, fused=not args.separate)
     wl.capture()
     for _ in range(max(args.warmup - 1, 0)):
         wl.step()
@@ -300,9 +306,10 @@ def run_ours(args, rank, world):
                                "(16-token blocks), shared 256-token prefix, W=1024, pos~U[1,4096]",
                    "seqs_per_gpu": CFG["seqs"], "layers": CFG["layers"], "window": CFG["window"],
                    "prefix": CFG["prefix"], "kv_resident_gb": round(wl.num_blocks * 81920 * CFG["layers"] / 1e9, 2),
-                   "l2_policy": "inputs larger than L2 (KV pool 4 GB vs 126 MB L2)", "step": "cuda graph of 12 x (append + attention)",
+                   "l2_policy": "inputs larger than L2 (KV pool 4 GB vs 126 MB L2)", "step": ("cuda graph of 12 x (append; plan; attention)" if args.separate else
+                            "cuda graph of 12 fused decode-step launches (append + attention in one kernel)"),
                    "parallelism": f"replicas x{world} (sequences shard by request, no collective)"},
-        "roofline": {"bound": "hbm", "kernel": "rswa_attn_partial_kernel<BF16,128,paged>", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": "rswa_attn_kernel<BF16,128,paged,%s>" % ("separate" if args.separate else "fused"), "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": k_ms,
                      "algorithmic_bytes_per_launch": bytes_layer, "traffic": None,
@@ -359,6 +366,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--separate", action="store_true",
+                    help="issue append and attention as the reference does (two entry points per layer) "
+                         "instead of the fused one-launch decode step")
     ap.add_argument("--layers", type=int, default=None,
                     help="profiling aid only: fewer layers so an ncu capture holds < 1 GB (not a bench number)")
     args = ap.parse_args()

@@ -189,13 +189,25 @@ UOCR_B200_API int uocr_b200_rswa_attention_paged(
     int prefill_len, const int* d_prefill_len, int seq, int q_start, int heads, int causal,
     float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* One decode step of one layer in a single launch: the batched ring append of
+ * uocr::cuda::rswa_append_decode_batch followed by uocr::cuda::rswa_attention_batch (the pair issued
+ * at src/engine/gpu_decoder.cu:990-996), on the paged layout.  Every CTA plans from the pre-append
+ * cursors, the warp that owns the tile holding a row's ring slot patches the new token into it (and
+ * writes it to the pool), and the last CTA to finish publishes the new d_len / d_ring_pos.  Results
+ * and final state are identical to calling the two separate entry points.  batch > 1024 falls back
+ * to those two launches. */
+UOCR_B200_API int uocr_b200_rswa_decode_step_paged(
+    const uocr_b200_paged_kv* kv, const float* q, const float* k, const float* v, int* d_len,
+    int* d_ring_pos, const int* d_prefill_len, const int* d_slots, int batch, int window, int heads,
+    float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
 /* Batched paged decode attention for callers that must not allocate.  It has no counterpart in the
  * reference.  Some hosts of this library cannot call cudaMalloc at all: an engine that hands the
  * whole GPU to its own arena at start-up (a later driver allocation fails or fragments it), a plugin
  * slot whose contract forbids allocations, or a serving loop that cannot afford the device-wide
  * synchronisation cudaMalloc/cudaFree imply.  Such a caller cannot create a uocr_b200_workspace, so
  * this variant of uocr_b200_rswa_attention_batch_paged keeps the split-KV scratch in a fixed
- * array that is part of the library image (about 2.7 MB of device memory on every GPU that loads
+ * array that is part of the library image (about 2.8 MB of device memory on every GPU that loads
  * the library, held until the process exits) and allocates nothing, ever.
  *
  * Limits, checked on every call (status UOCR_B200_ERR_WORKSPACE with a message otherwise):
@@ -204,7 +216,7 @@ UOCR_B200_API int uocr_b200_rswa_attention_paged(
  * The first call on a device looks up the device address of that array (a host-side query, no
  * allocation); make that first call before any stream capture begins.  All calls on one device
  * share the array: it still holds the previous call's contents when the next one starts (the call
- * clears the one word that has to start at zero itself), and two calls that overlap on the GPU --
+ * clears the parts that have to start at zero itself), and two calls that overlap on the GPU --
  * different streams, or different host threads -- race on it.  Issue them on one stream, or
  * serialise them yourself.  Results are identical to the workspace-based entry point. */
 UOCR_B200_API int uocr_b200_rswa_attention_batch_paged_noalloc(

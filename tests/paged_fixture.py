@@ -138,6 +138,21 @@ class PagedBatch:
                          for i, s in enumerate(row_slots)])
         return got, want
 
+    def step_fused(self, layer, k, v, q, row_slots):
+        """append + attention in one launch (decode_step_paged); oracle advanced alongside."""
+        torch = self.torch
+        dk, dv, dq = (torch.from_numpy(x).cuda() for x in (k, v, q))
+        ds = torch.tensor(row_slots, dtype=torch.int32, device="cuda")
+        out = torch.full((len(row_slots), self.heads * self.hd), float("nan"), device="cuda")
+        self.b.decode_step_paged(self.layer[layer], dq, dk, dv, self.d_len[layer], self.d_ring[layer],
+                                 self.d_prefill, ds, len(row_slots), self.W, self.heads, out, self.ws)
+        got = out.cpu().numpy()
+        want = []
+        for i, s in enumerate(row_slots):
+            self.cache[s].append_decode(layer, k[i], v[i])
+            want.append(self.cache[s].attention(layer, q[i:i + 1], self.cache[s].len(layer) - 1, self.heads, False)[0])
+        return got, np.stack(want)
+
     def gather(self, layer, slot_ids, out_dtype=0):
         torch = self.torch
         cap = max(self.P) + self.W

@@ -76,6 +76,7 @@ _SIGS = {
     "uocr_b200_rswa_write_prefill_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_decode_step_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged_noalloc": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_attention_ragged_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
@@ -195,6 +196,13 @@ def append_decode_batch_paged(layer, k, v, d_len, d_ring, d_prefill, d_slots, ba
 def attention_batch_paged(layer, q, d_len, d_prefill, d_slots, batch, heads, out, ws, stream=None):
     check(lib().uocr_b200_rswa_attention_batch_paged(layer.ref(), _p(q), _p(d_len), _p(d_prefill), _p(d_slots),
                                                       batch, heads, _p(out), ws.h, stream_handle(stream)))
+
+
+def decode_step_paged(layer, q, k, v, d_len, d_ring, d_prefill, d_slots, batch, window, heads, out, ws, stream=None):
+    """append + decode attention of one layer in one launch."""
+    check(lib().uocr_b200_rswa_decode_step_paged(layer.ref(), _p(q), _p(k), _p(v), _p(d_len), _p(d_ring),
+                                                  _p(d_prefill), _p(d_slots), batch, window, heads, _p(out), ws.h,
+                                                  stream_handle(stream)))
 
 
 def attention_batch_paged_noalloc(layer, q, d_len, d_prefill, d_slots, batch, heads, out, stream=None):

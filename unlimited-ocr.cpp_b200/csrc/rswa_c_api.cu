@@ -95,6 +95,8 @@ struct uocr_b200_workspace {
     RowInfo* info = nullptr;
     float* part_acc = nullptr;
     float* part_ml = nullptr;
+    int* counters = nullptr;   // [total_warps_max] arrival counters, zero between launches
+    int* done_ctas = nullptr;  // fused decode step: CTAs that have finished, zero between launches
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
@@ -133,7 +135,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_info = o_rs + up(sizeof(int) * (size_t)(max_rows + 1));
     const size_t o_acc = o_info + up(sizeof(RowInfo) * (size_t)max_rows);
     const size_t o_ml = o_acc + up(sizeof(float) * 2 * (size_t)ws->total_warps_max * kMaxHeadDim);
-    ws->bytes = o_ml + up(sizeof(float) * 4 * (size_t)ws->total_warps_max);
+    const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->total_warps_max);
+    ws->bytes = o_cnt + up(sizeof(int) * ((size_t)ws->total_warps_max + 64));
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -150,6 +153,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->info = reinterpret_cast<RowInfo*>(ws->base + o_info);
     ws->part_acc = reinterpret_cast<float*>(ws->base + o_acc);
     ws->part_ml = reinterpret_cast<float*>(ws->base + o_ml);
+    ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
+    ws->done_ctas = ws->counters + ws->total_warps_max;
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -187,6 +192,11 @@ int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_stream_t strea
     CHECK_CUDA(cudaMemcpyAsync(&v, ws->status, sizeof(int), cudaMemcpyDeviceToHost, st), "status D2H");
     CHECK_CUDA(cudaMemsetAsync(ws->status, 0, sizeof(int), st), "status clear");
     CHECK_CUDA(cudaStreamSynchronize(st), "status sync");
+    if (v != 0 && ws->counters) {
+        // a kernel that gave up may have left arrival counters half-way: start clean again
+        CHECK_CUDA(cudaMemsetAsync(ws->counters, 0, sizeof(int) * ((size_t)ws->total_warps_max + 64), st), "counter clear");
+        CHECK_CUDA(cudaStreamSynchronize(st), "counter clear sync");
+    }
     *device_status = v;
     return UOCR_B200_OK;
 }
@@ -212,21 +222,30 @@ struct AttnCall {
     const float* q = nullptr;
     float* out = nullptr;
     PlanParams plan{};
+    // fused decode step (append + attention in one launch)
+    bool fused = false;
+    const float* k_new = nullptr;
+    const float* v_new = nullptr;
+    int* d_len_rw = nullptr;
+    int* d_ring_rw = nullptr;
 };
 
-template <typename KV, int HD, bool PAGED>
+constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
+
+template <typename KV, int HD, bool PAGED, bool FUSED>
 int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, cudaStream_t st, bool dry) {
     using M = TileMap<KV, HD>;
     constexpr int per_warp = kStages * 2 * M::kTileBytes;
-    const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024;
+    const int plan_bytes = FUSED ? (int)(sizeof(RowInfo) * ap.rows + sizeof(int) * (ap.rows + 1 + 33) + 128) : 0;
+    const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024 - plan_bytes;
     int warps = budget / per_warp;
     if (warps > kMaxWarpsPerCta) warps = kMaxWarpsPerCta;
     if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
     *warps_used = warps;
     if (dry) return UOCR_B200_OK;
     const int bar_bytes = (warps * kStages * 2 * 8 + 127) & ~127;
-    const int smem = bar_bytes + warps * per_warp;
-    auto kern = rswa_attn_partial_kernel<KV, HD, PAGED, kStages>;
+    const int smem = bar_bytes + warps * per_warp + plan_bytes;
+    auto kern = rswa_attn_kernel<KV, HD, PAGED, FUSED, kStages>;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -235,31 +254,35 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
         configured_smem[dev] = smem;
     }
     kern<<<di.sms, warps * 32, smem, st>>>(ap);
-    return after_launch("attention partial kernel");
+    return after_launch("attention kernel");
 }
 
-template <typename KV, bool PAGED>
+template <typename KV, bool PAGED, bool FUSED>
 int dispatch_hd(int hd, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry) {
     switch (hd) {
-        case 8: return launch_partial<KV, 8, PAGED>(ap, di, warps, st, dry);
-        case 16: return launch_partial<KV, 16, PAGED>(ap, di, warps, st, dry);
-        case 32: return launch_partial<KV, 32, PAGED>(ap, di, warps, st, dry);
-        case 64: return launch_partial<KV, 64, PAGED>(ap, di, warps, st, dry);
-        case 128: return launch_partial<KV, 128, PAGED>(ap, di, warps, st, dry);
-        case 256: return launch_partial<KV, 256, PAGED>(ap, di, warps, st, dry);
+        case 8: return launch_partial<KV, 8, PAGED, FUSED>(ap, di, warps, st, dry);
+        case 16: return launch_partial<KV, 16, PAGED, FUSED>(ap, di, warps, st, dry);
+        case 32: return launch_partial<KV, 32, PAGED, FUSED>(ap, di, warps, st, dry);
+        case 64: return launch_partial<KV, 64, PAGED, FUSED>(ap, di, warps, st, dry);
+        case 128: return launch_partial<KV, 128, PAGED, FUSED>(ap, di, warps, st, dry);
+        case 256: return launch_partial<KV, 256, PAGED, FUSED>(ap, di, warps, st, dry);
         case 4:
-            if constexpr (KV::kBytes == 4) return launch_partial<KV, 4, PAGED>(ap, di, warps, st, dry);
+            if constexpr (KV::kBytes == 4) return launch_partial<KV, 4, PAGED, FUSED>(ap, di, warps, st, dry);
             [[fallthrough]];
         default: return fail(UOCR_B200_ERR_UNSUPPORTED, "head_dim must be a power of two in [8,256] (bf16) or [4,256] (fp32)");
     }
 }
 
 int dispatch_partial(const AttnCall& c, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry) {
-    if (c.paged) {
-        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true>(c.head_dim, ap, di, warps, st, dry);
-        return dispatch_hd<F32, true>(c.head_dim, ap, di, warps, st, dry);
+    if (c.fused) {
+        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, true>(c.head_dim, ap, di, warps, st, dry);
+        return dispatch_hd<F32, true, true>(c.head_dim, ap, di, warps, st, dry);
     }
-    return dispatch_hd<F32, false>(c.head_dim, ap, di, warps, st, dry);
+    if (c.paged) {
+        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, false>(c.head_dim, ap, di, warps, st, dry);
+        return dispatch_hd<F32, true, false>(c.head_dim, ap, di, warps, st, dry);
+    }
+    return dispatch_hd<F32, false, false>(c.head_dim, ap, di, warps, st, dry);
 }
 
 int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
@@ -294,29 +317,37 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.info = ws->info;
     ap.part_acc = ws->part_acc;
     ap.part_ml = ws->part_ml;
+    ap.counters = ws->counters;
     ap.status = ws->status;
-
-    int warps = 0;
-    if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/true)) return rc;
-    ap.total_warps = di->sms * warps;
-    if (ap.total_warps > ws->total_warps_max) return fail(UOCR_B200_ERR_WORKSPACE, "attention: workspace built for a smaller device");
+    ap.k_new = c.k_new;
+    ap.v_new = c.v_new;
+    ap.d_len = c.d_len_rw;
+    ap.d_ring_pos = c.d_ring_rw;
+    ap.done_ctas = ws->done_ctas;
 
     c.plan.rows = c.rows;
     c.plan.heads = c.heads;
     c.plan.paged = c.paged ? 1 : 0;
     c.plan.rs = ws->rs;
     c.plan.info = ws->info;
-    int pthreads = c.rows < 1024 ? ((c.rows + 31) & ~31) : 1024;
-    rswa_plan_kernel<<<1, pthreads, 0, st>>>(c.plan);
-    if (int rc = after_launch("plan kernel")) return rc;
+    c.plan.out = c.fused ? nullptr : c.out;
+    c.plan.out_row_elems = c.heads * c.head_dim;
+    ap.plan = c.plan;
 
+    int warps = 0;
+    if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/true)) return rc;
+    ap.total_warps = di->sms * warps;
+    if (ap.total_warps > ws->total_warps_max) return fail(UOCR_B200_ERR_WORKSPACE, "attention: workspace built for a smaller device");
+
+    if (!c.fused) {
+        int pthreads = c.rows < 1024 ? ((c.rows + 31) & ~31) : 1024;
+        rswa_plan_kernel<<<1, pthreads, 0, st>>>(c.plan);
+        if (int rc = after_launch("plan kernel")) return rc;
+    }
     if (ws->timing) CHECK_CUDA(cudaEventRecord(ws->ev0, st), "event record");
     if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/false)) return rc;
     if (ws->timing) CHECK_CUDA(cudaEventRecord(ws->ev1, st), "event record");
-
-    const int items = c.rows * c.heads;
-    rswa_attn_merge_kernel<<<(items + 7) / 8, 256, 0, st>>>(ap, c.head_dim);
-    return after_launch("merge kernel");
+    return UOCR_B200_OK;
 }
 
 int fill_paged(AttnCall& c, const uocr_b200_paged_kv* kv) {
@@ -515,6 +546,32 @@ int uocr_b200_rswa_attention_paged(const uocr_b200_paged_kv* kv, int slot, const
     return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// ---- fused decode step ---------------------------------------------------------------------------------
+int uocr_b200_rswa_decode_step_paged(const uocr_b200_paged_kv* kv, const float* q, const float* k, const float* v,
+                                     int* d_len, int* d_ring_pos, const int* d_prefill_len, const int* d_slots,
+                                     int batch, int window, int heads, float* out, uocr_b200_workspace* ws,
+                                     uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    if (!k || !v || !d_len || !d_ring_pos || !d_prefill_len || !d_slots)
+        return fail(UOCR_B200_ERR_INVALID, "decode_step_paged: null pointer");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "decode_step_paged: window must be positive");
+    if (!aligned16(k) || !aligned16(v)) return fail(UOCR_B200_ERR_INVALID, "decode_step_paged: k/v must be 16-byte aligned");
+    if (batch > kFusedMaxRows) {
+        // too many rows to plan in shared memory: same result from the two separate launches
+        if (int rc = uocr_b200_rswa_append_decode_batch_paged(kv, k, v, d_len, d_ring_pos, d_prefill_len, d_slots,
+                                                              batch, window, ws, stream))
+            return rc;
+        return uocr_b200_rswa_attention_batch_paged(kv, q, d_len, d_prefill_len, d_slots, batch, heads, out, ws, stream);
+    }
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.rows = batch; c.heads = heads; c.q = q; c.out = out;
+    c.fused = true; c.k_new = k; c.v_new = v; c.d_len_rw = d_len; c.d_ring_rw = d_ring_pos;
+    c.plan.mode = kPlanDecodeStep; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_ring_pos = d_ring_pos;
+    c.plan.d_prefill_len = d_prefill_len; c.plan.window = window;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
 // ---- gather ---------------------------------------------------------------------------------------------
 int uocr_b200_rswa_gather_paged(const uocr_b200_paged_kv* kv, const int* d_len, const int* d_prefill_len,
                                 const int* d_slots, int n, int capacity_rows, void* out_k, void* out_v,
@@ -565,7 +622,9 @@ constexpr size_t kNaRs = na_up(256);
 constexpr size_t kNaInfo = kNaRs + na_up(sizeof(int) * (kNoAllocMaxRows + 1));
 constexpr size_t kNaAcc = kNaInfo + na_up(sizeof(RowInfo) * kNoAllocMaxRows);
 constexpr size_t kNaMl = kNaAcc + na_up(sizeof(float) * 2 * size_t(kNoAllocMaxWarps) * kNoAllocMaxHeadDim);
-constexpr size_t kNoAllocBytes = kNaMl + na_up(sizeof(float) * 4 * size_t(kNoAllocMaxWarps));
+constexpr size_t kNaCnt = kNaMl + na_up(sizeof(float) * 4 * size_t(kNoAllocMaxWarps));
+constexpr size_t kNaCntBytes = sizeof(int) * (size_t(kNoAllocMaxWarps) + 64);
+constexpr size_t kNoAllocBytes = kNaCnt + na_up(kNaCntBytes);
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
@@ -606,11 +665,15 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     view.info = reinterpret_cast<RowInfo*>(base + kNaInfo);
     view.part_acc = reinterpret_cast<float*>(base + kNaAcc);
     view.part_ml = reinterpret_cast<float*>(base + kNaMl);
+    view.counters = reinterpret_cast<int*>(base + kNaCnt);
+    view.done_ctas = view.counters + kNoAllocMaxWarps;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    // the status word is the only part of the scratch that must start at zero; everything else is
-    // rewritten by the plan and partial kernels before it is read
+    // two parts of the scratch must start at zero: the status word and the arrival counters of the
+    // split items (the kernel returns them to zero itself, but an earlier call that was cut short
+    // could have left some behind); everything else is rewritten before it is read
     CHECK_CUDA(cudaMemsetAsync(view.status, 0, sizeof(int), st), "scratch status clear");
+    CHECK_CUDA(cudaMemsetAsync(view.counters, 0, kNaCntBytes, st), "scratch counter clear");
 
     AttnCall c;
     if (int rc = fill_paged(c, kv)) return rc;

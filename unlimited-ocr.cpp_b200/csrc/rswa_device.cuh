@@ -86,8 +86,36 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
 }
 
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// Widening a bf16 pair held in one 32-bit word.
+#ifndef UOCR_UNPACK_MODE
+#define UOCR_UNPACK_MODE 1
+#endif
+__device__ __forceinline__ float bf16_lo(uint32_t w) {
+    uint32_t r;
+#if UOCR_UNPACK_MODE == 0
+    r = w << 16;
+#elif UOCR_UNPACK_MODE == 1
+    asm("prmt.b32 %0, %1, 0, 0x1044;" : "=r"(r) : "r"(w));
+#elif UOCR_UNPACK_MODE == 2
+    asm("shl.b32 %0, %1, 16;" : "=r"(r) : "r"(w));
+#elif UOCR_UNPACK_MODE == 3
+    asm("mul.lo.u32 %0, %1, 65536;" : "=r"(r) : "r"(w));
+#elif UOCR_UNPACK_MODE == 4
+    asm("mad.lo.u32 %0, %1, 65536, 0;" : "=r"(r) : "r"(w));
+#endif
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ float bf16_hi(uint32_t w) {
+    uint32_t r;
+#if UOCR_UNPACK_MODE == 0
+    r = w & 0xffff0000u;
+#elif UOCR_UNPACK_MODE == 1
+    asm("prmt.b32 %0, %1, 0, 0x3244;" : "=r"(r) : "r"(w));
+#else
+    asm("and.b32 %0, %1, 0xffff0000;" : "=r"(r) : "r"(w));
+#endif
+    return __uint_as_float(r);
+}
 
 // ---------------------------------------------------------------------------------------------
 // KV element traits: how a 16-byte chunk of a cache row turns into floats
