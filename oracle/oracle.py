@@ -64,14 +64,18 @@ def _fp(a: np.ndarray):
 class Oracle:
     """Function table of one back end (prefix ``orc`` or ``ref``)."""
 
-    def __init__(self, kind: str):
+    def __init__(self, kind: str, path: str | None = None, prefix: str | None = None):
+        """`path`/`prefix` let the same driver run any library exporting this function set -- the
+        tests use that to drive the CUDA library's host classes through the identical scripts."""
         self.kind = kind
-        self.lib = C.CDLL(_PATHS[kind], mode=os.RTLD_LOCAL)
-        p = kind + "_"
+        self.lib = C.CDLL(path or _PATHS[kind], mode=os.RTLD_LOCAL)
+        p = (prefix or kind) + "_"
         L = self.lib
 
         def fn(name, res, args):
-            f = getattr(L, p + name)
+            f = getattr(L, p + name, None)
+            if f is None:  # optional entry (e.g. the timed decode leg)
+                return
             f.restype = res
             f.argtypes = args
             setattr(self, name, f)

@@ -1,0 +1,352 @@
+// GPU tests of the C++ host API (uocr::RSWACache, uocr::cuda::GpuRSWACache, the uocr::cuda::rswa_*
+// free functions with the reference's signatures, uocr::cuda::PagedBatchKV, uocr::SlotAllocator)
+// against the CPU oracle (oracle/rswa_oracle.h -- test infrastructure, linked here as the checker).
+// Cache contents and cursors must be bit-equal; attention within 2e-5.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "rswa_oracle.h"
+#include "uocr/cuda_ops.h"
+#include "uocr/gpu_cache.h"
+#include "uocr/kv_cache.h"
+
+using namespace uocr;
+
+static int g_fail = 0;
+#define EXPECT(cond)                                                          \
+    do {                                                                      \
+        if (!(cond)) {                                                        \
+            std::printf("  FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond);     \
+            ++g_fail;                                                         \
+        }                                                                     \
+    } while (0)
+
+static uint64_t g_state = 0x9e3779b97f4a7c15ull;
+static float rnd() {  // sum of four uniforms, centred: cheap bell-shaped values, exactly representable
+    float s = 0.f;
+    for (int i = 0; i < 4; ++i) {
+        g_state = g_state * 6364136223846793005ull + 1442695040888963407ull;
+        s += static_cast<float>((g_state >> 40) & 0xffff) / 65536.0f;
+    }
+    return (s - 2.0f) * 1.7f;
+}
+static std::vector<float> rvec(size_t n) {
+    std::vector<float> v(n);
+    for (auto& x : v) x = rnd();
+    return v;
+}
+template <typename T>
+static T* dev(const std::vector<T>& h) {
+    T* d = nullptr;
+    cudaMalloc(&d, std::max<size_t>(h.size(), 1) * sizeof(T));
+    cudaMemcpy(d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice);
+    return d;
+}
+template <typename T>
+static std::vector<T> host(const T* d, size_t n) {
+    std::vector<T> h(n);
+    cudaMemcpy(h.data(), d, n * sizeof(T), cudaMemcpyDeviceToHost);
+    return h;
+}
+static float max_abs_diff(const std::vector<float>& a, const float* b) {
+    float m = 0.f;
+    for (size_t i = 0; i < a.size(); ++i) m = std::max(m, std::fabs(a[i] - b[i]));
+    return m;
+}
+
+// ---- RSWACache (host pointers) -----------------------------------------------------------------------
+static void test_rswa_cache_host_interface() {
+    std::printf("RSWACache (device-backed, host interface)\n");
+    const int L = 2, kvh = 2, hd = 16, W = 8, P = 5, heads = 4, row = kvh * hd;
+    RSWACache c(L, kvh, hd, W);
+    orc_cache* o = orc_cache_create(L, kvh, hd, W);
+    c.reset(P);
+    orc_cache_reset(o, P);
+    EXPECT(c.capacity() == P + W && c.prefill_len() == P && c.length(0) == P);
+    for (int l = 0; l < L; ++l) {
+        auto k = rvec(P * row), v = rvec(P * row);
+        c.write_prefill(l, k.data(), v.data(), P);
+        orc_cache_write_prefill(o, l, k.data(), v.data(), P);
+    }
+    for (int t = 0; t < 3 * W + 1; ++t)
+        for (int l = 0; l < L; ++l) {
+            auto k = rvec(row), v = rvec(row);
+            c.append_decode(l, k.data(), v.data());
+            orc_cache_append_decode(o, l, k.data(), v.data());
+            EXPECT(c.length(l) == orc_cache_len(o, l) && c.ring_pos(l) == orc_cache_ring_pos(o, l));
+            EXPECT(c.ring_started(l) == (orc_cache_ring_started(o, l) != 0));
+        }
+    for (int l = 0; l < L; ++l) {
+        const size_t n = static_cast<size_t>(c.capacity()) * row;
+        EXPECT(std::memcmp(c.keys(l), orc_cache_keys(o, l), n * 4) == 0);
+        EXPECT(std::memcmp(c.values(l), orc_cache_values(o, l), n * 4) == 0);
+        auto q = rvec(heads * hd);
+        std::vector<float> got(heads * hd, NAN), want(heads * hd);
+        c.attention(l, q.data(), 1, c.length(l) - 1, got.data(), heads, false);
+        orc_cache_attention(o, l, q.data(), 1, orc_cache_len(o, l) - 1, want.data(), heads, 0);
+        EXPECT(max_abs_diff(got, want.data()) < 2e-5f);
+    }
+    // a write through mutable_keys() reaches the device before the next operation
+    float* mk = c.mutable_keys(0);
+    float* ok = const_cast<float*>(orc_cache_keys(o, 0));
+    mk[3 * row + 1] = 7.5f;
+    ok[3 * row + 1] = 7.5f;
+    auto q = rvec(heads * hd);
+    std::vector<float> got(heads * hd, NAN), want(heads * hd);
+    c.attention(0, q.data(), 1, c.length(0) - 1, got.data(), heads, false);
+    orc_cache_attention(o, 0, q.data(), 1, orc_cache_len(o, 0) - 1, want.data(), heads, 0);
+    EXPECT(max_abs_diff(got, want.data()) < 2e-5f);
+    EXPECT(c.keys(0)[3 * row + 1] == 7.5f);
+    EXPECT(c.bytes() == orc_cache_bytes(o));
+    bool threw = false;
+    try {
+        c.write_prefill(0, q.data(), q.data(), c.capacity() + 1);
+    } catch (const Error&) {
+        threw = true;
+    }
+    EXPECT(threw);
+    orc_cache_destroy(o);
+}
+
+// ---- GpuRSWACache (device pointers) ----------------------------------------------------------------------
+static void test_gpu_cache_device_interface() {
+    std::printf("cuda::GpuRSWACache\n");
+    const int L = 1, kvh = 10, hd = 128, W = 8, P = 4, heads = 10, row = kvh * hd;
+    cuda::GpuRSWACache g(L, kvh, hd, W);
+    orc_cache* o = orc_cache_create(L, kvh, hd, W);
+    g.reset(P);
+    orc_cache_reset(o, P);
+    auto pk = rvec(P * row), pv = rvec(P * row);
+    float *dk = dev(pk), *dv = dev(pv);
+    g.write_prefill(0, dk, dv, P);
+    orc_cache_write_prefill(o, 0, pk.data(), pv.data(), P);
+    // causal prefill attention (tests/test_rswa_cuda.cu:176-221 scenario)
+    auto qa = rvec(P * heads * hd);
+    float* dqa = dev(qa);
+    float* douta = nullptr;
+    cudaMalloc(&douta, qa.size() * 4);
+    g.attention(0, dqa, P, 0, douta, heads, true);
+    std::vector<float> wanta(qa.size());
+    orc_cache_attention(o, 0, qa.data(), P, 0, wanta.data(), heads, 1);
+    EXPECT(max_abs_diff(host(douta, qa.size()), wanta.data()) < 2e-5f);
+    for (int t = 0; t < 24; ++t) {
+        auto k = rvec(row), v = rvec(row);
+        cudaMemcpy(dk, k.data(), row * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(dv, v.data(), row * 4, cudaMemcpyHostToDevice);
+        if (t % 2) g.append_decode(0, dk, dv); else g.append_decode_device(0, dk, dv);
+        orc_cache_append_decode(o, 0, k.data(), v.data());
+    }
+    EXPECT(g.len(0) == orc_cache_len(o, 0));
+    EXPECT(host(g.len_dev(0), 1)[0] == orc_cache_len(o, 0));
+    const size_t n = static_cast<size_t>(g.capacity()) * row;
+    EXPECT(std::memcmp(host(g.keys(0), n).data(), orc_cache_keys(o, 0), n * 4) == 0);
+    EXPECT(std::memcmp(host(g.values(0), n).data(), orc_cache_values(o, 0), n * 4) == 0);
+    auto q = rvec(heads * hd);
+    float* dq = dev(q);
+    float* dout = nullptr;
+    cudaMalloc(&dout, q.size() * 4);
+    g.attention(0, dq, 1, g.len(0) - 1, dout, heads, false);
+    std::vector<float> want(q.size());
+    orc_cache_attention(o, 0, q.data(), 1, orc_cache_len(o, 0) - 1, want.data(), heads, 0);
+    EXPECT(max_abs_diff(host(dout, q.size()), want.data()) < 2e-5f);
+    cudaFree(dk); cudaFree(dv); cudaFree(dqa); cudaFree(douta); cudaFree(dq); cudaFree(dout);
+    orc_cache_destroy(o);
+}
+
+// ---- the reference's free functions, reference layout ----------------------------------------------------
+static void test_free_functions_reference_layout() {
+    std::printf("uocr::cuda::rswa_* (reference signatures, contiguous fp32 caches)\n");
+    const int kvh = 4, heads = 4, hd = 64, W = 8, batch = 3, cap = 6 + W, row = kvh * hd;
+    const int prefill[batch] = {4, 6, 3};
+    const int slots[batch] = {2, 1, 0};
+    std::vector<float> kb(static_cast<size_t>(batch) * cap * row, 0.f), vb(kb.size(), 0.f);
+    orc_cache* o[batch];
+    for (int s = 0; s < batch; ++s) {
+        o[s] = orc_cache_create(1, kvh, hd, W);
+        orc_cache_reset(o[s], prefill[s]);
+        auto k = rvec(prefill[s] * row), v = rvec(prefill[s] * row);
+        orc_cache_write_prefill(o[s], 0, k.data(), v.data(), prefill[s]);
+        std::copy(k.begin(), k.end(), kb.begin() + static_cast<size_t>(s) * cap * row);
+        std::copy(v.begin(), v.end(), vb.begin() + static_cast<size_t>(s) * cap * row);
+    }
+    float *dkb = dev(kb), *dvb = dev(vb);
+    std::vector<int> len(prefill, prefill + batch), zero(batch, 0), sl(slots, slots + batch);
+    int *d_len = dev(len), *d_ring = dev(zero), *d_pref = dev(len), *d_slots = dev(sl);
+    float *dk, *dv, *dq, *dout;
+    cudaMalloc(&dk, batch * row * 4); cudaMalloc(&dv, batch * row * 4);
+    cudaMalloc(&dq, batch * heads * hd * 4); cudaMalloc(&dout, batch * heads * hd * 4);
+    float worst = 0.f;
+    for (int step = 0; step < 3 * W; ++step) {
+        auto k = rvec(batch * row), v = rvec(batch * row), q = rvec(batch * heads * hd);
+        cudaMemcpy(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice);
+        cuda::rswa_append_decode_batch(dk, dv, dkb, dvb, d_len, d_ring, d_pref, d_slots, batch, cap, W, kvh, hd);
+        cuda::rswa_attention_batch(dq, dkb, dvb, d_len, d_slots, batch, cap, heads, kvh, hd, dout);
+        auto got = host(dout, q.size());
+        for (int r = 0; r < batch; ++r) {
+            orc_cache* c = o[slots[r]];
+            orc_cache_append_decode(c, 0, k.data() + r * row, v.data() + r * row);
+            std::vector<float> want(heads * hd);
+            orc_cache_attention(c, 0, q.data() + r * heads * hd, 1, orc_cache_len(c, 0) - 1, want.data(), heads, 0);
+            for (int i = 0; i < heads * hd; ++i) worst = std::max(worst, std::fabs(want[i] - got[r * heads * hd + i]));
+        }
+    }
+    EXPECT(worst < 2e-5f);
+    auto fk = host(dkb, kb.size()), fv = host(dvb, vb.size());
+    auto flen = host(d_len, batch), fring = host(d_ring, batch);
+    for (int s = 0; s < batch; ++s) {
+        const size_t n = static_cast<size_t>(orc_cache_len(o[s], 0)) * row;
+        EXPECT(flen[s] == orc_cache_len(o[s], 0) && fring[s] == orc_cache_ring_pos(o[s], 0));
+        EXPECT(std::memcmp(fk.data() + static_cast<size_t>(s) * cap * row, orc_cache_keys(o[s], 0), n * 4) == 0);
+        EXPECT(std::memcmp(fv.data() + static_cast<size_t>(s) * cap * row, orc_cache_values(o[s], 0), n * 4) == 0);
+        orc_cache_destroy(o[s]);
+    }
+    // single-cache decode entry point (rswa_attention_decode) on slot 0's cache
+    auto q1 = rvec(heads * hd);
+    cudaMemcpy(dq, q1.data(), q1.size() * 4, cudaMemcpyHostToDevice);
+    cuda::rswa_attention_decode(dq, dkb, dvb, flen[0], heads, kvh, hd, dout);
+    cuda::rswa_attention_devlen(dq, dkb, dvb, d_len, 1, 0, heads, kvh, hd, false, dout + heads * hd);
+    auto two = host(dout, 2 * heads * hd);
+    EXPECT(std::memcmp(two.data(), two.data() + heads * hd, heads * hd * 4) == 0);
+}
+
+// ---- PagedBatchKV + SlotAllocator ---------------------------------------------------------------------------
+static void test_paged_batch_kv() {
+    std::printf("cuda::PagedBatchKV + SlotAllocator\n");
+    SlotAllocator sa(4);
+    EXPECT(sa.acquire(100) == 3 && sa.acquire(101) == 2 && sa.acquire(102) == 1);
+    sa.release(101);
+    EXPECT(sa.acquire(103) == 2 && sa.slot_of(103) == 2 && sa.slot_of(101) == -1);
+    EXPECT(sa.acquire(104) == 0);
+    bool threw = false;
+    try { sa.acquire(105); } catch (const Error&) { threw = true; }
+    EXPECT(threw);
+
+    cuda::PagedBatchKV kv;
+    cuda::PagedBatchKV::Config cfg;
+    cfg.slots = 4; cfg.layers = 2; cfg.kv_heads = 2; cfg.head_dim = 16; cfg.window = 16;
+    cfg.max_prefix_tokens = 40; cfg.prefix_arena_blocks = 4; cfg.ring_arena_blocks = 4; cfg.dtype = DType::BF16;
+    EXPECT(kv.configure(cfg) == true);
+    EXPECT(kv.configure(cfg) == false);  // same shape: buffers reused, state cleared
+    const int row = cfg.kv_heads * cfg.head_dim, heads = 4, cap = cfg.max_prefix_tokens + cfg.window;
+    const int P[4] = {33, 33, 16, 0};
+    const char* keys[4] = {"docA", "docA", "docB", ""};
+    orc_cache* o[4];
+    for (int s = 0; s < 4; ++s) {
+        auto a = kv.admit(s, keys[s], P[s]);
+        EXPECT(a.prefix_is_new == (s == 0 || s == 2));
+        if (s == 1) EXPECT(a.prefix_refcount == 2);
+        o[s] = orc_cache_create(cfg.layers, cfg.kv_heads, cfg.head_dim, cfg.window);
+        orc_cache_reset(o[s], P[s]);
+    }
+    EXPECT(kv.table_row(0)[0] == kv.table_row(1)[0] && kv.table_row(0)[2] == kv.table_row(1)[2]);  // shared prefix
+    EXPECT(kv.table_row(0)[3] != kv.table_row(1)[3]);                                              // private rings
+    EXPECT(kv.blocks().stats().live_prefixes == 2 && kv.blocks().shared_prefix_bytes() == 3 * 256);
+    threw = false;
+    try { cuda::PagedBatchKV::Admission x = kv.admit(0, "docC", 8); (void)x; } catch (const Error&) { threw = true; }
+    EXPECT(threw);  // slot already bound
+
+    // prefixes are written once, through the slot that created them; bf16 pool -> oracle gets rounded values
+    auto round = [](std::vector<float> v) { for (auto& x : v) x = bf16_to_f32(f32_to_bf16(x)); return v; };
+    for (int l = 0; l < cfg.layers; ++l)
+        for (int s : {0, 2}) {
+            auto k = round(rvec(P[s] * row)), v = round(rvec(P[s] * row));
+            std::vector<int> rs(P[s], s), pos(P[s]);
+            for (int i = 0; i < P[s]; ++i) pos[i] = i;
+            float *dk = dev(k), *dv = dev(v);
+            int *drs = dev(rs), *dpos = dev(pos);
+            kv.write_prefill_ragged(l, dk, dv, drs, dpos, P[s]);
+            cudaDeviceSynchronize();
+            cudaFree(dk); cudaFree(dv); cudaFree(drs); cudaFree(dpos);
+            for (int t = 0; t < 4; ++t)
+                if (std::string(keys[t]) == keys[s] && P[t] == P[s]) orc_cache_write_prefill(o[t], l, k.data(), v.data(), P[s]);
+        }
+    std::vector<int> order = {2, 0, 3, 1};
+    int* d_slots = dev(order);
+    float *dq, *dk, *dv, *dout, *gk, *gv;
+    cudaMalloc(&dq, 4 * heads * cfg.head_dim * 4); cudaMalloc(&dout, 4 * heads * cfg.head_dim * 4);
+    cudaMalloc(&dk, 4 * row * 4); cudaMalloc(&dv, 4 * row * 4);
+    cudaMalloc(&gk, 4 * cap * row * 4); cudaMalloc(&gv, 4 * cap * row * 4);
+    float worst = 0.f;
+    for (int t = 0; t < 2 * cfg.window + 5; ++t)
+        for (int l = 0; l < cfg.layers; ++l) {
+            auto k = round(rvec(4 * row)), v = round(rvec(4 * row)), q = rvec(4 * heads * cfg.head_dim);
+            cudaMemcpy(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice);
+            cudaMemcpy(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+            cudaMemcpy(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice);
+            if (t % 2) {
+                kv.decode_step(l, dq, dk, dv, d_slots, 4, heads, dout);
+            } else {
+                kv.append_decode_batch(l, dk, dv, d_slots, 4);
+                kv.attention_batch(l, dq, d_slots, 4, heads, dout);
+            }
+            auto got = host(dout, q.size());
+            for (int r = 0; r < 4; ++r) {
+                orc_cache* c = o[order[r]];
+                orc_cache_append_decode(c, l, k.data() + r * row, v.data() + r * row);
+                std::vector<float> want(heads * cfg.head_dim);
+                orc_cache_attention(c, l, q.data() + r * heads * cfg.head_dim, 1, orc_cache_len(c, l) - 1, want.data(), heads, 0);
+                for (size_t i = 0; i < want.size(); ++i)
+                    worst = std::max(worst, std::fabs(want[i] - got[r * heads * cfg.head_dim + i]));
+            }
+        }
+    EXPECT(worst < 2e-5f);
+    std::vector<int> ident = {0, 1, 2, 3};
+    int* d_ident = dev(ident);
+    for (int l = 0; l < cfg.layers; ++l) {
+        kv.gather(l, d_ident, 4, gk, gv);
+        auto hk = host(gk, static_cast<size_t>(4) * cap * row), hv = host(gv, static_cast<size_t>(4) * cap * row);
+        auto dl = host(kv.d_len(l), 4), dr = host(kv.d_ring_pos(l), 4);
+        for (int s = 0; s < 4; ++s) {
+            const size_t n = static_cast<size_t>(orc_cache_len(o[s], l)) * row;
+            EXPECT(dl[s] == orc_cache_len(o[s], l) && dr[s] == orc_cache_ring_pos(o[s], l));
+            EXPECT(std::memcmp(hk.data() + static_cast<size_t>(s) * cap * row, orc_cache_keys(o[s], l), n * 4) == 0);
+            EXPECT(std::memcmp(hv.data() + static_cast<size_t>(s) * cap * row, orc_cache_values(o[s], l), n * 4) == 0);
+        }
+    }
+    EXPECT(kv.device_status() == 0);
+    // releases: refcount drops, prefix freed with its last user, everything back to zero at the end
+    kv.release(0);
+    EXPECT(kv.blocks().stats().live_prefixes == 2 && kv.blocks().shared_prefix_bytes() == 0);
+    kv.release(1);
+    EXPECT(kv.blocks().stats().live_prefixes == 1);
+    kv.release(1);  // releasing twice is harmless
+    kv.release(2);
+    kv.release(3);
+    auto st = kv.blocks().stats();
+    EXPECT(st.live_prefixes == 0 && st.prefix_live_bytes == 0 && st.ring_live_bytes == 0);
+    // exhaustion: four rings fit, a fifth admission (after re-binding all slots) cannot happen; a too
+    // large prefix set throws and leaves the arenas untouched
+    kv.admit(0, "big1", 40);
+    threw = false;
+    try { kv.admit(1, "big2", 40); } catch (const Error&) { threw = true; }  // 3 + 3 blocks > 4
+    EXPECT(threw);
+    EXPECT(kv.blocks().stats().live_prefixes == 1 && kv.blocks().stats().ring_live_bytes == 256);
+    for (int s = 0; s < 4; ++s) orc_cache_destroy(o[s]);
+}
+
+int main() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        std::printf("no CUDA device\n");
+        return 2;
+    }
+    try {
+        test_rswa_cache_host_interface();
+        test_gpu_cache_device_interface();
+        test_free_functions_reference_layout();
+        test_paged_batch_kv();
+    } catch (const std::exception& e) {
+        std::printf("  EXCEPTION: %s\n", e.what());
+        ++g_fail;
+    }
+    std::printf("%s (%d failures)\n", g_fail ? "FAILED" : "ALL OK", g_fail);
+    return g_fail ? 1 : 0;
+}

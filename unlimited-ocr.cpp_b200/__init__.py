@@ -86,11 +86,30 @@ _SIGS = {
 }
 
 
+_HOST_SYMBOLS = [
+    "pool_create", "pool_destroy", "pool_reset", "pool_allocate", "pool_free", "pool_total", "pool_used",
+    "pool_peak", "pool_num_free_blocks", "pool_fragmentation",
+    "bm_create", "bm_destroy", "bm_acquire_prefix", "bm_release_prefix", "bm_allocate_ring", "bm_free_ring",
+    "bm_live_prefixes", "bm_total_prefix_bytes", "bm_shared_prefix_bytes", "bm_peak_prefix_bytes", "bm_get_stats",
+    "sched_create", "sched_destroy", "sched_add_request", "sched_build_batch", "sched_mark_prefilled",
+    "sched_mark_prefilling", "sched_add_token", "sched_finish", "sched_state", "sched_num_outputs",
+    "sched_has_work", "sched_running", "sched_get_stats",
+    "cache_create", "cache_set_kv_dtype", "cache_destroy", "cache_reset", "cache_write_prefill",
+    "cache_append_decode", "cache_attention", "cache_len", "cache_ring_pos", "cache_ring_started",
+    "cache_capacity", "cache_prefill_len", "cache_keys", "cache_values", "cache_bytes",
+]
+
+
+def host_symbols():
+    """Entry points of include/uocr_rswa_b200_host.h (host classes behind the C ABI)."""
+    return ["uocr_b200_" + n for n in _HOST_SYMBOLS]
+
+
 def declared_symbols():
     """Names of every function declared in include/uocr_rswa_b200.h (parsed from the header)."""
     import re
     out = []
-    for name in ("uocr_rswa_b200.h",):
+    for name in ("uocr_rswa_b200.h", "uocr_rswa_b200_host.h"):
         text = open(os.path.join(ROOT, "include", name)).read()
         out += re.findall(r"UOCR_B200_API\s+[\w\s\*]+?\b(uocr_b200_\w+)\s*\(", text)
     return sorted(set(out))

@@ -1,0 +1,1024 @@
+// Host-side classes of the R-SWA path (see include/uocr/rswa_host.h): arena, block manager,
+// scheduler, slot list, and the device-backed caches built on the C ABI.
+#include "uocr/rswa_host.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <ctime>
+
+namespace uocr {
+
+namespace {
+
+inline void cuda_ok(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) UOCR_THROW(std::string(what) + ": " + cudaGetErrorString(e));
+}
+inline void abi_ok(int rc, const char* what) {
+    if (rc != UOCR_B200_OK) UOCR_THROW(std::string(what) + ": " + uocr_b200_status_string(rc) + ": " + uocr_b200_last_error());
+}
+inline int blocks_for(int tokens) { return (tokens + UOCR_B200_BLOCK_TOKENS - 1) / UOCR_B200_BLOCK_TOKENS; }
+inline double cpu_seconds() { return static_cast<double>(::clock()) / CLOCKS_PER_SEC; }
+
+}  // namespace
+
+// =================================================================================================
+// MemoryPool -- behaviour of src/scheduler/memory_pool.cpp:7-85
+// =================================================================================================
+MemoryPool::MemoryPool(std::size_t bytes, std::size_t alignment) : alignment_(alignment) {
+    if (bytes) reserve(bytes);
+}
+
+void MemoryPool::reserve(std::size_t bytes) {
+    total_ = bytes;
+    backing_.clear();
+    reset();
+}
+
+void MemoryPool::reset() {
+    used_ = peak_ = 0;
+    spans_.assign(1, Block{0, total_});
+}
+
+std::uint8_t* MemoryPool::base() {
+    if (backing_.size() != total_) backing_.assign(total_, 0);
+    return backing_.data();
+}
+const std::uint8_t* MemoryPool::base() const {
+    if (backing_.size() != total_) backing_.assign(total_, 0);
+    return backing_.data();
+}
+
+i64 MemoryPool::allocate(std::size_t bytes, std::size_t alignment) {
+    if (bytes == 0) return 0;
+    std::size_t a = alignment ? alignment : alignment_;
+    if (a == 0) a = 1;
+    for (auto it = spans_.begin(); it != spans_.end(); ++it) {
+        const std::size_t begin = it->offset, room = it->size;
+        const std::size_t pad = (a - begin % a) % a;
+        if (room < pad + bytes) continue;
+        const std::size_t at = begin + pad;
+        const std::size_t tail = room - pad - bytes;
+        // the span is replaced by [pad piece][tail piece], whichever exist, keeping offset order
+        if (pad && tail) {
+            it->size = pad;
+            spans_.insert(it + 1, Block{at + bytes, tail});
+        } else if (pad) {
+            it->size = pad;
+        } else if (tail) {
+            it->offset = at + bytes;
+            it->size = tail;
+        } else {
+            spans_.erase(it);
+        }
+        used_ += pad + bytes;
+        peak_ = std::max(peak_, used_);
+        return static_cast<i64>(at);
+    }
+    return -1;
+}
+
+void MemoryPool::free(i64 offset, std::size_t bytes) {
+    if (bytes == 0) return;
+    const std::size_t off = static_cast<std::size_t>(offset);
+    auto it = std::lower_bound(spans_.begin(), spans_.end(), off,
+                               [](const Block& b, std::size_t o) { return b.offset < o; });
+    it = spans_.insert(it, Block{off, bytes});
+    if (used_ >= bytes) used_ -= bytes;  // alignment padding is never given back
+    auto next = it + 1;
+    if (next != spans_.end() && it->offset + it->size == next->offset) {
+        it->size += next->size;
+        it = spans_.erase(next) - 1;
+    }
+    if (it != spans_.begin()) {
+        auto prev = it - 1;
+        if (prev->offset + prev->size == it->offset) {
+            prev->size += it->size;
+            spans_.erase(it);
+        }
+    }
+}
+
+double MemoryPool::fragmentation() const {
+    std::size_t all = 0, biggest = 0;
+    for (const Block& b : spans_) {
+        all += b.size;
+        biggest = std::max(biggest, b.size);
+    }
+    return all ? 1.0 - static_cast<double>(biggest) / static_cast<double>(all) : 0.0;
+}
+
+// =================================================================================================
+// BlockManager -- behaviour of src/scheduler/block_manager.cpp:7-77
+// =================================================================================================
+BlockManager::BlockManager(std::size_t prefix_pool_bytes, std::size_t ring_pool_bytes)
+    : prefix_arena_(prefix_pool_bytes), ring_arena_(ring_pool_bytes) {}
+
+void BlockManager::refresh_shared() {
+    std::size_t s = 0;
+    for (const auto& kv : table_)
+        if (kv.second.refcount >= 2) s += kv.second.bytes;
+    shared_now_ = s;
+    shared_peak_ = std::max(shared_peak_, s);
+}
+
+PrefixEntry* BlockManager::acquire_prefix(const std::string& key, int prefill_len, std::size_t bytes) {
+    auto hit = table_.find(key);
+    if (hit == table_.end()) {
+        const i64 off = prefix_arena_.allocate(bytes);
+        UOCR_CHECK(off >= 0, "prefix pool exhausted");
+        PrefixEntry fresh;
+        fresh.key = key;
+        fresh.prefill_len = prefill_len;
+        fresh.bytes = bytes;
+        fresh.refcount = 0;
+        fresh.offset = off;
+        hit = table_.emplace(key, std::move(fresh)).first;
+    }
+    hit->second.refcount += 1;
+    refresh_shared();
+    return &hit->second;
+}
+
+void BlockManager::release_prefix(const std::string& key) {
+    auto hit = table_.find(key);
+    if (hit == table_.end()) return;  // unknown key: nothing to do
+    if (--hit->second.refcount <= 0) {
+        prefix_arena_.free(hit->second.offset, hit->second.bytes);
+        table_.erase(hit);
+    }
+    refresh_shared();
+}
+
+i64 BlockManager::allocate_ring(std::size_t bytes) { return ring_arena_.allocate(bytes); }
+void BlockManager::free_ring(i64 offset, std::size_t bytes) { ring_arena_.free(offset, bytes); }
+
+std::size_t BlockManager::total_prefix_bytes() const {
+    std::size_t t = 0;
+    for (const auto& kv : table_) t += kv.second.bytes;
+    return t;
+}
+
+BlockManager::Stats BlockManager::stats() const {
+    Stats s;
+    s.prefix_live_bytes = prefix_arena_.used();
+    s.prefix_peak_bytes = prefix_arena_.peak();
+    s.prefix_shared_bytes = shared_now_;
+    s.ring_live_bytes = ring_arena_.used();
+    s.ring_peak_bytes = ring_arena_.peak();
+    s.prefix_fragmentation = prefix_arena_.fragmentation();
+    s.ring_fragmentation = ring_arena_.fragmentation();
+    s.live_prefixes = table_.size();
+    return s;
+}
+
+// =================================================================================================
+// ContinuousBatchScheduler -- behaviour of src/scheduler/continuous_batch.cpp:10-117
+// =================================================================================================
+int ContinuousBatchScheduler::add_request(Request r) {
+    const int id = next_id_++;
+    r.id = id;
+    if (r.arrival_time == 0.0) r.arrival_time = cpu_seconds();
+    queue_.push_back(id);
+    all_.emplace(id, std::move(r));
+    return id;
+}
+
+Batch ContinuousBatchScheduler::build_batch() {
+    Batch out;
+    auto filled = [&] { return static_cast<int>(out.prefill.size() + out.decode.size()); };
+    // requests already running keep their place first
+    for (int id : active_) {
+        auto it = all_.find(id);
+        if (it == all_.end() || it->second.is_finished()) continue;
+        if (filled() >= max_batch_) break;
+        if (it->second.state == ReqState::Decoding) out.decode.push_back(id);
+        else if (it->second.state == ReqState::Prefilling) out.prefill.push_back(id);
+    }
+    // then admit from the FIFO while there is room
+    while (!queue_.empty() && filled() < max_batch_) {
+        const int id = queue_.front();
+        queue_.pop_front();
+        auto it = all_.find(id);
+        if (it == all_.end()) continue;
+        it->second.state = ReqState::Prefilling;
+        active_.push_back(id);
+        out.prefill.push_back(id);
+    }
+    // drop what has finished in the meantime
+    std::vector<int> keep;
+    keep.reserve(active_.size());
+    for (int id : active_) {
+        auto it = all_.find(id);
+        if (it != all_.end() && !it->second.is_finished()) keep.push_back(id);
+    }
+    active_.swap(keep);
+    return out;
+}
+
+void ContinuousBatchScheduler::mark_prefilling(int id) {
+    if (Request* r = get(id)) r->state = ReqState::Prefilling;
+}
+
+void ContinuousBatchScheduler::mark_prefilled(int id) {
+    if (Request* r = get(id)) {
+        r->state = ReqState::Decoding;
+        r->prefill_time = cpu_seconds();
+    }
+}
+
+bool ContinuousBatchScheduler::add_token(int id, int token) {
+    Request* r = get(id);
+    if (!r) return true;
+    r->output_tokens.push_back(token);
+    r->decode_steps += 1;
+    if (r->first_token_time == 0.0) r->first_token_time = cpu_seconds();
+    if (static_cast<int>(r->output_tokens.size()) < r->max_new_tokens) return false;
+    finish(id);
+    return true;
+}
+
+void ContinuousBatchScheduler::finish(int id) {
+    Request* r = get(id);
+    if (!r) return;
+    r->state = ReqState::Finished;
+    r->finish_time = cpu_seconds();
+    r->cache.reset();
+    active_.erase(std::remove(active_.begin(), active_.end(), id), active_.end());
+}
+
+Request* ContinuousBatchScheduler::get(int id) {
+    auto it = all_.find(id);
+    return it == all_.end() ? nullptr : &it->second;
+}
+const Request* ContinuousBatchScheduler::get(int id) const {
+    auto it = all_.find(id);
+    return it == all_.end() ? nullptr : &it->second;
+}
+
+ContinuousBatchScheduler::Stats ContinuousBatchScheduler::stats() const {
+    Stats s;
+    s.total_requests = all_.size();
+    for (const auto& kv : all_) {
+        if (!kv.second.is_finished()) continue;
+        s.finished_requests += 1;
+        s.prefill_tokens += kv.second.prompt_tokens.size();
+        s.decode_tokens += kv.second.output_tokens.size();
+    }
+    s.waiting = queue_.size();
+    s.running = active_.size();
+    s.last_batch_size = static_cast<double>(active_.size());
+    return s;
+}
+
+// =================================================================================================
+// SlotAllocator -- src/engine/engine.cpp:306-318, 341-347
+// =================================================================================================
+void SlotAllocator::reset(int slots) {
+    free_.resize(static_cast<std::size_t>(std::max(slots, 0)));
+    for (int i = 0; i < slots; ++i) free_[static_cast<std::size_t>(i)] = i;
+    by_request_.clear();
+}
+
+int SlotAllocator::acquire(int request_id) {
+    UOCR_CHECK(!free_.empty(), "generate_batch: no free slot");
+    const int slot = free_.back();
+    free_.pop_back();
+    by_request_[request_id] = slot;
+    return slot;
+}
+
+void SlotAllocator::release(int request_id) {
+    auto it = by_request_.find(request_id);
+    if (it == by_request_.end()) return;
+    free_.push_back(it->second);
+    by_request_.erase(it);
+}
+
+int SlotAllocator::slot_of(int request_id) const {
+    auto it = by_request_.find(request_id);
+    return it == by_request_.end() ? -1 : it->second;
+}
+
+// =================================================================================================
+// detail::PagedSeqStore -- one sequence, all layers, private blocks, device cursors + host shadow
+// =================================================================================================
+namespace detail {
+
+class PagedSeqStore {
+public:
+    int layers = 0, kvh = 0, hd = 0, window = 128;
+    int prefill_len = 0, capacity = 0;
+    bool configured = false;
+    DType dtype = DType::F32;
+
+    // host shadow of the state machine (the device cursors advance identically)
+    std::vector<int> len, ring_pos;
+    std::vector<char> ring_started;
+
+    // device side
+    int n_blocks = 0, alloc_rows = 0;
+    std::vector<void*> kpool, vpool;  // per layer
+    int32_t* d_table = nullptr;
+    int* d_len = nullptr;       // [layers]
+    int* d_ring = nullptr;      // [layers]
+    int* d_prefill = nullptr;   // [1]
+    int* d_zero_slots = nullptr;  // [alloc_rows] zeros (row -> slot 0)
+    int* d_iota = nullptr;        // [alloc_rows] 0,1,2,...
+    float* d_stage_a = nullptr;   // staging for k / q / gathered K
+    float* d_stage_b = nullptr;   // staging for v / out / gathered V
+    std::size_t stage_elems = 0;
+    uocr_b200_workspace* ws = nullptr;
+    std::vector<uocr_b200_paged_kv> view;
+
+    // host mirrors (logical view, [capacity][row])
+    mutable std::vector<std::vector<float>> kmir, vmir;
+    mutable std::vector<char> mirror_fresh;  // mirror equals device
+    std::vector<char> host_dirty;            // caller may have written through mutable_*()
+
+    ~PagedSeqStore() { release_device(); }
+
+    int row() const { return kvh * hd; }
+    int esize() const { return dtype == DType::BF16 ? 2 : 4; }
+
+    void release_device() {
+        for (void* p : kpool) if (p) cudaFree(p);
+        for (void* p : vpool) if (p) cudaFree(p);
+        kpool.clear();
+        vpool.clear();
+        for (void* p : {static_cast<void*>(d_table), static_cast<void*>(d_len), static_cast<void*>(d_ring),
+                        static_cast<void*>(d_prefill), static_cast<void*>(d_zero_slots), static_cast<void*>(d_iota),
+                        static_cast<void*>(d_stage_a), static_cast<void*>(d_stage_b)})
+            if (p) cudaFree(p);
+        d_table = nullptr; d_len = d_ring = d_prefill = d_zero_slots = d_iota = nullptr;
+        d_stage_a = d_stage_b = nullptr;
+        stage_elems = 0;
+        if (ws) uocr_b200_workspace_destroy(ws);
+        ws = nullptr;
+        n_blocks = alloc_rows = 0;
+    }
+
+    void configure(int L, int kv_heads, int head_dim, int W) {
+        release_device();
+        layers = L; kvh = kv_heads; hd = head_dim; window = W;
+        len.assign(static_cast<std::size_t>(L), 0);
+        ring_pos.assign(static_cast<std::size_t>(L), 0);
+        ring_started.assign(static_cast<std::size_t>(L), 0);
+        kmir.assign(static_cast<std::size_t>(L), {});
+        vmir.assign(static_cast<std::size_t>(L), {});
+        mirror_fresh.assign(static_cast<std::size_t>(L), 0);
+        host_dirty.assign(static_cast<std::size_t>(L), 0);
+        prefill_len = capacity = 0;
+        configured = true;
+    }
+
+    void ensure_stage(std::size_t elems) {
+        if (elems <= stage_elems) return;
+        if (d_stage_a) cudaFree(d_stage_a);
+        if (d_stage_b) cudaFree(d_stage_b);
+        cuda_ok(cudaMalloc(&d_stage_a, elems * sizeof(float)), "stage alloc");
+        cuda_ok(cudaMalloc(&d_stage_b, elems * sizeof(float)), "stage alloc");
+        stage_elems = elems;
+    }
+
+    void publish_cursors(cudaStream_t st = nullptr) {
+        cuda_ok(cudaMemcpyAsync(d_len, len.data(), sizeof(int) * layers, cudaMemcpyHostToDevice, st), "len H2D");
+        cuda_ok(cudaMemcpyAsync(d_ring, ring_pos.data(), sizeof(int) * layers, cudaMemcpyHostToDevice, st), "ring H2D");
+        cuda_ok(cudaMemcpyAsync(d_prefill, &prefill_len, sizeof(int), cudaMemcpyHostToDevice, st), "prefill H2D");
+        cuda_ok(cudaStreamSynchronize(st), "cursor publish");  // sources are host members
+    }
+
+    void reset(int P) {
+        UOCR_CHECK(configured, "RSWACache not configured");
+        UOCR_CHECK(P >= 0, "prefill_len must be >= 0");
+        UOCR_CHECK(layers > 0 && kvh > 0 && hd > 0 && window > 0, "RSWACache geometry must be positive");
+        prefill_len = P;
+        capacity = P + window;
+        const int need_blocks = blocks_for(P) + blocks_for(window) + 1;
+        const int need_rows = need_blocks * UOCR_B200_BLOCK_TOKENS;
+        const std::size_t blk_bytes = static_cast<std::size_t>(kvh) * UOCR_B200_BLOCK_TOKENS * hd * esize();
+        if (need_blocks > n_blocks || kpool.empty()) {
+            release_device();
+            kpool.assign(static_cast<std::size_t>(layers), nullptr);
+            vpool.assign(static_cast<std::size_t>(layers), nullptr);
+            for (int l = 0; l < layers; ++l) {
+                cuda_ok(cudaMalloc(&kpool[l], blk_bytes * need_blocks), "K pool");
+                cuda_ok(cudaMalloc(&vpool[l], blk_bytes * need_blocks), "V pool");
+            }
+            n_blocks = need_blocks;
+            alloc_rows = need_rows;
+            cuda_ok(cudaMalloc(&d_table, sizeof(int32_t) * need_blocks), "table");
+            cuda_ok(cudaMalloc(&d_len, sizeof(int) * layers), "len");
+            cuda_ok(cudaMalloc(&d_ring, sizeof(int) * layers), "ring");
+            cuda_ok(cudaMalloc(&d_prefill, sizeof(int)), "prefill");
+            cuda_ok(cudaMalloc(&d_zero_slots, sizeof(int) * need_rows), "slots");
+            cuda_ok(cudaMalloc(&d_iota, sizeof(int) * need_rows), "iota");
+            std::vector<int> iota(static_cast<std::size_t>(need_rows));
+            for (int i = 0; i < need_rows; ++i) iota[static_cast<std::size_t>(i)] = i;
+            cuda_ok(cudaMemcpy(d_iota, iota.data(), sizeof(int) * need_rows, cudaMemcpyHostToDevice), "iota H2D");
+            cuda_ok(cudaMemset(d_zero_slots, 0, sizeof(int) * need_rows), "slots zero");
+            std::vector<int32_t> tbl(static_cast<std::size_t>(need_blocks));
+            for (int i = 0; i < need_blocks; ++i) tbl[static_cast<std::size_t>(i)] = i;
+            cuda_ok(cudaMemcpy(d_table, tbl.data(), sizeof(int32_t) * need_blocks, cudaMemcpyHostToDevice), "table H2D");
+            abi_ok(uocr_b200_workspace_create(std::max(need_rows, 64), &ws), "workspace");
+            view.assign(static_cast<std::size_t>(layers), uocr_b200_paged_kv{});
+            for (int l = 0; l < layers; ++l) {
+                view[l].k_pool = kpool[l];
+                view[l].v_pool = vpool[l];
+                view[l].block_table = d_table;
+                view[l].table_stride = need_blocks;
+                view[l].num_blocks = need_blocks;
+                view[l].kv_heads = kvh;
+                view[l].head_dim = hd;
+                view[l].dtype = dtype == DType::BF16 ? UOCR_B200_BF16 : UOCR_B200_F32;
+            }
+        }
+        for (int l = 0; l < layers; ++l) {
+            cuda_ok(cudaMemset(kpool[l], 0, blk_bytes * n_blocks), "K zero");
+            cuda_ok(cudaMemset(vpool[l], 0, blk_bytes * n_blocks), "V zero");
+            len[l] = P;
+            ring_pos[l] = 0;
+            ring_started[l] = 0;
+            kmir[l].assign(static_cast<std::size_t>(capacity) * row(), 0.0f);
+            vmir[l].assign(static_cast<std::size_t>(capacity) * row(), 0.0f);
+            mirror_fresh[l] = 1;  // all zeros on both sides
+            host_dirty[l] = 0;
+        }
+        publish_cursors();
+    }
+
+    // Physical "position" (token index along the table row) of logical slot s.
+    int phys_pos(int s) const {
+        return s < prefill_len ? s : blocks_for(prefill_len) * UOCR_B200_BLOCK_TOKENS + (s - prefill_len);
+    }
+
+    // If the caller wrote through mutable_keys()/mutable_values(), push the mirror back first.
+    void flush_host_edits(int layer) {
+        if (!host_dirty[layer]) return;
+        const int n = len[layer];
+        if (n > 0) {
+            ensure_stage(static_cast<std::size_t>(capacity) * row());
+            std::vector<int> pos(static_cast<std::size_t>(n));
+            for (int s = 0; s < n; ++s) pos[static_cast<std::size_t>(s)] = phys_pos(s);
+            int* d_pos = nullptr;
+            cuda_ok(cudaMalloc(&d_pos, sizeof(int) * n), "pos alloc");
+            cuda_ok(cudaMemcpy(d_pos, pos.data(), sizeof(int) * n, cudaMemcpyHostToDevice), "pos H2D");
+            cuda_ok(cudaMemcpy(d_stage_a, kmir[layer].data(), sizeof(float) * n * row(), cudaMemcpyHostToDevice), "K H2D");
+            cuda_ok(cudaMemcpy(d_stage_b, vmir[layer].data(), sizeof(float) * n * row(), cudaMemcpyHostToDevice), "V H2D");
+            abi_ok(uocr_b200_rswa_write_prefill_ragged_paged(&view[layer], d_stage_a, d_stage_b, d_zero_slots, d_pos, n,
+                                                             ws, nullptr), "mirror upload");
+            cuda_ok(cudaDeviceSynchronize(), "mirror upload sync");
+            cudaFree(d_pos);
+        }
+        host_dirty[layer] = 0;
+        mirror_fresh[layer] = 0;  // a bf16 pool rounds what was written
+    }
+
+    void advance_shadow(int layer) {
+        const int n = len[layer];
+        if (n < prefill_len + window) {
+            len[layer] = n + 1;
+            if (n + 1 >= prefill_len + window) {
+                ring_started[layer] = 1;
+                ring_pos[layer] = 0;
+            }
+        } else {
+            ring_started[layer] = 1;
+            ring_pos[layer] = (ring_pos[layer] + 1) % window;
+        }
+    }
+
+    void write_prefill_dev(int layer, const float* d_k, const float* d_v, int seq, cudaStream_t st) {
+        UOCR_CHECK(seq <= capacity, "prefill larger than cache capacity");
+        flush_host_edits(layer);
+        if (seq > 0)
+            abi_ok(uocr_b200_rswa_write_prefill_ragged_paged(&view[layer], d_k, d_v, d_zero_slots, d_iota, seq, ws, st),
+                   "write_prefill");
+        len[layer] = seq;
+        prefill_len = seq;
+        cuda_ok(cudaMemcpyAsync(d_len + layer, &len[layer], sizeof(int), cudaMemcpyHostToDevice, st), "len H2D");
+        cuda_ok(cudaMemcpyAsync(d_prefill, &prefill_len, sizeof(int), cudaMemcpyHostToDevice, st), "prefill H2D");
+        cuda_ok(cudaStreamSynchronize(st), "write_prefill sync");
+        mirror_fresh[layer] = 0;
+    }
+
+    void append_dev(int layer, const float* d_k, const float* d_v, cudaStream_t st) {
+        flush_host_edits(layer);
+        abi_ok(uocr_b200_rswa_append_decode_batch_paged(&view[layer], d_k, d_v, d_len + layer, d_ring + layer, d_prefill,
+                                                        d_zero_slots, 1, window, ws, st), "append_decode");
+        advance_shadow(layer);
+        mirror_fresh[layer] = 0;
+    }
+
+    void attention_dev(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads, bool causal,
+                       cudaStream_t st) {
+        flush_host_edits(layer);
+        if (seq > ws_rows()) grow_workspace(seq);
+        abi_ok(uocr_b200_rswa_attention_paged(&view[layer], 0, d_q, len[layer], nullptr, prefill_len, nullptr, seq,
+                                              q_start, heads, causal ? 1 : 0, d_out, ws, st), "attention");
+    }
+
+    int ws_rows_ = 0;
+    int ws_rows() { return ws_rows_ ? ws_rows_ : std::max(alloc_rows, 64); }
+    void grow_workspace(int rows) {
+        cuda_ok(cudaDeviceSynchronize(), "workspace grow sync");
+        if (ws) uocr_b200_workspace_destroy(ws);
+        ws = nullptr;
+        abi_ok(uocr_b200_workspace_create(rows, &ws), "workspace");
+        ws_rows_ = rows;
+    }
+
+    // Fills the device staging buffers with the logical fp32 view of `layer` (rows >= len are zero).
+    void gather_dev(int layer, cudaStream_t st) {
+        flush_host_edits(layer);
+        ensure_stage(static_cast<std::size_t>(std::max(capacity, 1)) * row());
+        if (capacity > 0)
+            abi_ok(uocr_b200_rswa_gather_paged(&view[layer], d_len + layer, d_prefill, d_zero_slots, 1, capacity, d_stage_a,
+                                               d_stage_b, UOCR_B200_F32, ws, st), "gather");
+    }
+
+    void refresh_mirror(int layer) const {
+        auto* self = const_cast<PagedSeqStore*>(this);
+        if (mirror_fresh[layer] || capacity == 0) return;
+        self->gather_dev(layer, nullptr);
+        const std::size_t n = static_cast<std::size_t>(capacity) * row();
+        kmir[layer].resize(n);
+        vmir[layer].resize(n);
+        cuda_ok(cudaMemcpy(kmir[layer].data(), d_stage_a, n * sizeof(float), cudaMemcpyDeviceToHost), "K D2H");
+        cuda_ok(cudaMemcpy(vmir[layer].data(), d_stage_b, n * sizeof(float), cudaMemcpyDeviceToHost), "V D2H");
+        mirror_fresh[layer] = 1;
+    }
+};
+
+}  // namespace detail
+
+// =================================================================================================
+// RSWACache -- interface of include/uocr/kv_cache.h:23-86, semantics of src/scheduler/kv_cache.cpp
+// =================================================================================================
+RSWACache::RSWACache() : s_(new detail::PagedSeqStore) {}
+RSWACache::RSWACache(int num_layers, int kv_heads, int head_dim, int window) : s_(new detail::PagedSeqStore) {
+    configure(num_layers, kv_heads, head_dim, window);
+}
+RSWACache::~RSWACache() = default;
+RSWACache::RSWACache(RSWACache&&) noexcept = default;
+RSWACache& RSWACache::operator=(RSWACache&&) noexcept = default;
+
+void RSWACache::configure(int num_layers, int kv_heads, int head_dim, int window) {
+    s_->configure(num_layers, kv_heads, head_dim, window);
+}
+void RSWACache::set_kv_dtype(DType t) {
+    UOCR_CHECK(t == DType::F32 || t == DType::BF16, "KV dtype must be F32 or BF16");
+    UOCR_CHECK(s_->kpool.empty(), "set_kv_dtype must precede reset()");
+    s_->dtype = t;
+}
+void RSWACache::reset(int prefill_len) { s_->reset(prefill_len); }
+
+int RSWACache::num_layers() const { return s_->layers; }
+int RSWACache::kv_heads() const { return s_->kvh; }
+int RSWACache::head_dim() const { return s_->hd; }
+int RSWACache::window() const { return s_->window; }
+int RSWACache::prefill_len() const { return s_->prefill_len; }
+int RSWACache::length(int layer) const { return s_->len[layer]; }
+int RSWACache::ring_pos(int layer) const { return s_->ring_pos[layer]; }
+bool RSWACache::ring_started(int layer) const { return s_->ring_started[layer] != 0; }
+int RSWACache::capacity() const { return s_->capacity; }
+
+void RSWACache::write_prefill(int layer, const float* k, const float* v, int seq) {
+    UOCR_CHECK(seq <= s_->capacity, "prefill larger than cache capacity");
+    s_->flush_host_edits(layer);  // before the staging buffers are reused for k / v
+    const std::size_t n = static_cast<std::size_t>(std::max(seq, 0)) * s_->row();
+    s_->ensure_stage(std::max<std::size_t>(n, 1));
+    if (n) {
+        cuda_ok(cudaMemcpy(s_->d_stage_a, k, n * sizeof(float), cudaMemcpyHostToDevice), "K H2D");
+        cuda_ok(cudaMemcpy(s_->d_stage_b, v, n * sizeof(float), cudaMemcpyHostToDevice), "V H2D");
+    }
+    s_->write_prefill_dev(layer, s_->d_stage_a, s_->d_stage_b, seq, nullptr);
+}
+
+void RSWACache::append_decode(int layer, const float* k, const float* v) {
+    s_->flush_host_edits(layer);
+    const std::size_t n = static_cast<std::size_t>(s_->row());
+    s_->ensure_stage(n);
+    cuda_ok(cudaMemcpy(s_->d_stage_a, k, n * sizeof(float), cudaMemcpyHostToDevice), "K H2D");
+    cuda_ok(cudaMemcpy(s_->d_stage_b, v, n * sizeof(float), cudaMemcpyHostToDevice), "V H2D");
+    s_->append_dev(layer, s_->d_stage_a, s_->d_stage_b, nullptr);
+}
+
+void RSWACache::attention(int layer, const float* q, int seq, int q_start, float* out, int heads, bool causal) const {
+    UOCR_CHECK(s_->hd <= 512, "head_dim too large for stack accumulator");
+    if (seq <= 0) return;
+    s_->flush_host_edits(layer);
+    const std::size_t n = static_cast<std::size_t>(seq) * heads * s_->hd;
+    s_->ensure_stage(n);
+    cuda_ok(cudaMemcpy(s_->d_stage_a, q, n * sizeof(float), cudaMemcpyHostToDevice), "q H2D");
+    s_->attention_dev(layer, s_->d_stage_a, seq, q_start, s_->d_stage_b, heads, causal, nullptr);
+    cuda_ok(cudaMemcpy(out, s_->d_stage_b, n * sizeof(float), cudaMemcpyDeviceToHost), "out D2H");
+}
+
+const float* RSWACache::keys(int layer) const {
+    s_->refresh_mirror(layer);
+    return s_->kmir[layer].data();
+}
+const float* RSWACache::values(int layer) const {
+    s_->refresh_mirror(layer);
+    return s_->vmir[layer].data();
+}
+float* RSWACache::mutable_keys(int layer) {
+    s_->refresh_mirror(layer);
+    s_->host_dirty[layer] = 1;
+    return s_->kmir[layer].data();
+}
+float* RSWACache::mutable_values(int layer) {
+    s_->refresh_mirror(layer);
+    s_->host_dirty[layer] = 1;
+    return s_->vmir[layer].data();
+}
+
+std::size_t RSWACache::bytes() const {
+    // the reference reports its fp32 footprint: 2 x layers x capacity x row x 4 (kv_cache.cpp:132-137)
+    return 2u * static_cast<std::size_t>(s_->layers) * s_->capacity * s_->row() * sizeof(float);
+}
+
+// =================================================================================================
+// cuda::GpuRSWACache -- interface of include/uocr/gpu_cache.h:21-72
+// =================================================================================================
+namespace cuda {
+
+GpuRSWACache::GpuRSWACache() : s_(new detail::PagedSeqStore) {}
+GpuRSWACache::GpuRSWACache(int num_layers, int kv_heads, int head_dim, int window) : s_(new detail::PagedSeqStore) {
+    configure(num_layers, kv_heads, head_dim, window);
+}
+GpuRSWACache::~GpuRSWACache() = default;
+
+void GpuRSWACache::configure(int num_layers, int kv_heads, int head_dim, int window) {
+    s_->configure(num_layers, kv_heads, head_dim, window);
+}
+void GpuRSWACache::set_kv_dtype(DType t) {
+    UOCR_CHECK(t == DType::F32 || t == DType::BF16, "KV dtype must be F32 or BF16");
+    UOCR_CHECK(s_->kpool.empty(), "set_kv_dtype must precede reset()");
+    s_->dtype = t;
+}
+void GpuRSWACache::reset(int prefill_len) {
+    UOCR_CHECK(s_->configured, "GpuRSWACache not configured");
+    s_->reset(prefill_len);
+}
+void GpuRSWACache::write_prefill(int layer, const float* d_k, const float* d_v, int seq, cudaStream_t stream) {
+    s_->write_prefill_dev(layer, d_k, d_v, seq, stream);
+}
+void GpuRSWACache::append_decode(int layer, const float* d_k, const float* d_v, cudaStream_t stream) {
+    s_->append_dev(layer, d_k, d_v, stream);
+}
+void GpuRSWACache::reset_device_state(int prefill_len, cudaStream_t stream) {
+    // device cursors <- (len = prefill_len, ring_pos = 0) for every layer (src/kernels/cuda/gpu_cache.cu:88-95)
+    for (int l = 0; l < s_->layers; ++l) {
+        s_->len[l] = prefill_len;
+        s_->ring_pos[l] = 0;
+        s_->ring_started[l] = 0;
+    }
+    s_->prefill_len = prefill_len;
+    s_->publish_cursors(stream);
+}
+void GpuRSWACache::append_decode_device(int layer, const float* d_k, const float* d_v, cudaStream_t stream) {
+    s_->append_dev(layer, d_k, d_v, stream);
+}
+const int* GpuRSWACache::len_dev(int layer) const { return s_->d_len + layer; }
+void GpuRSWACache::attention(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads, bool causal,
+                             cudaStream_t stream) const {
+    s_->attention_dev(layer, d_q, seq, q_start, d_out, heads, causal, stream);
+}
+int GpuRSWACache::len(int layer) const { return s_->len[layer]; }
+int GpuRSWACache::prefill_len() const { return s_->prefill_len; }
+int GpuRSWACache::window() const { return s_->window; }
+int GpuRSWACache::capacity() const { return s_->capacity; }
+int GpuRSWACache::num_layers() const { return s_->layers; }
+const float* GpuRSWACache::keys(int layer) const {
+    s_->gather_dev(layer, nullptr);
+    return s_->d_stage_a;
+}
+const float* GpuRSWACache::values(int layer) const {
+    s_->gather_dev(layer, nullptr);
+    return s_->d_stage_b;
+}
+
+// =================================================================================================
+// the reference's free functions (include/uocr/cuda_ops.h:59-123) over the C ABI
+// =================================================================================================
+namespace {
+
+uocr_b200_workspace* default_workspace(int rows) {
+    struct Slot {
+        uocr_b200_workspace* ws = nullptr;
+        int rows = 0;
+    };
+    static Slot per_device[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    Slot& s = per_device[dev & 63];
+    if (!s.ws || rows > s.rows) {
+        if (s.ws) {
+            cudaDeviceSynchronize();
+            uocr_b200_workspace_destroy(s.ws);
+            s.ws = nullptr;
+        }
+        const int want = std::max(rows, 4096);
+        if (uocr_b200_workspace_create(want, &s.ws) != UOCR_B200_OK) {
+            std::fprintf(stderr, "uocr::cuda: workspace: %s\n", uocr_b200_last_error());
+            return nullptr;
+        }
+        s.rows = want;
+    }
+    return s.ws;
+}
+
+// CUDA-side failures are reported, not thrown, like the reference's wrappers (gpu_cache.cu:10-18).
+void report(int rc, const char* what) {
+    if (rc != UOCR_B200_OK) std::fprintf(stderr, "uocr::cuda::%s: %s: %s\n", what, uocr_b200_status_string(rc), uocr_b200_last_error());
+}
+
+}  // namespace
+
+void rswa_attention_decode(const float* q, const float* kcache, const float* vcache, int kv_len, int heads,
+                           int kv_heads, int head_dim, float* out, cudaStream_t stream) {
+    report(uocr_b200_rswa_attention_f32(q, kcache, vcache, kv_len, nullptr, 1, 0, heads, kv_heads, head_dim, 0, out,
+                                        default_workspace(1), stream), "rswa_attention_decode");
+}
+void rswa_attention(const float* q, const float* kcache, const float* vcache, int kv_len, int seq, int q_start,
+                    int heads, int kv_heads, int head_dim, bool causal, float* out, cudaStream_t stream) {
+    report(uocr_b200_rswa_attention_f32(q, kcache, vcache, kv_len, nullptr, seq, q_start, heads, kv_heads, head_dim,
+                                        causal ? 1 : 0, out, default_workspace(seq), stream), "rswa_attention");
+}
+void rswa_attention_devlen(const float* q, const float* kcache, const float* vcache, const int* d_len, int seq,
+                           int q_start, int heads, int kv_heads, int head_dim, bool causal, float* out,
+                           cudaStream_t stream) {
+    report(uocr_b200_rswa_attention_f32(q, kcache, vcache, 0, d_len, seq, q_start, heads, kv_heads, head_dim,
+                                        causal ? 1 : 0, out, default_workspace(seq), stream), "rswa_attention_devlen");
+}
+void rswa_append_decode(const float* k, const float* v, float* kcache, float* vcache, int* d_len, int* d_ring_pos,
+                        int prefill_len, int window, int kv_heads, int head_dim, cudaStream_t stream) {
+    report(uocr_b200_rswa_append_decode_f32(k, v, kcache, vcache, d_len, d_ring_pos, prefill_len, window, kv_heads,
+                                            head_dim, stream), "rswa_append_decode");
+}
+void rswa_append_decode_batch(const float* k, const float* v, float* kcache_base, float* vcache_base, int* d_len,
+                              int* d_ring_pos, const int* d_prefill_len, const int* d_slots, int batch, int batch_cap,
+                              int window, int kv_heads, int head_dim, cudaStream_t stream) {
+    report(uocr_b200_rswa_append_decode_batch_f32(k, v, kcache_base, vcache_base, d_len, d_ring_pos, d_prefill_len,
+                                                  d_slots, batch, batch_cap, window, kv_heads, head_dim, stream),
+           "rswa_append_decode_batch");
+}
+void rswa_attention_batch(const float* q, const float* kcache_base, const float* vcache_base, const int* d_len,
+                          const int* d_slots, int batch, int batch_cap, int heads, int kv_heads, int head_dim,
+                          float* out, cudaStream_t stream) {
+    if (batch <= 0) return;
+    report(uocr_b200_rswa_attention_batch_f32(q, kcache_base, vcache_base, d_len, d_slots, batch, batch_cap, heads,
+                                              kv_heads, head_dim, out, default_workspace(batch), stream),
+           "rswa_attention_batch");
+}
+void rswa_write_prefill_ragged(const float* k, const float* v, float* kcache_base, float* vcache_base,
+                               const int* d_slots, const int* d_pos, int total, int batch_cap, int kv_heads,
+                               int head_dim, cudaStream_t stream) {
+    report(uocr_b200_rswa_write_prefill_ragged_f32(k, v, kcache_base, vcache_base, d_slots, d_pos, total, batch_cap,
+                                                   kv_heads, head_dim, stream), "rswa_write_prefill_ragged");
+}
+void rswa_attention_ragged(const float* q, const float* kcache_base, const float* vcache_base, const int* d_slots,
+                           const int* d_pos, int total, int batch_cap, int heads, int kv_heads, int head_dim,
+                           float* out, cudaStream_t stream) {
+    if (total <= 0) return;
+    report(uocr_b200_rswa_attention_ragged_f32(q, kcache_base, vcache_base, d_slots, d_pos, total, batch_cap, heads,
+                                               kv_heads, head_dim, out, default_workspace(total), stream),
+           "rswa_attention_ragged");
+}
+
+// =================================================================================================
+// PagedBatchKV
+// =================================================================================================
+struct PagedBatchKV::Impl {
+    Config cfg;
+    std::unique_ptr<BlockManager> bm;
+    int stride = 0, num_blocks = 0;
+    std::vector<void*> kpool, vpool;
+    int32_t* d_table = nullptr;
+    int* d_len = nullptr;      // [layers][slots]
+    int* d_ring = nullptr;     // [layers][slots]
+    int* d_prefill = nullptr;  // [slots]
+    int* d_state_stage = nullptr;  // packed upload target, see publish()
+    int* h_state_stage = nullptr;  // pinned
+    uocr_b200_workspace* ws = nullptr;
+    std::vector<uocr_b200_paged_kv> view;
+    struct SlotState {
+        bool bound = false;
+        std::string key;
+        bool has_prefix = false;
+        i64 ring_off = -1;
+        int prefix_len = 0;
+    };
+    std::vector<SlotState> slot;
+    std::vector<std::vector<int>> rows;  // host copy of the table
+
+    std::size_t block_bytes() const {
+        return static_cast<std::size_t>(cfg.kv_heads) * UOCR_B200_BLOCK_TOKENS * cfg.head_dim *
+               (cfg.dtype == DType::BF16 ? 2 : 4);
+    }
+    void free_all() {
+        for (void* p : kpool) if (p) cudaFree(p);
+        for (void* p : vpool) if (p) cudaFree(p);
+        kpool.clear();
+        vpool.clear();
+        if (d_table) cudaFree(d_table);
+        if (d_len) cudaFree(d_len);
+        if (d_ring) cudaFree(d_ring);
+        if (d_prefill) cudaFree(d_prefill);
+        if (d_state_stage) cudaFree(d_state_stage);
+        if (h_state_stage) cudaFreeHost(h_state_stage);
+        d_table = nullptr; d_len = d_ring = d_prefill = d_state_stage = nullptr; h_state_stage = nullptr;
+        if (ws) uocr_b200_workspace_destroy(ws);
+        ws = nullptr;
+    }
+    ~Impl() { free_all(); }
+};
+
+PagedBatchKV::PagedBatchKV() : p_(new Impl) {}
+PagedBatchKV::~PagedBatchKV() = default;
+const PagedBatchKV::Config& PagedBatchKV::config() const { return p_->cfg; }
+const BlockManager& PagedBatchKV::blocks() const { return *p_->bm; }
+const std::vector<int>& PagedBatchKV::table_row(int slot) const { return p_->rows[slot]; }
+const uocr_b200_paged_kv& PagedBatchKV::layer_view(int layer) const { return p_->view[layer]; }
+int* PagedBatchKV::d_len(int layer) const { return p_->d_len + static_cast<std::size_t>(layer) * p_->cfg.slots; }
+int* PagedBatchKV::d_ring_pos(int layer) const { return p_->d_ring + static_cast<std::size_t>(layer) * p_->cfg.slots; }
+int* PagedBatchKV::d_prefill_len() const { return p_->d_prefill; }
+
+bool PagedBatchKV::configure(const Config& c) {
+    UOCR_CHECK(c.slots > 0 && c.layers > 0 && c.kv_heads > 0 && c.head_dim > 0 && c.window > 0, "PagedBatchKV: bad geometry");
+    UOCR_CHECK(c.dtype == DType::BF16 || c.dtype == DType::F32, "PagedBatchKV: dtype must be BF16 or F32");
+    UOCR_CHECK(c.ring_arena_blocks >= blocks_for(c.window), "PagedBatchKV: ring arena smaller than one ring");
+    Impl& s = *p_;
+    const Config& o = s.cfg;
+    const bool same = !s.kpool.empty() && o.slots == c.slots && o.layers == c.layers && o.kv_heads == c.kv_heads &&
+                      o.head_dim == c.head_dim && o.window == c.window && o.max_prefix_tokens == c.max_prefix_tokens &&
+                      o.prefix_arena_blocks == c.prefix_arena_blocks && o.ring_arena_blocks == c.ring_arena_blocks &&
+                      o.dtype == c.dtype;
+    if (!same) {
+        s.free_all();
+        s.cfg = c;
+        s.stride = blocks_for(c.max_prefix_tokens) + blocks_for(c.window);
+        s.num_blocks = c.prefix_arena_blocks + c.ring_arena_blocks;
+        s.kpool.assign(static_cast<std::size_t>(c.layers), nullptr);
+        s.vpool.assign(static_cast<std::size_t>(c.layers), nullptr);
+        const std::size_t bytes = s.block_bytes() * s.num_blocks;
+        for (int l = 0; l < c.layers; ++l) {
+            cuda_ok(cudaMalloc(&s.kpool[l], bytes), "batch K pool");
+            cuda_ok(cudaMalloc(&s.vpool[l], bytes), "batch V pool");
+        }
+        cuda_ok(cudaMalloc(&s.d_table, sizeof(int32_t) * c.slots * s.stride), "batch table");
+        cuda_ok(cudaMalloc(&s.d_len, sizeof(int) * c.layers * c.slots), "batch len");
+        cuda_ok(cudaMalloc(&s.d_ring, sizeof(int) * c.layers * c.slots), "batch ring");
+        cuda_ok(cudaMalloc(&s.d_prefill, sizeof(int) * c.slots), "batch prefill");
+        cuda_ok(cudaMallocHost(&s.h_state_stage, sizeof(int) * (2 * c.layers + s.stride)), "state stage");
+        abi_ok(uocr_b200_workspace_create(std::max(c.slots, 4096), &s.ws), "batch workspace");
+        s.view.assign(static_cast<std::size_t>(c.layers), uocr_b200_paged_kv{});
+        for (int l = 0; l < c.layers; ++l) {
+            s.view[l].k_pool = s.kpool[l];
+            s.view[l].v_pool = s.vpool[l];
+            s.view[l].block_table = s.d_table;
+            s.view[l].table_stride = s.stride;
+            s.view[l].num_blocks = s.num_blocks;
+            s.view[l].kv_heads = c.kv_heads;
+            s.view[l].head_dim = c.head_dim;
+            s.view[l].dtype = c.dtype == DType::BF16 ? UOCR_B200_BF16 : UOCR_B200_F32;
+        }
+    }
+    // (re)start from an empty state: zero KV and cursors, fresh allocator
+    const std::size_t bytes = s.block_bytes() * s.num_blocks;
+    for (int l = 0; l < c.layers; ++l) {
+        cuda_ok(cudaMemset(s.kpool[l], 0, bytes), "batch K zero");
+        cuda_ok(cudaMemset(s.vpool[l], 0, bytes), "batch V zero");
+    }
+    cuda_ok(cudaMemset(s.d_table, 0xff, sizeof(int32_t) * c.slots * s.stride), "batch table clear");
+    cuda_ok(cudaMemset(s.d_len, 0, sizeof(int) * c.layers * c.slots), "batch len zero");
+    cuda_ok(cudaMemset(s.d_ring, 0, sizeof(int) * c.layers * c.slots), "batch ring zero");
+    cuda_ok(cudaMemset(s.d_prefill, 0, sizeof(int) * c.slots), "batch prefill zero");
+    s.bm.reset(new BlockManager(static_cast<std::size_t>(c.prefix_arena_blocks) * 256,
+                                static_cast<std::size_t>(c.ring_arena_blocks) * 256));
+    s.slot.assign(static_cast<std::size_t>(c.slots), Impl::SlotState{});
+    s.rows.assign(static_cast<std::size_t>(c.slots), std::vector<int>(static_cast<std::size_t>(s.stride), -1));
+    return !same;
+}
+
+void PagedBatchKV::publish_prefill_state(int slot, int prefix_len, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(slot >= 0 && slot < s.cfg.slots, "PagedBatchKV: slot out of range");
+    // one strided 2-D copy per cursor array instead of 2*layers+1 single-int copies
+    int* lens = s.h_state_stage;
+    int* zeros = s.h_state_stage + s.cfg.layers;
+    for (int l = 0; l < s.cfg.layers; ++l) {
+        lens[l] = prefix_len;
+        zeros[l] = 0;
+    }
+    cuda_ok(cudaMemcpy2DAsync(s.d_len + slot, sizeof(int) * s.cfg.slots, lens, sizeof(int), sizeof(int),
+                              s.cfg.layers, cudaMemcpyHostToDevice, stream), "publish len");
+    cuda_ok(cudaMemcpy2DAsync(s.d_ring + slot, sizeof(int) * s.cfg.slots, zeros, sizeof(int), sizeof(int),
+                              s.cfg.layers, cudaMemcpyHostToDevice, stream), "publish ring");
+    cuda_ok(cudaMemcpyAsync(s.d_prefill + slot, lens, sizeof(int), cudaMemcpyHostToDevice, stream),
+            "publish prefill");
+    cuda_ok(cudaStreamSynchronize(stream), "publish sync");
+    s.slot[slot].prefix_len = prefix_len;
+}
+
+PagedBatchKV::Admission PagedBatchKV::admit(int slot, const std::string& doc_key, int prefix_len, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(slot >= 0 && slot < s.cfg.slots, "PagedBatchKV: slot out of range");
+    UOCR_CHECK(!s.slot[slot].bound, "PagedBatchKV: slot already bound");
+    UOCR_CHECK(prefix_len >= 0 && prefix_len <= s.cfg.max_prefix_tokens, "PagedBatchKV: prefix longer than configured");
+    Admission a;
+    a.slot = slot;
+    const int pb = blocks_for(prefix_len), rb = blocks_for(s.cfg.window);
+    std::vector<int>& row = s.rows[slot];
+    std::fill(row.begin(), row.end(), -1);
+    if (pb > 0) {
+        const std::size_t live_before = s.bm->live_prefixes();
+        PrefixEntry* e = s.bm->acquire_prefix(doc_key, prefix_len, static_cast<std::size_t>(pb) * 256);  // throws when exhausted
+        UOCR_CHECK(e->prefill_len == prefix_len, "PagedBatchKV: doc_key reused with a different prefix length");
+        a.prefix_is_new = s.bm->live_prefixes() != live_before;
+        a.prefix_refcount = e->refcount;
+        for (int i = 0; i < pb; ++i) row[static_cast<std::size_t>(i)] = static_cast<int>(e->offset / 256) + i;
+    }
+    const i64 roff = s.bm->allocate_ring(static_cast<std::size_t>(rb) * 256);
+    if (roff < 0) {
+        if (pb > 0) s.bm->release_prefix(doc_key);
+        UOCR_THROW("ring pool exhausted");
+    }
+    for (int i = 0; i < rb; ++i)
+        row[static_cast<std::size_t>(pb + i)] = s.cfg.prefix_arena_blocks + static_cast<int>(roff / 256) + i;
+    Impl::SlotState& st = s.slot[slot];
+    st.bound = true;
+    st.key = doc_key;
+    st.has_prefix = pb > 0;
+    st.ring_off = roff;
+    int* row_stage = s.h_state_stage + 2 * s.cfg.layers;
+    std::memcpy(row_stage, row.data(), sizeof(int) * s.stride);
+    cuda_ok(cudaMemcpyAsync(s.d_table + static_cast<std::size_t>(slot) * s.stride, row_stage,
+                            sizeof(int) * s.stride, cudaMemcpyHostToDevice, stream), "table row H2D");
+    publish_prefill_state(slot, prefix_len, stream);
+    return a;
+}
+
+void PagedBatchKV::release(int slot) {
+    Impl& s = *p_;
+    UOCR_CHECK(slot >= 0 && slot < s.cfg.slots, "PagedBatchKV: slot out of range");
+    Impl::SlotState& st = s.slot[slot];
+    if (!st.bound) return;
+    s.bm->free_ring(st.ring_off, static_cast<std::size_t>(blocks_for(s.cfg.window)) * 256);
+    if (st.has_prefix) s.bm->release_prefix(st.key);
+    st = Impl::SlotState{};
+    std::fill(s.rows[slot].begin(), s.rows[slot].end(), -1);
+}
+
+void PagedBatchKV::append_decode_batch(int layer, const float* k, const float* v, const int* d_slots, int batch,
+                                       cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(batch <= s.cfg.slots, "batch_decode size out of range");
+    abi_ok(uocr_b200_rswa_append_decode_batch_paged(&s.view[layer], k, v, d_len(layer), d_ring_pos(layer), s.d_prefill,
+                                                    d_slots, batch, s.cfg.window, s.ws, stream), "append_decode_batch");
+}
+void PagedBatchKV::attention_batch(int layer, const float* q, const int* d_slots, int batch, int heads, float* out,
+                                   cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(batch <= s.cfg.slots, "batch_decode size out of range");
+    abi_ok(uocr_b200_rswa_attention_batch_paged(&s.view[layer], q, d_len(layer), s.d_prefill, d_slots, batch, heads, out,
+                                                s.ws, stream), "attention_batch");
+}
+void PagedBatchKV::decode_step(int layer, const float* q, const float* k, const float* v, const int* d_slots, int batch,
+                               int heads, float* out, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(batch <= s.cfg.slots, "batch_decode size out of range");
+    abi_ok(uocr_b200_rswa_decode_step_paged(&s.view[layer], q, k, v, d_len(layer), d_ring_pos(layer), s.d_prefill, d_slots,
+                                            batch, s.cfg.window, heads, out, s.ws, stream), "decode_step");
+}
+void PagedBatchKV::write_prefill_ragged(int layer, const float* k, const float* v, const int* d_row_slots,
+                                        const int* d_pos, int total, cudaStream_t stream) {
+    Impl& s = *p_;
+    abi_ok(uocr_b200_rswa_write_prefill_ragged_paged(&s.view[layer], k, v, d_row_slots, d_pos, total, s.ws, stream),
+           "write_prefill_ragged");
+}
+void PagedBatchKV::attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total,
+                                    int heads, float* out, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(total <= 4096 || total <= s.cfg.slots, "attention_ragged: more packed rows than the workspace holds (4096)");
+    abi_ok(uocr_b200_rswa_attention_ragged_paged(&s.view[layer], q, s.d_prefill, d_row_slots, d_pos, total, heads, out,
+                                                 s.ws, stream), "attention_ragged");
+}
+void PagedBatchKV::gather(int layer, const int* d_slots, int n, float* out_k, float* out_v, cudaStream_t stream) {
+    Impl& s = *p_;
+    abi_ok(uocr_b200_rswa_gather_paged(&s.view[layer], d_len(layer), s.d_prefill, d_slots, n,
+                                       s.cfg.max_prefix_tokens + s.cfg.window, out_k, out_v, UOCR_B200_F32, s.ws, stream),
+           "gather");
+}
+int PagedBatchKV::device_status(cudaStream_t stream) {
+    int v = 0;
+    abi_ok(uocr_b200_workspace_status(p_->ws, stream, &v), "device_status");
+    return v;
+}
+
+}  // namespace cuda
+}  // namespace uocr

@@ -1,0 +1,414 @@
+// Host-side C++17 mirror of the reference's R-SWA interfaces, backed by libuocr_rswa_b200.so.
+//
+// Same namespace, class names, method names, argument meaning and error behaviour as
+// vaachang/unlimited-ocr.cpp, so its callers and its own unit tests compile against these headers
+// unchanged:
+//
+//   uocr::Error, UOCR_CHECK                    include/uocr/common.h:33-43
+//   uocr::MemoryPool                           include/uocr/memory_pool.h:16-51
+//   uocr::PrefixEntry, uocr::BlockManager      include/uocr/block_manager.h:25-79
+//   uocr::ReqState/Request/Batch/
+//         ContinuousBatchScheduler             include/uocr/continuous_batch.h:21-104
+//   uocr::RSWACache                            include/uocr/kv_cache.h:23-86
+//   uocr::cuda::GpuRSWACache                   include/uocr/gpu_cache.h:21-72
+//   uocr::cuda::rswa_* free functions          include/uocr/cuda_ops.h:59-123
+//
+// What differs underneath: the KV of RSWACache / GpuRSWACache lives on the GPU in paged 16-token
+// blocks (block table + device cursors) and every operation is a kernel launch through the C ABI;
+// host pointers returned by keys()/values() are a mirror filled on demand by the block-table gather.
+// New on top of the reference surface: uocr::cuda::PagedBatchKV (the batch KV state that the
+// reference keeps inside GpuDecoder, src/engine/gpu_decoder.cu:904-970, gpu_decoder.h:246-258) and
+// uocr::SlotAllocator (the slot free-list of Engine::generate_batch, src/engine/engine.cpp:306-318).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <deque>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "uocr_rswa_b200.h"
+
+#if defined(__GNUC__)
+#define UOCR_HOST_API __attribute__((visibility("default")))
+#else
+#define UOCR_HOST_API
+#endif
+
+typedef struct CUstream_st* cudaStream_t;  // same type the CUDA runtime headers declare
+
+namespace uocr {
+
+using i32 = std::int32_t;
+using i64 = std::int64_t;
+using u32 = std::uint32_t;
+using u64 = std::uint64_t;
+
+enum class DType : std::uint8_t { F32 = 0, BF16 = 1, F16 = 2, I32 = 3, I8 = 4, U8 = 5, I4 = 6, U4 = 7 };
+
+// Exception carrying file:line, thrown by every host-side precondition check.
+class UOCR_HOST_API Error : public std::runtime_error {
+public:
+    Error(const std::string& what, const char* file, int line)
+        : std::runtime_error(std::string(file) + ":" + std::to_string(line) + ": " + what) {}
+};
+
+#define UOCR_THROW(msg) throw ::uocr::Error((msg), __FILE__, __LINE__)
+#define UOCR_CHECK(cond, msg)         \
+    do {                              \
+        if (!(cond)) UOCR_THROW(msg); \
+    } while (0)
+
+// bf16 <-> fp32 on raw bits (round to nearest even; NaN not special-cased), as common.h:49-64.
+inline float bf16_to_f32(std::uint16_t h) {
+    const u32 bits = static_cast<u32>(h) << 16;
+    float f;
+    __builtin_memcpy(&f, &bits, sizeof f);
+    return f;
+}
+inline std::uint16_t f32_to_bf16(float f) {
+    u32 bits;
+    __builtin_memcpy(&bits, &f, sizeof bits);
+    bits += 0x7fffu + ((bits >> 16) & 1u);
+    return static_cast<std::uint16_t>(bits >> 16);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Offset arena: first fit over an offset-ordered free list, alignment padding and tail returned to
+// the list, `used` counts padding, free() coalesces with both neighbours.
+// ------------------------------------------------------------------------------------------------
+class UOCR_HOST_API MemoryPool {
+public:
+    struct Block {
+        std::size_t offset = 0;
+        std::size_t size = 0;
+    };
+
+    explicit MemoryPool(std::size_t bytes = 0, std::size_t alignment = 256);
+
+    void reserve(std::size_t bytes);
+    void reset();
+    i64 allocate(std::size_t bytes, std::size_t alignment = 0);  // offset, or -1
+    void free(i64 offset, std::size_t bytes);
+
+    std::size_t total() const { return total_; }
+    std::size_t used() const { return used_; }
+    std::size_t peak() const { return peak_; }
+    std::size_t alignment() const { return alignment_; }
+    double fragmentation() const;
+    std::size_t num_free_blocks() const { return spans_.size(); }
+
+    // The reference backs the arena with host bytes; here they are materialised on first use only
+    // (the KV itself never lives in the arena, it is bookkeeping in both code bases).
+    std::uint8_t* base();
+    const std::uint8_t* base() const;
+
+private:
+    std::size_t total_ = 0, used_ = 0, peak_ = 0, alignment_ = 256;
+    std::vector<Block> spans_;  // free spans, ascending offset
+    mutable std::vector<std::uint8_t> backing_;
+};
+
+struct PrefixEntry {
+    std::string key;
+    int prefill_len = 0;
+    std::size_t bytes = 0;
+    int refcount = 0;
+    i64 offset = -1;
+};
+
+class UOCR_HOST_API BlockManager {
+public:
+    BlockManager(std::size_t prefix_pool_bytes, std::size_t ring_pool_bytes);
+
+    PrefixEntry* acquire_prefix(const std::string& key, int prefill_len, std::size_t bytes);
+    void release_prefix(const std::string& key);
+    i64 allocate_ring(std::size_t bytes);
+    void free_ring(i64 offset, std::size_t bytes);
+
+    std::size_t live_prefixes() const { return table_.size(); }
+    std::size_t total_prefix_bytes() const;
+    std::size_t shared_prefix_bytes() const { return shared_now_; }
+    std::size_t peak_prefix_bytes() const { return shared_peak_; }
+    const MemoryPool& prefix_pool() const { return prefix_arena_; }
+    const MemoryPool& ring_pool() const { return ring_arena_; }
+
+    struct Stats {
+        std::size_t prefix_live_bytes = 0;
+        std::size_t prefix_peak_bytes = 0;
+        std::size_t prefix_shared_bytes = 0;
+        std::size_t ring_live_bytes = 0;
+        std::size_t ring_peak_bytes = 0;
+        double prefix_fragmentation = 0.0;
+        double ring_fragmentation = 0.0;
+        std::size_t live_prefixes = 0;
+    };
+    Stats stats() const;
+
+private:
+    void refresh_shared();
+    MemoryPool prefix_arena_, ring_arena_;
+    std::unordered_map<std::string, PrefixEntry> table_;
+    std::size_t shared_now_ = 0, shared_peak_ = 0;
+};
+
+class RSWACache;
+
+enum class ReqState { Waiting, Prefilling, Decoding, Finished };
+
+struct Request {
+    int id = -1;
+    std::string doc_key;
+    std::vector<int> prompt_tokens;
+    std::vector<int> output_tokens;
+    ReqState state = ReqState::Waiting;
+    int max_new_tokens = 4096;
+    bool stopped = false;
+    std::shared_ptr<RSWACache> cache;
+    double arrival_time = 0.0, prefill_time = 0.0, first_token_time = 0.0, finish_time = 0.0;
+    int decode_steps = 0;
+
+    bool is_finished() const { return state == ReqState::Finished; }
+    int seq_len() const { return static_cast<int>(prompt_tokens.size() + output_tokens.size()); }
+};
+
+struct Batch {
+    std::vector<int> prefill;
+    std::vector<int> decode;
+    bool empty() const { return prefill.empty() && decode.empty(); }
+};
+
+class UOCR_HOST_API ContinuousBatchScheduler {
+public:
+    struct Stats {
+        std::uint64_t total_requests = 0, finished_requests = 0, prefill_tokens = 0, decode_tokens = 0;
+        std::size_t waiting = 0, running = 0;
+        double last_batch_size = 0.0;
+    };
+
+    explicit ContinuousBatchScheduler(int max_batch_size = 16, int min_batch_size = 4)
+        : max_batch_(max_batch_size), min_batch_(min_batch_size) {}
+
+    int add_request(Request r);
+    Batch build_batch();
+    void mark_prefilled(int id);
+    void mark_prefilling(int id);
+    bool add_token(int id, int token);
+    void finish(int id);
+    Request* get(int id);
+    const Request* get(int id) const;
+
+    bool empty() const { return all_.empty(); }
+    bool has_work() const { return !queue_.empty() || !active_.empty(); }
+    int max_batch_size() const { return max_batch_; }
+    int min_batch_size() const { return min_batch_; }
+    void set_max_batch_size(int v) { max_batch_ = v; }
+    void set_min_batch_size(int v) { min_batch_ = v; }
+    Stats stats() const;
+    const std::vector<int>& running() const { return active_; }
+
+private:
+    int max_batch_, min_batch_;
+    int next_id_ = 0;
+    std::deque<int> queue_;
+    std::vector<int> active_;
+    std::unordered_map<int, Request> all_;
+};
+
+// Slot free-list of the batch loop: slots are handed out from the back (so the first admissions get
+// the highest numbers) and a released slot is the next one reused (src/engine/engine.cpp:306-318,341-347).
+class UOCR_HOST_API SlotAllocator {
+public:
+    explicit SlotAllocator(int slots = 0) { reset(slots); }
+    void reset(int slots);
+    int acquire(int request_id);  // throws "no free slot" when exhausted
+    void release(int request_id);
+    int slot_of(int request_id) const;  // -1 when unknown
+    int free_count() const { return static_cast<int>(free_.size()); }
+
+private:
+    std::vector<int> free_;
+    std::unordered_map<int, int> by_request_;
+};
+
+namespace detail {
+class PagedSeqStore;  // one sequence, all layers, on the device
+}
+
+// ------------------------------------------------------------------------------------------------
+// RSWACache: host-pointer interface of the reference, KV held on the GPU.
+// ------------------------------------------------------------------------------------------------
+class UOCR_HOST_API RSWACache {
+public:
+    RSWACache();
+    RSWACache(int num_layers, int kv_heads, int head_dim, int window);
+    ~RSWACache();
+    RSWACache(RSWACache&&) noexcept;
+    RSWACache& operator=(RSWACache&&) noexcept;
+    RSWACache(const RSWACache&) = delete;
+    RSWACache& operator=(const RSWACache&) = delete;
+
+    void configure(int num_layers, int kv_heads, int head_dim, int window);
+    // Extension: choose the device payload type before reset() (default F32, which keeps the
+    // reference's bit-exact fp32 contents; BF16 halves the bytes and rounds on append).
+    void set_kv_dtype(DType t);
+    void reset(int prefill_len);
+
+    int num_layers() const;
+    int kv_heads() const;
+    int head_dim() const;
+    int window() const;
+    int prefill_len() const;
+    int length(int layer) const;
+    int ring_pos(int layer) const;
+    bool ring_started(int layer) const;
+    int capacity() const;
+
+    void write_prefill(int layer, const float* k, const float* v, int seq);
+    void append_decode(int layer, const float* k, const float* v);
+    void attention(int layer, const float* q, int seq, int q_start, float* out, int heads, bool causal) const;
+
+    int len(int layer) const { return length(layer); }
+    const float* keys(int layer) const;
+    const float* values(int layer) const;
+    float* mutable_keys(int layer);
+    float* mutable_values(int layer);
+    std::size_t bytes() const;
+
+private:
+    std::unique_ptr<detail::PagedSeqStore> s_;
+};
+
+namespace cuda {
+
+// Device-pointer interface of the reference's single-request GPU cache.
+class UOCR_HOST_API GpuRSWACache {
+public:
+    GpuRSWACache();
+    GpuRSWACache(int num_layers, int kv_heads, int head_dim, int window);
+    ~GpuRSWACache();
+    GpuRSWACache(const GpuRSWACache&) = delete;
+    GpuRSWACache& operator=(const GpuRSWACache&) = delete;
+
+    void configure(int num_layers, int kv_heads, int head_dim, int window);
+    void set_kv_dtype(DType t);
+    void reset(int prefill_len);
+    void write_prefill(int layer, const float* d_k, const float* d_v, int seq, cudaStream_t stream = nullptr);
+    void append_decode(int layer, const float* d_k, const float* d_v, cudaStream_t stream = nullptr);
+    void reset_device_state(int prefill_len, cudaStream_t stream = nullptr);
+    void append_decode_device(int layer, const float* d_k, const float* d_v, cudaStream_t stream = nullptr);
+    const int* len_dev(int layer) const;
+    void attention(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads, bool causal,
+                   cudaStream_t stream = nullptr) const;
+
+    int len(int layer) const;
+    int prefill_len() const;
+    int window() const;
+    int capacity() const;
+    int num_layers() const;
+    // Device pointers to the logical fp32 view [capacity][kv_heads*head_dim], refreshed by a gather;
+    // valid until the next call on this object.
+    const float* keys(int layer) const;
+    const float* values(int layer) const;
+
+private:
+    std::unique_ptr<detail::PagedSeqStore> s_;
+};
+
+// The reference's eight R-SWA entry points, same signatures (contiguous fp32 caches).  Scratch comes
+// from a per-device workspace created on first use: make the first call outside graph capture.
+UOCR_HOST_API void rswa_attention_decode(const float* q, const float* kcache, const float* vcache, int kv_len,
+                                         int heads, int kv_heads, int head_dim, float* out, cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_attention(const float* q, const float* kcache, const float* vcache, int kv_len, int seq,
+                                  int q_start, int heads, int kv_heads, int head_dim, bool causal, float* out,
+                                  cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_attention_devlen(const float* q, const float* kcache, const float* vcache, const int* d_len,
+                                         int seq, int q_start, int heads, int kv_heads, int head_dim, bool causal,
+                                         float* out, cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_append_decode(const float* k, const float* v, float* kcache, float* vcache, int* d_len,
+                                      int* d_ring_pos, int prefill_len, int window, int kv_heads, int head_dim,
+                                      cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_append_decode_batch(const float* k, const float* v, float* kcache_base, float* vcache_base,
+                                            int* d_len, int* d_ring_pos, const int* d_prefill_len, const int* d_slots,
+                                            int batch, int batch_cap, int window, int kv_heads, int head_dim,
+                                            cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_attention_batch(const float* q, const float* kcache_base, const float* vcache_base,
+                                        const int* d_len, const int* d_slots, int batch, int batch_cap, int heads,
+                                        int kv_heads, int head_dim, float* out, cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_write_prefill_ragged(const float* k, const float* v, float* kcache_base, float* vcache_base,
+                                             const int* d_slots, const int* d_pos, int total, int batch_cap,
+                                             int kv_heads, int head_dim, cudaStream_t stream = nullptr);
+UOCR_HOST_API void rswa_attention_ragged(const float* q, const float* kcache_base, const float* vcache_base,
+                                         const int* d_slots, const int* d_pos, int total, int batch_cap, int heads,
+                                         int kv_heads, int head_dim, float* out, cudaStream_t stream = nullptr);
+
+// ------------------------------------------------------------------------------------------------
+// PagedBatchKV: the batch KV state of the decoder (what GpuDecoder::batch_configure allocates and
+// attention_block_batch / attention_block_ragged drive), on the paged pool with physically shared
+// prefixes.  Block ids come from a BlockManager run in block units (1 block == 256 arena bytes).
+// ------------------------------------------------------------------------------------------------
+class UOCR_HOST_API PagedBatchKV {
+public:
+    struct Config {
+        int slots = 0, layers = 0, kv_heads = 0, head_dim = 0, window = 0;
+        int max_prefix_tokens = 0;     // longest fixed region a slot may have
+        int prefix_arena_blocks = 0;   // block ids [0, prefix_arena_blocks)
+        int ring_arena_blocks = 0;     // block ids [prefix_arena_blocks, +ring_arena_blocks)
+        DType dtype = DType::BF16;
+    };
+    struct Admission {
+        int slot = -1;
+        bool prefix_is_new = false;  // true: the caller must prefill the prefix through this slot
+        int prefix_refcount = 0;
+    };
+
+    PagedBatchKV();
+    ~PagedBatchKV();
+    PagedBatchKV(const PagedBatchKV&) = delete;
+    PagedBatchKV& operator=(const PagedBatchKV&) = delete;
+
+    // Reuses the allocation when the shape is unchanged (only state is cleared), like the reference's
+    // batch_configure; otherwise reallocates -- captured graphs must then be dropped by the caller.
+    // Returns true when buffers were (re)allocated.
+    bool configure(const Config& cfg);
+    const Config& config() const;
+
+    // Binds a slot to a document prefix (shared by doc_key, refcounted) and a private ring; uploads the
+    // slot's table row and publishes len = P, ring_pos = 0, prefill = P for every layer in one copy.
+    Admission admit(int slot, const std::string& doc_key, int prefix_len, cudaStream_t stream = nullptr);
+    void release(int slot);  // frees the ring, drops the prefix reference
+    // Engine-style state publication after a ragged prefill (src/engine/gpu_decoder.cu:1131-1150).
+    void publish_prefill_state(int slot, int prefix_len, cudaStream_t stream = nullptr);
+
+    // Per-layer calls; every pointer is a device pointer, d_slots maps batch rows to slots.
+    void append_decode_batch(int layer, const float* k, const float* v, const int* d_slots, int batch,
+                             cudaStream_t stream = nullptr);
+    void attention_batch(int layer, const float* q, const int* d_slots, int batch, int heads, float* out,
+                         cudaStream_t stream = nullptr);
+    void decode_step(int layer, const float* q, const float* k, const float* v, const int* d_slots, int batch,
+                     int heads, float* out, cudaStream_t stream = nullptr);
+    void write_prefill_ragged(int layer, const float* k, const float* v, const int* d_row_slots, const int* d_pos,
+                              int total, cudaStream_t stream = nullptr);
+    void attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total, int heads,
+                          float* out, cudaStream_t stream = nullptr);
+    // Logical fp32 view of `n` slots: out[i] is [max_prefix_tokens + window][kv_heads*head_dim].
+    void gather(int layer, const int* d_slots, int n, float* out_k, float* out_v, cudaStream_t stream = nullptr);
+
+    const BlockManager& blocks() const;
+    const std::vector<int>& table_row(int slot) const;  // host copy of the slot's block ids (-1 = unused)
+    int device_status(cudaStream_t stream = nullptr);   // synchronises; 0 = no kernel recorded a fault
+    const uocr_b200_paged_kv& layer_view(int layer) const;
+    int* d_len(int layer) const;
+    int* d_ring_pos(int layer) const;
+    int* d_prefill_len() const;
+
+private:
+    struct Impl;
+    std::unique_ptr<Impl> p_;
+};
+
+}  // namespace cuda
+}  // namespace uocr
