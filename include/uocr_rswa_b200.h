@@ -189,6 +189,31 @@ UOCR_B200_API int uocr_b200_rswa_attention_paged(
     int prefill_len, const int* d_prefill_len, int seq, int q_start, int heads, int causal,
     float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* Prefill of TEXT tokens over "fixed prefix + last-W window", for prompts that may be longer than
+ * the window.  The reference never wraps during prefill (its whole first prefill becomes the fixed
+ * region, src/engine/gpu_decoder.cu:1131-1150); this entry point implements the composition of
+ * reference calls that defines the wrapped case: for each text token in order, append_decode then
+ * attention(seq = 1) (src/scheduler/kv_cache.cpp:54-130).  Packed row t is text token d_pos[t] of
+ * slot d_slots[t]; its K/V are first written (rounded to the pool dtype) to a caller-provided text
+ * pool -- same block layout as the KV pool, `text_blocks` blocks, the request's tokens starting at
+ * block d_text_block0[t] -- and the row then attends the slot's whole fixed region plus text tokens
+ * (d_pos[t] - window, d_pos[t]].  Nothing is written to the KV pool; call
+ * uocr_b200_rswa_ring_fill_paged afterwards. */
+UOCR_B200_API int uocr_b200_rswa_prefill_text_paged(
+    const uocr_b200_paged_kv* kv, void* text_k_pool, void* text_v_pool, int text_blocks,
+    const float* q, const float* k, const float* v, const int* d_prefill_len, const int* d_slots,
+    const int* d_pos, const int* d_text_block0, int total, int window, int heads, float* out,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+/* Moves the last min(T, window) text tokens of every request from the text pool into its ring
+ * (slot pos % window) and publishes len = P + min(T, W), ring_pos = T < W ? 0 : (T - W) % W:
+ * the state T successive appends would leave.  d_text_len[t] = T of row t's request. */
+UOCR_B200_API int uocr_b200_rswa_ring_fill_paged(
+    const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool, int text_blocks,
+    const int* d_slots, const int* d_pos, const int* d_text_block0, const int* d_text_len,
+    const int* d_prefill_len, int* d_len, int* d_ring_pos, int total, int window,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
 /* One decode step of one layer in a single launch: the batched ring append of
  * uocr::cuda::rswa_append_decode_batch followed by uocr::cuda::rswa_attention_batch (the pair issued
  * at src/engine/gpu_decoder.cu:990-996), on the paged layout.  Every CTA plans from the pre-append

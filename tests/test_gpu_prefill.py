@@ -1,0 +1,107 @@
+"""Ragged prefill with ring fill (the configuration whose prompts can exceed the window) against the
+composed oracle: reset(Pv), write_prefill(vision), causal attention for the vision queries, then for
+every text token in order append_decode + attention(seq=1) -- only reference calls
+(src/scheduler/kv_cache.cpp:45-130).  Outputs within the attention tolerance (bf16: 2e-2 / 1e-3; the
+observed 2e-5 / 1e-5 is asserted too), final cache contents and cursors bit-exact, and decode steps
+that follow the prefill keep agreeing."""
+import numpy as np
+import pytest
+
+import synth
+from paged_fixture import PagedBatch, assert_attention_close, ceil_div, load_b200
+
+pytestmark = pytest.mark.gpu
+TIGHT = (2e-5, 1e-5)
+
+
+@pytest.fixture(scope="module")
+def b():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return load_b200()
+
+
+def run_prefill_case(orc, b, dtype, kvh, hd, heads, W, prefixes, text_lens, seed, decode_after=5):
+    import torch
+    slots = len(prefixes)
+    pb = PagedBatch(orc, slots, 1, kvh, hd, W, dtype, prefixes, heads=heads, seed=seed)
+    row = kvh * hd
+    rnd = pb.rnd
+    # ---- vision prefix: scatter + causal attention over packed rows of all requests ----------------
+    pb.write_prefixes()
+    vis_rows = [(s, p) for s in range(slots) for p in range(prefixes[s])]
+    if vis_rows:
+        rs = torch.tensor([s for s, _ in vis_rows], dtype=torch.int32, device="cuda")
+        pos = torch.tensor([p for _, p in vis_rows], dtype=torch.int32, device="cuda")
+        qv = synth.normal(seed, 41, (len(vis_rows), heads * hd))
+        out = torch.full((len(vis_rows), heads * hd), float("nan"), device="cuda")
+        big = b.Workspace(max(len(vis_rows), sum(text_lens), 64))
+        b.attention_ragged_paged(pb.layer[0], torch.from_numpy(qv).cuda(), pb.d_prefill, rs, pos, len(vis_rows), heads, out, big)
+        got = out.cpu().numpy()
+        at = 0
+        for s in range(slots):
+            n = prefixes[s]
+            if n:
+                want = pb.cache[s].attention(0, qv[at:at + n], 0, heads, True)
+                assert_attention_close(got[at:at + n], want, *TIGHT)
+            at += n
+    else:
+        big = b.Workspace(max(sum(text_lens), 64))
+    # ---- text tokens: packed rows, window may wrap ------------------------------------------------------
+    total = sum(text_lens)
+    block0, nb = [], 0
+    for T in text_lens:
+        block0.append(nb)
+        nb += ceil_div(max(T, 1), 16)
+    tdt = torch.bfloat16 if dtype == b.BF16 else torch.float32
+    text_k = torch.zeros((nb, kvh, 16, hd), dtype=tdt, device="cuda")
+    text_v = torch.zeros_like(text_k)
+    k = rnd(synth.normal(seed, 51, (total, row)))
+    v = rnd(synth.normal(seed, 52, (total, row)))
+    q = synth.normal(seed, 53, (total, heads * hd))
+    rs = np.concatenate([np.full(T, s) for s, T in enumerate(text_lens)]).astype(np.int32)
+    pos = np.concatenate([np.arange(T) for T in text_lens]).astype(np.int32)
+    b0 = np.concatenate([np.full(T, block0[s]) for s, T in enumerate(text_lens)]).astype(np.int32)
+    tl = np.concatenate([np.full(T, T) for T in text_lens]).astype(np.int32)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    drs, dpos, db0, dtl = d(rs), d(pos), d(b0), d(tl)
+    out = torch.full((total, heads * hd), float("nan"), device="cuda")
+    b.prefill_text_paged(pb.layer[0], text_k, text_v, nb, d(q), d(k), d(v), pb.d_prefill, drs, dpos, db0, total, W,
+                         heads, out, big)
+    b.ring_fill_paged(pb.layer[0], text_k, text_v, nb, drs, dpos, db0, dtl, pb.d_prefill, pb.d_len[0], pb.d_ring[0],
+                      total, W, big)
+    got = out.cpu().numpy()
+    at = 0
+    for s, T in enumerate(text_lens):
+        want = []
+        for i in range(T):
+            pb.cache[s].append_decode(0, k[at + i], v[at + i])
+            want.append(pb.cache[s].attention(0, q[at + i:at + i + 1], pb.cache[s].len(0) - 1, heads, False)[0])
+        if T:
+            tol = (2e-2, 1e-3) if dtype == b.BF16 else (1e-3, 1e-3)
+            assert_attention_close(got[at:at + T], np.array(want), *tol)
+            assert_attention_close(got[at:at + T], np.array(want), *TIGHT)
+        at += T
+    pb.check_logical_view(0)  # ring contents + len + ring_pos bit-exact after the fill
+    # ---- decode continues from the prefilled state -----------------------------------------------------------
+    rows = list(range(slots))
+    for t in range(decode_after):
+        kk, vv, qq = pb.step_inputs(t, 0, rows)
+        g, w = pb.step_fused(0, kk, vv, qq, rows)
+        assert_attention_close(g, w, *TIGHT)
+    pb.check_logical_view(0)
+    assert big.status() == 0 and pb.ws.status() == 0
+
+
+@pytest.mark.parametrize("dtype_name", ["bf16", "f32"])
+@pytest.mark.parametrize("W", [16, 24])
+def test_prefill_text_window_wraps_tiny(orc, b, dtype_name, W):
+    dtype = b.BF16 if dtype_name == "bf16" else b.F32
+    run_prefill_case(orc, b, dtype, 2, 8, 4, W, prefixes=[0, 7, 16, 33, 5, 16, 1],
+                     text_lens=[40, 1, 0, 70, 16, 17, W], seed=600 + W)
+
+
+def test_prefill_text_real_head_geometry(orc, b):
+    # 10 heads x 128; prefixes like "256 global + crops" scaled down; prompts shorter and longer than W
+    run_prefill_case(orc, b, b.BF16, 10, 128, 10, 32, prefixes=[48, 20, 65], text_lens=[80, 12, 33], seed=77)

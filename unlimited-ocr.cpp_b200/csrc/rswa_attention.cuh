@@ -30,10 +30,16 @@ struct RowInfo {
     int slot;  // cache slot of this query row
     int pe;    // attended tokens in the fixed (prefix) region; ring blocks start at table index ceil(pe/16)
     int re;    // attended tokens in the ring region (re > 0 implies pe == prefix length)
-    int aux;   // fused step: (unit index << 4 | offset) of the token appended this step; else -1
+    int aux;   // fused step: (unit index << 4 | offset) of the token appended this step;
+               // text prefill: (first block of the window in the text pool << 4 | tokens to skip in it);
+               // else -1
 };
 
-enum PlanMode : int { kPlanBatch = 0, kPlanRagged = 1, kPlanSingle = 2, kPlanDecodeStep = 3 };
+// kPlanPrefillText: packed text rows of several requests during prefill.  Row t is text token
+// d_pos[t] of slot d_slots[t]; it attends the slot's whole fixed region plus the text window
+// (d_pos[t] - window, d_pos[t]] held in a separate text pool whose blocks for this request start
+// at block d_text_block0[t].
+enum PlanMode : int { kPlanBatch = 0, kPlanRagged = 1, kPlanSingle = 2, kPlanDecodeStep = 3, kPlanPrefillText = 4 };
 
 struct PlanParams {
     int mode, rows, heads, paged;
@@ -42,6 +48,7 @@ struct PlanParams {
     const int* d_ring_pos;
     const int* d_pos;
     const int* d_prefill_len;
+    const int* d_text_block0;
     int fixed_slot, kv_len, prefill_len, q_start, causal, window;
     int* rs;        // [rows + 1] exclusive prefix sum of heads * units(row)
     RowInfo* info;  // [rows]
@@ -54,6 +61,9 @@ struct AttnParams {
     float* out;
     const uint8_t* k_base;
     const uint8_t* v_base;
+    const uint8_t* k_text;  // text prefill: second pool (same block layout) holding the window tokens
+    const uint8_t* v_text;
+    int text_blocks;
     const int32_t* table;
     int table_stride, num_blocks;
     long long slot_stride_bytes;  // contiguous layout: bytes between two slots' caches
@@ -92,6 +102,16 @@ __device__ __forceinline__ int plan_row(const PlanParams& p, int r, RowInfo& ri)
         slot = p.fixed_slot;
         len = p.d_len ? p.d_len[p.paged ? slot : 0] : p.kv_len;
         if (p.causal) len = min(len, p.q_start + r + 1);
+    } else if (p.mode == kPlanPrefillText) {
+        slot = p.d_slots[r];
+        const int i = p.d_pos[r];
+        const int lo = max(0, i - p.window + 1);
+        ri.slot = slot;
+        ri.pe = max(p.d_prefill_len[slot], 0);
+        ri.re = i - lo + 1;
+        const int skip = lo & (kBlockTokens - 1);
+        ri.aux = ((p.d_text_block0[r] + lo / kBlockTokens) << 4) | skip;
+        return ((ri.pe + kBlockTokens - 1) / kBlockTokens + (skip + ri.re + kBlockTokens - 1) / kBlockTokens) * p.heads;
     } else {  // decode step: lengths as they will be after this step's append
         slot = p.d_slots[r];
         const int pfx = p.d_prefill_len[slot];
@@ -245,9 +265,6 @@ struct RowReduce {
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
-#ifdef UOCR_X_EXP2F
-    return exp2f(x);
-#endif
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
@@ -316,18 +333,35 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             // come first on the unit line too), so the unit index is the table index
             const int idx = c.j;
             int blk = 0;
-            if (idx < p.table_stride) blk = __ldg(p.table + (size_t)c.info.slot * p.table_stride + idx);
-            else if (lane == 0) atomicOr(p.status, kStatusBadSlot);
-            if (blk < 0 || blk >= p.num_blocks) {
-                if (lane == 0) atomicOr(p.status, kStatusBadBlock);
-                blk = 0;
+            const uint8_t* kb = p.k_base;
+            const uint8_t* vb = p.v_base;
+            bool from_text = false;
+            if constexpr (!FUSED) {
+                // text prefill: units past the fixed region come from the text pool, consecutive blocks
+                from_text = p.k_text != nullptr && idx >= (c.info.pe + kBlockTokens - 1) / kBlockTokens;
+            }
+            if (from_text) {
+                blk = (c.info.aux >> 4) + (idx - (c.info.pe + kBlockTokens - 1) / kBlockTokens);
+                kb = p.k_text;
+                vb = p.v_text;
+                if (blk < 0 || blk >= p.text_blocks) {
+                    if (lane == 0) atomicOr(p.status, kStatusBadBlock);
+                    blk = 0;
+                }
+            } else {
+                if (idx < p.table_stride) blk = __ldg(p.table + (size_t)c.info.slot * p.table_stride + idx);
+                else if (lane == 0) atomicOr(p.status, kStatusBadSlot);
+                if (blk < 0 || blk >= p.num_blocks) {
+                    if (lane == 0) atomicOr(p.status, kStatusBadBlock);
+                    blk = 0;
+                }
             }
             if (lane == 0) {
                 const size_t off = ((size_t)blk * p.kv_heads + kvh) * (size_t)TILE;
                 mbar_arrive_expect_tx(kbar, TILE);
-                bulk_copy_g2s(kdst, p.k_base + off, TILE, kbar);
+                bulk_copy_g2s(kdst, kb + off, TILE, kbar);
                 mbar_arrive_expect_tx(vbar, TILE);
-                bulk_copy_g2s(vdst, p.v_base + off, TILE, vbar);
+                bulk_copy_g2s(vdst, vb + off, TILE, vbar);
             }
         } else {
             const int nvalid = min(kBlockTokens, c.info.pe - c.j * kBlockTokens);
@@ -391,11 +425,18 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             uint8_t* ktile = my_tiles + stage * 2 * TILE;
             uint8_t* vtile = ktile + TILE;
 
-            int nvalid;
+            int nvalid, nskip = 0;  // tokens [nskip, nvalid) of this tile are attended
             {
                 const int npb = (cc.info.pe + kBlockTokens - 1) / kBlockTokens;
-                nvalid = cc.j < npb ? min(kBlockTokens, cc.info.pe - cc.j * kBlockTokens)
-                                    : min(kBlockTokens, cc.info.re - (cc.j - npb) * kBlockTokens);
+                if (cc.j < npb) {
+                    nvalid = min(kBlockTokens, cc.info.pe - cc.j * kBlockTokens);
+                } else {
+                    int lead = 0;  // text prefill: the window may start inside its first block
+                    if constexpr (PAGED && !FUSED) lead = p.k_text != nullptr ? (cc.info.aux & 15) : 0;
+                    const int jr = cc.j - npb;
+                    nvalid = min(kBlockTokens, lead + cc.info.re - jr * kBlockTokens);
+                    nskip = jr == 0 ? lead : 0;
+                }
             }
             // fused step: does this tile hold the ring slot that receives the new token?
             bool patch = false;
@@ -446,7 +487,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             }
             RowReduce<ITER, LPR / 2>::run(sc, lane);
             const int my_tok = (LPR >= 2 ? (g >> 1) * RPW : 0) + rg;
-            const float s = (my_tok < nvalid) ? sc[0] : -INFINITY;
+            const float s = (my_tok >= nskip && my_tok < nvalid) ? sc[0] : -INFINITY;
 
             // ---- online softmax, one running max per row group ---------------------------------
             float mt = s;
@@ -489,11 +530,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                     __syncwarp();
                 }
             }
-#ifdef UOCR_X_ONEV
-            if (false) {
-#else
-            if (nvalid == kBlockTokens) {
-#endif
+            if (nvalid == kBlockTokens && nskip == 0) {
 #pragma unroll
                 for (int i = 0; i < ITER; ++i) {
                     const int t = (i * RPW + rg) & (kBlockTokens - 1);
@@ -513,7 +550,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                 for (int i = 0; i < ITER; ++i) {
                     const int t = i * RPW + rg;
                     const float pi = (LPR >= 2) ? __shfl_sync(FULL, pr, rg * LPR + 2 * i) : pr;
-                    if (t < nvalid) {  // rows past the valid count may hold anything: never multiply them
+                    if (t >= nskip && t < nvalid) {  // rows outside the valid range may hold anything
 #pragma unroll
                         for (int cp = 0; cp < CPL; ++cp) {
                             const uint4 w = *reinterpret_cast<const uint4*>(vtile + t * ROWB + (g + 32 * cp) * 16);

@@ -223,6 +223,9 @@ struct AttnCall {
     float* out = nullptr;
     PlanParams plan{};
     // fused decode step (append + attention in one launch)
+    const void* k_text = nullptr;
+    const void* v_text = nullptr;
+    int text_blocks = 0;
     bool fused = false;
     const float* k_new = nullptr;
     const float* v_new = nullptr;
@@ -303,6 +306,9 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.out = c.out;
     ap.k_base = static_cast<const uint8_t*>(c.k_base);
     ap.v_base = static_cast<const uint8_t*>(c.v_base);
+    ap.k_text = static_cast<const uint8_t*>(c.k_text);
+    ap.v_text = static_cast<const uint8_t*>(c.v_text);
+    ap.text_blocks = c.text_blocks;
     ap.table = c.table;
     ap.table_stride = c.table_stride;
     ap.num_blocks = c.num_blocks;
@@ -544,6 +550,64 @@ int uocr_b200_rswa_attention_paged(const uocr_b200_paged_kv* kv, int slot, const
     c.plan.prefill_len = prefill_len; c.plan.d_prefill_len = d_prefill_len;
     c.plan.q_start = q_start; c.plan.causal = causal ? 1 : 0;
     return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---- text prefill over prefix + window ----------------------------------------------------------------
+int uocr_b200_rswa_prefill_text_paged(const uocr_b200_paged_kv* kv, void* text_k_pool, void* text_v_pool, int text_blocks,
+                                      const float* q, const float* k, const float* v, const int* d_prefill_len,
+                                      const int* d_slots, const int* d_pos, const int* d_text_block0, int total,
+                                      int window, int heads, float* out, uocr_b200_workspace* ws,
+                                      uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!text_k_pool || !text_v_pool || text_blocks <= 0 || !k || !v || !d_prefill_len || !d_slots || !d_pos || !d_text_block0)
+        return fail(UOCR_B200_ERR_INVALID, "prefill_text_paged: null pointer");
+    if (!aligned16(text_k_pool) || !aligned16(text_v_pool) || !aligned16(k) || !aligned16(v))
+        return fail(UOCR_B200_ERR_INVALID, "prefill_text_paged: pointers must be 16-byte aligned");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "prefill_text_paged: window must be positive");
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "prefill_text_paged: workspace is null");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    PagedView text = pv;
+    text.k_pool = static_cast<uint8_t*>(text_k_pool);
+    text.v_pool = static_cast<uint8_t*>(text_v_pool);
+    text.table = nullptr;
+    text.table_stride = 0;
+    text.num_blocks = text_blocks;
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_scatter_text_kernel<BF16><<<total, 256, 0, st>>>(text, k, v, d_pos, d_text_block0, ws->status);
+    else
+        rswa_scatter_text_kernel<F32><<<total, 256, 0, st>>>(text, k, v, d_pos, d_text_block0, ws->status);
+    if (int rc = after_launch("text scatter")) return rc;
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.k_text = text_k_pool; c.v_text = text_v_pool; c.text_blocks = text_blocks;
+    c.rows = total; c.heads = heads; c.q = q; c.out = out;
+    c.plan.mode = kPlanPrefillText; c.plan.d_slots = d_slots; c.plan.d_pos = d_pos; c.plan.d_prefill_len = d_prefill_len;
+    c.plan.d_text_block0 = d_text_block0; c.plan.window = window;
+    return run_attention(c, ws, st);
+}
+
+int uocr_b200_rswa_ring_fill_paged(const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool,
+                                   int text_blocks, const int* d_slots, const int* d_pos, const int* d_text_block0,
+                                   const int* d_text_len, const int* d_prefill_len, int* d_len, int* d_ring_pos,
+                                   int total, int window, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!text_k_pool || !text_v_pool || text_blocks <= 0 || !d_slots || !d_pos || !d_text_block0 || !d_text_len ||
+        !d_prefill_len || !d_len || !d_ring_pos)
+        return fail(UOCR_B200_ERR_INVALID, "ring_fill_paged: null pointer");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "ring_fill_paged: window must be positive");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    const uint8_t* kt = static_cast<const uint8_t*>(text_k_pool);
+    const uint8_t* vt = static_cast<const uint8_t*>(text_v_pool);
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_ring_fill_kernel<BF16><<<total, 160, 0, st>>>(pv, kt, vt, d_slots, d_pos, d_text_block0, d_text_len, d_prefill_len, d_len, d_ring_pos, window, status);
+    else
+        rswa_ring_fill_kernel<F32><<<total, 160, 0, st>>>(pv, kt, vt, d_slots, d_pos, d_text_block0, d_text_len, d_prefill_len, d_len, d_ring_pos, window, status);
+    return after_launch("ring fill");
 }
 
 // ---- fused decode step ---------------------------------------------------------------------------------

@@ -174,6 +174,63 @@ __global__ void __launch_bounds__(256) rswa_scatter_paged_kernel(
     store_row_paged<KV>(pv, blk, pos & (kBlockTokens - 1), k + src, v + src);
 }
 
+// Text prefill scatter: packed row t (fp32) -> text pool token d_text_block0[t]*16 + d_pos[t].
+template <typename KV>
+__global__ void __launch_bounds__(256) rswa_scatter_text_kernel(
+    PagedView text, const float* __restrict__ k, const float* __restrict__ v, const int* __restrict__ d_pos,
+    const int* __restrict__ d_text_block0, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int tok = d_text_block0[t] * kBlockTokens + d_pos[t];
+    const int blk = tok / kBlockTokens;
+    if (tok < 0 || blk >= text.num_blocks) {
+        if (threadIdx.x == 0 && status) atomicOr(status, kStatusBadBlock);
+        return;
+    }
+    const size_t src = (size_t)t * text.kv_heads * text.head_dim;
+    store_row_paged<KV>(text, blk, tok & (kBlockTokens - 1), k + src, v + src);
+}
+
+// Ring fill after a text prefill: packed row t is text token d_pos[t] (of d_text_len[t] tokens) of slot
+// d_slots[t]; its K/V sit in the text pool at token d_text_block0[t]*16 + d_pos[t].  The last
+// min(T, window) tokens of each request are copied to ring slot (pos mod window) -- exactly where T
+// successive RSWACache::append_decode calls (src/scheduler/kv_cache.cpp:54-82) leave them -- and the
+// row holding the last token publishes the cursors: len = P + min(T, W), ring_pos = T < W ? 0 : (T - W) % W.
+template <typename KV>
+__global__ void __launch_bounds__(256) rswa_ring_fill_kernel(
+    PagedView pv, const uint8_t* __restrict__ k_text, const uint8_t* __restrict__ v_text,
+    const int* __restrict__ d_slots, const int* __restrict__ d_pos, const int* __restrict__ d_text_block0,
+    const int* __restrict__ d_text_len, const int* __restrict__ d_prefill_len, int* __restrict__ d_len,
+    int* __restrict__ d_ring_pos, int window, int* __restrict__ status) {
+    constexpr int EPC = KV::kPerChunk;
+    const int t = blockIdx.x;
+    const int slot = d_slots[t], i = d_pos[t], T = d_text_len[t];
+    const int pfx = d_prefill_len[slot];
+    if (i == T - 1 && threadIdx.x == 0) {
+        d_len[slot] = pfx + min(T, window);
+        d_ring_pos[slot] = T < window ? 0 : (T - window) % window;
+    }
+    if (i < T - window) return;  // overwritten by a later token of the same request
+    const int r = i % window;
+    const int idx = (pfx + kBlockTokens - 1) / kBlockTokens + r / kBlockTokens;
+    int blk = -1;
+    if (idx < pv.table_stride) blk = pv.table[(size_t)slot * pv.table_stride + idx];
+    if (blk < 0 || blk >= pv.num_blocks) {
+        if (threadIdx.x == 0 && status) atomicOr(status, kStatusBadBlock);
+        return;
+    }
+    const int src_tok = d_text_block0[t] * kBlockTokens + i;
+    const int sblk = src_tok / kBlockTokens, soff = src_tok & (kBlockTokens - 1), doff = r & (kBlockTokens - 1);
+    const int hd = pv.head_dim, chunks = pv.kv_heads * hd / EPC;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const int e0 = c * EPC;
+        const int head = e0 / hd, d = e0 - head * hd;
+        const size_t src = ((((size_t)sblk * pv.kv_heads + head) * kBlockTokens + soff) * hd + d) * KV::kBytes;
+        const size_t dst = ((((size_t)blk * pv.kv_heads + head) * kBlockTokens + doff) * hd + d) * KV::kBytes;
+        *reinterpret_cast<uint4*>(pv.k_pool + dst) = *reinterpret_cast<const uint4*>(k_text + src);
+        *reinterpret_cast<uint4*>(pv.v_pool + dst) = *reinterpret_cast<const uint4*>(v_text + src);
+    }
+}
+
 // Gather: logical row s of slot d_slots[i] -> out[i][s][:]; rows >= len are zero-filled.
 // grid = (capacity_rows, n); one thread per 16-byte pool chunk.
 template <typename KV, bool WIDEN>
