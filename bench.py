@@ -30,8 +30,10 @@ for _p in (ROOT, os.path.join(ROOT, "tests")):
 
 import numpy as np  # noqa: E402
 
-CFG = dict(seqs=64, layers=12, heads=10, kv_heads=10, head_dim=128, window=1024, prefix=256,
-           pos_lo=1, pos_hi=4096, block_tokens=16, seed=1234)
+CFG = dict(seqs=64, layers=12, heads=10, kv_heads=10, head_dim=128, window=1024, prefixes=(256,),
+           pos_lo=1, pos_hi=4096, block_tokens=16, seed=1234, total_seqs=None, name="cfg2")
+# Other configurations of the same path, selectable with --workload (cfg2 is the headline and the default):
+CFG4 = dict(CFG, window=4096, prefixes=(256, 656, 1056, 1456), pos_hi=16384, total_seqs=512, name="cfg4")
 METRIC = "rswa_decode_tokens_per_s"
 UNIT = "tokens/s"
 NOMINAL_HBM_GBS = 8000.0
@@ -53,15 +55,25 @@ def draw_positions(rank: int):
     return synth.integers(CFG["seed"], 77 + rank, CFG["pos_lo"], CFG["pos_hi"], (CFG["seqs"],)).astype(np.int64)
 
 
-def algorithmic_bytes_per_layer(pos_after_append: np.ndarray) -> float:
-    """Unique bytes one layer of one decode step must move: window tokens read + the shared prefix
-    once + appended rows written (bf16 K+V = 5120 B per token), plus q read, out written and new
-    k, v read in fp32."""
+def draw_prefix_ids(rank: int):
+    """Which of the distinct prefixes each sequence of this GPU uses (uniform; one prefix -> all 0)."""
+    import synth
+    n = len(CFG["prefixes"])
+    if n == 1:
+        return np.zeros(CFG["seqs"], np.int64)
+    return synth.integers(CFG["seed"], 177 + rank, 0, n - 1, (CFG["seqs"],)).astype(np.int64)
+
+
+def algorithmic_bytes_per_layer(pos_after_append: np.ndarray, prefix_ids: np.ndarray) -> float:
+    """Unique bytes one layer of one decode step must move: window tokens read + every distinct
+    prefix on this GPU once + appended rows written (bf16 K+V = 5120 B per token), plus q read, out
+    written and new k, v read in fp32."""
     row = CFG["kv_heads"] * CFG["head_dim"]
     kv_tok = row * 2 * 2
     n = np.minimum(pos_after_append, CFG["window"])
     B = len(pos_after_append)
-    return float(kv_tok * (n.sum() + CFG["prefix"] + B) + B * row * 4 * 4)
+    distinct = sum(CFG["prefixes"][i] for i in set(prefix_ids.tolist()))
+    return float(kv_tok * (n.sum() + distinct + B) + B * row * 4 * 4)
 
 
 def measured_peaks():
@@ -134,15 +146,20 @@ class DecodeWorkload:
         self.pkg, self.torch = pkg, torch
         self.fused = fused
         c = CFG
-        B, L, W, P, bt = c["seqs"], c["layers"], c["window"], c["prefix"], c["block_tokens"]
+        B, L, W, bt = c["seqs"], c["layers"], c["window"], c["block_tokens"]
         self.B, self.L = B, L
         self.row = c["kv_heads"] * c["head_dim"]
-        pb, rb = P // bt, W // bt
-        self.num_blocks = pb + B * rb
-        table = np.zeros((B, pb + rb), np.int32)
-        table[:, :pb] = np.arange(pb)  # one physical prefix, shared by every sequence
+        self.prefix_ids = draw_prefix_ids(rank)
+        plen = np.array([c["prefixes"][i] for i in self.prefix_ids], np.int64)
+        pbs = [p // bt for p in c["prefixes"]]
+        pstart = np.concatenate([[0], np.cumsum(pbs)])  # every distinct prefix stored once
+        rb = W // bt
+        self.num_blocks = int(pstart[-1]) + B * rb
+        table = np.full((B, max(pbs) + rb), -1, np.int32)
         for s in range(B):
-            table[s, pb:] = pb + s * rb + np.arange(rb)
+            i = self.prefix_ids[s]
+            table[s, :pbs[i]] = pstart[i] + np.arange(pbs[i])  # physically shared prefix blocks
+            table[s, pbs[i]:pbs[i] + rb] = pstart[-1] + s * rb + np.arange(rb)
         self.table = torch.from_numpy(table).cuda()
         g = torch.Generator(device="cuda")
         g.manual_seed(c["seed"] + rank)
@@ -153,7 +170,8 @@ class DecodeWorkload:
             lay.v.copy_(torch.randn(lay.v.shape, generator=g, device="cuda", dtype=torch.float32))
             self.layers.append(lay)
         self.pos0 = draw_positions(rank)
-        self.d_prefill = torch.full((B,), P, dtype=torch.int32, device="cuda")
+        self.plen = plen
+        self.d_prefill = torch.from_numpy(plen.astype(np.int32)).cuda()
         self.d_slots = torch.arange(B, dtype=torch.int32, device="cuda")
         self.d_len = torch.zeros((L, B), dtype=torch.int32, device="cuda")
         self.d_ring = torch.zeros((L, B), dtype=torch.int32, device="cuda")
@@ -170,7 +188,7 @@ class DecodeWorkload:
     def set_positions(self, pos):
         """Cursor state after `pos` appends (closed form of the ring state machine)."""
         torch = self.torch
-        W, P = CFG["window"], CFG["prefix"]
+        W, P = CFG["window"], self.plen
         ln = P + np.minimum(pos, W)
         rp = np.where(pos < W, 0, (pos - W) % W)
         self.d_len.copy_(torch.from_numpy(np.tile(ln.astype(np.int32), (self.L, 1))))
@@ -253,7 +271,7 @@ def run_ours(args, rank, world):
 
     # ---- roofline of the dominant kernel: per-launch duration of the partial-attention kernel ------
     pos_mid = wl.pos0 + steps_before + np.arange(args.steps)[:, None] + 1  # after each timed append
-    bytes_layer = float(np.mean([algorithmic_bytes_per_layer(p) for p in pos_mid]))
+    bytes_layer = float(np.mean([algorithmic_bytes_per_layer(p, wl.prefix_ids) for p in pos_mid]))
     wl.ws.set_timing(True)
     kms = []
     wl.step_plain(lambda l: kms.append(wl.ws.last_kernel_ms()))
@@ -300,13 +318,17 @@ def run_ours(args, rank, world):
     tokens = CFG["seqs"] * world * args.steps
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong" if CFG["total_seqs"] else "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg2: batched decode, 64 seqs/GPU x 12 layers, 10 heads x 128, bf16 paged KV "
-                               "(16-token blocks), shared 256-token prefix, W=1024, pos~U[1,4096]",
+        "config": {"workload": "%s: batched decode, %d seqs/GPU x %d layers, 10 heads x 128, bf16 paged KV "
+                               "(16-token blocks), shared prefixes %s, W=%d, pos~U[%d,%d]"
+                               % (CFG["name"], CFG["seqs"], CFG["layers"], list(CFG["prefixes"]), CFG["window"],
+                                  CFG["pos_lo"], CFG["pos_hi"]),
                    "seqs_per_gpu": CFG["seqs"], "layers": CFG["layers"], "window": CFG["window"],
-                   "prefix": CFG["prefix"], "kv_resident_gb": round(wl.num_blocks * 81920 * CFG["layers"] / 1e9, 2),
-                   "l2_policy": "inputs larger than L2 (KV pool 4 GB vs 126 MB L2)", "step": ("cuda graph of 12 x (append; plan; attention)" if args.separate else
+                   "prefixes": list(CFG["prefixes"]),
+                   "kv_resident_gb": round(wl.num_blocks * 81920 * CFG["layers"] / 1e9, 2),
+                   "l2_policy": "inputs larger than L2 (resident KV pool vs 126 MB L2)", "step": ("cuda graph of 12 x (append; plan; attention)" if args.separate else
                             "cuda graph of 12 fused decode-step launches (append + attention in one kernel)"),
                    "parallelism": f"replicas x{world} (sequences shard by request, no collective)"},
         "roofline": {"bound": "hbm", "kernel": "rswa_attn_kernel<BF16,128,paged,%s>" % ("separate" if args.separate else "fused"), "achieved": achieved,
@@ -332,7 +354,7 @@ def cpu_baseline(sample_seqs: int, steps: int, threads: int = 0):
     kind = "reference" if oracle.available("ref") else "port"
     o = oracle.load("ref" if kind == "reference" else "orc")
     pos = draw_positions(0)[:sample_seqs]
-    pl = np.full(sample_seqs, CFG["prefix"], np.int32)
+    pl = np.array([CFG["prefixes"][i] for i in draw_prefix_ids(0)[:sample_seqs]], np.int32)
     sec, used, _ = o.run_decode_bench(pl, pos, CFG["layers"], CFG["kv_heads"], CFG["head_dim"], CFG["window"],
                                       steps, threads=threads, seed=CFG["seed"])
     return {"value": sample_seqs * steps / sec, "unit": UNIT, "cores": used, "kind": kind,
@@ -359,6 +381,36 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+def run_churn(args, rank, world):
+    """Configuration 5: pool of 65536 blocks x 12 layers (64 GB), 1000 requests on a seeded Poisson
+    schedule, 8 prefixes, W=1024; reports append and block-table gather bandwidth (algorithmic bytes:
+    append reads the fp32 k, v rows and writes them as bf16; gather reads and writes len x 5120 B per
+    layer).  Table parity for this workload is asserted by tests/test_gpu_churn.py."""
+    if rank != 0:
+        return
+    import torch
+    import churn_driver
+    from oracle import oracle  # only its generic C-ABI driver class is used, on the CUDA library itself
+    pkg = load_pkg()
+    host = oracle.Oracle("b200-host", path=pkg.LIB_PATH, prefix="uocr_b200")
+    cfg = churn_driver.ChurnConfig(layers=args.layers or 12)
+    t0 = time.time()
+    res = churn_driver.run(cfg, host, check=None, time_kernels=True)
+    st = res["stats"]
+    append_gb = st["append_rows"] * (res["row_bytes_in"] + res["row_bytes_out"]) / 1e9
+    gather_gb = st["gather_tokens"] * res["row_bytes_out"] * 2 / 1e9
+    print(json.dumps({
+        "metric": "rswa_churn_append_gather", "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+        "config": {"workload": "cfg5: 65536-block pool x %d layers, 1000 requests, 8 prefixes 256..1456, "
+                               "out-len U[32,2048], W=1024, exponential inter-arrival mean 2 steps" % cfg.layers},
+        "append_gbs": append_gb / (st["append_ms"] * 1e-3), "append_rows": st["append_rows"],
+        "append_us_per_launch": st["append_ms"] * 1e3 / max(st["steps"] * cfg.layers, 1),
+        "gather_gbs": gather_gb / max(st["gather_ms"] * 1e-3, 1e-9), "gather_tokens": st["gather_tokens"],
+        "steps": st["steps"], "peak_running": st["peak_running"], "prefix_hits": st["prefix_hits"],
+        "prefix_misses": st["prefix_misses"], "arenas_empty_at_end": res["final"][0][0] == 0 and res["final"][0][3] == 0,
+        "wall_s": time.time() - t0}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -369,15 +421,25 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="issue append and attention as the reference does (two entry points per layer) "
                          "instead of the fused one-launch decode step")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "churn"],
+                    help="cfg2 (default, headline): 64 seqs/GPU, W=1024, one shared prefix, weak scaling; "
+                         "cfg4: 512 seqs in total sharded over the GPUs, W=4096, 4 prefixes, strong scaling; "
+                         "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
     ap.add_argument("--layers", type=int, default=None,
                     help="profiling aid only: fewer layers so an ncu capture holds < 1 GB (not a bench number)")
     args = ap.parse_args()
+    if args.workload == "cfg4":
+        CFG.update(CFG4)
     if args.layers:
         CFG["layers"] = args.layers
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
+    if CFG["total_seqs"]:
+        CFG["seqs"] = CFG["total_seqs"] // world
+    if args.workload == "churn":
+        run_churn(args, rank, world)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, world)
