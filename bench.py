@@ -86,6 +86,50 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+class Ranks:
+    """The multi-GPU plumbing of the benchmark: one process per GPU, no collective on the data path.
+    torch.distributed is used for exactly two things -- the barrier that brackets the timed region and
+    the MAX over ranks of the device-measured time.  `backend="gloo"` runs the same logic on CPU."""
+
+    def __init__(self, rank: int, world: int, backend: str = "nccl", device=None):
+        self.rank, self.world, self.dist, self.device = rank, world, None, device
+        if world > 1:
+            import torch.distributed as dist
+            kw = {"device_id": device} if (backend == "nccl" and device is not None) else {}
+            dist.init_process_group(backend, rank=rank, world_size=world, **kw)
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+
+    def max_over_ranks(self, value: float) -> float:
+        if not self.dist:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64, device=self.device if self.device is not None else "cpu")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def close(self):
+        if self.dist:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def shard_sequences(total_seqs: int, world: int, rank: int):
+    """Strong-scaling workloads: sequences are dealt to ranks in contiguous, near-equal shards
+    (requests are independent, so any partition is valid)."""
+    base, extra = divmod(total_seqs, world)
+    start = rank * base + min(rank, extra)
+    return start, base + (1 if rank < extra else 0)
+
+
+def aggregate_tokens_per_s(seqs_per_rank, steps: int, max_ms: float) -> float:
+    """Whole-job throughput: tokens produced by all ranks divided by the slowest rank's time."""
+    return sum(seqs_per_rank) * steps / (max_ms * 1e-3)
+
+
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -231,10 +275,7 @@ def run_ours(args, rank, world):
     pkg.lib()  # fails loudly when the CUDA library is missing
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ranks = Ranks(rank, world, "nccl", torch.device("cuda", local))
     wl = DecodeWorkload(pkg, rank, fused=not args.separate)
     wl.capture()
     for _ in range(max(args.warmup - 1, 0)):
@@ -242,8 +283,7 @@ def run_ours(args, rank, world):
     torch.cuda.synchronize()
 
     def barrier():
-        if dist:
-            dist.barrier()
+        ranks.barrier()
         torch.cuda.synchronize()
 
     # ---- timed region: K whole steps (12 layers x (append + attention)), one graph launch each ----
@@ -262,10 +302,7 @@ def run_ours(args, rank, world):
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
-    if dist:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
+    ms = ranks.max_over_ranks(ms)
     dev_status = wl.ws.status()
     assert dev_status == 0, f"device status {dev_status}"
 
@@ -300,22 +337,19 @@ def run_ours(args, rank, world):
     e1.record(stream)
     barrier()
     e2e_ms = e0.elapsed_time(e1)
-    if dist:
-        t = torch.tensor([e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t[0])
+    e2e_ms = ranks.max_over_ranks(e2e_ms)
     h2d = int(hq.numel() * 4 * 3)
     d2h = int(hout.numel() * 4)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(sample_seqs=16, steps=4)
-    if dist:
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
     if rank != 0:
         return
-    tokens = CFG["seqs"] * world * args.steps
+    seqs_all = [shard_sequences(CFG["total_seqs"], world, r)[1] for r in range(world)] if CFG["total_seqs"] \
+        else [CFG["seqs"]] * world
+    tokens = sum(seqs_all) * args.steps
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -436,7 +470,7 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if CFG["total_seqs"]:
-        CFG["seqs"] = CFG["total_seqs"] // world
+        CFG["seqs"] = shard_sequences(CFG["total_seqs"], world, rank)[1]
     if args.workload == "churn":
         run_churn(args, rank, world)
     elif args.impl == "reference":
