@@ -131,7 +131,7 @@ def aggregate_tokens_per_s(seqs_per_rank, steps: int, max_ms: float) -> float:
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -144,7 +144,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -268,6 +268,41 @@ class DecodeWorkload:
         self.graph.replay()
         self.steps_done += 1
 
+    def capture_e2e(self, hq, hk, hv, hout):
+        """One graph for a whole step fed from pinned host memory: three streams, layer-pipelined."""
+        torch, p = self.torch, self.pkg
+        h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            main = torch.cuda.current_stream()
+            h2d.wait_stream(main)
+            d2h.wait_stream(main)
+            for l in range(self.L):
+                with torch.cuda.stream(h2d):
+                    self.q[l].copy_(hq[l], non_blocking=True)
+                    self.k[l].copy_(hk[l], non_blocking=True)
+                    self.v[l].copy_(hv[l], non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(h2d)
+                main.wait_event(ready)
+                if self.fused:
+                    p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                        self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
+                                        self.ws)
+                else:
+                    p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                                self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
+                    p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots,
+                                            self.B, CFG["heads"], self.out[l], self.ws)
+                done = torch.cuda.Event()
+                done.record(main)
+                d2h.wait_event(done)
+                with torch.cuda.stream(d2h):
+                    hout[l].copy_(self.out[l], non_blocking=True)
+            main.wait_stream(h2d)
+            main.wait_stream(d2h)
+        return g
+
 
 def run_ours(args, rank, world):
     import torch
@@ -292,7 +327,7 @@ def run_ours(args, rank, world):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+        time.sleep(0.15)
     barrier()
     steps_before = wl.steps_done
     e0.record(stream)
@@ -321,18 +356,19 @@ def run_ours(args, rank, world):
     peak, peak_kind = measured_peaks()
     achieved = bytes_layer / (k_ms * 1e-3) / 1e9
 
-    # ---- e2e: same step from HOST buffers (pinned), H2D of q/k/v and D2H of out inside the timing --
+    # ---- e2e: the same step from HOST buffers (pinned): per layer, H2D of q/k/v on a copy stream, the
+    # fused kernel on the compute stream, D2H of out on a third stream -- all captured in one graph so
+    # the copies of layer l+1 overlap the kernel of layer l; the caller reads the result every step ----
     hq, hk, hv = (torch.randn(wl.q.shape).pin_memory() for _ in range(3))
     hout = torch.empty(wl.out.shape).pin_memory()
+    e2e_graph = wl.capture_e2e(hq, hk, hv, hout)
     for _ in range(2):
-        wl.q.copy_(hq, non_blocking=True); wl.k.copy_(hk, non_blocking=True); wl.v.copy_(hv, non_blocking=True)
-        wl.step(); hout.copy_(wl.out, non_blocking=True)
+        e2e_graph.replay()
     barrier()
     e0.record(stream)
     for _ in range(args.steps):
-        wl.q.copy_(hq, non_blocking=True); wl.k.copy_(hk, non_blocking=True); wl.v.copy_(hv, non_blocking=True)
-        wl.step()
-        hout.copy_(wl.out, non_blocking=True)
+        e2e_graph.replay()
+        wl.steps_done += 1
         stream.synchronize()  # the caller reads the step's result before the next step
     e1.record(stream)
     barrier()
@@ -343,7 +379,7 @@ def run_ours(args, rank, world):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(sample_seqs=16, steps=4)
+        cpu = cpu_baseline(sample_seqs=16, steps=4, threads=host_threads())
     ranks.close()
     if rank != 0:
         return
@@ -383,6 +419,15 @@ def run_ours(args, rank, world):
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the reference's own RSWACache (compiled, unmodified) or the oracle port
 # ---------------------------------------------------------------------------------------------
+def host_threads() -> int:
+    """All host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which would otherwise
+    silently make the CPU arm single-threaded)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(sample_seqs: int, steps: int, threads: int = 0):
     from oracle import oracle
     kind = "reference" if oracle.available("ref") else "port"
@@ -403,7 +448,7 @@ def run_reference(args, rank, world):
     seqs = 16
     steps = max(args.steps, 1)
     # warm-up steps are part of the same call (state set-up dominates); time K steps
-    cpu = cpu_baseline(sample_seqs=seqs, steps=steps)
+    cpu = cpu_baseline(sample_seqs=seqs, steps=steps, threads=host_threads())
     line = {
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": world,
         "steps": steps, "warmup": args.warmup, "ms_per_step": cpu["seconds"] / steps * 1e3,
@@ -448,7 +493,7 @@ def run_churn(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
