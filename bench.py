@@ -185,7 +185,7 @@ class ClockSampler:
 class DecodeWorkload:
     """Device state of the cfg2 workload on the current GPU, driven through the C ABI."""
 
-    def __init__(self, pkg, rank: int, fused: bool = True):
+    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True):
         import torch
         self.pkg, self.torch = pkg, torch
         self.fused = fused
@@ -225,6 +225,7 @@ class DecodeWorkload:
         self.v = torch.randn((L, B, self.row), generator=g, device="cuda")
         self.out = torch.zeros((L, B, self.row), device="cuda")
         self.ws = pkg.Workspace(B)
+        self.ws.set_overlap(overlap)  # consecutive launches belong to different layers: overlap is safe
         self.graph = None
         self.launches_per_step = 0
         self.steps_done = 0
@@ -311,7 +312,7 @@ def run_ours(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     ranks = Ranks(rank, world, "nccl", torch.device("cuda", local))
-    wl = DecodeWorkload(pkg, rank, fused=not args.separate)
+    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap)
     wl.capture()
     for _ in range(max(args.warmup - 1, 0)):
         wl.step()
@@ -504,6 +505,9 @@ def main():
                     help="cfg2 (default, headline): 64 seqs/GPU, W=1024, one shared prefix, weak scaling; "
                          "cfg4: 512 seqs in total sharded over the GPUs, W=4096, 4 prefixes, strong scaling; "
                          "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="launch the fused steps without programmatic dependent launch")
+    ap.add_argument("--seqs", type=int, default=None, help="profiling aid only: sequences per GPU (not a bench number)")
     ap.add_argument("--layers", type=int, default=None,
                     help="profiling aid only: fewer layers so an ncu capture holds < 1 GB (not a bench number)")
     args = ap.parse_args()
@@ -511,6 +515,8 @@ def main():
         CFG.update(CFG4)
     if args.layers:
         CFG["layers"] = args.layers
+    if args.seqs:
+        CFG["seqs"] = args.seqs
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

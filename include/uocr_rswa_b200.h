@@ -82,6 +82,15 @@ UOCR_B200_API int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_
 UOCR_B200_API int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled);
 UOCR_B200_API int uocr_b200_workspace_last_kernel_ms(uocr_b200_workspace* ws, float* ms);
 
+/* Opt-in launch overlap for uocr_b200_rswa_decode_step_paged calls that use this workspace.  When
+ * enabled, the step is launched with programmatic stream serialization: its prologue (planning from
+ * the layer's cursors, block-table reads, the first KV tiles) may run while the preceding kernel in
+ * the stream is still finishing; it waits for that kernel before reading q / k / v and before
+ * touching scratch.  Enable it only where the preceding kernel does not write THIS layer's cursors,
+ * block table or pool (true between the layers of a decoder, whose predecessor is another layer's
+ * work); leave it off otherwise, e.g. directly after a prefill of the same layer.  Default: off. */
+UOCR_B200_API int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled);
+
 /* ------------------------------------------------------------------------------------------------
  * Paged KV view of ONE layer.
  * Replaces: the per-layer buffers `batch_k_[li]`, `batch_v_[li]` + `batch_cap_` addressing

@@ -68,6 +68,7 @@ _SIGS = {
     "uocr_b200_workspace_destroy": (_i, [_vp]),
     "uocr_b200_workspace_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "uocr_b200_workspace_set_timing": (_i, [_vp, _i]),
+    "uocr_b200_workspace_set_overlap": (_i, [_vp, _i]),
     "uocr_b200_workspace_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
     "uocr_b200_rswa_append_decode_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
@@ -166,6 +167,9 @@ class Workspace:
 
     def set_timing(self, enabled: bool) -> None:
         check(lib().uocr_b200_workspace_set_timing(self.h, 1 if enabled else 0))
+
+    def set_overlap(self, enabled: bool) -> None:
+        check(lib().uocr_b200_workspace_set_overlap(self.h, 1 if enabled else 0))
 
     def last_kernel_ms(self) -> float:
         v = C.c_float(0)

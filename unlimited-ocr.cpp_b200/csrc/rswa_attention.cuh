@@ -66,8 +66,8 @@ struct AttnParams {
     int text_blocks;
     const int32_t* table;
     int table_stride, num_blocks;
-    long long slot_stride_bytes;  // contiguous layout: bytes between two slots' caches
-    int row_stride_bytes;         // contiguous layout: bytes between two tokens
+    int slot_rows;         // contiguous layout: cache rows per slot (batch_cap)
+    int row_stride_bytes;  // contiguous layout: bytes between two tokens
     int rows, heads, kv_heads, group;
     float scale_log2e;
     const int* rs;
@@ -273,11 +273,58 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // -------------------------------------------------------------------------------------------------
 // attention
 // -------------------------------------------------------------------------------------------------
-template <typename KV, int HD, bool PAGED, bool FUSED, int STAGES>
+#ifndef UOCR_RING
+#define UOCR_RING 3
+#endif
+#ifndef UOCR_FFMA2
+#define UOCR_FFMA2 1
+#endif
+constexpr int kRing = UOCR_RING;  // shared-memory tile slots per warp; tiles K(0) V(0) K(1) V(1) ... rotate through them
+
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+#if UOCR_FFMA2
+    return __ffma2_rn(a, b, c);
+#else
+    return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+#endif
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+#if UOCR_FFMA2
+    return __fmul2_rn(a, b);
+#else
+    return make_float2(a.x * b.x, a.y * b.y);
+#endif
+}
+
+// Unit descriptor bits (one 32-bit word per unit, built 32 units at a time, one per lane).
+constexpr uint32_t kMetaValidMask = 0x1f;       // bits 0-4   tokens [skip, valid) of the tile are attended
+constexpr int kMetaSkipShift = 5;               // bits 5-8
+constexpr uint32_t kMetaLast = 1u << 9;         // last unit of its (row, head) item
+constexpr uint32_t kMetaFirst = 1u << 10;       // first unit of its item
+constexpr uint32_t kMetaText = 1u << 11;        // tile comes from the text pool
+constexpr uint32_t kMetaPatch = 1u << 12;       // fused step: the new token lands in this tile
+constexpr int kMetaPatchOffShift = 13;          // bits 13-16
+constexpr int kMetaHeadShift = 17;              // bits 17-31 kv head (row-mode addressing)
+
+template <typename KV>
+__device__ __forceinline__ void unpack2(const uint4& w, float2 (&f)[KV::kPerChunk / 2]) {
+    if constexpr (KV::kBytes == 2) {
+        f[0] = make_float2(bf16_lo(w.x), bf16_hi(w.x));
+        f[1] = make_float2(bf16_lo(w.y), bf16_hi(w.y));
+        f[2] = make_float2(bf16_lo(w.z), bf16_hi(w.z));
+        f[3] = make_float2(bf16_lo(w.w), bf16_hi(w.w));
+    } else {
+        f[0] = make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
+        f[1] = make_float2(__uint_as_float(w.z), __uint_as_float(w.w));
+    }
+}
+
+template <typename KV, int HD, bool PAGED, bool FUSED>
 __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     using M = TileMap<KV, HD>;
     constexpr int LPR = M::kLanesPerRow, CPL = M::kChunksPerLane, RPW = M::kRowsPerLoad;
     constexpr int ITER = M::kIters, EPC = KV::kPerChunk, EPL = M::kElemsPerLane;
+    constexpr int PPC = EPC / 2, PPL = EPL / 2;  // float2 pairs per chunk / per lane
     constexpr int ROWB = M::kRowBytes, TILE = M::kTileBytes;
     constexpr unsigned FULL = 0xffffffffu;
 
@@ -286,13 +333,13 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gw = blockIdx.x * warps + warp;
 
-    const int bar_bytes = (warps * STAGES * 2 * 8 + 127) & ~127;
-    uint8_t* my_tiles = smem + bar_bytes + (size_t)warp * (STAGES * 2 * TILE);
-    const uint32_t bar0 = smem_addr(smem) + warp * (STAGES * 2 * 8);
+    const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
+    uint8_t* my_tiles = smem + bar_bytes + (size_t)warp * (kRing * TILE);
+    const uint32_t bar0 = smem_addr(smem) + warp * (kRing * 8);
     const uint32_t tile0 = smem_addr(my_tiles);
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < STAGES * 2; ++s) mbar_init(bar0 + 8 * s, 1);
+        for (int s = 0; s < kRing; ++s) mbar_init(bar0 + 8 * s, 1);
         mbar_init_fence();
     }
     __syncwarp();
@@ -301,7 +348,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     const int* rs = p.rs;
     const RowInfo* info = p.info;
     if constexpr (FUSED) {
-        uint8_t* plan_base = smem + bar_bytes + (size_t)warps * (STAGES * 2 * TILE);
+        uint8_t* plan_base = smem + bar_bytes + (size_t)warps * (kRing * TILE);
         RowInfo* info_s = reinterpret_cast<RowInfo*>(plan_base);
         int* rs_s = reinterpret_cast<int*>(plan_base + sizeof(RowInfo) * p.rows);
         int* scratch = rs_s + p.rows + 1;
@@ -323,132 +370,152 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     const int g = lane % LPR;   // chunk position inside the row
     const int rg = lane / LPR;  // which of the RPW rows of a warp-wide load
 
-    // ---- producer side: one stage = K tile + V tile of one unit ---------------------------------
-    auto issue = [&](const UnitCursor& c, int stage) {
-        const uint32_t kbar = bar0 + 16 * stage, vbar = kbar + 8;
-        const uint32_t kdst = tile0 + stage * 2 * TILE, vdst = kdst + TILE;
-        const int kvh = c.h / p.group;
-        if constexpr (PAGED) {
-            // table row = prefix blocks, then ring blocks right after them (ceil(pe/16) prefix units
-            // come first on the unit line too), so the unit index is the table index
-            const int idx = c.j;
-            int blk = 0;
-            const uint8_t* kb = p.k_base;
-            const uint8_t* vb = p.v_base;
-            bool from_text = false;
-            if constexpr (!FUSED) {
-                // text prefill: units past the fixed region come from the text pool, consecutive blocks
-                from_text = p.k_text != nullptr && idx >= (c.info.pe + kBlockTokens - 1) / kBlockTokens;
+    if (n_units > 0) {
+        // ---- unit descriptors: lane l describes unit (desc_base + l) of this piece -------------------
+        uint32_t d_tile = 0, d_meta = 0, d_item = 0;
+        int desc_base = 0;
+        auto build_desc = [&](int base) {
+            desc_base = base;
+            d_tile = d_meta = d_item = 0;
+            if (base + lane < n_units) {
+                UnitCursor c;
+                cursor_seek(c, rs, info, p.rows, p.heads, u0 + base + lane);
+                const int kvh = c.h / p.group;
+                const int npb = (c.info.pe + kBlockTokens - 1) / kBlockTokens;
+                int valid, skip = 0;
+                uint32_t m = 0;
+                if (c.j < npb) {
+                    valid = min(kBlockTokens, c.info.pe - c.j * kBlockTokens);
+                } else {
+                    int lead = 0;
+                    if constexpr (PAGED && !FUSED) lead = p.k_text != nullptr ? (c.info.aux & 15) : 0;
+                    const int jr = c.j - npb;
+                    valid = min(kBlockTokens, lead + c.info.re - jr * kBlockTokens);
+                    skip = jr == 0 ? lead : 0;
+                }
+                if constexpr (PAGED) {
+                    int blk;
+                    bool from_text = false;
+                    if constexpr (!FUSED) from_text = p.k_text != nullptr && c.j >= npb;
+                    if (from_text) {
+                        blk = (c.info.aux >> 4) + (c.j - npb);
+                        m |= kMetaText;
+                        if (blk < 0 || blk >= p.text_blocks) { atomicOr(p.status, kStatusBadBlock); blk = 0; }
+                    } else {
+                        // table row = prefix blocks, then ring blocks right after them: unit index == table index
+                        blk = -1;
+                        if (c.j < p.table_stride) blk = __ldg(p.table + (size_t)c.info.slot * p.table_stride + c.j);
+                        else atomicOr(p.status, kStatusBadSlot);
+                        if (blk < 0 || blk >= p.num_blocks) { atomicOr(p.status, kStatusBadBlock); blk = 0; }
+                    }
+                    d_tile = (uint32_t)blk * p.kv_heads + kvh;
+                } else {
+                    d_tile = (uint32_t)(c.info.slot * p.slot_rows + c.j * kBlockTokens);  // first cache row of the tile
+                    m |= (uint32_t)kvh << kMetaHeadShift;
+                }
+                if constexpr (FUSED) {
+                    if (c.info.aux >= 0 && (c.info.aux >> 4) == c.j)
+                        m |= kMetaPatch | ((uint32_t)(c.info.aux & 15) << kMetaPatchOffShift);
+                }
+                if (c.j == c.n - 1) m |= kMetaLast;
+                if (c.j == 0) m |= kMetaFirst;
+                d_meta = m | (uint32_t)valid | ((uint32_t)skip << kMetaSkipShift);
+                d_item = (uint32_t)(c.r * p.heads + c.h);
             }
-            if (from_text) {
-                blk = (c.info.aux >> 4) + (idx - (c.info.pe + kBlockTokens - 1) / kBlockTokens);
-                kb = p.k_text;
-                vb = p.v_text;
-                if (blk < 0 || blk >= p.text_blocks) {
-                    if (lane == 0) atomicOr(p.status, kStatusBadBlock);
-                    blk = 0;
+        };
+
+        // ---- producer side: tiles K(0) V(0) K(1) V(1) ... rotate through the kRing slots -------------
+        int issue_slot = 0, issue_seq = 0;  // issue_seq: position in the tile sequence (unit = seq / 2, V if odd)
+        auto issue_tile = [&](int unit, bool is_v) {
+            const uint32_t tile = __shfl_sync(FULL, d_tile, unit - desc_base);
+            const uint32_t meta = __shfl_sync(FULL, d_meta, unit - desc_base);
+            const uint32_t bar = bar0 + 8 * issue_slot;
+            const uint32_t dst = tile0 + issue_slot * TILE;
+            if constexpr (PAGED) {
+                if (lane == 0) {
+                    const uint8_t* base = (meta & kMetaText) ? (is_v ? p.v_text : p.k_text) : (is_v ? p.v_base : p.k_base);
+                    mbar_arrive_expect_tx(bar, TILE);
+                    bulk_copy_g2s(dst, base + (size_t)tile * TILE, TILE, bar);
                 }
             } else {
-                if (idx < p.table_stride) blk = __ldg(p.table + (size_t)c.info.slot * p.table_stride + idx);
-                else if (lane == 0) atomicOr(p.status, kStatusBadSlot);
-                if (blk < 0 || blk >= p.num_blocks) {
-                    if (lane == 0) atomicOr(p.status, kStatusBadBlock);
-                    blk = 0;
+                const int nvalid = (int)(meta & kMetaValidMask);
+                if (lane == 0) mbar_arrive_expect_tx(bar, nvalid * ROWB);
+                if (lane < nvalid) {
+                    const uint8_t* base = is_v ? p.v_base : p.k_base;
+                    const size_t off = ((size_t)tile + lane) * p.row_stride_bytes + (size_t)(meta >> kMetaHeadShift) * ROWB;
+                    bulk_copy_g2s(dst + lane * ROWB, base + off, ROWB, bar);
                 }
             }
-            if (lane == 0) {
-                const size_t off = ((size_t)blk * p.kv_heads + kvh) * (size_t)TILE;
-                mbar_arrive_expect_tx(kbar, TILE);
-                bulk_copy_g2s(kdst, kb + off, TILE, kbar);
-                mbar_arrive_expect_tx(vbar, TILE);
-                bulk_copy_g2s(vdst, vb + off, TILE, vbar);
-            }
-        } else {
-            const int nvalid = min(kBlockTokens, c.info.pe - c.j * kBlockTokens);
-            const size_t off = (size_t)c.info.slot * p.slot_stride_bytes +
-                               (size_t)(c.j * kBlockTokens) * p.row_stride_bytes + (size_t)kvh * ROWB;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(kbar, nvalid * ROWB);
-                mbar_arrive_expect_tx(vbar, nvalid * ROWB);
-            }
-            const int t = lane & 15;
-            if (t < nvalid) {
-                const size_t roff = off + (size_t)t * p.row_stride_bytes;
-                if (lane < 16) bulk_copy_g2s(kdst + t * ROWB, p.k_base + roff, ROWB, kbar);
-                else bulk_copy_g2s(vdst + t * ROWB, p.v_base + roff, ROWB, vbar);
-            }
-        }
-    };
+            issue_slot = issue_slot == kRing - 1 ? 0 : issue_slot + 1;
+        };
 
-    if (n_units > 0) {
-        UnitCursor ic;  // issue cursor runs STAGES units ahead of the compute cursor
-        cursor_seek(ic, rs, info, p.rows, p.heads, u0);
-        UnitCursor cc = ic;
-        int issued = 0;
-        for (; issued < STAGES && issued < n_units; ++issued) {
-            issue(ic, issued);
-            cursor_next(ic, rs, info, p.rows, p.heads);
-        }
+        auto issue_next = [&]() {
+            if (issue_seq < 2 * n_units) issue_tile(issue_seq >> 1, (issue_seq & 1) != 0);
+            ++issue_seq;
+        };
+        build_desc(0);
+#pragma unroll
+        for (int s = 0; s < kRing; ++s) issue_next();
 
         // ---- consumer state ---------------------------------------------------------------------
-        float qreg[EPL], acc[EPL];
+        float2 q2[PPL], acc2[PPL];
         float m_run = -INFINITY, l_run = 0.f;
-        auto load_q = [&](const UnitCursor& c) {
-            const float* qp = p.q + ((size_t)c.r * p.heads + c.h) * HD;
+        auto load_q = [&](uint32_t item) {
+            const float* qp = p.q + (size_t)item * HD;
 #pragma unroll
             for (int cp = 0; cp < CPL; ++cp) {
                 const int d0 = (g + 32 * cp) * EPC;
 #pragma unroll
                 for (int e = 0; e < EPC; e += 4) {
                     const float4 t = __ldg(reinterpret_cast<const float4*>(qp + d0 + e));
-                    qreg[cp * EPC + e + 0] = t.x * p.scale_log2e;
-                    qreg[cp * EPC + e + 1] = t.y * p.scale_log2e;
-                    qreg[cp * EPC + e + 2] = t.z * p.scale_log2e;
-                    qreg[cp * EPC + e + 3] = t.w * p.scale_log2e;
+                    q2[(cp * EPC + e) / 2] = make_float2(t.x * p.scale_log2e, t.y * p.scale_log2e);
+                    q2[(cp * EPC + e) / 2 + 1] = make_float2(t.z * p.scale_log2e, t.w * p.scale_log2e);
                 }
             }
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+            for (int e = 0; e < PPL; ++e) acc2[e] = make_float2(0.f, 0.f);
             m_run = -INFINITY;
             l_run = 0.f;
         };
-        load_q(cc);
+        if constexpr (FUSED) {
+            // Everything above (barriers, plan, descriptors, the first tiles in flight) reads only this
+            // layer's own cursors, table and pool.  When the launch allows overlap with its predecessor
+            // in the stream, wait for that kernel here -- before the first read of q / k_new / v_new and
+            // before any write to the shared scratch -- then let the next launch begin its own prologue.
+            // Both instructions are no-ops for an ordinary launch.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
+        uint32_t cur_item = __shfl_sync(FULL, d_item, 0);
+        load_q(cur_item);
         bool first_segment = true;
-        int seg_first_j = cc.j;
-        int pend_r0 = 0, pend_h0 = 0, pend_r1 = 0, pend_h1 = 0, pend_n = 0;  // partial segments left in scratch
+        bool seg_from_start = (__shfl_sync(FULL, d_meta, 0) & kMetaFirst) != 0;
+        int pend_item0 = 0, pend_item1 = 0, pend_n = 0;  // partial segments left in scratch
         bool gave_up = false;
+        int use_slot = 0;          // slot holding the next tile to consume
+        uint32_t phases = 0;       // one phase bit per slot
 
         for (int it = 0; it < n_units; ++it) {
-            const int stage = it % STAGES;
-            const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
-            const uint32_t kbar = bar0 + 16 * stage, vbar = kbar + 8;
-            uint8_t* ktile = my_tiles + stage * 2 * TILE;
-            uint8_t* vtile = ktile + TILE;
-
-            int nvalid, nskip = 0;  // tokens [nskip, nvalid) of this tile are attended
-            {
-                const int npb = (cc.info.pe + kBlockTokens - 1) / kBlockTokens;
-                if (cc.j < npb) {
-                    nvalid = min(kBlockTokens, cc.info.pe - cc.j * kBlockTokens);
-                } else {
-                    int lead = 0;  // text prefill: the window may start inside its first block
-                    if constexpr (PAGED && !FUSED) lead = p.k_text != nullptr ? (cc.info.aux & 15) : 0;
-                    const int jr = cc.j - npb;
-                    nvalid = min(kBlockTokens, lead + cc.info.re - jr * kBlockTokens);
-                    nskip = jr == 0 ? lead : 0;
-                }
+            if (it - desc_base >= 32 - 2) {  // the producer looks two units ahead: keep those described
+                build_desc(it);
             }
-            // fused step: does this tile hold the ring slot that receives the new token?
-            bool patch = false;
-            if constexpr (FUSED) patch = cc.info.aux >= 0 && (cc.info.aux >> 4) == cc.j;
+            const uint32_t meta = __shfl_sync(FULL, d_meta, it - desc_base);
+            const int nvalid = (int)(meta & kMetaValidMask);
+            const int nskip = (int)((meta >> kMetaSkipShift) & 15);
 
             // ---- scores: q . k for the 16 tokens of the tile -----------------------------------
-            if (!mbar_wait_bounded(kbar, parity, p.status)) { gave_up = true; break; }
+            uint8_t* ktile = my_tiles + use_slot * TILE;
+            if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status)) { gave_up = true; break; }
+            phases ^= 1u << use_slot;
+            use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
             if constexpr (FUSED) {
-                if (patch) {  // lanes 0..kChunks-1 convert one 16-byte chunk of the new K row each
-                    const int kvh = cc.h / p.group, off = cc.info.aux & 15;
+                if (meta & kMetaPatch) {  // the new K row replaces whatever the ring slot held
+                    const int off = (int)((meta >> kMetaPatchOffShift) & 15);
+                    const int r = (int)(cur_item / p.heads), h = (int)(cur_item - r * p.heads);
+                    const int kvh = h / p.group;
+                    const uint32_t tile = __shfl_sync(FULL, d_tile, it - desc_base);
                     for (int ch = lane; ch < M::kChunks; ch += 32) {
-                        const float* src = p.k_new + ((size_t)cc.r * p.kv_heads + kvh) * HD + ch * EPC;
+                        const float* src = p.k_new + ((size_t)r * p.kv_heads + kvh) * HD + ch * EPC;
                         uint4 w;
                         if constexpr (EPC == 8) {
                             const float4 a = __ldg(reinterpret_cast<const float4*>(src));
@@ -459,13 +526,9 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                             w = __ldg(reinterpret_cast<const uint4*>(src));
                         }
                         *reinterpret_cast<uint4*>(ktile + off * ROWB + ch * 16) = w;
-                        if (cc.h % p.group == 0) {
-                            const int blk = __ldg(p.table + (size_t)cc.info.slot * p.table_stride + cc.j);
-                            if (blk >= 0 && blk < p.num_blocks)
-                                *reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.k_base) +
-                                                          ((size_t)blk * p.kv_heads + kvh) * (size_t)TILE +
-                                                          off * ROWB + ch * 16) = w;
-                        }
+                        if (h % p.group == 0)
+                            *reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.k_base) + (size_t)tile * TILE + off * ROWB +
+                                                      ch * 16) = w;
                     }
                     __syncwarp();
                 }
@@ -474,17 +537,24 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
 #pragma unroll
             for (int i = 0; i < ITER; ++i) {
                 const int t = (i * RPW + rg) & (kBlockTokens - 1);
-                float d = 0.f;
+                float2 d2 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int cp = 0; cp < CPL; ++cp) {
                     const uint4 w = *reinterpret_cast<const uint4*>(ktile + t * ROWB + (g + 32 * cp) * 16);
-                    float f[EPC];
-                    KV::unpack(w, f);
+                    float2 f[PPC];
+                    unpack2<KV>(w, f);
 #pragma unroll
-                    for (int e = 0; e < EPC; ++e) d = fmaf(qreg[cp * EPC + e], f[e], d);
+                    for (int e = 0; e < PPC; ++e) d2 = fma2(q2[cp * PPC + e], f[e], d2);
                 }
-                sc[i] = d;
+                sc[i] = d2.x + d2.y;
             }
+            // the K slot is free: the tile kRing positions further down the sequence goes there
+            __syncwarp();
+            if constexpr (FUSED) {
+                if (meta & kMetaPatch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            issue_next();
+
             RowReduce<ITER, LPR / 2>::run(sc, lane);
             const int my_tok = (LPR >= 2 ? (g >> 1) * RPW : 0) + rg;
             const float s = (my_tok >= nskip && my_tok < nvalid) ? sc[0] : -INFINITY;
@@ -499,16 +569,23 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             const float pr = fast_exp2(s - m_safe);
             l_run = l_run * alpha + pr;
             m_run = m_new;
+            const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) acc[e] *= alpha;
+            for (int e = 0; e < PPL; ++e) acc2[e] = mul2(acc2[e], alpha2);
 
             // ---- acc += p . v ----------------------------------------------------------------------
-            if (!mbar_wait_bounded(vbar, parity, p.status)) { gave_up = true; break; }
+            uint8_t* vtile = my_tiles + use_slot * TILE;
+            if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status)) { gave_up = true; break; }
+            phases ^= 1u << use_slot;
+            use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
             if constexpr (FUSED) {
-                if (patch) {
-                    const int kvh = cc.h / p.group, off = cc.info.aux & 15;
+                if (meta & kMetaPatch) {
+                    const int off = (int)((meta >> kMetaPatchOffShift) & 15);
+                    const int r = (int)(cur_item / p.heads), h = (int)(cur_item - r * p.heads);
+                    const int kvh = h / p.group;
+                    const uint32_t tile = __shfl_sync(FULL, d_tile, it - desc_base);
                     for (int ch = lane; ch < M::kChunks; ch += 32) {
-                        const float* src = p.v_new + ((size_t)cc.r * p.kv_heads + kvh) * HD + ch * EPC;
+                        const float* src = p.v_new + ((size_t)r * p.kv_heads + kvh) * HD + ch * EPC;
                         uint4 w;
                         if constexpr (EPC == 8) {
                             const float4 a = __ldg(reinterpret_cast<const float4*>(src));
@@ -519,13 +596,9 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                             w = __ldg(reinterpret_cast<const uint4*>(src));
                         }
                         *reinterpret_cast<uint4*>(vtile + off * ROWB + ch * 16) = w;
-                        if (cc.h % p.group == 0) {
-                            const int blk = __ldg(p.table + (size_t)cc.info.slot * p.table_stride + cc.j);
-                            if (blk >= 0 && blk < p.num_blocks)
-                                *reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.v_base) +
-                                                          ((size_t)blk * p.kv_heads + kvh) * (size_t)TILE +
-                                                          off * ROWB + ch * 16) = w;
-                        }
+                        if (h % p.group == 0)
+                            *reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.v_base) + (size_t)tile * TILE + off * ROWB +
+                                                      ch * 16) = w;
                     }
                     __syncwarp();
                 }
@@ -536,13 +609,14 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                     const int t = (i * RPW + rg) & (kBlockTokens - 1);
                     float pi = (LPR >= 2) ? __shfl_sync(FULL, pr, rg * LPR + 2 * i) : pr;
                     if (RPW > kBlockTokens && rg >= kBlockTokens) pi = 0.f;
+                    const float2 pi2 = make_float2(pi, pi);
 #pragma unroll
                     for (int cp = 0; cp < CPL; ++cp) {
                         const uint4 w = *reinterpret_cast<const uint4*>(vtile + t * ROWB + (g + 32 * cp) * 16);
-                        float f[EPC];
-                        KV::unpack(w, f);
+                        float2 f[PPC];
+                        unpack2<KV>(w, f);
 #pragma unroll
-                        for (int e = 0; e < EPC; ++e) acc[cp * EPC + e] = fmaf(pi, f[e], acc[cp * EPC + e]);
+                        for (int e = 0; e < PPC; ++e) acc2[cp * PPC + e] = fma2(pi2, f[e], acc2[cp * PPC + e]);
                     }
                 }
             } else {
@@ -550,32 +624,29 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                 for (int i = 0; i < ITER; ++i) {
                     const int t = i * RPW + rg;
                     const float pi = (LPR >= 2) ? __shfl_sync(FULL, pr, rg * LPR + 2 * i) : pr;
+                    const float2 pi2 = make_float2(pi, pi);
                     if (t >= nskip && t < nvalid) {  // rows outside the valid range may hold anything
 #pragma unroll
                         for (int cp = 0; cp < CPL; ++cp) {
                             const uint4 w = *reinterpret_cast<const uint4*>(vtile + t * ROWB + (g + 32 * cp) * 16);
-                            float f[EPC];
-                            KV::unpack(w, f);
+                            float2 f[PPC];
+                            unpack2<KV>(w, f);
 #pragma unroll
-                            for (int e = 0; e < EPC; ++e) acc[cp * EPC + e] = fmaf(pi, f[e], acc[cp * EPC + e]);
+                            for (int e = 0; e < PPC; ++e) acc2[cp * PPC + e] = fma2(pi2, f[e], acc2[cp * PPC + e]);
                         }
                     }
                 }
             }
 
-            // ---- this stage is free again: refill it ------------------------------------------------
+            // ---- the V slot is free as well -------------------------------------------------------------
             __syncwarp();
             if constexpr (FUSED) {
-                if (patch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (meta & kMetaPatch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            if (issued < n_units) {
-                issue(ic, stage);
-                cursor_next(ic, rs, info, p.rows, p.heads);
-                ++issued;
-            }
+            issue_next();
 
             // ---- end of an item (or of the piece): emit ----------------------------------------------
-            const bool item_done = (cc.j == cc.n - 1);
+            const bool item_done = (meta & kMetaLast) != 0;
             const bool piece_done = (it == n_units - 1);
             if (item_done || piece_done) {
                 float mx = m_run;
@@ -587,17 +658,23 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) lsum += __shfl_xor_sync(FULL, lsum, d);
                 if (LPR >= 2) lsum *= 0.5f;  // the two lanes of a pair carry the same token
+                float acc[EPL];
+#pragma unroll
+                for (int e = 0; e < PPL; ++e) {
+                    acc[2 * e] = acc2[e].x * wgt;
+                    acc[2 * e + 1] = acc2[e].y * wgt;
+                }
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) {
-                    float a = acc[e] * wgt;
+                    float a = acc[e];
 #pragma unroll
                     for (int d = LPR; d < 32; d <<= 1) a += __shfl_xor_sync(FULL, a, d);
                     acc[e] = a;
                 }
-                const bool whole = item_done && seg_first_j == 0;
-                float* out_item = p.out + ((size_t)cc.r * p.heads + cc.h) * HD;
+                const bool whole = item_done && seg_from_start;
                 if (whole) {
                     if (lane < LPR) {
+                        float* out_item = p.out + (size_t)cur_item * HD;
                         const float mul = lsum > 0.f ? 1.f / lsum : 0.f;
 #pragma unroll
                         for (int cp = 0; cp < CPL; ++cp) {
@@ -610,7 +687,8 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                         }
                     }
                 } else {
-                    // leave a partial, then see whether every other piece of this item has arrived
+                    // leave a partial; the arrival (fence + counter) is deferred to the end of the piece so
+                    // that one fence covers both partial segments and no copy is in flight when it executes
                     const int my_slot = 2 * gw + (first_segment ? 0 : 1);
                     if (lane < LPR) {
                         float* dst = p.part_acc + (size_t)my_slot * HD;
@@ -628,19 +706,15 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                             __stcg(p.part_ml + 2 * my_slot + 1, lsum);
                         }
                     }
-                    // the arrival (fence + counter) is deferred to the end of the piece so that one
-                    // fence covers both partial segments and no copy is in flight when it executes
-                    if (pend_n == 0) { pend_r0 = cc.r; pend_h0 = cc.h; } else { pend_r1 = cc.r; pend_h1 = cc.h; }
+                    if (pend_n == 0) pend_item0 = (int)cur_item; else pend_item1 = (int)cur_item;
                     ++pend_n;
                 }
                 first_segment = false;
                 if (!piece_done) {
-                    cursor_next(cc, rs, info, p.rows, p.heads);
-                    seg_first_j = 0;
-                    load_q(cc);
+                    cur_item = __shfl_sync(FULL, d_item, it + 1 - desc_base);
+                    seg_from_start = true;
+                    load_q(cur_item);
                 }
-            } else {
-                cursor_next(cc, rs, info, p.rows, p.heads);
             }
         }
 
@@ -648,7 +722,8 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
         if (pend_n > 0 && !gave_up) {
             __threadfence();  // this warp's partial stores are visible before its arrivals
             for (int k = 0; k < pend_n; ++k) {
-                const int r = k ? pend_r1 : pend_r0, h = k ? pend_h1 : pend_h0;
+                const int item = k ? pend_item1 : pend_item0;
+                const int r = item / p.heads, h = item - r * p.heads;
                 const int n = (rs[r + 1] - rs[r]) / p.heads;
                 const long long s0 = (long long)rs[r] + (long long)h * n;
                 const int wf = piece_of(s0, total, nw);
@@ -664,28 +739,44 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                 last = __shfl_sync(FULL, last, 0);
                 if (!last) continue;
                 __threadfence();  // the other arrivers' partials are visible after their arrivals
-                float* out_item = p.out + ((size_t)r * p.heads + h) * HD;
+                // merge, lanes in parallel over the partials: (max, sum) first, then the accumulators
+                float* out_item = p.out + (size_t)item * HD;
+                const bool wf_second = piece_start(wf, total, nw) < s0;  // the item is wf's second segment
                 float mall = -INFINITY;
-                for (int w = wf; w <= wl; ++w) {
-                    const int slot = 2 * w + ((w == wf && piece_start(w, total, nw) < s0) ? 1 : 0);
-                    mall = fmaxf(mall, __ldcg(p.part_ml + 2 * slot));
+                for (int w0 = wf; w0 <= wl; w0 += 32) {
+                    const int w = w0 + lane;
+                    const float mi = w <= wl ? __ldcg(p.part_ml + 2 * (2 * w + (w == wf && wf_second ? 1 : 0))) : -INFINITY;
+                    mall = fmaxf(mall, mi);
                 }
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) mall = fmaxf(mall, __shfl_xor_sync(FULL, mall, d));
                 const float mall_safe = (mall == -INFINITY) ? 0.f : mall;
                 float lall = 0.f;
                 float o[(HD + 31) / 32];
 #pragma unroll
                 for (int i = 0; i < (HD + 31) / 32; ++i) o[i] = 0.f;
-                for (int w = wf; w <= wl; ++w) {
-                    const int slot = 2 * w + ((w == wf && piece_start(w, total, nw) < s0) ? 1 : 0);
-                    const float wg = fast_exp2(__ldcg(p.part_ml + 2 * slot) - mall_safe);
-                    lall += __ldcg(p.part_ml + 2 * slot + 1) * wg;
-                    const float* pa = p.part_acc + (size_t)slot * HD;
+                for (int w0 = wf; w0 <= wl; w0 += 32) {
+                    const int w = w0 + lane;
+                    const int my_slot = 2 * w + (w == wf && wf_second ? 1 : 0);
+                    float wg = 0.f;
+                    if (w <= wl) {
+                        wg = fast_exp2(__ldcg(p.part_ml + 2 * my_slot) - mall_safe);
+                        lall += __ldcg(p.part_ml + 2 * my_slot + 1) * wg;
+                    }
+                    const int cnt = min(32, wl - w0 + 1);
+                    for (int i = 0; i < cnt; ++i) {
+                        const float wi = __shfl_sync(FULL, wg, i);
+                        const int si = __shfl_sync(FULL, my_slot, i);
+                        const float* pa = p.part_acc + (size_t)si * HD;
 #pragma unroll
-                    for (int i = 0; i < (HD + 31) / 32; ++i) {
-                        const int d = lane + 32 * i;
-                        if (d < HD) o[i] = fmaf(__ldcg(pa + d), wg, o[i]);
+                        for (int k = 0; k < (HD + 31) / 32; ++k) {
+                            const int d = lane + 32 * k;
+                            if (d < HD) o[k] = fmaf(__ldcg(pa + d), wi, o[k]);
+                        }
                     }
                 }
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) lall += __shfl_xor_sync(FULL, lall, d);
                 const float inv = lall > 0.f ? 1.f / lall : 0.f;
 #pragma unroll
                 for (int i = 0; i < (HD + 31) / 32; ++i) {
@@ -696,10 +787,13 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
         }
     }
 
-    // (arrivals of this warp's partial segments happen inside the block above)
     // ---- fused step: the last CTA to finish publishes the new cursors -------------------------------
     if constexpr (FUSED) {
         __shared__ int is_last;
+        if (n_units == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();

@@ -68,7 +68,6 @@ int device_info(const DeviceInfo** out) {
     return UOCR_B200_OK;
 }
 
-constexpr int kStages = 2;
 constexpr int kMaxWarpsPerCta = 16;
 constexpr int kMaxHeadDim = 256;
 
@@ -98,6 +97,7 @@ struct uocr_b200_workspace {
     int* counters = nullptr;   // [total_warps_max] arrival counters, zero between launches
     int* done_ctas = nullptr;  // fused decode step: CTAs that have finished, zero between launches
     bool timing = false;
+    bool overlap = false;  // fused decode step may start its prologue before the preceding kernel ends
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
 
@@ -178,6 +178,12 @@ int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled) {
     return UOCR_B200_OK;
 }
 
+int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled) {
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_set_overlap: null workspace");
+    ws->overlap = enabled != 0;
+    return UOCR_B200_OK;
+}
+
 int uocr_b200_workspace_last_kernel_ms(uocr_b200_workspace* ws, float* ms) {
     if (!ws || !ms || !ws->ev0) return fail(UOCR_B200_ERR_INVALID, "workspace_last_kernel_ms: timing was never enabled");
     CHECK_CUDA(cudaEventSynchronize(ws->ev1), "event sync");
@@ -216,7 +222,7 @@ struct AttnCall {
     const void* v_base = nullptr;
     const int32_t* table = nullptr;
     int table_stride = 0, num_blocks = 0;
-    long long slot_stride_elems = 0;
+    int slot_rows = 0;
     // geometry
     int rows = 0, heads = 0, kv_heads = 0, head_dim = 0;
     const float* q = nullptr;
@@ -236,9 +242,10 @@ struct AttnCall {
 constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
 
 template <typename KV, int HD, bool PAGED, bool FUSED>
-int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, cudaStream_t st, bool dry) {
+int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, cudaStream_t st, bool dry,
+                   bool overlap = false) {
     using M = TileMap<KV, HD>;
-    constexpr int per_warp = kStages * 2 * M::kTileBytes;
+    constexpr int per_warp = kRing * M::kTileBytes;
     const int plan_bytes = FUSED ? (int)(sizeof(RowInfo) * ap.rows + sizeof(int) * (ap.rows + 1 + 33) + 128) : 0;
     const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024 - plan_bytes;
     int warps = budget / per_warp;
@@ -246,9 +253,9 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
     if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
     *warps_used = warps;
     if (dry) return UOCR_B200_OK;
-    const int bar_bytes = (warps * kStages * 2 * 8 + 127) & ~127;
+    const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     const int smem = bar_bytes + warps * per_warp + plan_bytes;
-    auto kern = rswa_attn_kernel<KV, HD, PAGED, FUSED, kStages>;
+    auto kern = rswa_attn_kernel<KV, HD, PAGED, FUSED>;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -256,36 +263,52 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
         CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "smem attribute");
         configured_smem[dev] = smem;
     }
-    kern<<<di.sms, warps * 32, smem, st>>>(ap);
+    if (FUSED && overlap) {
+        // programmatic dependent launch: this grid may become resident while the previous kernel in the
+        // stream is still draining; the kernel itself waits for it before consuming inputs or scratch
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(di.sms);
+        cfg.blockDim = dim3(warps * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ap), "attention kernel launch");
+    } else {
+        kern<<<di.sms, warps * 32, smem, st>>>(ap);
+    }
     return after_launch("attention kernel");
 }
 
 template <typename KV, bool PAGED, bool FUSED>
-int dispatch_hd(int hd, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry) {
+int dispatch_hd(int hd, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry, bool ov) {
     switch (hd) {
-        case 8: return launch_partial<KV, 8, PAGED, FUSED>(ap, di, warps, st, dry);
-        case 16: return launch_partial<KV, 16, PAGED, FUSED>(ap, di, warps, st, dry);
-        case 32: return launch_partial<KV, 32, PAGED, FUSED>(ap, di, warps, st, dry);
-        case 64: return launch_partial<KV, 64, PAGED, FUSED>(ap, di, warps, st, dry);
-        case 128: return launch_partial<KV, 128, PAGED, FUSED>(ap, di, warps, st, dry);
-        case 256: return launch_partial<KV, 256, PAGED, FUSED>(ap, di, warps, st, dry);
+        case 8: return launch_partial<KV, 8, PAGED, FUSED>(ap, di, warps, st, dry, ov);
+        case 16: return launch_partial<KV, 16, PAGED, FUSED>(ap, di, warps, st, dry, ov);
+        case 32: return launch_partial<KV, 32, PAGED, FUSED>(ap, di, warps, st, dry, ov);
+        case 64: return launch_partial<KV, 64, PAGED, FUSED>(ap, di, warps, st, dry, ov);
+        case 128: return launch_partial<KV, 128, PAGED, FUSED>(ap, di, warps, st, dry, ov);
+        case 256: return launch_partial<KV, 256, PAGED, FUSED>(ap, di, warps, st, dry, ov);
         case 4:
-            if constexpr (KV::kBytes == 4) return launch_partial<KV, 4, PAGED, FUSED>(ap, di, warps, st, dry);
+            if constexpr (KV::kBytes == 4) return launch_partial<KV, 4, PAGED, FUSED>(ap, di, warps, st, dry, ov);
             [[fallthrough]];
         default: return fail(UOCR_B200_ERR_UNSUPPORTED, "head_dim must be a power of two in [8,256] (bf16) or [4,256] (fp32)");
     }
 }
 
-int dispatch_partial(const AttnCall& c, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry) {
+int dispatch_partial(const AttnCall& c, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry, bool ov = false) {
     if (c.fused) {
-        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, true>(c.head_dim, ap, di, warps, st, dry);
-        return dispatch_hd<F32, true, true>(c.head_dim, ap, di, warps, st, dry);
+        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, true>(c.head_dim, ap, di, warps, st, dry, ov);
+        return dispatch_hd<F32, true, true>(c.head_dim, ap, di, warps, st, dry, ov);
     }
     if (c.paged) {
-        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, false>(c.head_dim, ap, di, warps, st, dry);
-        return dispatch_hd<F32, true, false>(c.head_dim, ap, di, warps, st, dry);
+        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, false>(c.head_dim, ap, di, warps, st, dry, ov);
+        return dispatch_hd<F32, true, false>(c.head_dim, ap, di, warps, st, dry, ov);
     }
-    return dispatch_hd<F32, false, false>(c.head_dim, ap, di, warps, st, dry);
+    return dispatch_hd<F32, false, false>(c.head_dim, ap, di, warps, st, dry, ov);
 }
 
 int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
@@ -312,7 +335,7 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.table = c.table;
     ap.table_stride = c.table_stride;
     ap.num_blocks = c.num_blocks;
-    ap.slot_stride_bytes = c.slot_stride_elems * 4;
+    ap.slot_rows = c.slot_rows;
     ap.row_stride_bytes = c.kv_heads * c.head_dim * 4;
     ap.rows = c.rows;
     ap.heads = c.heads;
@@ -351,7 +374,7 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
         if (int rc = after_launch("plan kernel")) return rc;
     }
     if (ws->timing) CHECK_CUDA(cudaEventRecord(ws->ev0, st), "event record");
-    if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/false)) return rc;
+    if (int rc = dispatch_partial(c, ap, *di, &warps, st, /*dry=*/false, ws->overlap)) return rc;
     if (ws->timing) CHECK_CUDA(cudaEventRecord(ws->ev1, st), "event record");
     return UOCR_B200_OK;
 }
@@ -479,7 +502,7 @@ int uocr_b200_rswa_attention_batch_f32(const float* q, const float* kbase, const
     if (!d_len || !d_slots) return fail(UOCR_B200_ERR_INVALID, "attention_batch_f32: null index array");
     AttnCall c;
     c.k_base = kbase; c.v_base = vbase;
-    c.slot_stride_elems = (long long)batch_cap * kv_heads * head_dim;
+    c.slot_rows = batch_cap;
     c.rows = batch; c.heads = heads; c.kv_heads = kv_heads; c.head_dim = head_dim;
     c.q = q; c.out = out;
     c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len;
@@ -505,7 +528,7 @@ int uocr_b200_rswa_attention_ragged_f32(const float* q, const float* kbase, cons
     if (!d_slots || !d_pos) return fail(UOCR_B200_ERR_INVALID, "attention_ragged_f32: null index array");
     AttnCall c;
     c.k_base = kbase; c.v_base = vbase;
-    c.slot_stride_elems = (long long)batch_cap * kv_heads * head_dim;
+    c.slot_rows = batch_cap;
     c.rows = total; c.heads = heads; c.kv_heads = kv_heads; c.head_dim = head_dim;
     c.q = q; c.out = out;
     c.plan.mode = kPlanRagged; c.plan.d_slots = d_slots; c.plan.d_pos = d_pos;
@@ -530,7 +553,7 @@ int uocr_b200_rswa_attention_f32(const float* q, const float* kcache, const floa
     if (seq <= 0) return UOCR_B200_OK;
     AttnCall c;
     c.k_base = kcache; c.v_base = vcache;
-    c.slot_stride_elems = 0;
+    c.slot_rows = 0;
     c.rows = seq; c.heads = heads; c.kv_heads = kv_heads; c.head_dim = head_dim;
     c.q = q; c.out = out;
     c.plan.mode = kPlanSingle; c.plan.fixed_slot = 0; c.plan.kv_len = kv_len; c.plan.d_len = d_len;
