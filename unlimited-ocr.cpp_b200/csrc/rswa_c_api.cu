@@ -251,7 +251,20 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
     int warps = budget / per_warp;
     if (warps > kMaxWarpsPerCta) warps = kMaxWarpsPerCta;
     if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
-    *warps_used = warps;
+    // Two half-size CTAs per SM when the tiles allow it: with the overlapped launch of the fused step a
+    // CTA of the next launch can then move in as soon as half an SM has drained.
+    int ctas = 1;
+#ifndef UOCR_ONE_CTA_PER_SM
+    if (warps >= 16) {
+        const int half_budget = budget / 2 - 1024 - plan_bytes / 2;
+        const int w2 = half_budget / per_warp;
+        if (w2 >= 8) {
+            warps = 8;
+            ctas = 2;
+        }
+    }
+#endif
+    *warps_used = warps * ctas;
     if (dry) return UOCR_B200_OK;
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     const int smem = bar_bytes + warps * per_warp + plan_bytes;
@@ -267,7 +280,7 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
         // programmatic dependent launch: this grid may become resident while the previous kernel in the
         // stream is still draining; the kernel itself waits for it before consuming inputs or scratch
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(di.sms);
+        cfg.gridDim = dim3(di.sms * ctas);
         cfg.blockDim = dim3(warps * 32);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
@@ -278,7 +291,7 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
         cfg.numAttrs = 1;
         CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ap), "attention kernel launch");
     } else {
-        kern<<<di.sms, warps * 32, smem, st>>>(ap);
+        kern<<<di.sms * ctas, warps * 32, smem, st>>>(ap);
     }
     return after_launch("attention kernel");
 }
