@@ -72,9 +72,11 @@ struct AttnParams {
     float scale_log2e;
     const int* rs;
     const RowInfo* info;
-    float* part_acc;  // [2 * total_warps][head_dim]
-    float* part_ml;   // [2 * total_warps][2]  (max in log2 domain, sum)
-    int* counters;    // [total_warps] arrival counters, zero between launches
+    float* part_acc;  // [2 * pieces][head_dim]
+    float* part_ml;   // [2 * pieces][2]  (max in log2 domain, sum)
+    int* counters;    // [pieces] arrival counters, zero between launches
+    int* dyn_next;    // next dynamic piece to hand out, zero between launches
+    int dyn_cap;      // most dynamic pieces the scratch can hold (0 = static split only)
     int* status;
     int total_warps;
     // fused decode step only
@@ -230,12 +232,46 @@ __device__ __forceinline__ void cursor_next(UnitCursor& c, const int* rs, const 
     c.info = info[c.r];
 }
 
-__device__ __forceinline__ long long piece_start(long long w, long long total, int warps) {
-    return (w * total) / warps;
-}
-// the warp whose piece holds unit u: the largest w with piece_start(w) <= u
-__device__ __forceinline__ int piece_of(long long u, long long total, int warps) {
-    return (int)(((u + 1) * warps - 1) / total);
+// How the unit line [0, total) is cut into pieces.  The first `ns` pieces are static, one per warp,
+// and cover [0, u1) evenly; the remaining `nd` pieces of `chunk` units each cover [u1, total) and are
+// handed out at run time (one atomic per piece) to whichever warps finish early: SMs differ by
+// +-15 % in how fast they stream, and a purely static split makes everybody wait for the slowest.
+// Every piece is non-empty and pieces are consecutive, so an item spans pieces of(first)..of(last).
+struct PieceMap {
+    long long total, u1;
+    int ns, nd, chunk;
+    __device__ __forceinline__ long long start(int k) const {
+        return k < ns ? ((long long)k * u1) / ns : u1 + (long long)(k - ns) * chunk;
+    }
+    __device__ __forceinline__ long long end(int k) const {
+        return k < ns ? ((long long)(k + 1) * u1) / ns : u1 + (long long)(k - ns + 1) * chunk;
+    }
+    __device__ __forceinline__ int of(long long u) const {
+        return u < u1 ? (int)(((u + 1) * ns - 1) / u1) : ns + (int)((u - u1) / chunk);
+    }
+};
+
+#ifndef UOCR_DYN_CHUNK
+#define UOCR_DYN_CHUNK 4
+#endif
+#ifndef UOCR_DYN_SHARE
+#define UOCR_DYN_SHARE 0
+#endif
+constexpr int kDynChunk = UOCR_DYN_CHUNK;  // units per dynamic piece
+constexpr int kDynShare = UOCR_DYN_SHARE;  // 1/kDynShare of the units are handed out dynamically (0: none)
+constexpr int kDynPerWarp = 4;    // scratch is sized for this many dynamic pieces per warp
+constexpr int kPendMax = 32;      // per-warp list of partial segments awaiting their arrival
+
+__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int dyn_cap) {
+    PieceMap m;
+    m.total = total;
+    m.chunk = kDynChunk;
+    m.nd = 0;
+    if (kDynShare > 0 && dyn_cap > 0 && total >= 8LL * total_warps)
+        m.nd = (int)min((long long)dyn_cap, total / (max(kDynShare, 1) * kDynChunk));
+    m.u1 = total - (long long)m.nd * kDynChunk;
+    m.ns = (int)min((long long)total_warps, m.u1);
+    return m;
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -278,6 +314,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #endif
 #ifndef UOCR_FFMA2
 #define UOCR_FFMA2 1
+#endif
+#ifdef UOCR_TRACE
+__device__ unsigned long long g_trace[8 * 4096];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TRACE(slot) do { if (lane == 0 && gw < 4096) { g_trace[gw * 8 + (slot)] = gtime(); if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_trace[gw * 8 + 7] = sm; } } } while (0)
+#else
+#define TRACE(slot) do {} while (0)
 #endif
 constexpr int kRing = UOCR_RING;  // shared-memory tile slots per warp; tiles K(0) V(0) K(1) V(1) ... rotate through them
 
@@ -332,6 +375,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gw = blockIdx.x * warps + warp;
+    TRACE(0);
 
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     uint8_t* my_tiles = smem + bar_bytes + (size_t)warp * (kRing * TILE);
@@ -348,7 +392,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     const int* rs = p.rs;
     const RowInfo* info = p.info;
     if constexpr (FUSED) {
-        uint8_t* plan_base = smem + bar_bytes + (size_t)warps * (kRing * TILE);
+        uint8_t* plan_base = smem + bar_bytes + (size_t)warps * (kRing * TILE) + (size_t)warps * kPendMax * sizeof(int);
         RowInfo* info_s = reinterpret_cast<RowInfo*>(plan_base);
         int* rs_s = reinterpret_cast<int*>(plan_base + sizeof(RowInfo) * p.rows);
         int* scratch = rs_s + p.rows + 1;
@@ -358,19 +402,23 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
         info = info_s;
     }
 
+    TRACE(1);
     const long long total = rs[p.rows];
-    const int nw = (int)min((long long)p.total_warps, total);  // every piece is non-empty
+    const PieceMap pm = make_piece_map(total, p.total_warps, p.dyn_cap);
+    int piece = gw < pm.ns ? gw : -1;  // the warp's static piece; dynamic ones follow
     int n_units = 0;
     long long u0 = 0;
-    if (gw < nw) {
-        u0 = piece_start(gw, total, nw);
-        n_units = (int)(piece_start(gw + 1, total, nw) - u0);
-    }
+    int* pend = reinterpret_cast<int*>(smem + bar_bytes + (size_t)warps * (kRing * TILE)) + warp * kPendMax;
+    int pend_n = 0;
+    bool gave_up = false, dep_synced = false;
+    int issue_slot = 0, issue_seq = 0;  // issue_seq: position in the piece's tile sequence (unit = seq / 2, V if odd)
+    int use_slot = 0;                   // slot holding the next tile to consume
+    uint32_t phases = 0;                // one phase bit per slot
 
     const int g = lane % LPR;   // chunk position inside the row
     const int rg = lane / LPR;  // which of the RPW rows of a warp-wide load
 
-    if (n_units > 0) {
+    {
         // ---- unit descriptors: lane l describes unit (desc_base + l) of this piece -------------------
         uint32_t d_tile = 0, d_meta = 0, d_item = 0;
         int desc_base = 0;
@@ -425,7 +473,6 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
         };
 
         // ---- producer side: tiles K(0) V(0) K(1) V(1) ... rotate through the kRing slots -------------
-        int issue_slot = 0, issue_seq = 0;  // issue_seq: position in the tile sequence (unit = seq / 2, V if odd)
         auto issue_tile = [&](int unit, bool is_v) {
             const uint32_t tile = __shfl_sync(FULL, d_tile, unit - desc_base);
             const uint32_t meta = __shfl_sync(FULL, d_meta, unit - desc_base);
@@ -453,10 +500,6 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             if (issue_seq < 2 * n_units) issue_tile(issue_seq >> 1, (issue_seq & 1) != 0);
             ++issue_seq;
         };
-        build_desc(0);
-#pragma unroll
-        for (int s = 0; s < kRing; ++s) issue_next();
-
         // ---- consumer state ---------------------------------------------------------------------
         float2 q2[PPL], acc2[PPL];
         float m_run = -INFINITY, l_run = 0.f;
@@ -477,23 +520,124 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             m_run = -INFINITY;
             l_run = 0.f;
         };
-        if constexpr (FUSED) {
-            // Everything above (barriers, plan, descriptors, the first tiles in flight) reads only this
-            // layer's own cursors, table and pool.  When the launch allows overlap with its predecessor
-            // in the stream, wait for that kernel here -- before the first read of q / k_new / v_new and
-            // before any write to the shared scratch -- then let the next launch begin its own prologue.
-            // Both instructions are no-ops for an ordinary launch.
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        }
-        uint32_t cur_item = __shfl_sync(FULL, d_item, 0);
-        load_q(cur_item);
-        bool first_segment = true;
-        bool seg_from_start = (__shfl_sync(FULL, d_meta, 0) & kMetaFirst) != 0;
-        int pend_item0 = 0, pend_item1 = 0, pend_n = 0;  // partial segments left in scratch
-        bool gave_up = false;
-        int use_slot = 0;          // slot holding the next tile to consume
-        uint32_t phases = 0;       // one phase bit per slot
+        // Before the first read of q / k_new / v_new and before any access to the shared scratch, a
+        // launch that was allowed to overlap its predecessor in the stream waits for it, then lets the
+        // next launch begin its own prologue.  Both instructions are no-ops for an ordinary launch.
+        auto dependency_sync = [&]() {
+            if constexpr (FUSED) {
+                if (!dep_synced) {
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+                }
+            }
+            dep_synced = true;
+        };
+
+        // ---- arrivals: whoever completes an item's set of partials merges them ------------------------
+        auto flush_arrivals = [&]() {
+            if (pend_n == 0) return;
+            __threadfence();  // this warp's partial stores are visible before its arrivals
+            __syncwarp();
+            // every lane arrives for one pending segment (the atomics overlap), then the warp merges the
+            // items for which one of its arrivals was the last
+            int my_item = -1, my_wf = 0, my_wl = 0;
+            long long my_s0 = 0;
+            bool my_last = false;
+            if (lane < pend_n) {
+                my_item = pend[lane];
+                const int r = my_item / p.heads, h = my_item - r * p.heads;
+                const int n = (rs[r + 1] - rs[r]) / p.heads;
+                my_s0 = (long long)rs[r] + (long long)h * n;
+                my_wf = pm.of(my_s0);
+                my_wl = pm.of(my_s0 + n - 1);
+                const int old = atomicAdd(p.counters + my_wf, 1);
+                if (old == my_wl - my_wf) {
+                    my_last = true;
+                    p.counters[my_wf] = 0;  // ready for the next launch
+                }
+            }
+            unsigned todo = __ballot_sync(FULL, my_last);
+            if (todo) __threadfence();  // the other arrivers' partials are visible after their arrivals
+            while (todo) {
+                const int src = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const int item = __shfl_sync(FULL, my_item, src);
+                const int wf = __shfl_sync(FULL, my_wf, src);
+                const int wl = __shfl_sync(FULL, my_wl, src);
+                const long long s0 = __shfl_sync(FULL, my_s0, src);
+                // merge, lanes in parallel over the partials: (max, sum) first, then the accumulators
+                float* out_item = p.out + (size_t)item * HD;
+                const bool wf_second = pm.start(wf) < s0;  // the item is piece wf's second segment
+                float mall = -INFINITY;
+                for (int w0 = wf; w0 <= wl; w0 += 32) {
+                    const int w = w0 + lane;
+                    const float mi = w <= wl ? __ldcg(p.part_ml + 2 * (2 * w + (w == wf && wf_second ? 1 : 0))) : -INFINITY;
+                    mall = fmaxf(mall, mi);
+                }
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) mall = fmaxf(mall, __shfl_xor_sync(FULL, mall, d));
+                const float mall_safe = (mall == -INFINITY) ? 0.f : mall;
+                float lall = 0.f;
+                float o[(HD + 31) / 32];
+#pragma unroll
+                for (int i = 0; i < (HD + 31) / 32; ++i) o[i] = 0.f;
+                for (int w0 = wf; w0 <= wl; w0 += 32) {
+                    const int w = w0 + lane;
+                    const int slot_w = 2 * w + (w == wf && wf_second ? 1 : 0);
+                    float wg = 0.f;
+                    if (w <= wl) {
+                        wg = fast_exp2(__ldcg(p.part_ml + 2 * slot_w) - mall_safe);
+                        lall += __ldcg(p.part_ml + 2 * slot_w + 1) * wg;
+                    }
+                    const int cnt = min(32, wl - w0 + 1);
+                    for (int i = 0; i < cnt; ++i) {
+                        const float wi = __shfl_sync(FULL, wg, i);
+                        const int si = __shfl_sync(FULL, slot_w, i);
+                        const float* pa = p.part_acc + (size_t)si * HD;
+#pragma unroll
+                        for (int kk = 0; kk < (HD + 31) / 32; ++kk) {
+                            const int d = lane + 32 * kk;
+                            if (d < HD) o[kk] = fmaf(__ldcg(pa + d), wi, o[kk]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) lall += __shfl_xor_sync(FULL, lall, d);
+                const float inv = lall > 0.f ? 1.f / lall : 0.f;
+#pragma unroll
+                for (int i = 0; i < (HD + 31) / 32; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < HD) out_item[d] = o[i] * inv;
+                }
+            }
+            pend_n = 0;
+            __syncwarp();
+        };
+
+        // ---- pieces: the static one first, then dynamic ones until none are left ----------------------
+        for (;;) {
+            if (piece < 0) {
+                if (pm.nd == 0 || gave_up) break;
+                dependency_sync();  // the hand-out counter is scratch shared with the previous launch
+                int k = 0;
+                if (lane == 0) k = atomicAdd(p.dyn_next, 1);
+                k = __shfl_sync(FULL, k, 0);
+                if (k >= pm.nd) break;
+                piece = pm.ns + k;
+            }
+            u0 = pm.start(piece);
+            n_units = (int)(pm.end(piece) - u0);
+            issue_seq = 0;
+            build_desc(0);
+#pragma unroll
+            for (int s = 0; s < kRing; ++s) issue_next();
+            // everything up to here read only this layer's own cursors, table and pool
+            dependency_sync();
+            TRACE(2);
+            uint32_t cur_item = __shfl_sync(FULL, d_item, 0);
+            load_q(cur_item);
+            bool first_segment = true;
+            bool seg_from_start = (__shfl_sync(FULL, d_meta, 0) & kMetaFirst) != 0;
 
         for (int it = 0; it < n_units; ++it) {
             if (it - desc_base >= 32 - 2) {  // the producer looks two units ahead: keep those described
@@ -508,6 +652,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status)) { gave_up = true; break; }
             phases ^= 1u << use_slot;
             use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
+            if (it == 0) TRACE(3);
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) {  // the new K row replaces whatever the ring slot held
                     const int off = (int)((meta >> kMetaPatchOffShift) & 15);
@@ -689,7 +834,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                 } else {
                     // leave a partial; the arrival (fence + counter) is deferred to the end of the piece so
                     // that one fence covers both partial segments and no copy is in flight when it executes
-                    const int my_slot = 2 * gw + (first_segment ? 0 : 1);
+                    const int my_slot = 2 * piece + (first_segment ? 0 : 1);
                     if (lane < LPR) {
                         float* dst = p.part_acc + (size_t)my_slot * HD;
 #pragma unroll
@@ -706,8 +851,8 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
                             __stcg(p.part_ml + 2 * my_slot + 1, lsum);
                         }
                     }
-                    if (pend_n == 0) pend_item0 = (int)cur_item; else pend_item1 = (int)cur_item;
-                    ++pend_n;
+                    if (lane == 0) pend[pend_n] = (int)cur_item;
+                    if (++pend_n == kPendMax) flush_arrivals();
                 }
                 first_segment = false;
                 if (!piece_done) {
@@ -718,105 +863,52 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             }
         }
 
-        // ---- arrivals: whoever completes an item's set of partials merges them ------------------------
-        if (pend_n > 0 && !gave_up) {
-            __threadfence();  // this warp's partial stores are visible before its arrivals
-            for (int k = 0; k < pend_n; ++k) {
-                const int item = k ? pend_item1 : pend_item0;
-                const int r = item / p.heads, h = item - r * p.heads;
-                const int n = (rs[r + 1] - rs[r]) / p.heads;
-                const long long s0 = (long long)rs[r] + (long long)h * n;
-                const int wf = piece_of(s0, total, nw);
-                const int wl = piece_of(s0 + n - 1, total, nw);
-                int last = 0;
-                if (lane == 0) {
-                    const int old = atomicAdd(p.counters + wf, 1);
-                    if (old == wl - wf) {
-                        last = 1;
-                        p.counters[wf] = 0;  // ready for the next launch
-                    }
-                }
-                last = __shfl_sync(FULL, last, 0);
-                if (!last) continue;
-                __threadfence();  // the other arrivers' partials are visible after their arrivals
-                // merge, lanes in parallel over the partials: (max, sum) first, then the accumulators
-                float* out_item = p.out + (size_t)item * HD;
-                const bool wf_second = piece_start(wf, total, nw) < s0;  // the item is wf's second segment
-                float mall = -INFINITY;
-                for (int w0 = wf; w0 <= wl; w0 += 32) {
-                    const int w = w0 + lane;
-                    const float mi = w <= wl ? __ldcg(p.part_ml + 2 * (2 * w + (w == wf && wf_second ? 1 : 0))) : -INFINITY;
-                    mall = fmaxf(mall, mi);
-                }
-#pragma unroll
-                for (int d = 16; d >= 1; d >>= 1) mall = fmaxf(mall, __shfl_xor_sync(FULL, mall, d));
-                const float mall_safe = (mall == -INFINITY) ? 0.f : mall;
-                float lall = 0.f;
-                float o[(HD + 31) / 32];
-#pragma unroll
-                for (int i = 0; i < (HD + 31) / 32; ++i) o[i] = 0.f;
-                for (int w0 = wf; w0 <= wl; w0 += 32) {
-                    const int w = w0 + lane;
-                    const int my_slot = 2 * w + (w == wf && wf_second ? 1 : 0);
-                    float wg = 0.f;
-                    if (w <= wl) {
-                        wg = fast_exp2(__ldcg(p.part_ml + 2 * my_slot) - mall_safe);
-                        lall += __ldcg(p.part_ml + 2 * my_slot + 1) * wg;
-                    }
-                    const int cnt = min(32, wl - w0 + 1);
-                    for (int i = 0; i < cnt; ++i) {
-                        const float wi = __shfl_sync(FULL, wg, i);
-                        const int si = __shfl_sync(FULL, my_slot, i);
-                        const float* pa = p.part_acc + (size_t)si * HD;
-#pragma unroll
-                        for (int k = 0; k < (HD + 31) / 32; ++k) {
-                            const int d = lane + 32 * k;
-                            if (d < HD) o[k] = fmaf(__ldcg(pa + d), wi, o[k]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int d = 16; d >= 1; d >>= 1) lall += __shfl_xor_sync(FULL, lall, d);
-                const float inv = lall > 0.f ? 1.f / lall : 0.f;
-#pragma unroll
-                for (int i = 0; i < (HD + 31) / 32; ++i) {
-                    const int d = lane + 32 * i;
-                    if (d < HD) out_item[d] = o[i] * inv;
-                }
-            }
+            if (gave_up) break;
+            piece = -1;
         }
+        TRACE(4);
+        if (!gave_up) flush_arrivals();
     }
 
-    // ---- fused step: the last CTA to finish publishes the new cursors -------------------------------
-    if constexpr (FUSED) {
+    TRACE(5);
+    // ---- the last CTA to finish re-arms the scratch counters; fused step: it publishes the cursors ----
+    {
         __shared__ int is_last;
-        if (n_units == 0) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        if constexpr (FUSED) {
+            if (!dep_synced) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            }
         }
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();
             const int old = atomicAdd(p.done_ctas, 1);
             is_last = (old == (int)gridDim.x - 1);
-            if (is_last) *p.done_ctas = 0;
+            if (is_last) {
+                *p.done_ctas = 0;
+                *p.dyn_next = 0;
+            }
         }
-        __syncthreads();
-        if (is_last) {
-            // every CTA has planned from the old cursors by now; nobody reads them again in this launch
-            for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
-                const int slot = p.plan.d_slots[r];
-                const int pfx = p.plan.d_prefill_len[slot];
-                const int cur = p.d_len[slot];
-                if (cur < pfx + p.plan.window) {
-                    p.d_len[slot] = cur + 1;
-                    if (cur + 1 >= pfx + p.plan.window) p.d_ring_pos[slot] = 0;
-                } else {
-                    p.d_ring_pos[slot] = (p.d_ring_pos[slot] + 1) % p.plan.window;
+        if constexpr (FUSED) {
+            __syncthreads();
+            if (is_last) {
+                // every CTA has planned from the old cursors by now; nobody reads them again in this launch
+                for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+                    const int slot = p.plan.d_slots[r];
+                    const int pfx = p.plan.d_prefill_len[slot];
+                    const int cur = p.d_len[slot];
+                    if (cur < pfx + p.plan.window) {
+                        p.d_len[slot] = cur + 1;
+                        if (cur + 1 >= pfx + p.plan.window) p.d_ring_pos[slot] = 0;
+                    } else {
+                        p.d_ring_pos[slot] = (p.d_ring_pos[slot] + 1) % p.plan.window;
+                    }
                 }
             }
         }
     }
+    TRACE(6);
 }
 
 }  // namespace uocr_b200

@@ -94,8 +94,11 @@ struct uocr_b200_workspace {
     RowInfo* info = nullptr;
     float* part_acc = nullptr;
     float* part_ml = nullptr;
-    int* counters = nullptr;   // [total_warps_max] arrival counters, zero between launches
-    int* done_ctas = nullptr;  // fused decode step: CTAs that have finished, zero between launches
+    int* counters = nullptr;   // [pieces_max] arrival counters, zero between launches
+    int* done_ctas = nullptr;  // CTAs that have finished, zero between launches
+    int* dyn_next = nullptr;   // next dynamic piece to hand out, zero between launches
+    int dyn_cap = 0;           // dynamic pieces the scratch is sized for (0: static split only)
+    int pieces_max = 0;
     bool timing = false;
     bool overlap = false;  // fused decode step may start its prologue before the preceding kernel ends
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -133,10 +136,12 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_status = 0;
     const size_t o_rs = up(256);
     const size_t o_info = o_rs + up(sizeof(int) * (size_t)(max_rows + 1));
+    ws->dyn_cap = kDynShare > 0 ? ws->total_warps_max * kDynPerWarp : 0;
+    ws->pieces_max = ws->total_warps_max + ws->dyn_cap;
     const size_t o_acc = o_info + up(sizeof(RowInfo) * (size_t)max_rows);
-    const size_t o_ml = o_acc + up(sizeof(float) * 2 * (size_t)ws->total_warps_max * kMaxHeadDim);
-    const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->total_warps_max);
-    ws->bytes = o_cnt + up(sizeof(int) * ((size_t)ws->total_warps_max + 64));
+    const size_t o_ml = o_acc + up(sizeof(float) * 2 * (size_t)ws->pieces_max * kMaxHeadDim);
+    const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->pieces_max);
+    ws->bytes = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -154,7 +159,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->part_acc = reinterpret_cast<float*>(ws->base + o_acc);
     ws->part_ml = reinterpret_cast<float*>(ws->base + o_ml);
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
-    ws->done_ctas = ws->counters + ws->total_warps_max;
+    ws->done_ctas = ws->counters + ws->pieces_max;
+    ws->dyn_next = ws->done_ctas + 1;
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -200,7 +206,7 @@ int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_stream_t strea
     CHECK_CUDA(cudaStreamSynchronize(st), "status sync");
     if (v != 0 && ws->counters) {
         // a kernel that gave up may have left arrival counters half-way: start clean again
-        CHECK_CUDA(cudaMemsetAsync(ws->counters, 0, sizeof(int) * ((size_t)ws->total_warps_max + 64), st), "counter clear");
+        CHECK_CUDA(cudaMemsetAsync(ws->counters, 0, sizeof(int) * ((size_t)ws->pieces_max + 64), st), "counter clear");
         CHECK_CUDA(cudaStreamSynchronize(st), "counter clear sync");
     }
     *device_status = v;
@@ -247,14 +253,15 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
     using M = TileMap<KV, HD>;
     constexpr int per_warp = kRing * M::kTileBytes;
     const int plan_bytes = FUSED ? (int)(sizeof(RowInfo) * ap.rows + sizeof(int) * (ap.rows + 1 + 33) + 128) : 0;
-    const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024 - plan_bytes;
+    const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024 - plan_bytes -
+                       kMaxWarpsPerCta * kPendMax * (int)sizeof(int);
     int warps = budget / per_warp;
     if (warps > kMaxWarpsPerCta) warps = kMaxWarpsPerCta;
     if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
     // Two half-size CTAs per SM when the tiles allow it: with the overlapped launch of the fused step a
     // CTA of the next launch can then move in as soon as half an SM has drained.
     int ctas = 1;
-#ifndef UOCR_ONE_CTA_PER_SM
+#ifdef UOCR_TWO_CTAS_PER_SM  // measured: no gain over one CTA per SM on cfg2 / cfg4
     if (warps >= 16) {
         const int half_budget = budget / 2 - 1024 - plan_bytes / 2;
         const int w2 = half_budget / per_warp;
@@ -267,7 +274,7 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
     *warps_used = warps * ctas;
     if (dry) return UOCR_B200_OK;
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
-    const int smem = bar_bytes + warps * per_warp + plan_bytes;
+    const int smem = bar_bytes + warps * per_warp + warps * kPendMax * (int)sizeof(int) + plan_bytes;
     auto kern = rswa_attn_kernel<KV, HD, PAGED, FUSED>;
     static int configured_smem[64] = {0};
     int dev = 0;
@@ -366,6 +373,8 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.d_len = c.d_len_rw;
     ap.d_ring_pos = c.d_ring_rw;
     ap.done_ctas = ws->done_ctas;
+    ap.dyn_next = ws->dyn_next;
+    ap.dyn_cap = ws->dyn_cap;
 
     c.plan.rows = c.rows;
     c.plan.heads = c.heads;
@@ -767,6 +776,9 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     view.part_ml = reinterpret_cast<float*>(base + kNaMl);
     view.counters = reinterpret_cast<int*>(base + kNaCnt);
     view.done_ctas = view.counters + kNoAllocMaxWarps;
+    view.dyn_next = view.done_ctas + 1;
+    view.dyn_cap = 0;  // the built-in scratch holds one piece per warp: static split only
+    view.pieces_max = kNoAllocMaxWarps;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     // two parts of the scratch must start at zero: the status word and the arrival counters of the
@@ -781,3 +793,10 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_prefill_len = d_prefill_len;
     return run_attention(c, &view, st);
 }
+
+#ifdef UOCR_TRACE
+extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_trace(unsigned long long* out, int n) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_trace, sizeof(unsigned long long) * n);
+}
+#endif
