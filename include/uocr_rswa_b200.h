@@ -223,6 +223,37 @@ UOCR_B200_API int uocr_b200_rswa_ring_fill_paged(
     const int* d_prefill_len, int* d_len, int* d_ring_pos, int total, int window,
     uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* Writes packed text rows (fp32 k, v) into the text pool at token d_text_block0[t]*16 + d_pos[t],
+ * rounded to the pool dtype: the first half of uocr_b200_rswa_prefill_text_paged on its own, for
+ * callers that run the tensor-core attention below. */
+UOCR_B200_API int uocr_b200_rswa_text_scatter_paged(
+    const uocr_b200_paged_kv* kv, void* text_k_pool, void* text_v_pool, int text_blocks,
+    const float* k, const float* v, const int* d_pos, const int* d_text_block0, int total,
+    uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
+/* Ragged prefill attention on the tcgen05 tensor cores (bf16 KV, head_dim 128).  The caller
+ * describes the packed query rows as tiles of at most 128 consecutive positions of one request
+ * (host array, copied to the device by this call):
+ *   kind 0: vision rows, causal over the slot's fixed region -- the semantics of
+ *           uocr::cuda::rswa_attention_ragged (src/kernels/cuda/rswa_attention.cu:218-284);
+ *   kind 1: text rows, whole fixed region + text tokens (pos - window, pos] from the text pool --
+ *           the semantics of uocr_b200_rswa_prefill_text_paged.
+ * K/V must already be in the pools (uocr_b200_rswa_write_prefill_ragged_paged for the fixed
+ * region, uocr_b200_rswa_text_scatter_paged for the text).  Same results as the CUDA-core entry
+ * points within the attention tolerance. */
+typedef struct {
+    int32_t row0;   /* first packed row of the tile */
+    int32_t rows;   /* 1..128 */
+    int32_t slot;
+    int32_t kind;   /* 0 vision / causal prefix, 1 text */
+    int32_t pos0;   /* position of the first row: prefix index (kind 0) or text index (kind 1) */
+    int32_t block0; /* kind 1: first block of the request in the text pool */
+} uocr_b200_prefill_tile;
+UOCR_B200_API int uocr_b200_rswa_prefill_attention_tc(
+    const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool, int text_blocks,
+    const float* q, const int* d_prefill_len, const uocr_b200_prefill_tile* h_tiles, int n_tiles,
+    int window, int heads, float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
 /* One decode step of one layer in a single launch: the batched ring append of
  * uocr::cuda::rswa_append_decode_batch followed by uocr::cuda::rswa_attention_batch (the pair issued
  * at src/engine/gpu_decoder.cu:990-996), on the paged layout.  Every CTA plans from the pre-append

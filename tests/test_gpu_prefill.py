@@ -12,6 +12,7 @@ from paged_fixture import PagedBatch, assert_attention_close, ceil_div, load_b20
 
 pytestmark = pytest.mark.gpu
 TIGHT = (2e-5, 1e-5)
+TC_TIGHT = (2e-4, 1e-4)  # tensor-core path: Q and P enter as bf16 hi+lo pairs (~16 mantissa bits)
 
 
 @pytest.fixture(scope="module")
@@ -22,7 +23,7 @@ def b():
     return load_b200()
 
 
-def run_prefill_case(orc, b, dtype, kvh, hd, heads, W, prefixes, text_lens, seed, decode_after=5):
+def run_prefill_case(orc, b, dtype, kvh, hd, heads, W, prefixes, text_lens, seed, decode_after=5, engine="cuda"):
     import torch
     slots = len(prefixes)
     pb = PagedBatch(orc, slots, 1, kvh, hd, W, dtype, prefixes, heads=heads, seed=seed)
@@ -37,14 +38,23 @@ def run_prefill_case(orc, b, dtype, kvh, hd, heads, W, prefixes, text_lens, seed
         qv = synth.normal(seed, 41, (len(vis_rows), heads * hd))
         out = torch.full((len(vis_rows), heads * hd), float("nan"), device="cuda")
         big = b.Workspace(max(len(vis_rows), sum(text_lens), 64))
-        b.attention_ragged_paged(pb.layer[0], torch.from_numpy(qv).cuda(), pb.d_prefill, rs, pos, len(vis_rows), heads, out, big)
+        if engine == "tc":
+            reqs, at = [], 0
+            for s in range(slots):
+                if prefixes[s]:
+                    reqs.append((at, prefixes[s], s, 0, 0, 0))
+                at += prefixes[s]
+            b.prefill_attention_tc(pb.layer[0], None, None, 0, torch.from_numpy(qv).cuda(), pb.d_prefill,
+                                   b.make_prefill_tiles(reqs), W, heads, out, big)
+        else:
+            b.attention_ragged_paged(pb.layer[0], torch.from_numpy(qv).cuda(), pb.d_prefill, rs, pos, len(vis_rows), heads, out, big)
         got = out.cpu().numpy()
         at = 0
         for s in range(slots):
             n = prefixes[s]
             if n:
                 want = pb.cache[s].attention(0, qv[at:at + n], 0, heads, True)
-                assert_attention_close(got[at:at + n], want, *TIGHT)
+                assert_attention_close(got[at:at + n], want, *(TC_TIGHT if engine == "tc" else TIGHT))
             at += n
     else:
         big = b.Workspace(max(sum(text_lens), 64))
@@ -67,8 +77,18 @@ def run_prefill_case(orc, b, dtype, kvh, hd, heads, W, prefixes, text_lens, seed
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     drs, dpos, db0, dtl = d(rs), d(pos), d(b0), d(tl)
     out = torch.full((total, heads * hd), float("nan"), device="cuda")
-    b.prefill_text_paged(pb.layer[0], text_k, text_v, nb, d(q), d(k), d(v), pb.d_prefill, drs, dpos, db0, total, W,
-                         heads, out, big)
+    if engine == "tc":
+        b.text_scatter_paged(pb.layer[0], text_k, text_v, nb, d(k), d(v), dpos, db0, total, big)
+        reqs, at = [], 0
+        for s, T in enumerate(text_lens):
+            if T:
+                reqs.append((at, T, s, 1, 0, block0[s]))
+            at += T
+        b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, b.make_prefill_tiles(reqs), W, heads,
+                               out, big)
+    else:
+        b.prefill_text_paged(pb.layer[0], text_k, text_v, nb, d(q), d(k), d(v), pb.d_prefill, drs, dpos, db0, total, W,
+                             heads, out, big)
     b.ring_fill_paged(pb.layer[0], text_k, text_v, nb, drs, dpos, db0, dtl, pb.d_prefill, pb.d_len[0], pb.d_ring[0],
                       total, W, big)
     got = out.cpu().numpy()
@@ -81,7 +101,7 @@ def run_prefill_case(orc, b, dtype, kvh, hd, heads, W, prefixes, text_lens, seed
         if T:
             tol = (2e-2, 1e-3) if dtype == b.BF16 else (1e-3, 1e-3)
             assert_attention_close(got[at:at + T], np.array(want), *tol)
-            assert_attention_close(got[at:at + T], np.array(want), *TIGHT)
+            assert_attention_close(got[at:at + T], np.array(want), *(TC_TIGHT if engine == "tc" else TIGHT))
         at += T
     pb.check_logical_view(0)  # ring contents + len + ring_pos bit-exact after the fill
     # ---- decode continues from the prefilled state -----------------------------------------------------------
@@ -105,3 +125,14 @@ def test_prefill_text_window_wraps_tiny(orc, b, dtype_name, W):
 def test_prefill_text_real_head_geometry(orc, b):
     # 10 heads x 128; prefixes like "256 global + crops" scaled down; prompts shorter and longer than W
     run_prefill_case(orc, b, b.BF16, 10, 128, 10, 32, prefixes=[48, 20, 65], text_lens=[80, 12, 33], seed=77)
+
+
+def test_prefill_tensor_core_small(orc, b):
+    # tcgen05 path, one head, short rows: every mask shape (causal prefix, partial tiles, window wrap)
+    run_prefill_case(orc, b, b.BF16, 1, 128, 1, 32, prefixes=[20, 0, 130], text_lens=[40, 7, 150], seed=91, engine="tc")
+
+
+def test_prefill_tensor_core_real_geometry(orc, b):
+    # 10 heads x 128, prefixes and prompts spanning several 128-row / 128-key tiles, window shorter than prompts
+    run_prefill_case(orc, b, b.BF16, 10, 128, 10, 160, prefixes=[272, 48, 656], text_lens=[300, 130, 64], seed=92,
+                     engine="tc")

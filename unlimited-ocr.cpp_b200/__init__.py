@@ -78,6 +78,8 @@ _SIGS = {
     "uocr_b200_rswa_attention_batch_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_prefill_text_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_text_scatter_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 4 + [_i, _vp, _vp]),
+    "uocr_b200_rswa_prefill_attention_tc": (_i, [C.POINTER(PagedKV), _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_ring_fill_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_decode_step_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged_noalloc": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp]),
@@ -228,6 +230,31 @@ def prefill_text_paged(layer, text_k, text_v, text_blocks, q, k, v, d_prefill, d
     check(lib().uocr_b200_rswa_prefill_text_paged(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(q), _p(k), _p(v),
                                                    _p(d_prefill), _p(d_slots), _p(d_pos), _p(d_block0), total, window,
                                                    heads, _p(out), ws.h, stream_handle(stream)))
+
+
+def text_scatter_paged(layer, text_k, text_v, text_blocks, k, v, d_pos, d_block0, total, ws=None, stream=None):
+    check(lib().uocr_b200_rswa_text_scatter_paged(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(k), _p(v),
+                                                   _p(d_pos), _p(d_block0), total, ws.h if ws else None,
+                                                   stream_handle(stream)))
+
+
+def prefill_attention_tc(layer, text_k, text_v, text_blocks, q, d_prefill, tiles, window, heads, out, ws, stream=None):
+    """tiles: int32 numpy array [n, 6] = (row0, rows, slot, kind, pos0, block0) per query tile (host)."""
+    import numpy as np
+    t = np.ascontiguousarray(tiles, dtype=np.int32)
+    check(lib().uocr_b200_rswa_prefill_attention_tc(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(q),
+                                                     _p(d_prefill), t.ctypes.data, t.shape[0], window, heads, _p(out),
+                                                     ws.h, stream_handle(stream)))
+
+
+def make_prefill_tiles(requests):
+    """requests: iterable of (row0, n_rows, slot, kind, pos0, block0); cut into tiles of <= 128 rows."""
+    import numpy as np
+    out = []
+    for row0, n, slot, kind, pos0, block0 in requests:
+        for a in range(0, n, 128):
+            out.append((row0 + a, min(128, n - a), slot, kind, pos0 + a, block0))
+    return np.array(out, dtype=np.int32).reshape(-1, 6)
 
 
 def ring_fill_paged(layer, text_k, text_v, text_blocks, d_slots, d_pos, d_block0, d_text_len, d_prefill, d_len, d_ring,

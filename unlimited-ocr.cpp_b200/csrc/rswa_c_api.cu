@@ -11,6 +11,7 @@
 
 #include "rswa_attention.cuh"
 #include "rswa_copy.cuh"
+#include "rswa_prefill_tc.cuh"
 #include "uocr_rswa_b200.h"
 
 using namespace uocr_b200;
@@ -99,6 +100,8 @@ struct uocr_b200_workspace {
     int* dyn_next = nullptr;   // next dynamic piece to hand out, zero between launches
     int dyn_cap = 0;           // dynamic pieces the scratch is sized for (0: static split only)
     int pieces_max = 0;
+    PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
+    int tiles_cap = 0;
     bool timing = false;
     bool overlap = false;  // fused decode step may start its prologue before the preceding kernel ends
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -141,7 +144,9 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_acc = o_info + up(sizeof(RowInfo) * (size_t)max_rows);
     const size_t o_ml = o_acc + up(sizeof(float) * 2 * (size_t)ws->pieces_max * kMaxHeadDim);
     const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->pieces_max);
-    ws->bytes = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
+    const size_t o_tiles = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
+    ws->tiles_cap = max_rows;
+    ws->bytes = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -161,6 +166,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
     ws->done_ctas = ws->counters + ws->pieces_max;
     ws->dyn_next = ws->done_ctas + 1;
+    ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -653,6 +659,91 @@ int uocr_b200_rswa_ring_fill_paged(const uocr_b200_paged_kv* kv, const void* tex
     else
         rswa_ring_fill_kernel<F32><<<total, 160, 0, st>>>(pv, kt, vt, d_slots, d_pos, d_text_block0, d_text_len, d_prefill_len, d_len, d_ring_pos, window, status);
     return after_launch("ring fill");
+}
+
+int uocr_b200_rswa_text_scatter_paged(const uocr_b200_paged_kv* kv, void* text_k_pool, void* text_v_pool, int text_blocks,
+                                      const float* k, const float* v, const int* d_pos, const int* d_text_block0,
+                                      int total, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!text_k_pool || !text_v_pool || text_blocks <= 0 || !k || !v || !d_pos || !d_text_block0)
+        return fail(UOCR_B200_ERR_INVALID, "text_scatter_paged: null pointer");
+    if (!aligned16(text_k_pool) || !aligned16(text_v_pool) || !aligned16(k) || !aligned16(v))
+        return fail(UOCR_B200_ERR_INVALID, "text_scatter_paged: pointers must be 16-byte aligned");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    PagedView text = pv;
+    text.k_pool = static_cast<uint8_t*>(text_k_pool);
+    text.v_pool = static_cast<uint8_t*>(text_v_pool);
+    text.table = nullptr;
+    text.table_stride = 0;
+    text.num_blocks = text_blocks;
+    int* status = ws ? ws->status : nullptr;
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_scatter_text_kernel<BF16><<<total, 256, 0, st>>>(text, k, v, d_pos, d_text_block0, status);
+    else
+        rswa_scatter_text_kernel<F32><<<total, 256, 0, st>>>(text, k, v, d_pos, d_text_block0, status);
+    return after_launch("text scatter");
+}
+
+int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool,
+                                        int text_blocks, const float* q, const int* d_prefill_len,
+                                        const uocr_b200_prefill_tile* h_tiles, int n_tiles, int window, int heads,
+                                        float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (n_tiles <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (kv->dtype != UOCR_B200_BF16 || kv->head_dim != kTcTile)
+        return fail(UOCR_B200_ERR_UNSUPPORTED, "prefill_attention_tc: needs bf16 KV and head_dim 128");
+    if (!q || !out || !d_prefill_len || !h_tiles || !ws) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: null pointer");
+    if (!aligned16(q) || !aligned16(out)) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: q/out must be 16-byte aligned");
+    if (heads <= 0 || heads % kv->kv_heads != 0) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: heads must be a multiple of kv_heads");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: window must be positive");
+    if (n_tiles > ws->tiles_cap) return fail(UOCR_B200_ERR_WORKSPACE, "prefill_attention_tc: more tiles than the workspace holds");
+    bool any_text = false;
+    for (int i = 0; i < n_tiles; ++i) {
+        const uocr_b200_prefill_tile& t = h_tiles[i];
+        if (t.rows < 1 || t.rows > kTcTile || t.row0 < 0 || t.slot < 0 || t.pos0 < 0 || (t.kind != 0 && t.kind != 1))
+            return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: bad tile descriptor");
+        any_text |= t.kind == 1;
+    }
+    if (any_text && (!text_k_pool || !text_v_pool || text_blocks <= 0))
+        return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: text tiles need the text pool");
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    static_assert(sizeof(uocr_b200_prefill_tile) == sizeof(PrefillTile), "tile descriptor layouts must match");
+    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, h_tiles, sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
+               "tile descriptors H2D");
+    PrefillParams pp{};
+    pp.q = q;
+    pp.out = out;
+    pp.k_pool = pv.k_pool;
+    pp.v_pool = pv.v_pool;
+    pp.k_text = static_cast<const uint8_t*>(text_k_pool);
+    pp.v_text = static_cast<const uint8_t*>(text_v_pool);
+    pp.table = pv.table;
+    pp.d_prefill_len = d_prefill_len;
+    pp.tiles = ws->tiles;
+    pp.table_stride = pv.table_stride;
+    pp.num_blocks = pv.num_blocks;
+    pp.text_blocks = text_blocks;
+    pp.heads = heads;
+    pp.kv_heads = kv->kv_heads;
+    pp.group = heads / kv->kv_heads;
+    pp.window = window;
+    pp.scale_log2e = (1.0f / std::sqrt(128.0f)) * 1.4426950408889634f;
+    pp.status = ws->status;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev & 63]) {
+        CHECK_CUDA(cudaFuncSetAttribute(rswa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes),
+                   "prefill smem attribute");
+        configured[dev & 63] = true;
+    }
+    rswa_prefill_tc_kernel<<<dim3(n_tiles, heads), 128, kTcSmemBytes, st>>>(pp);
+    return after_launch("tensor-core prefill attention");
 }
 
 // ---- fused decode step ---------------------------------------------------------------------------------
