@@ -470,6 +470,114 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+def run_prefill(args, rank, world):
+    """Configuration 3: ragged prefill + ring fill.  16 sequences, 12 layers, 10 heads x 128, bf16;
+    vision prefix lengths from {256, 656, 1056}, text prompt lengths uniform in [64, 2048], W=1024
+    (prompts longer than W wrap).  Per layer: scatter of the vision K/V into the prefix blocks and of
+    the text K/V into the text pool, attention (vision rows causal over the prefix; text rows over
+    prefix + window) on the tcgen05 kernel, ring fill.  Reports prefill tokens/s and TFLOP/s
+    (4*D*H = 5120 flop per attended (query, key) pair).  Parity of this path: tests/test_gpu_prefill.py."""
+    if rank != 0:
+        return
+    import torch
+    import synth
+    pkg = load_pkg()
+    c = CFG
+    S, L, W, H, D, bt = 16, args.layers or c["layers"], c["window"], c["heads"], c["head_dim"], 16
+    row = H * D
+    pv = np.array([(256, 656, 1056)[i] for i in synth.integers(c["seed"], 301, 0, 2, (S,))])
+    tl = synth.integers(c["seed"], 302, 64, 2048, (S,)).astype(np.int64)
+    pb, rb = pv // bt, W // bt
+    pstart = np.concatenate([[0], np.cumsum(pb)])
+    num_blocks = int(pstart[-1]) + S * rb
+    table = np.full((S, int(pb.max()) + rb), -1, np.int32)
+    for s in range(S):
+        table[s, :pb[s]] = pstart[s] + np.arange(pb[s])
+        table[s, pb[s]:pb[s] + rb] = pstart[-1] + s * rb + np.arange(rb)
+    d_table = torch.from_numpy(table).cuda()
+    layers = [pkg.PagedLayer(num_blocks, H, D, pkg.BF16, d_table) for _ in range(L)]
+    tb = -(-tl // bt)
+    block0 = np.concatenate([[0], np.cumsum(tb)])[:-1]
+    text_blocks = int(tb.sum())
+    text_k = torch.zeros((text_blocks, H, bt, D), dtype=torch.bfloat16, device="cuda")
+    text_v = torch.zeros_like(text_k)
+    nv, nt = int(pv.sum()), int(tl.sum())
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    v_slots = d(np.concatenate([np.full(pv[s], s) for s in range(S)]).astype(np.int32))
+    v_pos = d(np.concatenate([np.arange(pv[s]) for s in range(S)]).astype(np.int32))
+    t_slots = d(np.concatenate([np.full(tl[s], s) for s in range(S)]).astype(np.int32))
+    t_pos = d(np.concatenate([np.arange(tl[s]) for s in range(S)]).astype(np.int32))
+    t_b0 = d(np.concatenate([np.full(tl[s], block0[s]) for s in range(S)]).astype(np.int32))
+    t_len = d(np.concatenate([np.full(tl[s], tl[s]) for s in range(S)]).astype(np.int32))
+    d_prefill = d(pv.astype(np.int32))
+    d_len = torch.zeros((L, S), dtype=torch.int32, device="cuda")
+    d_ring = torch.zeros((L, S), dtype=torch.int32, device="cuda")
+    g = torch.Generator(device="cuda")
+    g.manual_seed(c["seed"])
+    q = torch.randn((nv + nt, row), generator=g, device="cuda")
+    k = torch.randn((nv + nt, row), generator=g, device="cuda")
+    v = torch.randn((nv + nt, row), generator=g, device="cuda")
+    out = torch.zeros((nv + nt, row), device="cuda")
+    reqs, at = [], 0
+    for s in range(S):
+        reqs.append((at, int(pv[s]), s, 0, 0, 0))
+        at += int(pv[s])
+    for s in range(S):
+        reqs.append((at, int(tl[s]), s, 1, 0, int(block0[s])))
+        at += int(tl[s])
+    tiles = pkg.make_prefill_tiles(reqs)
+    ws = pkg.Workspace(nv + nt)
+    pairs = sum(int(p) * (int(p) + 1) // 2 for p in pv) + sum(
+        int(t) * int(p) + (int(t) * (int(t) + 1) // 2 if t <= W else W * (W + 1) // 2 + (int(t) - W) * W)
+        for t, p in zip(tl, pv))
+    flops = pairs * 4.0 * D * H
+
+    def layer_pass(l, tc=True):
+        pkg.write_prefill_ragged_paged(layers[l], k[:nv], v[:nv], v_slots, v_pos, nv, ws)
+        if tc:
+            pkg.text_scatter_paged(layers[l], text_k, text_v, text_blocks, k[nv:], v[nv:], t_pos, t_b0, nt, ws)
+            pkg.prefill_attention_tc(layers[l], text_k, text_v, text_blocks, q, d_prefill, tiles, W, H, out, ws)
+        else:
+            pkg.attention_ragged_paged(layers[l], q[:nv], d_prefill, v_slots, v_pos, nv, H, out[:nv], ws)
+            pkg.prefill_text_paged(layers[l], text_k, text_v, text_blocks, q[nv:], k[nv:], v[nv:], d_prefill, t_slots,
+                                   t_pos, t_b0, nt, W, H, out[nv:], ws)
+        pkg.ring_fill_paged(layers[l], text_k, text_v, text_blocks, t_slots, t_pos, t_b0, t_len, d_prefill, d_len[l],
+                            d_ring[l], nt, W, ws)
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(max(args.warmup, 1)):
+        layer_pass(0)
+    torch.cuda.synchronize()
+    steps = max(1, min(args.steps, 20))
+    e0.record()
+    for _ in range(steps):
+        for l in range(L):
+            layer_pass(l)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    layer_pass(0, tc=False)
+    torch.cuda.synchronize()
+    e0.record()
+    layer_pass(0, tc=False)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_cuda_core_layer = e0.elapsed_time(e1)
+    assert ws.status() == 0
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    tf = flops * L / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "rswa_prefill_tokens_per_s", "value": (nv + nt) / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "ms_per_step": ms, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg3: ragged prefill + ring fill, 16 seqs x %d layers, prefixes {256,656,1056}, "
+                               "text U[64,2048], W=1024" % L, "vision_tokens": nv, "text_tokens": nt,
+                   "query_tiles": int(tiles.shape[0]), "attended_pairs_per_layer": pairs},
+        "roofline": {"bound": "tensor", "kernel": "rswa_prefill_tc_kernel", "achieved": tf, "unit": "TFLOP/s",
+                     "peak": peaks.get("bf16_tflops"), "frac": (tf / peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
+                     "note": "useful flops only; the kernel issues 2x (hi+lo operands) and is not yet pipelined"},
+        "cuda_core_path_ms_per_layer": ms_cuda_core_layer, "tensor_core_path_ms_per_layer": ms / L}))
+
+
 def run_churn(args, rank, world):
     """Configuration 5: pool of 65536 blocks x 12 layers (64 GB), 1000 requests on a seeded Poisson
     schedule, 8 prefixes, W=1024; reports append and block-table gather bandwidth (algorithmic bytes:
@@ -510,7 +618,7 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="issue append and attention as the reference does (two entry points per layer) "
                          "instead of the fused one-launch decode step")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "churn"],
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "churn"],
                     help="cfg2 (default, headline): 64 seqs/GPU, W=1024, one shared prefix, weak scaling; "
                          "cfg4: 512 seqs in total sharded over the GPUs, W=4096, 4 prefixes, strong scaling; "
                          "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
@@ -533,6 +641,8 @@ def main():
         CFG["seqs"] = shard_sequences(CFG["total_seqs"], world, rank)[1]
     if args.workload == "churn":
         run_churn(args, rank, world)
+    elif args.workload == "cfg3":
+        run_prefill(args, rank, world)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
