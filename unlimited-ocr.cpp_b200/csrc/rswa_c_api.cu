@@ -686,6 +686,35 @@ int uocr_b200_rswa_text_scatter_paged(const uocr_b200_paged_kv* kv, void* text_k
     return after_launch("text scatter");
 }
 
+// Tensor map of a K or V pool seen as a [rows][128] bf16 matrix, fetched in boxes of 16 rows x 64
+// elements (one 16-token block of one head, one 128-byte half of each row) with the 128-byte swizzle
+// the tensor-core operand layout uses.  Rows at or beyond `rows` read as zeros.
+static int make_kv_map(CUtensorMap* map, const void* pool, long rows) {
+    using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiled encode = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return reinterpret_cast<EncodeTiled>(fn);
+    }();
+    if (!encode) return fail(UOCR_B200_ERR_CUDA, "prefill_attention_tc: the driver does not export the tensor-map encoder");
+    if (!aligned16(pool) || rows <= 0 || rows >= (1L << 31))
+        return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: pool must be 16-byte aligned and hold fewer than 2^31 token rows");
+    const cuuint64_t dims[2] = {(cuuint64_t)kTcTile, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)kTcTile * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kBlockTokens};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem_strides,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(UOCR_B200_ERR_CUDA, "prefill_attention_tc: tensor-map encoding failed");
+    return UOCR_B200_OK;
+}
+
 int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool,
                                         int text_blocks, const float* q, const int* d_prefill_len,
                                         const uocr_b200_prefill_tile* h_tiles, int n_tiles, int window, int heads,
@@ -742,7 +771,19 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
                    "prefill smem attribute");
         configured[dev & 63] = true;
     }
-    rswa_prefill_tc_kernel<<<dim3(n_tiles, heads), 128, kTcSmemBytes, st>>>(pp);
+    PrefillMaps maps;
+    const long pool_rows = (long)kv->num_blocks * kv->kv_heads * kBlockTokens;
+    const long text_rows = (long)text_blocks * kv->kv_heads * kBlockTokens;
+    if (int rc = make_kv_map(&maps.k, pv.k_pool, pool_rows)) return rc;
+    if (int rc = make_kv_map(&maps.v, pv.v_pool, pool_rows)) return rc;
+    if (any_text) {
+        if (int rc = make_kv_map(&maps.tk, text_k_pool, text_rows)) return rc;
+        if (int rc = make_kv_map(&maps.tv, text_v_pool, text_rows)) return rc;
+    } else {  // never read: no text tile in this launch
+        maps.tk = maps.k;
+        maps.tv = maps.v;
+    }
+    rswa_prefill_tc_kernel<<<dim3(n_tiles, heads), kTcThreads, kTcSmemBytes, st>>>(pp, maps);
     return after_launch("tensor-core prefill attention");
 }
 

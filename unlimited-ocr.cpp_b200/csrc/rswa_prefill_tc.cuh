@@ -1,15 +1,21 @@
 // Ragged prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// One CTA (128 threads) owns one tile of up to 128 consecutive query rows of one request and one
-// head, and walks the 128-key tiles those rows can see: first the fixed (prefix) region through the
-// block table, then -- for text rows -- the sliding text window in the text pool.  Per key tile:
+// One CTA owns one tile of up to 128 consecutive query rows of one request and one head, and walks
+// the 128-key tiles those rows can see: first the fixed (prefix) region through the block table,
+// then -- for text rows -- the sliding text window in the text pool.  The CTA is warp-specialised:
 //
-//   S = Q K^T      tcgen05.mma kind::f16, M=128 N=128, K and Q tiles in shared memory (K-major,
-//                  128-byte swizzle), accumulator in TMEM (128 lanes x 128 fp32 columns)
-//   softmax        thread r owns query row r == TMEM lane r: tcgen05.ld, mask, online max/sum in the
-//                  exp2 domain, probabilities written back to shared memory as the A operand
-//   O_tile = P V   tcgen05.mma again, V tile as the MN-major B operand; the result is read from TMEM
-//                  and folded into a per-thread fp32 accumulator with the usual rescale
+//   warp 4      producer: per key tile, 32 tiled TMA loads (one 16-token block half of K or V each,
+//               SWIZZLE_128B) into a two-deep K/V ring in shared memory; blocks the rows cannot
+//               see are fetched from an out-of-range coordinate, which fills zeros
+//   warp 5      one thread issues the MMAs: S = Q K^T (tcgen05.mma kind::f16, M = N = 128, operands
+//               in shared memory, accumulator in TMEM) one tile ahead of the softmax, and
+//               O_tile = P V with P read straight from TMEM and V as the MN-major B operand
+//   warps 0-3   softmax: thread r owns query row r == TMEM lane r: tcgen05.ld of S, mask, online
+//               max/sum in the exp2 domain, P written over S in TMEM (tcgen05.st) as bf16 pairs, and
+//               the previous tile's O_tile folded into a per-thread fp32 accumulator with the usual
+//               rescale while the tensor core works on the next products
+//
+// TMEM (512 columns): S/P double-buffered in [0,256), O_tile double-buffered in [256,512).
 //
 // The queries arrive in fp32 and the oracle computes in fp32, so Q and P are each fed to the tensor
 // cores as a bf16 pair (hi + lo): two MMAs per operand keep ~16 mantissa bits, which holds the
@@ -18,8 +24,11 @@
 // rows (causal over the fixed region) and, for text rows, the append-then-attend composition that
 // defines "prefix + last W tokens".
 //
-// Every wait is bounded; a wait that runs out sets a status bit and the CTA still frees its TMEM.
+// Every wait is bounded; a wait that runs out sets a status bit, every role leaves its loop, the
+// copies and MMAs in flight are drained (bounded again) and the CTA frees its TMEM.
 #pragma once
+
+#include <cuda.h>  // CUtensorMap (type only; the encoder is fetched through the runtime)
 
 #include "rswa_device.cuh"
 
@@ -95,6 +104,29 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
         : "memory");
 }
 
+// A operand from TMEM (lane = row, two bf16 per 32-bit column), B from shared memory.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -115,18 +147,13 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// hi/lo bf16 split of eight floats into two 16-byte chunks
-__device__ __forceinline__ void tc_split8(const float (&x)[8], uint4& hi, uint4& lo) {
-    uint32_t h[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t a = f32_to_bf16_bits(x[2 * i]), b = f32_to_bf16_bits(x[2 * i + 1]);
-        h[i] = a | (b << 16);
-        const float ra = x[2 * i] - __uint_as_float(a << 16), rb = x[2 * i + 1] - __uint_as_float(b << 16);
-        l[i] = f32_to_bf16_bits(ra) | (f32_to_bf16_bits(rb) << 16);
-    }
-    hi = make_uint4(h[0], h[1], h[2], h[3]);
-    lo = make_uint4(l[0], l[1], l[2], l[3]);
+// Truncating hi/lo split of two floats into packed bf16 pairs: hi keeps the top 16 bits, lo the top
+// 16 bits of the exact remainder, so hi + lo carries 16 mantissa bits of the input.
+__device__ __forceinline__ void tc_split2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
+    hi = __byte_perm(ua, ub, 0x7632);
+    const float ra = a - __uint_as_float(ua & 0xffff0000u), rb = b - __uint_as_float(ub & 0xffff0000u);
+    lo = __byte_perm(__float_as_uint(ra), __float_as_uint(rb), 0x7632);
 }
 
 __device__ __forceinline__ float tc_exp2(float x) {
@@ -135,72 +162,131 @@ __device__ __forceinline__ float tc_exp2(float x) {
     return y;
 }
 
-constexpr int kTcSmemBytes = 6 * kTcTileBytes + 64 + 1024;  // Qhi Qlo K V Phi Plo + barriers + alignment slack
 
-__global__ void __launch_bounds__(128, 1) rswa_prefill_tc_kernel(const PrefillParams p) {
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Tiled TMA load of one box (64 elements x 16 rows of a [rows][128] bf16 matrix) into shared memory.
+// x (innermost coordinate) is 0 or 64: a multiple of 16 bytes as the engine requires.  A row
+// coordinate at or beyond the matrix's extent fills the box with zeros and still completes the full
+// byte count on the barrier.
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+struct PrefillMaps {
+    CUtensorMap k, v;    // paged pool, as a [num_blocks * kv_heads * 16][128] bf16 matrix
+    CUtensorMap tk, tv;  // text pool, same shape with text_blocks
+};
+
+constexpr int kTcThreads = 192;  // warps 0-3 softmax, warp 4 producer, warp 5 MMA issue + TMEM owner
+constexpr int kTcSmemBytes = 6 * kTcTileBytes + 128 + 1024;  // Qhi Qlo K[2] V[2] + barriers + alignment slack
+constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;         // one K tile + one V tile
+
+// One key tile of the online softmax for this thread's row.  Reads S from TMEM twice (max, then
+// exponentials) and overwrites it chunk by chunk with P: per 32-key chunk, 16 words of hi pairs then
+// 16 words of lo pairs.  FULL: every key of the tile is visible to every row of the warp.
+template <bool FULL>
+__device__ __forceinline__ void tc_softmax_tile(uint32_t tS, int vlo, int vhi, float& m_run, float& l_run, float& alpha) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+        float v[32];
+        tc_ld32(tS + cc * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int key = cc * 32 + j;
+            if (FULL || (key >= vlo && key < vhi)) mx = fmaxf(mx, v[j]);
+        }
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+    alpha = tc_exp2(m_run - m_safe);
+    float lsum = 0.f;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+        float v[32];
+        tc_ld32(tS + cc * 32, v);
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            float pr[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int key = cc * 32 + 2 * e + u;
+                const bool valid = FULL || (key >= vlo && key < vhi);
+                pr[u] = valid ? tc_exp2(v[2 * e + u] - m_safe) : 0.f;
+                lsum += pr[u];
+            }
+            tc_split2(pr[0], pr[1], pk[e], pk[16 + e]);
+        }
+        tc_st32(tS + cc * 32, pk);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    l_run = l_run * alpha + lsum;
+    m_run = m_new;
+}
+
+__device__ __forceinline__ void tc_fold(uint32_t tO, float alpha, float (&acc)[kTcTile]) {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+        float v[32];
+        tc_ld32(tO + cc * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(acc[cc * 32 + j], alpha, v[j]);
+    }
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMaps maps) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQh = base;
     uint8_t* sQl = base + 1 * kTcTileBytes;
-    uint8_t* sK = base + 2 * kTcTileBytes;
-    uint8_t* sV = base + 3 * kTcTileBytes;
-    uint8_t* sPh = base + 4 * kTcTileBytes;
-    uint8_t* sPl = base + 5 * kTcTileBytes;
+    uint8_t* sKV = base + 2 * kTcTileBytes;  // stage b: K at sKV + b * kTcStageBytes, V one tile after it
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTcTileBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
-    const uint32_t bar_s = smem_addr(bars), bar_o = smem_addr(bars + 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    const uint32_t bar0 = smem_addr(bars);
+    // barrier b of group g sits at bar0 + (2 * g + b) * 8
+    auto kv_full = [&](int b) { return bar0 + (0 + b) * 8; };  // TMA bytes of stage b have landed
+    auto kv_free = [&](int b) { return bar0 + (2 + b) * 8; };  // the MMAs reading stage b are done
+    auto s_full = [&](int b) { return bar0 + (4 + b) * 8; };   // S buffer b holds Q K^T
+    auto p_full = [&](int b) { return bar0 + (6 + b) * 8; };   // all 128 rows wrote P over S buffer b
+    auto o_full = [&](int b) { return bar0 + (8 + b) * 8; };   // O_tile buffer b holds P V
+    const uint32_t q_full = bar0 + 10 * 8, drained = bar0 + 11 * 8;
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const PrefillTile t = p.tiles[blockIdx.x];
     const int head = blockIdx.y, kvh = head / p.group;
 
     if (tid == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(kv_full(b), 1);
+            mbar_init(kv_free(b), 1);
+            mbar_init(s_full(b), 1);
+            mbar_init(p_full(b), 128);
+            mbar_init(o_full(b), 1);
+        }
+        mbar_init(q_full, 128);
+        mbar_init(drained, 1);
         mbar_init_fence();
     }
-    if (warp == 0) {  // 256 TMEM columns: S in [0,128), O_tile in [128,256)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(256u) : "memory");
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const uint32_t tS = tmem + lane_base, tO = tmem + 128 + lane_base;
 
-    // ---- this thread's query row ------------------------------------------------------------------
-    const int r = tid;
-    const bool live = r < t.rows;
-    const int i = t.pos0 + r;
+    // ---- key tiles this query tile can see (uniform over the CTA) ------------------------------------
     const int pfx = max(p.d_prefill_len[t.slot], 0);
-    const int phi = !live ? 0 : (t.kind == 0 ? min(i + 1, pfx) : pfx);  // fixed-region tokens [0, phi)
-    const int tlo = max(0, i - p.window + 1);
-    const int thi = (live && t.kind == 1) ? i + 1 : 0;                   // text tokens [tlo, thi)
-    {
-        const float* qp = p.q + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
-#pragma unroll 4
-        for (int c = 0; c < 16; ++c) {
-            float x[8];
-            if (live) {
-                const float4 a = __ldg(reinterpret_cast<const float4*>(qp + c * 8));
-                const float4 b = __ldg(reinterpret_cast<const float4*>(qp + c * 8 + 4));
-                x[0] = a.x * p.scale_log2e; x[1] = a.y * p.scale_log2e; x[2] = a.z * p.scale_log2e; x[3] = a.w * p.scale_log2e;
-                x[4] = b.x * p.scale_log2e; x[5] = b.y * p.scale_log2e; x[6] = b.z * p.scale_log2e; x[7] = b.w * p.scale_log2e;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = 0.f;
-            }
-            uint4 hi, lo;
-            tc_split8(x, hi, lo);
-            const uint32_t off = tc_tile_offset(r, c);
-            *reinterpret_cast<uint4*>(sQh + off) = hi;
-            *reinterpret_cast<uint4*>(sQl + off) = lo;
-        }
-    }
-
-    // ---- key tiles this query tile can see ----------------------------------------------------------
     const int plim = t.kind == 0 ? min(t.pos0 + t.rows, pfx) : pfx;
     const int n_prefix_tiles = (plim + kTcTile - 1) / kTcTile;
     int text_tile0 = 0, n_text_tiles = 0;
@@ -208,165 +294,181 @@ __global__ void __launch_bounds__(128, 1) rswa_prefill_tc_kernel(const PrefillPa
         text_tile0 = max(0, t.pos0 - p.window + 1) / kTcTile;
         n_text_tiles = (t.pos0 + t.rows - 1) / kTcTile - text_tile0 + 1;
     }
-    const int prefix_blocks = (pfx + kBlockTokens - 1) / kBlockTokens;
-    const uint32_t idesc_s = tc_instr_desc(false), idesc_o = tc_instr_desc(true);
+    const int n_steps = n_prefix_tiles + n_text_tiles;
 
-    float acc[kTcTile];
+    if (warp < 4) {
+        // ================= softmax warps: thread r owns query row r ================================
+        const int r = tid;
+        const bool live = r < t.rows;
+        const int i = t.pos0 + r;
+        const int phi = !live ? 0 : (t.kind == 0 ? min(i + 1, pfx) : pfx);  // fixed-region tokens [0, phi)
+        const int tlo = max(0, i - p.window + 1);
+        const int thi = (live && t.kind == 1) ? i + 1 : 0;                   // text tokens [tlo, thi)
+        {
+            const float* qp = p.q + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
+#pragma unroll 4
+            for (int c = 0; c < 16; ++c) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (live) {
+                    a = __ldg(reinterpret_cast<const float4*>(qp + c * 8));
+                    b = __ldg(reinterpret_cast<const float4*>(qp + c * 8 + 4));
+                }
+                const float s = p.scale_log2e;
+                uint4 hi, lo;
+                tc_split2(a.x * s, a.y * s, hi.x, lo.x);
+                tc_split2(a.z * s, a.w * s, hi.y, lo.y);
+                tc_split2(b.x * s, b.y * s, hi.z, lo.z);
+                tc_split2(b.z * s, b.w * s, hi.w, lo.w);
+                const uint32_t off = tc_tile_offset(r, c);
+                *reinterpret_cast<uint4*>(sQh + off) = hi;
+                *reinterpret_cast<uint4*>(sQl + off) = lo;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
+            mbar_arrive(q_full);
+        }
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float acc[kTcTile];
 #pragma unroll
-    for (int d = 0; d < kTcTile; ++d) acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    bool ok = true;
-
-    for (int step = 0; step < n_prefix_tiles + n_text_tiles && ok; ++step) {
-        const bool text = step >= n_prefix_tiles;
-        const int t0 = text ? (text_tile0 + step - n_prefix_tiles) * kTcTile : step * kTcTile;
-        const uint32_t parity = (uint32_t)step & 1u;
-
-        // ---- stage K and V (128 keys x 256 B each) in the swizzled operand layout -------------------
-        for (int c = tid; c < kTcTile * 16; c += 128) {
-            const int key = c >> 4, ch = c & 15;
-            const int tok = t0 + key;
-            int blk = -1;
-            const uint8_t* kb = p.k_pool;
-            const uint8_t* vb = p.v_pool;
+        for (int d = 0; d < kTcTile; ++d) acc[d] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        bool ok = true;
+        int folded = 0;  // O_tiles folded into acc so far
+        for (int n = 0; n < n_steps; ++n) {
+            const int b = n & 1;
+            const uint32_t par = (uint32_t)(n >> 1) & 1u;
+            const bool text = n >= n_prefix_tiles;
+            const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
+            const int vlo = text ? tlo - t0 : -(1 << 30);
+            const int vhi = (text ? thi : phi) - t0;
+            // warp-uniform outcome: the TMEM instructions below need the whole warp
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tS = tmem + lane_base + b * 128;
+            float alpha;
+            if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
+                tc_softmax_tile<true>(tS, vlo, vhi, m_run, l_run, alpha);
+            else
+                tc_softmax_tile<false>(tS, vlo, vhi, m_run, l_run, alpha);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_full(b));
+            if (n >= 1) {  // fold the previous tile's product while the tensor core works on this one
+                const int k = n - 1;
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tc_fold(tmem + lane_base + 256 + (k & 1) * 128, alpha_prev, acc);
+                folded = n;
+            }
+            alpha_prev = alpha;
+        }
+        if (ok && folded < n_steps) {
+            const int k = n_steps - 1;
+            if (__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tc_fold(tmem + lane_base + 256 + (k & 1) * 128, alpha_prev, acc);
+            }
+        }
+        // ---- write the row; rows that attended nothing give zeros ------------------------------------
+        if (live) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            float* op = p.out + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
+#pragma unroll
+            for (int d = 0; d < kTcTile; d += 4)
+                *reinterpret_cast<float4*>(op + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+        }
+    } else if (warp == 4) {
+        // ================= producer warp: lane = (K|V, 64-dim half, block of the tile) ================
+        const int blk_i = lane & 7, half = (lane >> 3) & 1, is_v = lane >> 4;
+        const int prefix_blocks = (pfx + kBlockTokens - 1) / kBlockTokens;
+        const int pool_rows = p.num_blocks * p.kv_heads * kBlockTokens;
+        const int text_rows = p.text_blocks * p.kv_heads * kBlockTokens;
+        int issued = 0;
+        for (int n = 0; n < n_steps; ++n) {
+            const int b = n & 1;
+            if (n >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(kv_free(b), (uint32_t)((n >> 1) - 1) & 1u, p.status))) break;
+            const bool text = n >= n_prefix_tiles;
+            const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
+            const int idx = t0 / kBlockTokens + blk_i;  // block index within the request's region
+            int y;
+            const CUtensorMap* map;
             if (text) {
-                blk = t.block0 + tok / kBlockTokens;
-                if (blk >= p.text_blocks) blk = -1;
-                kb = p.k_text;
-                vb = p.v_text;
+                const int blk = t.block0 + idx;
+                y = blk < p.text_blocks ? (blk * p.kv_heads + kvh) * kBlockTokens : text_rows;
+                map = is_v ? &maps.tv : &maps.tk;
             } else {
-                const int idx = tok / kBlockTokens;
+                y = pool_rows;
                 if (idx < prefix_blocks && idx < p.table_stride) {
-                    blk = __ldg(p.table + (size_t)t.slot * p.table_stride + idx);
-                    if (blk < 0 || blk >= p.num_blocks) {
+                    const int blk = __ldg(p.table + (size_t)t.slot * p.table_stride + idx);
+                    if (blk < 0 || blk >= p.num_blocks)
                         atomicOr(p.status, kStatusBadBlock);
-                        blk = -1;
+                    else
+                        y = (blk * p.kv_heads + kvh) * kBlockTokens;
+                }
+                map = is_v ? &maps.v : &maps.k;
+            }
+            if (lane == 0) mbar_arrive_expect_tx(kv_full(b), kTcStageBytes);
+            __syncwarp();
+            const uint32_t dst = smem_addr(sKV) + b * kTcStageBytes + is_v * kTcTileBytes + half * kTcHalfBytes + blk_i * 2048;
+            tma_load_box(dst, map, half * 64, y, kv_full(b));
+            issued = n + 1;
+        }
+        // the last two stages may still be landing if a consumer gave up: wait for them before leaving
+        for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_bounded(kv_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status);
+    } else {
+        // ================= MMA warp: one thread issues every tensor-core instruction ==================
+        if (lane == 0) {
+            const uint32_t idesc_s = tc_instr_desc(false), idesc_o = tc_instr_desc(true);
+            const uint32_t aQ[2] = {smem_addr(sQh), smem_addr(sQl)};
+            auto issue_qk = [&](int n) {  // S[n & 1] = (Qhi + Qlo) K(n)^T
+                const uint32_t b0 = smem_addr(sKV) + (n & 1) * kTcStageBytes;
+#pragma unroll
+                for (int hq = 0; hq < 2; ++hq)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
+                        tc_mma(tmem + (n & 1) * 128, tc_smem_desc(aQ[hq] + koff, 16, 1024), tc_smem_desc(b0 + koff, 16, 1024),
+                               idesc_s, !(hq == 0 && j == 0));
                     }
+                tc_commit(s_full(n & 1));
+            };
+            bool ok = mbar_wait_bounded(q_full, 0, p.status);
+            for (int n = 0; n < n_steps && ok; ++n) {
+                if (n == 0) {
+                    if (!mbar_wait_bounded(kv_full(0), 0, p.status)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_qk(0);
                 }
-            }
-            uint4 kw = make_uint4(0, 0, 0, 0), vw = kw;
-            if (blk >= 0) {
-                const size_t src = ((((size_t)blk * p.kv_heads + kvh) * kBlockTokens + (tok & (kBlockTokens - 1))) * kTcTile) * 2 + ch * 16;
-                kw = __ldg(reinterpret_cast<const uint4*>(kb + src));
-                vw = __ldg(reinterpret_cast<const uint4*>(vb + src));
-            }
-            const uint32_t off = tc_tile_offset(key, ch);
-            *reinterpret_cast<uint4*>(sK + off) = kw;
-            *reinterpret_cast<uint4*>(sV + off) = vw;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
-        __syncthreads();
-
-        // ---- S = (Qhi + Qlo) K^T ------------------------------------------------------------------
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int hq = 0; hq < 2; ++hq) {
-                const uint32_t a0 = smem_addr(hq ? sQl : sQh), b0 = smem_addr(sK);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
-                    tc_mma(tmem, tc_smem_desc(a0 + koff, 16, 1024), tc_smem_desc(b0 + koff, 16, 1024), idesc_s,
-                           !(hq == 0 && j == 0));
+                if (n + 1 < n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
+                    if (!mbar_wait_bounded(kv_full((n + 1) & 1), (uint32_t)((n + 1) >> 1) & 1u, p.status)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_qk(n + 1);
                 }
+                if (!mbar_wait_bounded(p_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v0 = smem_addr(sKV) + (n & 1) * kTcStageBytes + kTcTileBytes;
+                const uint32_t tP = tmem + (n & 1) * 128, tO = tmem + 256 + (n & 1) * 128;
+#pragma unroll
+                for (int hp = 0; hp < 2; ++hp)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        // P: 16 keys = 8 TMEM columns; per 32-key chunk the hi words come first, then the lo words.
+                        // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
+                        tc_mma_ts(tO, tP + (j >> 1) * 32 + hp * 16 + (j & 1) * 8, tc_smem_desc(v0 + j * 2048, kTcHalfBytes, 1024),
+                                  idesc_o, !(hp == 0 && j == 0));
+                tc_commit(o_full(n & 1));
+                tc_commit(kv_free(n & 1));
             }
-            tc_commit(bar_s);
+            // every MMA issued above has finished before the TMEM is released
+            tc_commit(drained);
+            mbar_wait_bounded(drained, 0, p.status);
         }
-        if (!mbar_wait_bounded(bar_s, parity, p.status)) { ok = false; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-        // ---- softmax on this thread's row --------------------------------------------------------------
-        float alpha = 1.f, m_safe = 0.f;
-        if (ok) {
-            float mx = -INFINITY;
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                float v[32];
-                tc_ld32(tS + cc * 32, v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int tok = t0 + cc * 32 + j;
-                    const bool valid = text ? (tok >= tlo && tok < thi) : (tok < phi);
-                    if (valid) mx = fmaxf(mx, v[j]);
-                }
-            }
-            const float m_new = fmaxf(m_run, mx);
-            m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha = tc_exp2(m_run - m_safe);
-            float lsum = 0.f;
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                float v[32];
-                tc_ld32(tS + cc * 32, v);
-#pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {
-                    float pr[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int tok = t0 + cc * 32 + g8 * 8 + e;
-                        const bool valid = text ? (tok >= tlo && tok < thi) : (tok < phi);
-                        pr[e] = valid ? tc_exp2(v[g8 * 8 + e] - m_safe) : 0.f;
-                        lsum += pr[e];
-                    }
-                    uint4 hi, lo;
-                    tc_split8(pr, hi, lo);
-                    const uint32_t off = tc_tile_offset(r, cc * 4 + g8);
-                    *reinterpret_cast<uint4*>(sPh + off) = hi;
-                    *reinterpret_cast<uint4*>(sPl + off) = lo;
-                }
-            }
-            l_run = l_run * alpha + lsum;
-            m_run = m_new;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (!ok) break;  // `ok` can differ between threads only after a wait ran out: leave together below
-
-        // ---- O_tile = (Phi + Plo) V ------------------------------------------------------------------
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int hp = 0; hp < 2; ++hp) {
-                const uint32_t a0 = smem_addr(hp ? sPl : sPh), b0 = smem_addr(sV);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
-                    // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
-                    tc_mma(tmem + 128, tc_smem_desc(a0 + koff, 16, 1024), tc_smem_desc(b0 + j * 2048, kTcHalfBytes, 1024),
-                           idesc_o, !(hp == 0 && j == 0));
-                }
-            }
-            tc_commit(bar_o);
-        }
-        if (!mbar_wait_bounded(bar_o, parity, p.status)) { ok = false; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                float v[32];
-                tc_ld32(tO + cc * 32, v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(acc[cc * 32 + j], alpha, v[j]);
-            }
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // TMEM and the K/V/P tiles are free for the next step
+        __syncwarp();
     }
 
-    // ---- write the row; rows that attended nothing give zeros ------------------------------------------
-    if (live) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        float* op = p.out + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
-#pragma unroll
-        for (int d = 0; d < kTcTile; d += 4)
-            *reinterpret_cast<float4*>(op + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 5) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
