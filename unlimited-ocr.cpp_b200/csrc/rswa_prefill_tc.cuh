@@ -82,7 +82,8 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_byte_addr, uint32
     return d;
 }
 
-// Instruction descriptor, kind::f16: D fp32, A and B bf16, M = N = 128; B K-major or MN-major.
+// Instruction descriptor, kind::f16: D fp32, A and B bf16 (an fp16 A with a bf16 B raised an illegal
+// instruction on this part, so both operands keep the cache's type), M = N = 128; B K-major or MN-major.
 __device__ __forceinline__ uint32_t tc_instr_desc(bool b_mn_major) {
     uint32_t d = 0;
     d |= 1u << 4;              // D format: f32
@@ -131,22 +132,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // Truncating hi/lo split of two floats into packed bf16 pairs: hi keeps the top 16 bits, lo the top
 // 16 bits of the exact remainder, so hi + lo carries 16 mantissa bits of the input.
 __device__ __forceinline__ void tc_split2(float a, float b, uint32_t& hi, uint32_t& lo) {
@@ -183,62 +168,92 @@ struct PrefillMaps {
     CUtensorMap tk, tv;  // text pool, same shape with text_blocks
 };
 
-constexpr int kTcThreads = 192;  // warps 0-3 softmax, warp 4 producer, warp 5 MMA issue + TMEM owner
-constexpr int kTcSmemBytes = 6 * kTcTileBytes + 128 + 1024;  // Qhi Qlo K[2] V[2] + barriers + alignment slack
-constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;         // one K tile + one V tile
 
-// One key tile of the online softmax for this thread's row.  Reads S from TMEM twice (max, then
-// exponentials) and overwrites it chunk by chunk with P: per 32-key chunk, 16 words of hi pairs then
-// 16 words of lo pairs.  FULL: every key of the tile is visible to every row of the warp.
+constexpr int kTcSoftmaxThreads = 256;  // warps 0-7: warp w owns rows 32*(w%4).., key/dim half w/4
+constexpr int kTcThreads = 352;         // + warp 8 K producer, warp 9 MMA issue and TMEM owner, warp 10 V producer
+constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchange (double-buffered) + row-sum exchange
+constexpr int kTcSmemBytes = 6 * kTcTileBytes + 256 + kTcExchangeBytes + 1024;  // Qhi Qlo K[2] V[2], barriers, exchange, alignment slack
+constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;                            // one K tile + one V tile
+
+// 64 consecutive TMEM columns of this thread's lane into registers: two loads, one wait.  The wait
+// and the empty statement after it name the registers so that no use can be scheduled before them.
+#define UOCR_R32(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7]), \
+    "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]), "=r"(r[o + 12]), "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15]), \
+    "=r"(r[o + 16]), "=r"(r[o + 17]), "=r"(r[o + 18]), "=r"(r[o + 19]), "=r"(r[o + 20]), "=r"(r[o + 21]), "=r"(r[o + 22]), "=r"(r[o + 23]), \
+    "=r"(r[o + 24]), "=r"(r[o + 25]), "=r"(r[o + 26]), "=r"(r[o + 27]), "=r"(r[o + 28]), "=r"(r[o + 29]), "=r"(r[o + 30]), "=r"(r[o + 31])
+#define UOCR_RW32(r, o) "+r"(r[o + 0]), "+r"(r[o + 1]), "+r"(r[o + 2]), "+r"(r[o + 3]), "+r"(r[o + 4]), "+r"(r[o + 5]), "+r"(r[o + 6]), "+r"(r[o + 7]), \
+    "+r"(r[o + 8]), "+r"(r[o + 9]), "+r"(r[o + 10]), "+r"(r[o + 11]), "+r"(r[o + 12]), "+r"(r[o + 13]), "+r"(r[o + 14]), "+r"(r[o + 15]), \
+    "+r"(r[o + 16]), "+r"(r[o + 17]), "+r"(r[o + 18]), "+r"(r[o + 19]), "+r"(r[o + 20]), "+r"(r[o + 21]), "+r"(r[o + 22]), "+r"(r[o + 23]), \
+    "+r"(r[o + 24]), "+r"(r[o + 25]), "+r"(r[o + 26]), "+r"(r[o + 27]), "+r"(r[o + 28]), "+r"(r[o + 29]), "+r"(r[o + 30]), "+r"(r[o + 31])
+#define UOCR_LD32_ASM                                                                                          \
+    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                  \
+    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                   \
+    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(UOCR_LD32_ASM : UOCR_R32(r, 0) : "r"(taddr));
+    asm volatile(UOCR_LD32_ASM : UOCR_R32(r, 32) : "r"(taddr + 32));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : UOCR_RW32(r, 0) : : "memory");
+    asm volatile("" : UOCR_RW32(r, 32) : : "memory");
+}
+
+// Bounded rendezvous of the 64 threads that share a TMEM lane quadrant (one mbarrier phase per call).
+__device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t parity, int* status) {
+    mbar_arrive(bar);
+    return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
+}
+
+// One key tile of the online softmax for this thread: its row, its half (64 keys) of the tile.
+// Reads S once, agrees on the row maximum with the thread that owns the other half (shared-memory
+// exchange + a 64-thread rendezvous), writes P as bf16 pairs over its own 64 columns of the S buffer:
+// 32 words of hi pairs, then 32 words of lo pairs.  FULL: every key of the tile is visible to every row of the warp.  False if the rendezvous
+// ran out of time.
 template <bool FULL>
-__device__ __forceinline__ void tc_softmax_tile(uint32_t tS, int vlo, int vhi, float& m_run, float& l_run, float& alpha) {
+__device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
+                                                uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_run, float& l_run,
+                                                float& alpha) {
+    uint32_t s[64];
+    tc_ld64(tS + h * 64, s);
     float mx = -INFINITY;
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-        float v[32];
-        tc_ld32(tS + cc * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const int key = cc * 32 + j;
-            if (FULL || (key >= vlo && key < vhi)) mx = fmaxf(mx, v[j]);
-        }
+    for (int j = 0; j < 64; ++j) {
+        const int key = h * 64 + j;
+        if (FULL || (key >= vlo && key < vhi)) mx = fmaxf(mx, __uint_as_float(s[j]));
     }
-    const float m_new = fmaxf(m_run, mx);
+    *my_max = mx;
+    // also: both halves of S are in registers from here on, P may overwrite them
+    if (!pair_sync(pair_bar, pair_parity, status)) return false;
+    const float m_new = fmaxf(m_run, fmaxf(mx, *other_max));
     const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
     alpha = tc_exp2(m_run - m_safe);
     float lsum = 0.f;
+    uint32_t hi[32], lo[32];
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-        float v[32];
-        tc_ld32(tS + cc * 32, v);
-        uint32_t pk[32];
+    for (int e = 0; e < 32; ++e) {
+        float pr[2];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            float pr[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int key = cc * 32 + 2 * e + u;
-                const bool valid = FULL || (key >= vlo && key < vhi);
-                pr[u] = valid ? tc_exp2(v[2 * e + u] - m_safe) : 0.f;
-                lsum += pr[u];
-            }
-            tc_split2(pr[0], pr[1], pk[e], pk[16 + e]);
+        for (int u = 0; u < 2; ++u) {
+            const int key = h * 64 + 2 * e + u;
+            const bool valid = FULL || (key >= vlo && key < vhi);
+            pr[u] = valid ? tc_exp2(__uint_as_float(s[2 * e + u]) - m_safe) : 0.f;
+            lsum += pr[u];
         }
-        tc_st32(tS + cc * 32, pk);
+        tc_split2(pr[0], pr[1], hi[e], lo[e]);
     }
+    tc_st32(tS + h * 64, hi);
+    tc_st32(tS + h * 64 + 32, lo);
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     l_run = l_run * alpha + lsum;
     m_run = m_new;
+    return true;
 }
 
-__device__ __forceinline__ void tc_fold(uint32_t tO, float alpha, float (&acc)[kTcTile]) {
+// acc = acc * alpha + this thread's 64 dims of the O_tile in TMEM
+__device__ __forceinline__ void tc_fold(uint32_t tO, float alpha, float (&acc)[64]) {
+    uint32_t o[64];
+    tc_ld64(tO, o);
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-        float v[32];
-        tc_ld32(tO + cc * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = fmaf(acc[cc * 32 + j], alpha, v[j]);
-    }
+    for (int j = 0; j < 64; ++j) acc[j] = fmaf(acc[j], alpha, __uint_as_float(o[j]));
 }
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -249,15 +264,19 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     uint8_t* sQl = base + 1 * kTcTileBytes;
     uint8_t* sKV = base + 2 * kTcTileBytes;  // stage b: K at sKV + b * kTcStageBytes, V one tile after it
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTcTileBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    float* xmax = reinterpret_cast<float*>(base + 6 * kTcTileBytes + 256);  // [step parity][half][row]
+    float* xsum = xmax + 2 * 2 * 128;                                       // [half][row]
     const uint32_t bar0 = smem_addr(bars);
-    // barrier b of group g sits at bar0 + (2 * g + b) * 8
-    auto kv_full = [&](int b) { return bar0 + (0 + b) * 8; };  // TMA bytes of stage b have landed
-    auto kv_free = [&](int b) { return bar0 + (2 + b) * 8; };  // the MMAs reading stage b are done
+    auto k_full = [&](int b) { return bar0 + (0 + b) * 8; };   // TMA bytes of K stage b have landed
+    auto k_free = [&](int b) { return bar0 + (2 + b) * 8; };   // the S MMAs reading K stage b are done
+    auto v_full = [&](int b) { return bar0 + (16 + b) * 8; };  // same for V and the O MMAs
+    auto v_free = [&](int b) { return bar0 + (18 + b) * 8; };
     auto s_full = [&](int b) { return bar0 + (4 + b) * 8; };   // S buffer b holds Q K^T
-    auto p_full = [&](int b) { return bar0 + (6 + b) * 8; };   // all 128 rows wrote P over S buffer b
+    auto p_full = [&](int b) { return bar0 + (6 + b) * 8; };   // all 256 softmax threads wrote their P over S buffer b
     auto o_full = [&](int b) { return bar0 + (8 + b) * 8; };   // O_tile buffer b holds P V
     const uint32_t q_full = bar0 + 10 * 8, drained = bar0 + 11 * 8;
+    auto pair_bar = [&](int quad) { return bar0 + (12 + quad) * 8; };  // the two softmax warps of a lane quadrant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const PrefillTile t = p.tiles[blockIdx.x];
@@ -266,17 +285,21 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     if (tid == 0) {
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
-            mbar_init(kv_full(b), 1);
-            mbar_init(kv_free(b), 1);
+            mbar_init(k_full(b), 1);
+            mbar_init(k_free(b), 1);
+            mbar_init(v_full(b), 1);
+            mbar_init(v_free(b), 1);
             mbar_init(s_full(b), 1);
-            mbar_init(p_full(b), 128);
+            mbar_init(p_full(b), kTcSoftmaxThreads);
             mbar_init(o_full(b), 1);
         }
-        mbar_init(q_full, 128);
+        mbar_init(q_full, kTcSoftmaxThreads);
         mbar_init(drained, 1);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
         mbar_init_fence();
     }
-    if (warp == 5) {
+    if (warp == 9) {  // 512 TMEM columns: S/P buffers at 0 and 128, O_tile buffers at 256 and 384
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -296,9 +319,10 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     }
     const int n_steps = n_prefix_tiles + n_text_tiles;
 
-    if (warp < 4) {
-        // ================= softmax warps: thread r owns query row r ================================
-        const int r = tid;
+    if (warp < 8) {
+        // ================= softmax warps ==============================================================
+        const int quad = warp & 3, h = warp >> 2;  // TMEM lane quadrant; key half of S and dim half of O
+        const int r = quad * 32 + lane;            // query row of the tile == TMEM lane
         const bool live = r < t.rows;
         const int i = t.pos0 + r;
         const int phi = !live ? 0 : (t.kind == 0 ? min(i + 1, pfx) : pfx);  // fixed-region tokens [0, phi)
@@ -306,30 +330,30 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         const int thi = (live && t.kind == 1) ? i + 1 : 0;                   // text tokens [tlo, thi)
         {
             const float* qp = p.q + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
+            const float s = p.scale_log2e;
 #pragma unroll 4
-            for (int c = 0; c < 16; ++c) {
+            for (int c = h * 8; c < h * 8 + 8; ++c) {
                 float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
                 if (live) {
                     a = __ldg(reinterpret_cast<const float4*>(qp + c * 8));
                     b = __ldg(reinterpret_cast<const float4*>(qp + c * 8 + 4));
                 }
-                const float s = p.scale_log2e;
+                const uint32_t off = tc_tile_offset(r, c);
                 uint4 hi, lo;
                 tc_split2(a.x * s, a.y * s, hi.x, lo.x);
                 tc_split2(a.z * s, a.w * s, hi.y, lo.y);
                 tc_split2(b.x * s, b.y * s, hi.z, lo.z);
                 tc_split2(b.z * s, b.w * s, hi.w, lo.w);
-                const uint32_t off = tc_tile_offset(r, c);
                 *reinterpret_cast<uint4*>(sQh + off) = hi;
                 *reinterpret_cast<uint4*>(sQl + off) = lo;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
             mbar_arrive(q_full);
         }
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        float acc[kTcTile];
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        float acc[64];
 #pragma unroll
-        for (int d = 0; d < kTcTile; ++d) acc[d] = 0.f;
+        for (int d = 0; d < 64; ++d) acc[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
         bool ok = true;
         int folded = 0;  // O_tiles folded into acc so far
@@ -344,18 +368,21 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tS = tmem + lane_base + b * 128;
-            float alpha;
+            float* my_max = xmax + (b * 2 + h) * 128 + r;
+            const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
+            float alpha = 1.f;
             if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
-                tc_softmax_tile<true>(tS, vlo, vhi, m_run, l_run, alpha);
+                ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
             else
-                tc_softmax_tile<false>(tS, vlo, vhi, m_run, l_run, alpha);
+                ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
+            if (!ok) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full(b));
             if (n >= 1) {  // fold the previous tile's product while the tensor core works on this one
                 const int k = n - 1;
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tc_fold(tmem + lane_base + 256 + (k & 1) * 128, alpha_prev, acc);
+                tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
                 folded = n;
             }
             alpha_prev = alpha;
@@ -364,27 +391,35 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             const int k = n_steps - 1;
             if (__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tc_fold(tmem + lane_base + 256 + (k & 1) * 128, alpha_prev, acc);
+                tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
             }
         }
-        // ---- write the row; rows that attended nothing give zeros ------------------------------------
+        // ---- row sum over both key halves, then this thread's 64 dims of the row ------------------------
+        // (after a wait that ran out the partner warp may be elsewhere: no rendezvous then, zeros out)
+        xsum[h * 128 + r] = l_run;
+        if (ok) ok = pair_sync(pair_bar(quad), (uint32_t)n_steps & 1u, p.status);
+        const float l_tot = ok ? l_run + xsum[(h ^ 1) * 128 + r] : 0.f;
         if (live) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            float* op = p.out + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            float* op = p.out + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile + h * 64;
 #pragma unroll
-            for (int d = 0; d < kTcTile; d += 4)
+            for (int d = 0; d < 64; d += 4)
                 *reinterpret_cast<float4*>(op + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
         }
-    } else if (warp == 4) {
-        // ================= producer warp: lane = (K|V, 64-dim half, block of the tile) ================
-        const int blk_i = lane & 7, half = (lane >> 3) & 1, is_v = lane >> 4;
+    } else if (warp == 8 || warp == 10) {
+        // ================= producer warps: warp 8 feeds K, warp 10 feeds V ============================
+        // lane = (64-dim half, block of the tile); K runs further ahead than V because its stage is
+        // free again as soon as the S product has read it.
+        const int is_v = warp == 10 ? 1 : 0;
+        const int blk_i = lane & 7, half = (lane >> 3) & 1;
         const int prefix_blocks = (pfx + kBlockTokens - 1) / kBlockTokens;
         const int pool_rows = p.num_blocks * p.kv_heads * kBlockTokens;
         const int text_rows = p.text_blocks * p.kv_heads * kBlockTokens;
         int issued = 0;
         for (int n = 0; n < n_steps; ++n) {
             const int b = n & 1;
-            if (n >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(kv_free(b), (uint32_t)((n >> 1) - 1) & 1u, p.status))) break;
+            const uint32_t full = is_v ? v_full(b) : k_full(b), freed = is_v ? v_free(b) : k_free(b);
+            if (n >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(freed, (uint32_t)((n >> 1) - 1) & 1u, p.status))) break;
             const bool text = n >= n_prefix_tiles;
             const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
             const int idx = t0 / kBlockTokens + blk_i;  // block index within the request's region
@@ -405,20 +440,21 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 }
                 map = is_v ? &maps.v : &maps.k;
             }
-            if (lane == 0) mbar_arrive_expect_tx(kv_full(b), kTcStageBytes);
+            if (lane == 0) mbar_arrive_expect_tx(full, kTcTileBytes);
             __syncwarp();
             const uint32_t dst = smem_addr(sKV) + b * kTcStageBytes + is_v * kTcTileBytes + half * kTcHalfBytes + blk_i * 2048;
-            tma_load_box(dst, map, half * 64, y, kv_full(b));
+            if (lane < 16) tma_load_box(dst, map, half * 64, y, full);
             issued = n + 1;
         }
         // the last two stages may still be landing if a consumer gave up: wait for them before leaving
-        for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_bounded(kv_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status);
+        for (int n = max(0, issued - 2); n < issued; ++n)
+            mbar_wait_bounded(is_v ? v_full(n & 1) : k_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status);
     } else {
         // ================= MMA warp: one thread issues every tensor-core instruction ==================
         if (lane == 0) {
             const uint32_t idesc_s = tc_instr_desc(false), idesc_o = tc_instr_desc(true);
             const uint32_t aQ[2] = {smem_addr(sQh), smem_addr(sQl)};
-            auto issue_qk = [&](int n) {  // S[n & 1] = (Qhi + Qlo) K(n)^T
+            auto issue_qk = [&](int n) {  // S[n & 1] = Q K(n)^T
                 const uint32_t b0 = smem_addr(sKV) + (n & 1) * kTcStageBytes;
 #pragma unroll
                 for (int hq = 0; hq < 2; ++hq)
@@ -429,19 +465,21 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                                idesc_s, !(hq == 0 && j == 0));
                     }
                 tc_commit(s_full(n & 1));
+                tc_commit(k_free(n & 1));
             };
             bool ok = mbar_wait_bounded(q_full, 0, p.status);
             for (int n = 0; n < n_steps && ok; ++n) {
                 if (n == 0) {
-                    if (!mbar_wait_bounded(kv_full(0), 0, p.status)) { ok = false; break; }
+                    if (!mbar_wait_bounded(k_full(0), 0, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_qk(0);
                 }
                 if (n + 1 < n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
-                    if (!mbar_wait_bounded(kv_full((n + 1) & 1), (uint32_t)((n + 1) >> 1) & 1u, p.status)) { ok = false; break; }
+                    if (!mbar_wait_bounded(k_full((n + 1) & 1), (uint32_t)((n + 1) >> 1) & 1u, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_qk(n + 1);
                 }
+                if (!mbar_wait_bounded(v_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
                 if (!mbar_wait_bounded(p_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v0 = smem_addr(sKV) + (n & 1) * kTcStageBytes + kTcTileBytes;
@@ -450,12 +488,12 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 for (int hp = 0; hp < 2; ++hp)
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        // P: 16 keys = 8 TMEM columns; per 32-key chunk the hi words come first, then the lo words.
+                        // P: 16 keys = 8 TMEM columns per MMA; each 64-key half holds its hi words, then its lo words.
                         // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
-                        tc_mma_ts(tO, tP + (j >> 1) * 32 + hp * 16 + (j & 1) * 8, tc_smem_desc(v0 + j * 2048, kTcHalfBytes, 1024),
+                        tc_mma_ts(tO, tP + (j >> 2) * 64 + hp * 32 + (j & 3) * 8, tc_smem_desc(v0 + j * 2048, kTcHalfBytes, 1024),
                                   idesc_o, !(hp == 0 && j == 0));
                 tc_commit(o_full(n & 1));
-                tc_commit(kv_free(n & 1));
+                tc_commit(v_free(n & 1));
             }
             // every MMA issued above has finished before the TMEM is released
             tc_commit(drained);
@@ -466,7 +504,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
