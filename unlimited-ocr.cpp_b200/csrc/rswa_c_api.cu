@@ -4,10 +4,12 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "rswa_attention.cuh"
 #include "rswa_copy.cuh"
@@ -742,7 +744,19 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     if (int rc = device_info(&di)) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     static_assert(sizeof(uocr_b200_prefill_tile) == sizeof(PrefillTile), "tile descriptor layouts must match");
-    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, h_tiles, sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
+    // Longest tiles first: CTAs are handed out in index order, so the short ones fill the tail.  The
+    // prefix length lives on the device; its share of a text tile's work is taken as the same for all.
+    std::vector<uocr_b200_prefill_tile> order(h_tiles, h_tiles + n_tiles);
+    auto key_tiles = [window](const uocr_b200_prefill_tile& t) {
+        const int last = t.pos0 + t.rows - 1;
+        if (t.kind == 0) return last / kTcTile + 1;
+        const int first = t.pos0 - window + 1 > 0 ? t.pos0 - window + 1 : 0;
+        return 9 + last / kTcTile - first / kTcTile + 1;
+    };
+    std::stable_sort(order.begin(), order.end(),
+                     [&](const uocr_b200_prefill_tile& a, const uocr_b200_prefill_tile& b) { return key_tiles(a) > key_tiles(b); });
+    // pageable source: the copy has read `order` when the call returns
+    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, order.data(), sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
                "tile descriptors H2D");
     PrefillParams pp{};
     pp.q = q;
@@ -925,6 +939,20 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_prefill_len = d_prefill_len;
     return run_attention(c, &view, st);
 }
+
+#ifdef UOCR_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_tc_trace(unsigned long long* out, int n) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_tc_trace, sizeof(unsigned long long) * n);
+}
+#endif
+
+#ifdef UOCR_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_tc_cta_trace(unsigned long long* out, int n) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_tc_cta, sizeof(unsigned long long) * n);
+}
+#endif
 
 #ifdef UOCR_TRACE
 extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_trace(unsigned long long* out, int n) {

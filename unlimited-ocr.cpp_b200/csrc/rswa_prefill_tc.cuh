@@ -95,25 +95,26 @@ __device__ __forceinline__ uint32_t tc_instr_desc(bool b_mn_major) {
     return d;
 }
 
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
-    const uint32_t acc = accumulate ? 1u : 0u;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u)
-        : "memory");
+// D[tmem_d] (+)= A * B with both operands in shared memory.  ACC false overwrites D.
+template <bool ACC>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    if (ACC)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
 }
 
 // A operand from TMEM (lane = row, two bf16 per 32-bit column), B from shared memory.
-__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
-    const uint32_t acc = accumulate ? 1u : 0u;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u)
-        : "memory");
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+    if (ACC)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                     ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                     ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc) : "memory");
 }
 
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -175,6 +176,37 @@ constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchan
 constexpr int kTcSmemBytes = 6 * kTcTileBytes + 256 + kTcExchangeBytes + 1024;  // Qhi Qlo K[2] V[2], barriers, exchange, alignment slack
 constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;                            // one K tile + one V tile
 
+// Optional timeline of the first CTAs (cycle stamps per key tile and role), compiled in with -DUOCR_TC_TRACE.
+#ifdef UOCR_TC_TRACE
+#ifndef UOCR_TC_TRACE_FIRST
+#define UOCR_TC_TRACE_FIRST 0  // first traced query tile (blockIdx.x), head 0
+#endif
+constexpr int kTcTraceCtas = 64, kTcTraceSteps = 24, kTcTraceSlots = 16;
+__device__ unsigned long long g_tc_trace[kTcTraceCtas * kTcTraceSteps * kTcTraceSlots];
+__device__ __forceinline__ void tc_trace(int step, int slot) {
+    const int cta = (int)blockIdx.x - UOCR_TC_TRACE_FIRST;
+    if (blockIdx.y == 0 && cta >= 0 && cta < kTcTraceCtas && step < kTcTraceSteps)
+        g_tc_trace[(cta * kTcTraceSteps + step) * kTcTraceSlots + slot] = clock64();
+}
+#define TC_TRACE(cond, step, slot) do { if (cond) tc_trace(step, slot); } while (0)
+// per CTA: start and end (global nanosecond timer), SM id, key tiles walked
+constexpr int kTcTraceCtaRows = 8192;
+__device__ unsigned long long g_tc_cta[kTcTraceCtaRows * 8];
+__device__ __forceinline__ void tc_trace_cta(int field, unsigned long long v) {
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta < kTcTraceCtaRows) g_tc_cta[cta * 8 + field] = v;
+}
+__device__ __forceinline__ unsigned long long tc_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TC_TRACE_CTA(field, value) do { if (threadIdx.x == 0) tc_trace_cta(field, value); } while (0)
+#else
+#define TC_TRACE(cond, step, slot) do { } while (0)
+#define TC_TRACE_CTA(field, value) do { } while (0)
+#endif
+
 // 64 consecutive TMEM columns of this thread's lane into registers: two loads, one wait.  The wait
 // and the empty statement after it name the registers so that no use can be scheduled before them.
 #define UOCR_R32(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7]), \
@@ -203,6 +235,12 @@ __device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t parity, int* st
     return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
 }
 
+// Bounded rendezvous of all softmax threads (one mbarrier phase per call).
+__device__ __forceinline__ bool softmax_sync(uint32_t bar, uint32_t parity, int* status) {
+    mbar_arrive(bar);
+    return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
+}
+
 // One key tile of the online softmax for this thread: its row, its half (64 keys) of the tile.
 // Reads S once, agrees on the row maximum with the thread that owns the other half (shared-memory
 // exchange + a 64-thread rendezvous), writes P as bf16 pairs over its own 64 columns of the S buffer:
@@ -211,9 +249,10 @@ __device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t parity, int* st
 template <bool FULL>
 __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
                                                 uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_run, float& l_run,
-                                                float& alpha) {
+                                                float& alpha, int tstep) {
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
+    TC_TRACE(tstep >= 0, tstep, 2);
     float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < 64; ++j) {
@@ -223,6 +262,7 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     *my_max = mx;
     // also: both halves of S are in registers from here on, P may overwrite them
     if (!pair_sync(pair_bar, pair_parity, status)) return false;
+    TC_TRACE(tstep >= 0, tstep, 3);
     const float m_new = fmaxf(m_run, fmaxf(mx, *other_max));
     const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
     alpha = tc_exp2(m_run - m_safe);
@@ -243,6 +283,7 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     tc_st32(tS + h * 64, hi);
     tc_st32(tS + h * 64 + 32, lo);
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    TC_TRACE(tstep >= 0, tstep, 4);
     l_run = l_run * alpha + lsum;
     m_run = m_new;
     return true;
@@ -264,7 +305,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     uint8_t* sQl = base + 1 * kTcTileBytes;
     uint8_t* sKV = base + 2 * kTcTileBytes;  // stage b: K at sKV + b * kTcStageBytes, V one tile after it
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTcTileBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
     float* xmax = reinterpret_cast<float*>(base + 6 * kTcTileBytes + 256);  // [step parity][half][row]
     float* xsum = xmax + 2 * 2 * 128;                                       // [half][row]
     const uint32_t bar0 = smem_addr(bars);
@@ -281,6 +322,14 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const PrefillTile t = p.tiles[blockIdx.x];
     const int head = blockIdx.y, kvh = head / p.group;
+#ifdef UOCR_TC_TRACE
+    TC_TRACE_CTA(0, tc_globaltimer());
+    {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        TC_TRACE_CTA(2, smid);
+    }
+#endif
 
     if (tid == 0) {
 #pragma unroll
@@ -297,6 +346,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         mbar_init(drained, 1);
 #pragma unroll
         for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
+        mbar_init(bar0 + 20 * 8, kTcSoftmaxThreads);  // output rows staged in shared memory
         mbar_init_fence();
     }
     if (warp == 9) {  // 512 TMEM columns: S/P buffers at 0 and 128, O_tile buffers at 256 and 384
@@ -307,6 +357,9 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+#ifdef UOCR_TC_TRACE
+    TC_TRACE_CTA(4, tc_globaltimer());
+#endif
 
     // ---- key tiles this query tile can see (uniform over the CTA) ------------------------------------
     const int pfx = max(p.d_prefill_len[t.slot], 0);
@@ -329,26 +382,32 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         const int tlo = max(0, i - p.window + 1);
         const int thi = (live && t.kind == 1) ? i + 1 : 0;                   // text tokens [tlo, thi)
         {
-            const float* qp = p.q + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile;
+            // Q tile -> bf16 hi/lo operand tiles.  Warp w stages rows 16w..16w+15; a row (512 B) is one
+            // coalesced request of the warp, lane l holding dims 4l..4l+3, and all 16 rows are in flight
+            // together.  The 8-byte hi and lo words land in the swizzled operand layout.
             const float s = p.scale_log2e;
-#pragma unroll 4
-            for (int c = h * 8; c < h * 8 + 8; ++c) {
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                if (live) {
-                    a = __ldg(reinterpret_cast<const float4*>(qp + c * 8));
-                    b = __ldg(reinterpret_cast<const float4*>(qp + c * 8 + 4));
-                }
-                const uint32_t off = tc_tile_offset(r, c);
-                uint4 hi, lo;
-                tc_split2(a.x * s, a.y * s, hi.x, lo.x);
-                tc_split2(a.z * s, a.w * s, hi.y, lo.y);
-                tc_split2(b.x * s, b.y * s, hi.z, lo.z);
-                tc_split2(b.z * s, b.w * s, hi.w, lo.w);
-                *reinterpret_cast<uint4*>(sQh + off) = hi;
-                *reinterpret_cast<uint4*>(sQl + off) = lo;
+            float4 qv[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int row = warp * 16 + k;
+                qv[k] = row < t.rows ? __ldg(reinterpret_cast<const float4*>(p.q + ((size_t)(t.row0 + row) * p.heads + head) * kTcTile) + lane)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int row = warp * 16 + k;
+                uint2 hi, lo;
+                tc_split2(qv[k].x * s, qv[k].y * s, hi.x, lo.x);
+                tc_split2(qv[k].z * s, qv[k].w * s, hi.y, lo.y);
+                const uint32_t off = tc_tile_offset(row, lane >> 1) + (lane & 1) * 8;
+                *reinterpret_cast<uint2*>(sQh + off) = hi;
+                *reinterpret_cast<uint2*>(sQl + off) = lo;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
             mbar_arrive(q_full);
+#ifdef UOCR_TC_TRACE
+            TC_TRACE_CTA(5, tc_globaltimer());
+#endif
         }
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         float acc[64];
@@ -364,17 +423,20 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
             const int vlo = text ? tlo - t0 : -(1 << 30);
             const int vhi = (text ? thi : phi) - t0;
+            const int tstep = tid == 0 ? n : -1;
+            TC_TRACE(tstep >= 0, tstep, 0);
             // warp-uniform outcome: the TMEM instructions below need the whole warp
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_TRACE(tstep >= 0, tstep, 1);
             const uint32_t tS = tmem + lane_base + b * 128;
             float* my_max = xmax + (b * 2 + h) * 128 + r;
             const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
             float alpha = 1.f;
             if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
-                ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
+                ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha, tstep);
             else
-                ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
+                ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha, tstep);
             if (!ok) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full(b));
@@ -382,8 +444,10 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 const int k = n - 1;
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                TC_TRACE(tstep >= 0, tstep, 5);
                 tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
                 folded = n;
+                TC_TRACE(tstep >= 0, tstep, 6);
             }
             alpha_prev = alpha;
         }
@@ -394,18 +458,38 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
             }
         }
+#ifdef UOCR_TC_TRACE
+        TC_TRACE_CTA(6, tc_globaltimer());
+#endif
         // ---- row sum over both key halves, then this thread's 64 dims of the row ------------------------
         // (after a wait that ran out the partner warp may be elsewhere: no rendezvous then, zeros out)
         xsum[h * 128 + r] = l_run;
         if (ok) ok = pair_sync(pair_bar(quad), (uint32_t)n_steps & 1u, p.status);
         const float l_tot = ok ? l_run + xsum[(h ^ 1) * 128 + r] : 0.f;
-        if (live) {
+        // The row goes out through shared memory (the K/V ring is idle now: every MMA has completed and
+        // every load was consumed) so that each warp writes whole 512-byte rows.  16-byte chunk c of row
+        // r sits at chunk c ^ (r % 32): conflict-free both for the row-owning writer and the row-wide reader.
+        {
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            float* op = p.out + ((size_t)(t.row0 + r) * p.heads + head) * kTcTile + h * 64;
+            float4* so = reinterpret_cast<float4*>(sKV);
 #pragma unroll
-            for (int d = 0; d < 64; d += 4)
-                *reinterpret_cast<float4*>(op + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+            for (int c = 0; c < 16; ++c)
+                so[r * 32 + ((h * 16 + c) ^ (r & 31))] =
+                    make_float4(acc[4 * c] * inv, acc[4 * c + 1] * inv, acc[4 * c + 2] * inv, acc[4 * c + 3] * inv);
+            if (ok) ok = softmax_sync(bar0 + 20 * 8, 0, p.status);
+            if (ok) {
+#pragma unroll 4
+                for (int k = 0; k < 16; ++k) {
+                    const int row = warp * 16 + k;
+                    if (row < t.rows)
+                        reinterpret_cast<float4*>(p.out + ((size_t)(t.row0 + row) * p.heads + head) * kTcTile)[lane] =
+                            so[row * 32 + (lane ^ (row & 31))];
+                }
+            }
         }
+#ifdef UOCR_TC_TRACE
+        TC_TRACE_CTA(7, tc_globaltimer());
+#endif
     } else if (warp == 8 || warp == 10) {
         // ================= producer warps: warp 8 feeds K, warp 10 feeds V ============================
         // lane = (64-dim half, block of the tile); K runs further ahead than V because its stage is
@@ -440,6 +524,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 }
                 map = is_v ? &maps.v : &maps.k;
             }
+            TC_TRACE(lane == 0, n, 14 + is_v);
             if (lane == 0) mbar_arrive_expect_tx(full, kTcTileBytes);
             __syncwarp();
             const uint32_t dst = smem_addr(sKV) + b * kTcStageBytes + is_v * kTcTileBytes + half * kTcHalfBytes + blk_i * 2048;
@@ -453,22 +538,31 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         // ================= MMA warp: one thread issues every tensor-core instruction ==================
         if (lane == 0) {
             const uint32_t idesc_s = tc_instr_desc(false), idesc_o = tc_instr_desc(true);
-            const uint32_t aQ[2] = {smem_addr(sQh), smem_addr(sQl)};
-            auto issue_qk = [&](int n) {  // S[n & 1] = Q K(n)^T
-                const uint32_t b0 = smem_addr(sKV) + (n & 1) * kTcStageBytes;
+            // Every operand descriptor is fixed for the CTA's lifetime except for the stage (0/1) of
+            // K and V, which only moves the address field: build them once, so that one MMA costs the
+            // issuing thread one instruction and a 32-bit add.
+            uint64_t dQ[16], dK[8], dV[8];
 #pragma unroll
-                for (int hq = 0; hq < 2; ++hq)
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
+                dQ[j] = tc_smem_desc(smem_addr(sQh) + koff, 16, 1024);
+                dQ[8 + j] = tc_smem_desc(smem_addr(sQl) + koff, 16, 1024);
+                dK[j] = tc_smem_desc(smem_addr(sKV) + koff, 16, 1024);
+                // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
+                dV[j] = tc_smem_desc(smem_addr(sKV) + kTcTileBytes + j * 2048, kTcHalfBytes, 1024);
+            }
+            auto issue_qk = [&](int n) {  // S[n & 1] = (Qhi + Qlo) K(n)^T
+                const uint64_t stage = (uint64_t)((n & 1) * (kTcStageBytes >> 4));  // address field counts 16-byte units
+                const uint32_t tS = tmem + (n & 1) * 128;
+                tc_mma<false>(tS, dQ[0], dK[0] + stage, idesc_s);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
-                        tc_mma(tmem + (n & 1) * 128, tc_smem_desc(aQ[hq] + koff, 16, 1024), tc_smem_desc(b0 + koff, 16, 1024),
-                               idesc_s, !(hq == 0 && j == 0));
-                    }
+                for (int j = 1; j < 16; ++j) tc_mma<true>(tS, dQ[j], dK[j & 7] + stage, idesc_s);
                 tc_commit(s_full(n & 1));
                 tc_commit(k_free(n & 1));
             };
             bool ok = mbar_wait_bounded(q_full, 0, p.status);
             for (int n = 0; n < n_steps && ok; ++n) {
+                TC_TRACE(true, n, 8);
                 if (n == 0) {
                     if (!mbar_wait_bounded(k_full(0), 0, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -477,23 +571,27 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 if (n + 1 < n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
                     if (!mbar_wait_bounded(k_full((n + 1) & 1), (uint32_t)((n + 1) >> 1) & 1u, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    TC_TRACE(true, n, 9);
                     issue_qk(n + 1);
+                    TC_TRACE(true, n, 10);
                 }
                 if (!mbar_wait_bounded(v_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
+                TC_TRACE(true, n, 11);
                 if (!mbar_wait_bounded(p_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v0 = smem_addr(sKV) + (n & 1) * kTcStageBytes + kTcTileBytes;
+                TC_TRACE(true, n, 12);
+                const uint64_t stage = (uint64_t)((n & 1) * (kTcStageBytes >> 4));
                 const uint32_t tP = tmem + (n & 1) * 128, tO = tmem + 256 + (n & 1) * 128;
+                // P: 16 keys = 8 TMEM columns per MMA; each 64-key half holds its hi words, then its lo words.
+                tc_mma_ts<false>(tO, tP, dV[0] + stage, idesc_o);
 #pragma unroll
-                for (int hp = 0; hp < 2; ++hp)
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        // P: 16 keys = 8 TMEM columns per MMA; each 64-key half holds its hi words, then its lo words.
-                        // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
-                        tc_mma_ts(tO, tP + (j >> 2) * 64 + hp * 32 + (j & 3) * 8, tc_smem_desc(v0 + j * 2048, kTcHalfBytes, 1024),
-                                  idesc_o, !(hp == 0 && j == 0));
+                for (int u = 1; u < 16; ++u) {
+                    const int hp = u >> 3, j = u & 7;
+                    tc_mma_ts<true>(tO, tP + (j >> 2) * 64 + hp * 32 + (j & 3) * 8, dV[j] + stage, idesc_o);
+                }
                 tc_commit(o_full(n & 1));
                 tc_commit(v_free(n & 1));
+                TC_TRACE(true, n, 13);
             }
             // every MMA issued above has finished before the TMEM is released
             tc_commit(drained);
@@ -504,6 +602,10 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+#ifdef UOCR_TC_TRACE
+    TC_TRACE_CTA(1, tc_globaltimer());
+    TC_TRACE_CTA(3, (unsigned long long)n_steps);
+#endif
     if (warp == 9) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
