@@ -332,6 +332,96 @@ static void test_paged_batch_kv() {
     for (int s = 0; s < 4; ++s) orc_cache_destroy(o[s]);
 }
 
+// ---- windowed ragged prefill through the host class: oracle by composition of reference calls ----------
+static void test_windowed_prefill(bool tensor_cores) {
+    std::printf("cuda::PagedBatchKV windowed prefill (%s)\n", tensor_cores ? "tcgen05 path" : "CUDA-core path");
+    cuda::PagedBatchKV kv;
+    cuda::PagedBatchKV::Config cfg;
+    cfg.slots = 3; cfg.layers = 2; cfg.kv_heads = 2; cfg.dtype = DType::BF16;
+    cfg.head_dim = tensor_cores ? 128 : 16;
+    cfg.window = tensor_cores ? 160 : 16;
+    cfg.max_prefix_tokens = tensor_cores ? 200 : 40;
+    cfg.prefix_arena_blocks = 32; cfg.ring_arena_blocks = 3 * ((cfg.window + 15) / 16);
+    kv.configure(cfg);
+    const int heads = 4, row = cfg.kv_heads * cfg.head_dim, qrow = heads * cfg.head_dim;
+    const int cap = cfg.max_prefix_tokens + cfg.window;
+    // slot 2 and slot 0 share document A (slot 2 prefills it); slot 1 has its own; text shorter and longer than W
+    const int P[3] = {tensor_cores ? 150 : 33, tensor_cores ? 200 : 16, tensor_cores ? 150 : 33};
+    const int T[3] = {tensor_cores ? 70 : 9, tensor_cores ? 300 : 37, tensor_cores ? 401 : 50};
+    const char* keys[3] = {"docA", "docB", "docA"};
+    const int order[3] = {2, 1, 0};
+    std::vector<cuda::PagedBatchKV::WindowedPrefill> reqs;
+    for (int i = 0; i < 3; ++i) {
+        const int sl = order[i];
+        auto a = kv.admit(sl, keys[sl], P[sl]);
+        reqs.push_back({sl, a.prefix_is_new ? P[sl] : 0, T[sl]});
+    }
+    EXPECT(reqs[0].vision_rows == P[2] && reqs[1].vision_rows == P[1] && reqs[2].vision_rows == 0);
+    const int total = kv.plan_windowed_prefill(reqs);
+    int nv = 0, nt = 0;
+    for (auto& r : reqs) { nv += r.vision_rows; nt += r.text_rows; }
+    EXPECT(total == nv + nt);
+    auto round = [](std::vector<float> v) { for (auto& x : v) x = bf16_to_f32(f32_to_bf16(x)); return v; };
+    orc_cache* o[3];
+    for (int sl = 0; sl < 3; ++sl) {
+        o[sl] = orc_cache_create(cfg.layers, cfg.kv_heads, cfg.head_dim, cfg.window);
+        orc_cache_reset(o[sl], P[sl]);
+    }
+    float *dq, *dk, *dv, *dout;
+    cudaMalloc(&dq, (size_t)total * qrow * 4); cudaMalloc(&dout, (size_t)total * qrow * 4);
+    cudaMalloc(&dk, (size_t)total * row * 4); cudaMalloc(&dv, (size_t)total * row * 4);
+    float worst = 0.f;
+    for (int l = 0; l < cfg.layers; ++l) {
+        auto q = rvec((size_t)total * qrow), k = round(rvec((size_t)total * row)), v = round(rvec((size_t)total * row));
+        cudaMemcpy(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemset(dout, 0xff, (size_t)total * qrow * 4);
+        kv.windowed_prefill_layer(l, dq, dk, dv, heads, dout);
+        auto got = host(dout, (size_t)total * qrow);
+        // oracle: vision rows causal over the prefix (the sharing slot gets the same prefix without queries)
+        std::vector<float> want((size_t)total * qrow, 0.f);
+        int at = 0;
+        for (auto& r : reqs) {
+            if (r.vision_rows == 0) continue;
+            for (int sl = 0; sl < 3; ++sl)
+                if (std::string(keys[sl]) == keys[r.slot])
+                    orc_cache_write_prefill(o[sl], l, k.data() + (size_t)at * row, v.data() + (size_t)at * row, r.vision_rows);
+            orc_cache_attention(o[r.slot], l, q.data() + (size_t)at * qrow, r.vision_rows, 0, want.data() + (size_t)at * qrow, heads, 1);
+            at += r.vision_rows;
+        }
+        for (auto& r : reqs) {  // text rows: append, then attend everything cached
+            for (int i = 0; i < r.text_rows; ++i, ++at) {
+                orc_cache_append_decode(o[r.slot], l, k.data() + (size_t)at * row, v.data() + (size_t)at * row);
+                orc_cache_attention(o[r.slot], l, q.data() + (size_t)at * qrow, 1, orc_cache_len(o[r.slot], l) - 1,
+                                    want.data() + (size_t)at * qrow, heads, 0);
+            }
+        }
+        worst = std::max(worst, max_abs_diff(want, got.data()));
+    }
+    std::printf("  max abs difference %.3g\n", worst);
+    EXPECT(worst < (tensor_cores ? 2e-4f : 2e-5f));
+    // cursors and logical cache contents are those of the appends, bit for bit
+    std::vector<int> ident = {0, 1, 2};
+    int* d_ident = dev(ident);
+    float *gk, *gv;
+    cudaMalloc(&gk, (size_t)3 * cap * row * 4); cudaMalloc(&gv, (size_t)3 * cap * row * 4);
+    for (int l = 0; l < cfg.layers; ++l) {
+        kv.gather(l, d_ident, 3, gk, gv);
+        auto hk = host(gk, (size_t)3 * cap * row), hv = host(gv, (size_t)3 * cap * row);
+        auto dl = host(kv.d_len(l), 3), dr = host(kv.d_ring_pos(l), 3);
+        for (int sl = 0; sl < 3; ++sl) {
+            const size_t n = (size_t)orc_cache_len(o[sl], l) * row;
+            EXPECT(dl[sl] == orc_cache_len(o[sl], l) && dr[sl] == orc_cache_ring_pos(o[sl], l));
+            EXPECT(std::memcmp(hk.data() + (size_t)sl * cap * row, orc_cache_keys(o[sl], l), n * 4) == 0);
+            EXPECT(std::memcmp(hv.data() + (size_t)sl * cap * row, orc_cache_values(o[sl], l), n * 4) == 0);
+        }
+    }
+    EXPECT(kv.device_status() == 0);
+    for (int sl = 0; sl < 3; ++sl) orc_cache_destroy(o[sl]);
+    cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dout); cudaFree(gk); cudaFree(gv); cudaFree(d_ident);
+}
+
 int main() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -343,6 +433,8 @@ int main() {
         test_gpu_cache_device_interface();
         test_free_functions_reference_layout();
         test_paged_batch_kv();
+        test_windowed_prefill(false);
+        test_windowed_prefill(true);
     } catch (const std::exception& e) {
         std::printf("  EXCEPTION: %s\n", e.what());
         ++g_fail;

@@ -815,6 +815,14 @@ struct PagedBatchKV::Impl {
     };
     std::vector<SlotState> slot;
     std::vector<std::vector<int>> rows;  // host copy of the table
+    // windowed prefill plan (plan_windowed_prefill): text pool shared by all layers, row index arrays
+    void* text_k = nullptr;
+    void* text_v = nullptr;
+    int text_blocks_cap = 0, text_blocks = 0;
+    int* d_pf = nullptr;  // [v_slots nv][v_pos nv][t_slots nt][t_pos nt][t_block0 nt][t_len nt]
+    int pf_cap = 0, pf_nv = 0, pf_nt = 0;
+    std::vector<uocr_b200_prefill_tile> pf_tiles;
+    int ws_rows = 0;
 
     std::size_t block_bytes() const {
         return static_cast<std::size_t>(cfg.kv_heads) * UOCR_B200_BLOCK_TOKENS * cfg.head_dim *
@@ -831,6 +839,13 @@ struct PagedBatchKV::Impl {
         if (d_prefill) cudaFree(d_prefill);
         if (d_state_stage) cudaFree(d_state_stage);
         if (h_state_stage) cudaFreeHost(h_state_stage);
+        if (text_k) cudaFree(text_k);
+        if (text_v) cudaFree(text_v);
+        if (d_pf) cudaFree(d_pf);
+        text_k = text_v = nullptr;
+        d_pf = nullptr;
+        text_blocks_cap = text_blocks = pf_cap = pf_nv = pf_nt = 0;
+        pf_tiles.clear();
         d_table = nullptr; d_len = d_ring = d_prefill = d_state_stage = nullptr; h_state_stage = nullptr;
         if (ws) uocr_b200_workspace_destroy(ws);
         ws = nullptr;
@@ -875,7 +890,8 @@ bool PagedBatchKV::configure(const Config& c) {
         cuda_ok(cudaMalloc(&s.d_ring, sizeof(int) * c.layers * c.slots), "batch ring");
         cuda_ok(cudaMalloc(&s.d_prefill, sizeof(int) * c.slots), "batch prefill");
         cuda_ok(cudaMallocHost(&s.h_state_stage, sizeof(int) * (2 * c.layers + s.stride)), "state stage");
-        abi_ok(uocr_b200_workspace_create(std::max(c.slots, 4096), &s.ws), "batch workspace");
+        s.ws_rows = std::max(c.slots, 4096);
+        abi_ok(uocr_b200_workspace_create(s.ws_rows, &s.ws), "batch workspace");
         s.view.assign(static_cast<std::size_t>(c.layers), uocr_b200_paged_kv{});
         for (int l = 0; l < c.layers; ++l) {
             s.view[l].k_pool = s.kpool[l];
@@ -1001,6 +1017,126 @@ void PagedBatchKV::write_prefill_ragged(int layer, const float* k, const float* 
     abi_ok(uocr_b200_rswa_write_prefill_ragged_paged(&s.view[layer], k, v, d_row_slots, d_pos, total, s.ws, stream),
            "write_prefill_ragged");
 }
+int PagedBatchKV::plan_windowed_prefill(const std::vector<WindowedPrefill>& reqs, cudaStream_t stream) {
+    Impl& s = *p_;
+    int nv = 0, nt = 0, blocks = 0;
+    for (const WindowedPrefill& r : reqs) {
+        UOCR_CHECK(r.slot >= 0 && r.slot < s.cfg.slots && s.slot[r.slot].bound, "windowed prefill: slot not admitted");
+        UOCR_CHECK(r.vision_rows == 0 || r.vision_rows == s.slot[r.slot].prefix_len,
+                   "windowed prefill: vision rows must be the slot's whole prefix, or 0 when it is resident");
+        UOCR_CHECK(r.text_rows >= 0, "windowed prefill: negative text length");
+        nv += r.vision_rows;
+        nt += r.text_rows;
+        blocks += blocks_for(r.text_rows);
+    }
+    std::vector<int> idx(static_cast<std::size_t>(2 * nv + 4 * nt));
+    int* v_slots = idx.data();
+    int* v_pos = v_slots + nv;
+    int* t_slots = v_pos + nv;
+    int* t_pos = t_slots + nt;
+    int* t_b0 = t_pos + nt;
+    int* t_len = t_b0 + nt;
+    s.pf_tiles.clear();
+    auto add_tiles = [&](int row0, int n, int slot, int kind, int block0) {
+        for (int a = 0; a < n; a += 128) s.pf_tiles.push_back({row0 + a, std::min(128, n - a), slot, kind, a, block0});
+    };
+    int at = 0;
+    for (const WindowedPrefill& r : reqs) {
+        for (int i = 0; i < r.vision_rows; ++i) {
+            v_slots[at + i] = r.slot;
+            v_pos[at + i] = i;
+        }
+        add_tiles(at, r.vision_rows, r.slot, 0, 0);
+        at += r.vision_rows;
+    }
+    int tt = 0, b0 = 0;
+    for (const WindowedPrefill& r : reqs) {
+        for (int i = 0; i < r.text_rows; ++i) {
+            t_slots[tt + i] = r.slot;
+            t_pos[tt + i] = i;
+            t_b0[tt + i] = b0;
+            t_len[tt + i] = r.text_rows;
+        }
+        add_tiles(nv + tt, r.text_rows, r.slot, 1, b0);
+        tt += r.text_rows;
+        b0 += blocks_for(r.text_rows);
+    }
+    UOCR_CHECK(static_cast<int>(s.pf_tiles.size()) <= s.ws_rows, "windowed prefill: more query tiles than the workspace holds");
+    if (blocks > s.text_blocks_cap) {  // finite contents everywhere: rows past a request's last token are read, masked
+        if (s.text_k) cudaFree(s.text_k);
+        if (s.text_v) cudaFree(s.text_v);
+        s.text_k = s.text_v = nullptr;
+        const std::size_t bytes = s.block_bytes() * static_cast<std::size_t>(blocks);
+        cuda_ok(cudaMalloc(&s.text_k, bytes), "text K pool");
+        cuda_ok(cudaMalloc(&s.text_v, bytes), "text V pool");
+        cuda_ok(cudaMemset(s.text_k, 0, bytes), "text K zero");
+        cuda_ok(cudaMemset(s.text_v, 0, bytes), "text V zero");
+        s.text_blocks_cap = blocks;
+    }
+    if (static_cast<int>(idx.size()) > s.pf_cap) {
+        if (s.d_pf) cudaFree(s.d_pf);
+        s.d_pf = nullptr;
+        cuda_ok(cudaMalloc(&s.d_pf, sizeof(int) * idx.size()), "prefill index arrays");
+        s.pf_cap = static_cast<int>(idx.size());
+    }
+    if (!idx.empty()) {
+        cuda_ok(cudaMemcpyAsync(s.d_pf, idx.data(), sizeof(int) * idx.size(), cudaMemcpyHostToDevice, stream), "prefill index H2D");
+        cuda_ok(cudaStreamSynchronize(stream), "prefill index sync");  // idx is a local
+    }
+    s.pf_nv = nv;
+    s.pf_nt = nt;
+    s.text_blocks = blocks;
+    return nv + nt;
+}
+
+void PagedBatchKV::windowed_prefill_layer(int layer, const float* q, const float* k, const float* v, int heads, float* out,
+                                          cudaStream_t stream) {
+    Impl& s = *p_;
+    const int nv = s.pf_nv, nt = s.pf_nt;
+    if (nv + nt == 0) return;
+    const uocr_b200_paged_kv* view = &s.view[layer];
+    const int row = s.cfg.kv_heads * s.cfg.head_dim, qrow = heads * s.cfg.head_dim;
+    const int* v_slots = s.d_pf;
+    const int* v_pos = v_slots + nv;
+    const int* t_slots = v_pos + nv;
+    const int* t_pos = t_slots + nt;
+    const int* t_b0 = t_pos + nt;
+    const int* t_len = t_b0 + nt;
+    const float* kt = k + static_cast<std::size_t>(nv) * row;
+    const float* vt = v + static_cast<std::size_t>(nv) * row;
+    if (nv > 0)
+        abi_ok(uocr_b200_rswa_write_prefill_ragged_paged(view, k, v, v_slots, v_pos, nv, s.ws, stream), "windowed prefill: prefix scatter");
+    const bool tensor_cores = s.cfg.dtype == DType::BF16 && s.cfg.head_dim == 128;
+    if (tensor_cores) {
+        if (nt > 0)
+            abi_ok(uocr_b200_rswa_text_scatter_paged(view, s.text_k, s.text_v, s.text_blocks, kt, vt, t_pos, t_b0, nt, s.ws, stream),
+                   "windowed prefill: text scatter");
+        abi_ok(uocr_b200_rswa_prefill_attention_tc(view, s.text_k, s.text_v, s.text_blocks, q, s.d_prefill, s.pf_tiles.data(),
+                                                   static_cast<int>(s.pf_tiles.size()), s.cfg.window, heads, out, s.ws, stream),
+               "windowed prefill: attention");
+    } else {
+        for (int a = 0; a < nv; a += s.ws_rows) {  // the split-KV scratch holds ws_rows query rows per call
+            const int n = std::min(s.ws_rows, nv - a);
+            abi_ok(uocr_b200_rswa_attention_ragged_paged(view, q + static_cast<std::size_t>(a) * qrow, s.d_prefill, v_slots + a,
+                                                         v_pos + a, n, heads, out + static_cast<std::size_t>(a) * qrow, s.ws, stream),
+                   "windowed prefill: vision attention");
+        }
+        for (int a = 0; a < nt; a += s.ws_rows) {
+            const int n = std::min(s.ws_rows, nt - a);
+            const std::size_t r0 = static_cast<std::size_t>(nv + a);
+            abi_ok(uocr_b200_rswa_prefill_text_paged(view, s.text_k, s.text_v, s.text_blocks, q + r0 * qrow,
+                                                     kt + static_cast<std::size_t>(a) * row, vt + static_cast<std::size_t>(a) * row,
+                                                     s.d_prefill, t_slots + a, t_pos + a, t_b0 + a, n, s.cfg.window, heads,
+                                                     out + r0 * qrow, s.ws, stream),
+                   "windowed prefill: text attention");
+        }
+    }
+    if (nt > 0)
+        abi_ok(uocr_b200_rswa_ring_fill_paged(view, s.text_k, s.text_v, s.text_blocks, t_slots, t_pos, t_b0, t_len, s.d_prefill,
+                                              d_len(layer), d_ring_pos(layer), nt, s.cfg.window, s.ws, stream),
+               "windowed prefill: ring fill");
+}
+
 void PagedBatchKV::attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total,
                                     int heads, float* out, cudaStream_t stream) {
     Impl& s = *p_;

@@ -4,16 +4,20 @@
 // the 128-key tiles those rows can see: first the fixed (prefix) region through the block table,
 // then -- for text rows -- the sliding text window in the text pool.  The CTA is warp-specialised:
 //
-//   warp 4      producer: per key tile, 32 tiled TMA loads (one 16-token block half of K or V each,
-//               SWIZZLE_128B) into a two-deep K/V ring in shared memory; blocks the rows cannot
-//               see are fetched from an out-of-range coordinate, which fills zeros
-//   warp 5      one thread issues the MMAs: S = Q K^T (tcgen05.mma kind::f16, M = N = 128, operands
-//               in shared memory, accumulator in TMEM) one tile ahead of the softmax, and
-//               O_tile = P V with P read straight from TMEM and V as the MN-major B operand
-//   warps 0-3   softmax: thread r owns query row r == TMEM lane r: tcgen05.ld of S, mask, online
-//               max/sum in the exp2 domain, P written over S in TMEM (tcgen05.st) as bf16 pairs, and
-//               the previous tile's O_tile folded into a per-thread fp32 accumulator with the usual
-//               rescale while the tensor core works on the next products
+//   warps 8, 10  producers (K and V): per key tile, 16 tiled TMA loads each (one 16-token block half,
+//                SWIZZLE_128B) into two-deep K and V rings in shared memory; blocks the rows cannot
+//                see are fetched from an out-of-range coordinate, which fills zeros.  K runs further
+//                ahead than V: its stage is free as soon as the S product has read it
+//   warp 9       one thread issues the MMAs: S = Q K^T (tcgen05.mma kind::f16, M = N = 128, operands
+//                in shared memory, accumulator in TMEM) one tile ahead of the softmax, and
+//                O_tile = P V with P read straight from TMEM and V as the MN-major B operand
+//   warps 0-7    softmax: warp w owns rows 32*(w%4).. (its TMEM lane quadrant) and half w/4 of the
+//                keys of S and of the dims of O: tcgen05.ld of S, mask, row maximum agreed with the
+//                partner warp through shared memory, exp2-domain probabilities written over S in
+//                TMEM (tcgen05.st) as bf16 hi and lo pairs, and the previous tile's O_tile folded into
+//                a per-thread fp32 accumulator with the usual rescale while the tensor core works on
+//                the next products.  Q staging and the output rows go through shared memory so that
+//                global accesses are whole 512-byte rows
 //
 // TMEM (512 columns): S/P double-buffered in [0,256), O_tile double-buffered in [256,512).
 //

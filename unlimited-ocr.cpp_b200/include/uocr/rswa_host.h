@@ -394,6 +394,24 @@ public:
                               int total, cudaStream_t stream = nullptr);
     void attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total, int heads,
                           float* out, cudaStream_t stream = nullptr);
+    // Windowed ragged prefill, for prompts that may be longer than the window: the prefix is the vision
+    // part, text tokens attend prefix + the last `window` text tokens, and the ring and cursors end up as
+    // text_rows successive append_decode calls would leave them (src/scheduler/kv_cache.cpp:54-130 by
+    // composition).  Packed row order of q / k / v / out: the vision rows of every request, in request
+    // order, then the text rows of every request.
+    struct WindowedPrefill {
+        int slot = -1;
+        int vision_rows = 0;  // the slot's prefix length, or 0 when the (shared) prefix is already resident
+        int text_rows = 0;
+    };
+    // Builds and uploads the row index arrays and the query-tile list and grows the text pool when it is
+    // too small (allocates and synchronises: call outside stream capture).  Returns the packed row count.
+    int plan_windowed_prefill(const std::vector<WindowedPrefill>& requests, cudaStream_t stream = nullptr);
+    // One layer of the planned prefill: scatter of K/V (prefix blocks; text pool), attention, ring fill and
+    // cursor publication.  bf16 KV with head_dim 128 runs on the tensor cores, everything else on CUDA cores.
+    void windowed_prefill_layer(int layer, const float* q, const float* k, const float* v, int heads, float* out,
+                                cudaStream_t stream = nullptr);
+
     // Logical fp32 view of `n` slots: out[i] is [max_prefix_tokens + window][kv_heads*head_dim].
     void gather(int layer, const int* d_slots, int n, float* out_k, float* out_v, cudaStream_t stream = nullptr);
 
