@@ -185,7 +185,7 @@ class ClockSampler:
 class DecodeWorkload:
     """Device state of the cfg2 workload on the current GPU, driven through the C ABI."""
 
-    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True):
+    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True, weighted: bool = False):
         import torch
         self.pkg, self.torch = pkg, torch
         self.fused = fused
@@ -226,6 +226,8 @@ class DecodeWorkload:
         self.out = torch.zeros((L, B, self.row), device="cuda")
         self.ws = pkg.Workspace(B)
         self.ws.set_overlap(overlap)  # consecutive launches belong to different layers: overlap is safe
+        if weighted:
+            self.ws.calibrate(int(os.environ.get("UOCR_SPLIT_MODE", "1")))  # per-SM shares from a measured streaming rate instead of an even split
         self.graph = None
         self.launches_per_step = 0
         self.steps_done = 0
@@ -312,7 +314,7 @@ def run_ours(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     ranks = Ranks(rank, world, "nccl", torch.device("cuda", local))
-    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap)
+    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap, weighted=args.weighted)
     wl.capture()
     for _ in range(max(args.warmup - 1, 0)):
         wl.step()
@@ -622,6 +624,7 @@ def main():
                     help="cfg2 (default, headline): 64 seqs/GPU, W=1024, one shared prefix, weak scaling; "
                          "cfg4: 512 seqs in total sharded over the GPUs, W=4096, 4 prefixes, strong scaling; "
                          "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
+    ap.add_argument("--weighted", action="store_true", help="SM-weighted split (calibrates per-SM streaming rates first)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch the fused steps without programmatic dependent launch")
     ap.add_argument("--seqs", type=int, default=None, help="profiling aid only: sequences per GPU (not a bench number)")

@@ -263,6 +263,32 @@ def test_fused_decode_step_real_geometry_and_mixed_calls(orc, b):
     assert pb.ws.status() == 0
 
 
+@pytest.mark.parametrize("slots,P,W", [(24, 1600, 64), (5, 273, 48)])
+def test_sm_weighted_split(orc, b, slots, P, W):
+    # calibrated workspace: every CTA claims the share measured for its SM.  The large case has enough
+    # units (24 rows x 10 heads x 101 tiles) for the weighted bounds; the small one goes through the
+    # claims with the even split.  Same parity bar as the default split, fused and separate calls.
+    pb = PagedBatch(orc, slots, 1, 10, 128, W, b.BF16, [P] * slots, prefix_keys=["doc"] * slots, seed=91)
+    pb.ws.calibrate(True)
+    shares = pb.ws.split_shares()
+    assert len(shares) >= 2 and shares[0] == 0 and shares[-1] == 1 << 20
+    assert all(b_ > a_ for a_, b_ in zip(shares, shares[1:]))
+    pb.write_prefixes()
+    rows = list(range(slots))[::-1]
+    for t in range(5):
+        k, v, q = pb.step_inputs(t, 0, rows)
+        if t == 3:
+            pb.append(0, k, v, rows)
+            got, want = pb.attend(0, q, rows)
+        else:
+            got, want = pb.step_fused(0, k, v, q, rows)
+        assert_attention_close(got, want, *TIGHT)
+    pb.check_logical_view(0)
+    assert pb.ws.status() == 0
+    pb.ws.calibrate(False)
+    assert pb.ws.split_shares() == []
+
+
 def test_fused_step_graph_replay(orc, b):
     import torch
     slots, W, P, kvh, hd = 4, 16, 9, 2, 64

@@ -69,6 +69,8 @@ _SIGS = {
     "uocr_b200_workspace_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "uocr_b200_workspace_set_timing": (_i, [_vp, _i]),
     "uocr_b200_workspace_set_overlap": (_i, [_vp, _i]),
+    "uocr_b200_workspace_calibrate": (_i, [_vp, _i, _vp]),
+    "uocr_b200_workspace_split_shares": (_i, [_vp, _vp, _i]),
     "uocr_b200_workspace_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
     "uocr_b200_rswa_append_decode_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
@@ -172,6 +174,16 @@ class Workspace:
 
     def set_overlap(self, enabled: bool) -> None:
         check(lib().uocr_b200_workspace_set_overlap(self.h, 1 if enabled else 0))
+
+    def calibrate(self, enabled: bool = True, stream=None) -> None:
+        """SM-weighted split for the attention kernels of this workspace (measures per-SM streaming rates)."""
+        check(lib().uocr_b200_workspace_calibrate(self.h, int(enabled), stream_handle(stream)))
+
+    def split_shares(self):
+        """Cumulative per-SM shares scaled to 1 << 20 (empty list: even split)."""
+        buf = (C.c_int * 161)()
+        n = lib().uocr_b200_workspace_split_shares(self.h, buf, 161)
+        return [buf[i] for i in range(max(n, 0))]
 
     def last_kernel_ms(self) -> float:
         v = C.c_float(0)

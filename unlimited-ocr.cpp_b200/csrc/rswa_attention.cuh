@@ -22,6 +22,7 @@
 // RSWACache::append_decode (src/scheduler/kv_cache.cpp:54-82).
 #pragma once
 
+#include "rswa_calibrate.cuh"
 #include "rswa_device.cuh"
 
 namespace uocr_b200 {
@@ -79,6 +80,14 @@ struct AttnParams {
     int dyn_cap;      // most dynamic pieces the scratch can hold (0 = static split only)
     int* status;
     int total_warps;
+    // SM-weighted split (cta_frac null: even split).  A CTA takes the share measured for the SM it
+    // runs on; `claim` (zero between launches) makes sure every share is taken exactly once even if
+    // two CTAs land on one SM.
+    // The table travels in the kernel parameters (constant bank: no global load before the claim).
+    int split_ctas;                        // 0: even split
+    int cta_frac[kMaxCtas + 1];            // cumulative shares scaled to 1 << 20
+    uint8_t slot_of_smid[kMaxSmid];        // share index of an SM id, 255 if it was never seen
+    int* claim;                            // [ctas]
     // fused decode step only
     PlanParams plan;
     const float* k_new;
@@ -240,14 +249,34 @@ __device__ __forceinline__ void cursor_next(UnitCursor& c, const int* rs, const 
 struct PieceMap {
     long long total, u1;
     int ns, nd, chunk;
+    const int* frac;  // weighted split: cumulative CTA shares scaled to 1 << 20 (kernel parameter space); else null
+    int wpc;          // warps per CTA (weighted split: piece k belongs to CTA k / wpc)
+    // first unit of CTA c's share (weighted split only; u1 < 2^26, so the product fits 64 bits with room)
+    __device__ __forceinline__ int bound(int c) const { return (int)((u1 * (long long)frac[c]) >> 20); }
     __device__ __forceinline__ long long start(int k) const {
-        return k < ns ? ((long long)k * u1) / ns : u1 + (long long)(k - ns) * chunk;
+        if (k >= ns) return u1 + (long long)(k - ns) * chunk;
+        if (frac == nullptr) return ((long long)k * u1) / ns;
+        const int c = k / wpc, j = k - c * wpc;
+        const int b0 = bound(c);
+        return b0 + (j * (bound(c + 1) - b0)) / wpc;
     }
     __device__ __forceinline__ long long end(int k) const {
-        return k < ns ? ((long long)(k + 1) * u1) / ns : u1 + (long long)(k - ns + 1) * chunk;
+        if (k >= ns) return u1 + (long long)(k - ns + 1) * chunk;
+        if (frac == nullptr) return ((long long)(k + 1) * u1) / ns;
+        const int c = k / wpc, j = k - c * wpc;
+        const int b0 = bound(c);
+        return b0 + ((j + 1) * (bound(c + 1) - b0)) / wpc;
     }
     __device__ __forceinline__ int of(long long u) const {
-        return u < u1 ? (int)(((u + 1) * ns - 1) / u1) : ns + (int)((u - u1) / chunk);
+        if (u >= u1) return ns + (int)((u - u1) / chunk);
+        if (frac == nullptr) return (int)(((u + 1) * ns - 1) / u1);
+        // the CTA owning unit v: start from the even split's answer, the shares move it by a step or two
+        const int v = (int)u, n = ns / wpc;
+        int lo = (int)(((long long)v * n) / u1);
+        int b0 = bound(lo), b1 = bound(lo + 1);
+        while (lo > 0 && b0 > v) { --lo; b1 = b0; b0 = bound(lo); }
+        while (lo < n - 1 && b1 <= v) { ++lo; b0 = b1; b1 = bound(lo + 1); }
+        return lo * wpc + ((v - b0 + 1) * wpc - 1) / (b1 - b0);
     }
 };
 
@@ -262,9 +291,17 @@ constexpr int kDynShare = UOCR_DYN_SHARE;  // 1/kDynShare of the units are hande
 constexpr int kDynPerWarp = 4;    // scratch is sized for this many dynamic pieces per warp
 constexpr int kPendMax = 32;      // per-warp list of partial segments awaiting their arrival
 
-__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int dyn_cap) {
+// Whether the weighted split applies to a launch: enough units that no piece can be empty (the shares
+// differ by tens of percent at most) and few enough that the bounds fit 32-bit arithmetic.
+__device__ __forceinline__ bool weighted_split_ok(long long total, int total_warps) {
+    return total >= 8LL * total_warps && total < (1LL << 26);
+}
+
+__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int dyn_cap, const int* frac, int wpc) {
     PieceMap m;
     m.total = total;
+    m.frac = frac;
+    m.wpc = wpc;
     m.chunk = kDynChunk;
     m.nd = 0;
     if (kDynShare > 0 && dyn_cap > 0 && total >= 8LL * total_warps)
@@ -318,7 +355,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifdef UOCR_TRACE
 __device__ unsigned long long g_trace[8 * 4096];
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { if (lane == 0 && gw < 4096) { g_trace[gw * 8 + (slot)] = gtime(); if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_trace[gw * 8 + 7] = sm; } } } while (0)
+#define TRACE(slot) do { const int tw_ = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if ((threadIdx.x & 31) == 0 && tw_ < 4096) { g_trace[tw_ * 8 + (slot)] = gtime(); if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_trace[tw_ * 8 + 7] = sm; } } } while (0)
 #else
 #define TRACE(slot) do {} while (0)
 #endif
@@ -362,8 +399,21 @@ __device__ __forceinline__ void unpack2(const uint4& w, float2 (&f)[KV::kPerChun
     }
 }
 
+// Weighted split: which share this CTA processes.  `first` is the answer to the claim of the share
+// measured for this CTA's SM (`want`); if somebody else holds it, take the next free one.
+__device__ __forceinline__ int resolve_claim(int first, int want, int* claim, int* status) {
+    if (first == 0) return want;
+    const int n = (int)gridDim.x;
+    for (int i = 1; i < n; ++i) {
+        const int c = want + i < n ? want + i : want + i - n;
+        if (atomicAdd(claim + c, 1) == 0) return c;
+    }
+    atomicOr(status, kStatusClaim);  // cannot happen while claims are reset between launches; results are flagged
+    return blockIdx.x;
+}
+
 template <typename KV, int HD, bool PAGED, bool FUSED>
-__global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant__ AttnParams p) {
     using M = TileMap<KV, HD>;
     constexpr int LPR = M::kLanesPerRow, CPL = M::kChunksPerLane, RPW = M::kRowsPerLoad;
     constexpr int ITER = M::kIters, EPC = KV::kPerChunk, EPL = M::kElemsPerLane;
@@ -374,8 +424,21 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int gw = blockIdx.x * warps + warp;
     TRACE(0);
+
+    // ---- which share of the unit line this CTA takes -------------------------------------------------
+    __shared__ int s_cta;
+    const bool weighted = p.split_ctas == (int)gridDim.x;
+    int first_claim = 1, want = blockIdx.x;
+    if (weighted) {
+        if (threadIdx.x == 0) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            const int slot = smid < (unsigned)kMaxSmid ? p.slot_of_smid[smid] : 255;
+            if (slot < (int)gridDim.x) want = slot;
+            first_claim = atomicAdd(p.claim + want, 1);  // the answer is looked at after the plan is built
+        }
+    }
 
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     uint8_t* my_tiles = smem + bar_bytes + (size_t)warp * (kRing * TILE);
@@ -397,14 +460,22 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
         int* rs_s = reinterpret_cast<int*>(plan_base + sizeof(RowInfo) * p.rows);
         int* scratch = rs_s + p.rows + 1;
         plan_all_rows(p.plan, rs_s, info_s, scratch);
+        if (weighted && threadIdx.x == 0) s_cta = resolve_claim(first_claim, want, p.claim, p.status);
         __syncthreads();
         rs = rs_s;
         info = info_s;
+    } else {
+        if (weighted) {
+            if (threadIdx.x == 0) s_cta = resolve_claim(first_claim, want, p.claim, p.status);
+            __syncthreads();
+        }
     }
 
-    TRACE(1);
     const long long total = rs[p.rows];
-    const PieceMap pm = make_piece_map(total, p.total_warps, p.dyn_cap);
+    const bool use_split = weighted && weighted_split_ok(total, p.total_warps);
+    TRACE(1);
+    const int gw = (weighted ? s_cta : (int)blockIdx.x) * warps + warp;
+    const PieceMap pm = make_piece_map(total, p.total_warps, p.dyn_cap, use_split ? p.cta_frac : nullptr, warps);
     int piece = gw < pm.ns ? gw : -1;  // the warp's static piece; dynamic ones follow
     int n_units = 0;
     long long u0 = 0;
@@ -888,11 +959,17 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const AttnParams p) {
             if (is_last) {
                 *p.done_ctas = 0;
                 *p.dyn_next = 0;
+                if constexpr (!FUSED) {
+                    if (weighted)
+                        for (int i = 0; i < (int)gridDim.x; ++i) p.claim[i] = 0;
+                }
             }
         }
         if constexpr (FUSED) {
             __syncthreads();
             if (is_last) {
+                if (weighted)
+                    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
                 // every CTA has planned from the old cursors by now; nobody reads them again in this launch
                 for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
                     const int slot = p.plan.d_slots[r];

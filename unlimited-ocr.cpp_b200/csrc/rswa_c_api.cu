@@ -104,6 +104,13 @@ struct uocr_b200_workspace {
     int pieces_max = 0;
     PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
     int tiles_cap = 0;
+    // SM-weighted split (uocr_b200_workspace_calibrate): cumulative shares, SM id -> share, and two
+    // claim arrays used alternately, because a fused step may overlap the tail of its predecessor
+    int cta_frac[kMaxCtas + 1] = {0};     // host copies: they travel in the kernel parameters
+    uint8_t slot_of_smid[kMaxSmid] = {0};
+    int* claim = nullptr;                 // device, [2][kMaxCtas]
+    int calibrated_ctas = 0;      // 0: even split
+    unsigned seq = 0;             // launches issued; its low bit picks the claim array
     bool timing = false;
     bool overlap = false;  // fused decode step may start its prologue before the preceding kernel ends
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -148,7 +155,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->pieces_max);
     const size_t o_tiles = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
     ws->tiles_cap = max_rows;
-    ws->bytes = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
+    const size_t o_split = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
+    ws->bytes = o_split + up(sizeof(int) * (size_t)(2 * kMaxCtas));
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -169,6 +177,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->done_ctas = ws->counters + ws->pieces_max;
     ws->dyn_next = ws->done_ctas + 1;
     ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
+    ws->claim = reinterpret_cast<int*>(ws->base + o_split);
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -190,6 +199,104 @@ int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled) {
     }
     ws->timing = enabled != 0;
     return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_calibrate(uocr_b200_workspace* ws, int enabled, uocr_b200_stream_t stream) {
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_calibrate: null workspace");
+    if (!enabled) {
+        ws->calibrated_ctas = 0;
+        return UOCR_B200_OK;
+    }
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+    const int ctas = di->sms;
+    if (ctas > kMaxCtas) return fail(UOCR_B200_ERR_UNSUPPORTED, "workspace_calibrate: more SMs than the split table holds");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // 2 MB per SM, walked kPasses times per run: the whole buffer (0.3 GB) is far larger than L2, so every
+    // pass streams from HBM, and a run is long (~0.2 ms) against the few microseconds by which CTAs start apart
+    constexpr int kTilesPerCta = 512, kPasses = 4, kRuns = 5, kWarm = 1;
+    constexpr int warps = 16;
+    const size_t bytes = (size_t)ctas * kTilesPerCta * kCalTile;
+    uint8_t* buf = nullptr;
+    unsigned long long* d_out = nullptr;
+    CHECK_CUDA(cudaMalloc(&buf, bytes), "calibration buffer");
+    cudaError_t e = cudaMalloc(&d_out, sizeof(unsigned long long) * 2 * ctas * kRuns);
+    if (e != cudaSuccess) {
+        cudaFree(buf);
+        return cuda_fail(e, "calibration results");
+    }
+    const int smem = ((warps * kCalRing * 8 + 127) & ~127) + warps * kCalRing * kCalTile;
+    e = cudaFuncSetAttribute(rswa_calibrate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaMemsetAsync(buf, 0, bytes, st);
+    for (int r = 0; r < kWarm + kRuns && e == cudaSuccess; ++r) {
+        CalibrateParams cp{buf, kTilesPerCta, kPasses, d_out + (size_t)2 * ctas * (r < kWarm ? 0 : r - kWarm), ws->status};
+        rswa_calibrate_kernel<<<ctas, warps * 32, smem, st>>>(cp);
+        e = cudaGetLastError();
+    }
+    std::vector<unsigned long long> h((size_t)2 * ctas * kRuns);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h.data(), d_out, sizeof(unsigned long long) * h.size(), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(buf);
+    cudaFree(d_out);
+    if (e != cudaSuccess) return cuda_fail(e, "calibration run");
+    // median duration per SM id over the runs
+    std::vector<std::vector<double>> per_sm(kMaxSmid);
+    for (int r = 0; r < kRuns; ++r)
+        for (int c = 0; c < ctas; ++c) {
+            const unsigned long long ns = h[(size_t)2 * (r * ctas + c)], smid = h[(size_t)2 * (r * ctas + c) + 1];
+            if (smid < (unsigned long long)kMaxSmid && ns > 0) per_sm[smid].push_back((double)ns);
+        }
+    // Share c belongs to the SM that ran CTA c of the last calibration launch: on an idle GPU a grid of
+    // one CTA per SM is placed the same way every time, so a CTA normally claims the share with its own
+    // index and neighbouring shares stay spread over the chip the way neighbouring CTAs are.
+    std::vector<int> slot(kMaxSmid, 255);
+    std::vector<double> rate((size_t)ctas, 0.0);
+    int covered = 0;
+    for (int c = 0; c < ctas; ++c) {
+        const unsigned long long smid = h[(size_t)2 * ((kRuns - 1) * ctas + c) + 1];
+        if (smid >= (unsigned long long)kMaxSmid || slot[smid] != 255 || per_sm[smid].empty()) continue;
+        std::sort(per_sm[smid].begin(), per_sm[smid].end());
+        slot[smid] = c;
+        rate[c] = 1.0 / per_sm[smid][per_sm[smid].size() / 2];
+        ++covered;
+    }
+    if (covered != ctas)
+        return fail(UOCR_B200_ERR_UNSUPPORTED, "workspace_calibrate: the calibration grid did not cover every SM exactly once");
+    // The attention kernel is only partly bound by the SM's streaming rate (the rest is its own
+    // instruction stream and latency): measured on the bf16 x 128 decode step, an SM that streams at
+    // 0.80 / 1.34 of the median runs its share of attention at 0.89 / 1.12 of the median speed.  The
+    // square root of the measured ratio models that; proportional shares overshoot and are slower.
+    std::vector<double> sorted_rate(rate);
+    std::sort(sorted_rate.begin(), sorted_rate.end());
+    const double mean = sorted_rate[sorted_rate.size() / 2];
+    if (enabled != 3)
+        for (double& r : rate) r = mean * std::sqrt(r / mean);
+    std::vector<int> frac(kMaxCtas + 1, 0);
+    double total = 0, run = 0;
+    for (double& r : rate) {  // keep every share within [0.5, 2] of the mean: pieces must not become empty
+        r = std::min(std::max(r, 0.5 * mean), 2.0 * mean);  // (enabled == 3, diagnostic: proportional shares)
+        if (enabled == 2) r = mean;  // diagnostic: even shares through the SM-mapped, claimed path
+        total += r;
+    }
+    for (int c = 0; c < ctas; ++c) {
+        run += rate[c];
+        frac[c + 1] = (int)std::llround(run / total * (double)(1 << 20));
+    }
+    frac[ctas] = 1 << 20;
+    for (int c = 0; c <= kMaxCtas; ++c) ws->cta_frac[c] = frac[c];
+    for (int sm = 0; sm < kMaxSmid; ++sm) ws->slot_of_smid[sm] = (uint8_t)slot[sm];
+    CHECK_CUDA(cudaMemsetAsync(ws->claim, 0, sizeof(int) * 2 * kMaxCtas, st), "claims zero");
+    CHECK_CUDA(cudaStreamSynchronize(st), "calibration sync");
+    ws->calibrated_ctas = ctas;
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_split_shares(const uocr_b200_workspace* ws, int* out_frac, int n) {
+    if (!ws || !out_frac || n <= 0) return fail(UOCR_B200_ERR_INVALID, "workspace_split_shares: bad arguments");
+    if (ws->calibrated_ctas == 0) return 0;
+    const int m = std::min(n, ws->calibrated_ctas + 1);
+    std::memcpy(out_frac, ws->cta_frac, sizeof(int) * m);
+    return m;
 }
 
 int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled) {
@@ -383,6 +490,12 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.done_ctas = ws->done_ctas;
     ap.dyn_next = ws->dyn_next;
     ap.dyn_cap = ws->dyn_cap;
+    if (ws->calibrated_ctas == di->sms) {
+        ap.split_ctas = ws->calibrated_ctas;
+        std::memcpy(ap.cta_frac, ws->cta_frac, sizeof(ap.cta_frac));
+        std::memcpy(ap.slot_of_smid, ws->slot_of_smid, sizeof(ap.slot_of_smid));
+        ap.claim = ws->claim + (ws->seq++ & 1u) * kMaxCtas;
+    }
 
     c.plan.rows = c.rows;
     c.plan.heads = c.heads;
