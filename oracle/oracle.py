@@ -84,6 +84,7 @@ class Oracle:
         fn("f32_to_bf16", C.c_uint16, [C.c_float])
         fn("bf16_to_f32", C.c_float, [C.c_uint16])
         fn("round_bf16_inplace", None, [_f32p, C.c_size_t])
+        fn("rope", None, [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float])
         fn("cache_create", vp, [C.c_int] * 4)
         fn("cache_destroy", None, [vp])
         fn("cache_reset", C.c_int, [vp, C.c_int])
@@ -142,6 +143,16 @@ class Oracle:
 
     def Scheduler(self, max_batch=16, min_batch=4):
         return _Sched(self, max_batch, min_batch)
+
+    def apply_rope(self, q: np.ndarray, k, positions: np.ndarray, n_heads: int, n_kv_heads: int, head_dim: int,
+                   theta: float):
+        """RoPE on copies of q [seq, n_heads*hd] and k [seq, n_kv_heads*hd] (k may be None)."""
+        q2 = np.ascontiguousarray(q, dtype=np.float32).copy()
+        k2 = None if k is None else np.ascontiguousarray(k, dtype=np.float32).copy()
+        pos = np.ascontiguousarray(positions, dtype=np.int32)
+        self.rope(_fp(q2), _fp(k2) if k2 is not None else None, pos.ctypes.data_as(_i32p), int(pos.shape[0]), n_heads,
+                  n_kv_heads, head_dim, theta)
+        return q2, k2
 
     def round_bf16(self, x: np.ndarray) -> np.ndarray:
         y = np.ascontiguousarray(x, dtype=np.float32).copy()

@@ -20,6 +20,7 @@
 #include "uocr/continuous_batch.h"
 #include "uocr/kv_cache.h"
 #include "uocr/memory_pool.h"
+#include "uocr/ops.h"
 
 #define REF_API extern "C" __attribute__((visibility("default")))
 
@@ -30,6 +31,12 @@ REF_API uint16_t ref_f32_to_bf16(float f) { return f32_to_bf16(f); }
 REF_API float ref_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }
 REF_API void ref_round_bf16_inplace(float* x, size_t n) {
     for (size_t i = 0; i < n; ++i) x[i] = bf16_to_f32(f32_to_bf16(x[i]));
+}
+
+// ---- RoPE (src/kernels/cpu_ops.cpp) --------------------------------------------------------------
+REF_API void ref_rope(float* q, float* k, const int* positions, int seq, int n_heads, int n_kv_heads, int head_dim,
+                      float theta) {
+    ops::rope(q, k, positions, seq, n_heads, n_kv_heads, head_dim, theta);
 }
 
 // ---- RSWACache ---------------------------------------------------------------------------------

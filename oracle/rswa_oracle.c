@@ -676,3 +676,37 @@ double orc_decode_bench(int n_seq, int layers, int kv_heads, int head_dim, int w
     free(out);
     return dt;
 }
+
+/* ---- RoPE: src/kernels/cpu_ops.cpp:146-180 (rope_row + rope) ------------------------------------
+ * Same float arithmetic as the reference: powf / cosf / sinf on floats, the angle as an fp32 product
+ * of the integer position and the frequency. */
+void orc_rope(float* q, float* k, const int* positions, int seq, int n_heads, int n_kv_heads, int head_dim,
+              float theta) {
+    const int half = head_dim / 2;
+    float* c = (float*)malloc(sizeof(float) * (size_t)(half > 0 ? half : 1));
+    float* s = (float*)malloc(sizeof(float) * (size_t)(half > 0 ? half : 1));
+    for (int t = 0; t < seq; ++t) {
+        const int p = positions ? positions[t] : t;
+        for (int i = 0; i < half; ++i) {
+            const float freq = powf(theta, -2.0f * i / (float)head_dim);
+            const float angle = p * freq;
+            c[i] = cosf(angle);
+            s[i] = sinf(angle);
+        }
+        for (int pass = 0; pass < 2; ++pass) {
+            float* base = pass == 0 ? q : k;
+            const int heads = pass == 0 ? n_heads : n_kv_heads;
+            if (!base) continue;
+            for (int h = 0; h < heads; ++h) {
+                float* v = base + ((size_t)t * heads + h) * head_dim;
+                for (int i = 0; i < half; ++i) {
+                    const float x0 = v[i], x1 = v[i + half];
+                    v[i] = x0 * c[i] - x1 * s[i];
+                    v[i + half] = x0 * s[i] + x1 * c[i];
+                }
+            }
+        }
+    }
+    free(c);
+    free(s);
+}

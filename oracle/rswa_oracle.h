@@ -26,6 +26,12 @@ uint16_t orc_f32_to_bf16(float f);
 float orc_bf16_to_f32(uint16_t h);
 void orc_round_bf16_inplace(float* x, size_t n); /* x <- widen(round_bf16(x)) */
 
+/* ---- RoPE in place on q [seq][n_heads][hd] and k [seq][n_kv_heads][hd] (k may be null):
+ * src/kernels/cpu_ops.cpp:157-180.  Half-split pairs (i, i + hd/2), freq = powf(theta, -2i/hd),
+ * angle = position * freq in fp32, positions == null means 0..seq-1. */
+void orc_rope(float* q, float* k, const int* positions, int seq, int n_heads, int n_kv_heads, int head_dim,
+              float theta);
+
 /* ---- R-SWA cache: include/uocr/kv_cache.h:23-86, src/scheduler/kv_cache.cpp:10-137 ---------- */
 typedef struct orc_cache orc_cache;
 orc_cache* orc_cache_create(int layers, int kv_heads, int head_dim, int window);

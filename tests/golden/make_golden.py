@@ -66,6 +66,9 @@ def main():
     out["sched/res"] = traces.run_sched_trace(ref, script, 16)
     out["sched/res_early"] = traces.run_sched_trace(ref, script, 5, early_finish_every=7)
 
+    for name, case in traces.ROPE_CASES.items():
+        out[f"rope/{name}/q"], out[f"rope/{name}/k"] = traces.run_rope_case(ref, *case)
+
     path = os.path.join(HERE, "rswa_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes;", len(out), "arrays")

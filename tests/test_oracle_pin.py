@@ -212,6 +212,13 @@ def test_oracle_scheduler_matches_golden(orc):
                           GOLD["sched/res_early"])
 
 
+@pytest.mark.parametrize("name", list(traces.ROPE_CASES))
+def test_oracle_rope_matches_golden(orc, name):
+    # the restatement calls the same libm float functions as the reference build: bit-exact
+    q, k = traces.run_rope_case(orc, *traces.ROPE_CASES[name])
+    assert np.array_equal(q, GOLD[f"rope/{name}/q"]) and np.array_equal(k, GOLD[f"rope/{name}/k"])
+
+
 # ---- 3. live comparison with the compiled reference ---------------------------------------------
 
 def test_golden_is_what_the_reference_produces(ref):

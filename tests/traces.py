@@ -185,3 +185,18 @@ def run_cache_trace(lib, layers, kv_heads, head_dim, window, prefix, n_append, h
         out["prefill_attn"] = np.zeros((0,), np.float32)
     out["meta"] = np.array([c.capacity(), c.prefill_len(), c.bytes()], dtype=np.int64)
     return out
+
+
+ROPE_CASES = {
+    # name: (seq, heads, kv_heads, head_dim, theta, max_position, seed)
+    "hd128": (19, 10, 10, 128, 10000.0, 6000, 31),
+    "hd16_gqa": (7, 4, 2, 16, 1000000.0, 300000, 32),
+}
+
+
+def run_rope_case(o, seq, heads, kv_heads, hd, theta, max_pos, seed):
+    """RoPE of seeded q / k at seeded positions through back end `o`: (q_out, k_out)."""
+    q = synth.normal(seed, 0, (seq, heads * hd))
+    k = synth.normal(seed, 1, (seq, kv_heads * hd))
+    pos = synth.integers(seed, 2, 0, max_pos, (seq,)).astype(np.int32)
+    return o.apply_rope(q, k, pos, heads, kv_heads, hd, theta)
