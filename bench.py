@@ -185,7 +185,9 @@ class ClockSampler:
 class DecodeWorkload:
     """Device state of the cfg2 workload on the current GPU, driven through the C ABI."""
 
-    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True, weighted: bool = False):
+    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True, weighted: bool = False,
+                 rope: bool = False):
+        self.rope = rope
         import torch
         self.pkg, self.torch = pkg, torch
         self.fused = fused
@@ -220,6 +222,7 @@ class DecodeWorkload:
         self.d_len = torch.zeros((L, B), dtype=torch.int32, device="cuda")
         self.d_ring = torch.zeros((L, B), dtype=torch.int32, device="cuda")
         self.set_positions(self.pos0)
+        self.d_positions = torch.from_numpy((plen + self.pos0).astype(np.int32)).cuda()  # rotary positions (--rope)
         self.q = torch.randn((L, B, self.row), generator=g, device="cuda")
         self.k = torch.randn((L, B, self.row), generator=g, device="cuda")
         self.v = torch.randn((L, B, self.row), generator=g, device="cuda")
@@ -244,7 +247,11 @@ class DecodeWorkload:
     def step_plain(self, per_layer_hook=None):
         p = self.pkg
         for l in range(self.L):
-            if self.fused:
+            if self.fused and self.rope:
+                p.decode_step_rope_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_positions, 10000.0,
+                                         self.d_len[l], self.d_ring[l], self.d_prefill, self.d_slots, self.B,
+                                         CFG["window"], CFG["heads"], self.out[l], self.ws)
+            elif self.fused:
                 p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
                                     self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
                                     self.ws)
@@ -314,7 +321,8 @@ def run_ours(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     ranks = Ranks(rank, world, "nccl", torch.device("cuda", local))
-    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap, weighted=args.weighted)
+    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap, weighted=args.weighted,
+                        rope=args.rope)
     wl.capture()
     for _ in range(max(args.warmup - 1, 0)):
         wl.step()
@@ -624,6 +632,8 @@ def main():
                     help="cfg2 (default, headline): 64 seqs/GPU, W=1024, one shared prefix, weak scaling; "
                          "cfg4: 512 seqs in total sharded over the GPUs, W=4096, 4 prefixes, strong scaling; "
                          "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
+    ap.add_argument("--rope", action="store_true",
+                    help="fused step with the rotary embedding folded in (q, k un-rotated; one position per row)")
     ap.add_argument("--weighted", action="store_true", help="SM-weighted split (calibrates per-SM streaming rates first)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch the fused steps without programmatic dependent launch")

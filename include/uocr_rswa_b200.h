@@ -285,6 +285,18 @@ UOCR_B200_API int uocr_b200_rswa_decode_step_paged(
     int* d_ring_pos, const int* d_prefill_len, const int* d_slots, int batch, int window, int heads,
     float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* The same step with the rotary embedding folded in: replaces uocr::cuda::rope followed by the two
+ * calls above (src/engine/gpu_decoder.cu:988-996).  q and k are the un-rotated projections; row b is
+ * rotated for position d_positions[b] exactly as src/kernels/cuda/rope_fused.cu:12-40 does (pairs
+ * (i, i + head_dim/2), freq = theta^(-2i/head_dim) in fp32, angle = position * freq), q as it is
+ * loaded and k before it is rounded to the pool dtype and written; v is untouched and q / k in
+ * global memory are left as they are.  head_dim >= 16 (bf16) or 8 (fp32); at most 1024 rows. */
+UOCR_B200_API int uocr_b200_rswa_decode_step_rope_paged(
+    const uocr_b200_paged_kv* kv, const float* q, const float* k, const float* v,
+    const int* d_positions, float theta, int* d_len, int* d_ring_pos, const int* d_prefill_len,
+    const int* d_slots, int batch, int window, int heads, float* out, uocr_b200_workspace* ws,
+    uocr_b200_stream_t stream);
+
 /* Batched paged decode attention for callers that must not allocate.  It has no counterpart in the
  * reference.  Some hosts of this library cannot call cudaMalloc at all: an engine that hands the
  * whole GPU to its own arena at start-up (a later driver allocation fails or fragments it), a plugin

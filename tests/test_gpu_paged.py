@@ -9,6 +9,7 @@ fed the bf16-rounded values, the observed error is fp32 reassociation only, so a
 import numpy as np
 import pytest
 
+import synth
 from paged_fixture import PagedBatch, assert_attention_close, load_b200
 
 pytestmark = pytest.mark.gpu
@@ -287,6 +288,55 @@ def test_sm_weighted_split(orc, b, slots, P, W):
     assert pb.ws.status() == 0
     pb.ws.calibrate(False)
     assert pb.ws.split_shares() == []
+
+
+@pytest.mark.parametrize("dtype_name,hd,theta", [("bf16", 128, 10000.0), ("f32", 16, 10000.0), ("bf16", 16, 1e6)])
+def test_fused_decode_step_with_rope(orc, b, dtype_name, hd, theta):
+    # rope + append + attention in one launch against the oracle's rope (restating the reference's CPU
+    # rope) followed by append_decode and attention.  The device evaluates sin/cos with its own libm, so
+    # a rotated k can land on the other side of a bf16 rounding boundary: K is compared to one bf16 ulp
+    # on a handful of elements, everything else (V, cursors) bit for bit.
+    import torch
+    dtype = b.BF16 if dtype_name == "bf16" else b.F32
+    slots, W, P, kvh, heads = 4, 32, 17, 2, 4
+    pb = PagedBatch(orc, slots, 1, kvh, hd, W, dtype, [P] * slots, heads=heads, seed=55)
+    pb.write_prefixes()
+    rows = [2, 0, 3, 1]
+    ds = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    worst = (0.0, 0.0)
+    for t in range(2 * W + 3):
+        k = np.ascontiguousarray(synth.normal(55, 100000 + t, (slots, kvh * hd)))
+        v = np.ascontiguousarray(pb.rnd(synth.normal(55, 300000 + t, (slots, kvh * hd))))
+        q = np.ascontiguousarray(synth.normal(55, 500000 + t, (slots, heads * hd)))
+        pos = np.array([P + t + 977 * i for i in range(slots)], dtype=np.int32)  # up to ~3000: many turns of the fast pairs
+        out = torch.full((slots, heads * hd), float("nan"), device="cuda")
+        b.decode_step_rope_paged(pb.layer[0], torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(),
+                                 torch.from_numpy(v).cuda(), torch.from_numpy(pos).cuda(), theta, pb.d_len[0], pb.d_ring[0],
+                                 pb.d_prefill, ds, slots, W, heads, out, pb.ws)
+        got = out.cpu().numpy()
+        q_rot, k_rot = orc.apply_rope(q, k, pos, heads, kvh, hd, theta)
+        k_rot = np.ascontiguousarray(pb.rnd(k_rot))
+        want = []
+        for i, s in enumerate(rows):
+            pb.cache[s].append_decode(0, k_rot[i], v[i])
+            want.append(pb.cache[s].attention(0, q_rot[i:i + 1], pb.cache[s].len(0) - 1, heads, False)[0])
+        e = assert_attention_close(got, np.stack(want), *TIGHT)
+        worst = (max(worst[0], e[0]), max(worst[1], e[1]))
+    print("rope step worst max-abs / rel-L2:", worst)
+    gk, gv = pb.gather(0, list(range(slots)))
+    dl, dr = pb.d_len[0].cpu().numpy(), pb.d_ring[0].cpu().numpy()
+    for s in range(slots):
+        c = pb.cache[s]
+        n = c.len(0)
+        assert dl[s] == n and dr[s] == c.ring_pos(0)
+        assert np.array_equal(gv[s, :n], c.values(0))
+        wk = c.keys(0)
+        diff = np.abs(gk[s, :n] - wk)
+        ulp = np.abs(wk) * 2.0 ** -7 + 1e-30 if dtype_name == "bf16" else np.abs(wk) * 2.0 ** -20 + 1e-6
+        assert (diff <= ulp).all(), "rotated K off by more than one ulp of the pool dtype"
+        if dtype_name == "bf16":
+            assert (diff > 0).mean() < 5e-3, "too many rotated K elements rounded differently"
+    assert pb.ws.status() == 0
 
 
 def test_fused_step_graph_replay(orc, b):

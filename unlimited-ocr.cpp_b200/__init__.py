@@ -84,6 +84,8 @@ _SIGS = {
     "uocr_b200_rswa_prefill_attention_tc": (_i, [C.POINTER(PagedKV), _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_ring_fill_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_decode_step_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_decode_step_rope_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [C.c_float] + [_vp] * 4 +
+                                              [_i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged_noalloc": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_attention_ragged_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
@@ -274,6 +276,14 @@ def ring_fill_paged(layer, text_k, text_v, text_blocks, d_slots, d_pos, d_block0
     check(lib().uocr_b200_rswa_ring_fill_paged(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(d_slots), _p(d_pos),
                                                 _p(d_block0), _p(d_text_len), _p(d_prefill), _p(d_len), _p(d_ring),
                                                 total, window, ws.h if ws else None, stream_handle(stream)))
+
+
+def decode_step_rope_paged(layer, q, k, v, d_positions, theta, d_len, d_ring, d_prefill, d_slots, batch, window, heads,
+                           out, ws, stream=None):
+    """rope + append + decode attention of one layer in one launch (q, k un-rotated)."""
+    check(lib().uocr_b200_rswa_decode_step_rope_paged(layer.ref(), _p(q), _p(k), _p(v), _p(d_positions), float(theta),
+                                                       _p(d_len), _p(d_ring), _p(d_prefill), _p(d_slots), batch, window,
+                                                       heads, _p(out), ws.h, stream_handle(stream)))
 
 
 def decode_step_paged(layer, q, k, v, d_len, d_ring, d_prefill, d_slots, batch, window, heads, out, ws, stream=None):

@@ -88,6 +88,10 @@ struct AttnParams {
     int cta_frac[kMaxCtas + 1];            // cumulative shares scaled to 1 << 20
     uint8_t slot_of_smid[kMaxSmid];        // share index of an SM id, 255 if it was never seen
     int* claim;                            // [ctas]
+    // fused decode step with rotary embedding: q and the new k row are rotated on the fly
+    // (uocr::cuda::rope, src/kernels/cuda/rope_fused.cu:12-40; src/kernels/cpu_ops.cpp:157-180)
+    const int* rope_pos;    // [rows] position of each batch row
+    float rope_freq[128];   // theta^(-2i/head_dim), i < head_dim/2, computed on the host in fp32
     // fused decode step only
     PlanParams plan;
     const float* k_new;
@@ -412,8 +416,24 @@ __device__ __forceinline__ int resolve_claim(int first, int want, int* claim, in
     return blockIdx.x;
 }
 
-template <typename KV, int HD, bool PAGED, bool FUSED>
+// Rotation of one 16-byte chunk's worth of elements (EPC of them, first dim d0) of a head row.  `own`
+// are the elements themselves, `other` the elements HD/2 away (the chunk lies in one half of the row):
+// v[i] = x0 c - x1 s, v[i + HD/2] = x0 s + x1 c with x0 the lower-half and x1 the upper-half element.
+template <int HD, int EPC>
+__device__ __forceinline__ void rope_chunk(const float* freq, float pos, int d0, const float (&own)[EPC],
+                                           const float (&other)[EPC], float (&out)[EPC]) {
+    const bool lower = d0 < HD / 2;
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) {
+        float sn, cs;
+        sincosf(pos * freq[(d0 + e) & (HD / 2 - 1)], &sn, &cs);
+        out[e] = lower ? own[e] * cs - other[e] * sn : other[e] * sn + own[e] * cs;
+    }
+}
+
+template <typename KV, int HD, bool PAGED, bool FUSED, bool ROPE = false>
 __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant__ AttnParams p) {
+    static_assert(!ROPE || (FUSED && HD >= 2 * KV::kPerChunk), "rotary embedding: fused step only, a chunk must lie in one half of the head");
     using M = TileMap<KV, HD>;
     constexpr int LPR = M::kLanesPerRow, CPL = M::kChunksPerLane, RPW = M::kRowsPerLoad;
     constexpr int ITER = M::kIters, EPC = KV::kPerChunk, EPL = M::kElemsPerLane;
@@ -579,11 +599,26 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
 #pragma unroll
             for (int cp = 0; cp < CPL; ++cp) {
                 const int d0 = (g + 32 * cp) * EPC;
+                if constexpr (ROPE) {
+                    float own[EPC], other[EPC], rot[EPC];
 #pragma unroll
-                for (int e = 0; e < EPC; e += 4) {
-                    const float4 t = __ldg(reinterpret_cast<const float4*>(qp + d0 + e));
-                    q2[(cp * EPC + e) / 2] = make_float2(t.x * p.scale_log2e, t.y * p.scale_log2e);
-                    q2[(cp * EPC + e) / 2 + 1] = make_float2(t.z * p.scale_log2e, t.w * p.scale_log2e);
+                    for (int e = 0; e < EPC; e += 4) {
+                        const float4 a = __ldg(reinterpret_cast<const float4*>(qp + d0 + e));
+                        const float4 b = __ldg(reinterpret_cast<const float4*>(qp + (d0 ^ (HD / 2)) + e));
+                        own[e] = a.x; own[e + 1] = a.y; own[e + 2] = a.z; own[e + 3] = a.w;
+                        other[e] = b.x; other[e + 1] = b.y; other[e + 2] = b.z; other[e + 3] = b.w;
+                    }
+                    rope_chunk<HD, EPC>(p.rope_freq, (float)__ldg(p.rope_pos + item / p.heads), d0, own, other, rot);
+#pragma unroll
+                    for (int e = 0; e < EPC; e += 2)
+                        q2[(cp * EPC + e) / 2] = make_float2(rot[e] * p.scale_log2e, rot[e + 1] * p.scale_log2e);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < EPC; e += 4) {
+                        const float4 t = __ldg(reinterpret_cast<const float4*>(qp + d0 + e));
+                        q2[(cp * EPC + e) / 2] = make_float2(t.x * p.scale_log2e, t.y * p.scale_log2e);
+                        q2[(cp * EPC + e) / 2 + 1] = make_float2(t.z * p.scale_log2e, t.w * p.scale_log2e);
+                    }
                 }
             }
 #pragma unroll
@@ -733,7 +768,24 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
                     for (int ch = lane; ch < M::kChunks; ch += 32) {
                         const float* src = p.k_new + ((size_t)r * p.kv_heads + kvh) * HD + ch * EPC;
                         uint4 w;
-                        if constexpr (EPC == 8) {
+                        if constexpr (ROPE) {
+                            const float* oth = p.k_new + ((size_t)r * p.kv_heads + kvh) * HD + ((ch * EPC) ^ (HD / 2));
+                            float own[EPC], other[EPC], rot[EPC];
+#pragma unroll
+                            for (int e = 0; e < EPC; e += 4) {
+                                const float4 a = __ldg(reinterpret_cast<const float4*>(src + e));
+                                const float4 b = __ldg(reinterpret_cast<const float4*>(oth + e));
+                                own[e] = a.x; own[e + 1] = a.y; own[e + 2] = a.z; own[e + 3] = a.w;
+                                other[e] = b.x; other[e + 1] = b.y; other[e + 2] = b.z; other[e + 3] = b.w;
+                            }
+                            rope_chunk<HD, EPC>(p.rope_freq, (float)__ldg(p.rope_pos + r), ch * EPC, own, other, rot);
+                            if constexpr (EPC == 8)
+                                w = make_uint4(pack_bf16x2(rot[0], rot[1]), pack_bf16x2(rot[2], rot[3]),
+                                               pack_bf16x2(rot[4], rot[5]), pack_bf16x2(rot[6], rot[7]));
+                            else
+                                w = make_uint4(__float_as_uint(rot[0]), __float_as_uint(rot[1]), __float_as_uint(rot[2]),
+                                               __float_as_uint(rot[3]));
+                        } else if constexpr (EPC == 8) {
                             const float4 a = __ldg(reinterpret_cast<const float4*>(src));
                             const float4 b = __ldg(reinterpret_cast<const float4*>(src + 4));
                             w = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),

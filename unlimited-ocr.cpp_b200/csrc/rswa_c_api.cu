@@ -358,11 +358,13 @@ struct AttnCall {
     const float* v_new = nullptr;
     int* d_len_rw = nullptr;
     int* d_ring_rw = nullptr;
+    const int* rope_pos = nullptr;  // fused step with rotary embedding
+    float rope_theta = 0.f;
 };
 
 constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
 
-template <typename KV, int HD, bool PAGED, bool FUSED>
+template <typename KV, int HD, bool PAGED, bool FUSED, bool ROPE = false>
 int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, cudaStream_t st, bool dry,
                    bool overlap = false) {
     using M = TileMap<KV, HD>;
@@ -390,8 +392,8 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
     if (dry) return UOCR_B200_OK;
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     const int smem = bar_bytes + warps * per_warp + warps * kPendMax * (int)sizeof(int) + plan_bytes;
-    auto kern = rswa_attn_kernel<KV, HD, PAGED, FUSED>;
-    static int configured_smem[64] = {0};
+    auto kern = rswa_attn_kernel<KV, HD, PAGED, FUSED, ROPE>;
+    static int configured_smem[64] = {0};  // one per instantiation of this template
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_smem[dev] < smem) {
@@ -418,23 +420,31 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
     return after_launch("attention kernel");
 }
 
-template <typename KV, bool PAGED, bool FUSED>
+template <typename KV, bool PAGED, bool FUSED, bool ROPE = false>
 int dispatch_hd(int hd, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry, bool ov) {
     switch (hd) {
-        case 8: return launch_partial<KV, 8, PAGED, FUSED>(ap, di, warps, st, dry, ov);
-        case 16: return launch_partial<KV, 16, PAGED, FUSED>(ap, di, warps, st, dry, ov);
-        case 32: return launch_partial<KV, 32, PAGED, FUSED>(ap, di, warps, st, dry, ov);
-        case 64: return launch_partial<KV, 64, PAGED, FUSED>(ap, di, warps, st, dry, ov);
-        case 128: return launch_partial<KV, 128, PAGED, FUSED>(ap, di, warps, st, dry, ov);
-        case 256: return launch_partial<KV, 256, PAGED, FUSED>(ap, di, warps, st, dry, ov);
+        case 8:
+            if constexpr (!ROPE || KV::kBytes == 4) return launch_partial<KV, 8, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
+            break;
+        case 16: return launch_partial<KV, 16, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
+        case 32: return launch_partial<KV, 32, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
+        case 64: return launch_partial<KV, 64, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
+        case 128: return launch_partial<KV, 128, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
+        case 256: return launch_partial<KV, 256, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
         case 4:
-            if constexpr (KV::kBytes == 4) return launch_partial<KV, 4, PAGED, FUSED>(ap, di, warps, st, dry, ov);
-            [[fallthrough]];
-        default: return fail(UOCR_B200_ERR_UNSUPPORTED, "head_dim must be a power of two in [8,256] (bf16) or [4,256] (fp32)");
+            if constexpr (KV::kBytes == 4 && !ROPE) return launch_partial<KV, 4, PAGED, FUSED, ROPE>(ap, di, warps, st, dry, ov);
+            break;
+        default: break;
     }
+    if (ROPE) return fail(UOCR_B200_ERR_UNSUPPORTED, "rotary step: head_dim must be a power of two in [16,256] (bf16) or [8,256] (fp32)");
+    return fail(UOCR_B200_ERR_UNSUPPORTED, "head_dim must be a power of two in [8,256] (bf16) or [4,256] (fp32)");
 }
 
 int dispatch_partial(const AttnCall& c, const AttnParams& ap, const DeviceInfo& di, int* warps, cudaStream_t st, bool dry, bool ov = false) {
+    if (c.fused && c.rope_pos) {
+        if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, true, true>(c.head_dim, ap, di, warps, st, dry, ov);
+        return dispatch_hd<F32, true, true, true>(c.head_dim, ap, di, warps, st, dry, ov);
+    }
     if (c.fused) {
         if (c.dtype == UOCR_B200_BF16) return dispatch_hd<BF16, true, true>(c.head_dim, ap, di, warps, st, dry, ov);
         return dispatch_hd<F32, true, true>(c.head_dim, ap, di, warps, st, dry, ov);
@@ -488,6 +498,11 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.d_len = c.d_len_rw;
     ap.d_ring_pos = c.d_ring_rw;
     ap.done_ctas = ws->done_ctas;
+    if (c.rope_pos) {
+        ap.rope_pos = c.rope_pos;
+        // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
+        for (int i = 0; i < c.head_dim / 2; ++i) ap.rope_freq[i] = std::pow(c.rope_theta, -2.0f * i / static_cast<float>(c.head_dim));
+    }
     ap.dyn_next = ws->dyn_next;
     ap.dyn_cap = ws->dyn_cap;
     if (ws->calibrated_ctas == di->sms) {
@@ -935,6 +950,28 @@ int uocr_b200_rswa_decode_step_paged(const uocr_b200_paged_kv* kv, const float* 
     if (int rc = fill_paged(c, kv)) return rc;
     c.rows = batch; c.heads = heads; c.q = q; c.out = out;
     c.fused = true; c.k_new = k; c.v_new = v; c.d_len_rw = d_len; c.d_ring_rw = d_ring_pos;
+    c.plan.mode = kPlanDecodeStep; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_ring_pos = d_ring_pos;
+    c.plan.d_prefill_len = d_prefill_len; c.plan.window = window;
+    return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uocr_b200_rswa_decode_step_rope_paged(const uocr_b200_paged_kv* kv, const float* q, const float* k, const float* v,
+                                          const int* d_positions, float theta, int* d_len, int* d_ring_pos,
+                                          const int* d_prefill_len, const int* d_slots, int batch, int window, int heads,
+                                          float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    if (!k || !v || !d_positions || !d_len || !d_ring_pos || !d_prefill_len || !d_slots)
+        return fail(UOCR_B200_ERR_INVALID, "decode_step_rope_paged: null pointer");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "decode_step_rope_paged: window must be positive");
+    if (!(theta > 0.f)) return fail(UOCR_B200_ERR_INVALID, "decode_step_rope_paged: theta must be positive");
+    if (!aligned16(k) || !aligned16(v)) return fail(UOCR_B200_ERR_INVALID, "decode_step_rope_paged: k/v must be 16-byte aligned");
+    if (batch > kFusedMaxRows)
+        return fail(UOCR_B200_ERR_UNSUPPORTED, "decode_step_rope_paged: at most 1024 rows per call");
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    c.rows = batch; c.heads = heads; c.q = q; c.out = out;
+    c.fused = true; c.k_new = k; c.v_new = v; c.d_len_rw = d_len; c.d_ring_rw = d_ring_pos;
+    c.rope_pos = d_positions; c.rope_theta = theta;
     c.plan.mode = kPlanDecodeStep; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_ring_pos = d_ring_pos;
     c.plan.d_prefill_len = d_prefill_len; c.plan.window = window;
     return run_attention(c, ws, reinterpret_cast<cudaStream_t>(stream));

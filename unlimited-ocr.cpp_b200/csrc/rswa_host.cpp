@@ -1011,6 +1011,14 @@ void PagedBatchKV::decode_step(int layer, const float* q, const float* k, const 
     abi_ok(uocr_b200_rswa_decode_step_paged(&s.view[layer], q, k, v, d_len(layer), d_ring_pos(layer), s.d_prefill, d_slots,
                                             batch, s.cfg.window, heads, out, s.ws, stream), "decode_step");
 }
+void PagedBatchKV::decode_step_rope(int layer, const float* q, const float* k, const float* v, const int* d_positions,
+                                    float theta, const int* d_slots, int batch, int heads, float* out, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(batch <= s.cfg.slots, "batch_decode size out of range");
+    abi_ok(uocr_b200_rswa_decode_step_rope_paged(&s.view[layer], q, k, v, d_positions, theta, d_len(layer), d_ring_pos(layer),
+                                                 s.d_prefill, d_slots, batch, s.cfg.window, heads, out, s.ws, stream),
+           "decode_step_rope");
+}
 void PagedBatchKV::write_prefill_ragged(int layer, const float* k, const float* v, const int* d_row_slots,
                                         const int* d_pos, int total, cudaStream_t stream) {
     Impl& s = *p_;

@@ -390,6 +390,10 @@ public:
                          cudaStream_t stream = nullptr);
     void decode_step(int layer, const float* q, const float* k, const float* v, const int* d_slots, int batch,
                      int heads, float* out, cudaStream_t stream = nullptr);
+    // decode_step with uocr::cuda::rope folded in: q and k are the un-rotated projections, d_positions[b]
+    // the position of batch row b (src/engine/gpu_decoder.cu:988-996 in one launch).
+    void decode_step_rope(int layer, const float* q, const float* k, const float* v, const int* d_positions, float theta,
+                          const int* d_slots, int batch, int heads, float* out, cudaStream_t stream = nullptr);
     void write_prefill_ragged(int layer, const float* k, const float* v, const int* d_row_slots, const int* d_pos,
                               int total, cudaStream_t stream = nullptr);
     void attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total, int heads,
