@@ -331,6 +331,14 @@ UOCR_B200_API int uocr_b200_rswa_gather_paged(
     int n, int capacity_rows, void* out_k, void* out_v, int out_dtype, uocr_b200_workspace* ws,
     uocr_b200_stream_t stream);
 
+/* The same view in the layout of the reference's cache snapshots (tools/reference/export_reference.py:
+ * 110-117, read back by tools/compare_reference.cpp:219-241): fp32 out[i][kv_head][s][head_dim], rows
+ * at and beyond the slot's length zero-filled.  Used by the snapshot export of the host classes. */
+UOCR_B200_API int uocr_b200_rswa_gather_heads_paged(
+    const uocr_b200_paged_kv* kv, const int* d_len, const int* d_prefill_len, const int* d_slots,
+    int n, int capacity_rows, float* out_k, float* out_v, uocr_b200_workspace* ws,
+    uocr_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

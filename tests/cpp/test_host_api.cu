@@ -418,6 +418,32 @@ static void test_windowed_prefill(bool tensor_cores) {
         }
     }
     EXPECT(kv.device_status() == 0);
+    if (!tensor_cores) {
+        // snapshot of slot 1 in the reference's export format: [kv_heads, len, head_dim] fp32 per layer
+        const char* env = std::getenv("UOCR_SNAPSHOT_DIR");
+        const std::string dir = env ? env : "/tmp";
+        kv.export_snapshot(dir, 1, "final");
+        for (int l = 0; l < cfg.layers; ++l) {
+            const int n = orc_cache_len(o[1], l);
+            for (int which = 0; which < 2; ++which) {
+                const std::string path = dir + "/final_" + (which ? "v_" : "k_") + std::to_string(l) + ".bin";
+                std::vector<float> file((size_t)cfg.kv_heads * n * cfg.head_dim);
+                FILE* f = std::fopen(path.c_str(), "rb");
+                EXPECT(f != nullptr);
+                if (!f) continue;
+                EXPECT(std::fread(file.data(), 4, file.size(), f) == file.size());
+                EXPECT(std::fgetc(f) == EOF);
+                std::fclose(f);
+                const float* want = which ? orc_cache_values(o[1], l) : orc_cache_keys(o[1], l);
+                bool same = true;
+                for (int h = 0; h < cfg.kv_heads && same; ++h)
+                    for (int t = 0; t < n && same; ++t)
+                        same = std::memcmp(&file[((size_t)h * n + t) * cfg.head_dim],
+                                           want + ((size_t)t * cfg.kv_heads + h) * cfg.head_dim, cfg.head_dim * 4) == 0;
+                EXPECT(same);
+            }
+        }
+    }
     for (int sl = 0; sl < 3; ++sl) orc_cache_destroy(o[sl]);
     cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dout); cudaFree(gk); cudaFree(gv); cudaFree(d_ident);
 }

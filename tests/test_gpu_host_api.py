@@ -46,11 +46,23 @@ def test_rswa_cache_class_matches_reference_golden(host, name):
         assert np.abs(r["prefill_attn"] - g("prefill_attn")).max() <= 2e-5
 
 
-def test_cpp_host_api_binary():
+def test_cpp_host_api_binary(tmp_path):
     if not os.path.exists(build_cpp_tests.HOST_API_BIN):
         build_cpp_tests.build(ref_root="/nonexistent")
-    out = subprocess.run([build_cpp_tests.HOST_API_BIN], capture_output=True, text=True, timeout=600)
+    env = dict(os.environ, UOCR_SNAPSHOT_DIR=str(tmp_path))
+    out = subprocess.run([build_cpp_tests.HOST_API_BIN], capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0 and "ALL OK" in out.stdout, out.stdout + out.stderr
+    # the snapshot the binary exported (contents already checked there against the oracle): the manifest
+    # must be real JSON in the reference's export layout, and every tensor file as large as its shape says
+    import json
+    man = json.loads((tmp_path / "manifest.json").read_text())
+    assert man["cache_layers"] == 2 and man["window"] == 16 and man["final_cache_len"] > 0
+    assert sorted(man["tensors"]) == ["final_k_0", "final_k_1", "final_v_0", "final_v_1"]
+    for name, entry in man["tensors"].items():
+        assert entry["dtype"] == "<f4" and entry["file"] == name + ".bin"
+        assert entry["shape"] == [man["kv_heads"], man["final_cache_len"], man["head_dim"]]
+        data = np.fromfile(tmp_path / entry["file"], dtype="<f4")
+        assert data.size == int(np.prod(entry["shape"])) and np.isfinite(data).all() and np.abs(data).max() > 0
 
 
 def test_reference_kv_ring_buffer_tests_on_this_library():

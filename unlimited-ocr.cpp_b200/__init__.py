@@ -92,6 +92,7 @@ _SIGS = {
     "uocr_b200_rswa_attention_f32": (_i, [_vp] * 3 + [_i, _vp] + [_i] * 6 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_paged": (_i, [C.POINTER(PagedKV), _i, _vp, _i, _vp, _i, _vp] + [_i] * 4 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_gather_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 3 + [_i, _i, _vp, _vp, _i, _vp, _vp]),
+    "uocr_b200_rswa_gather_heads_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 3 + [_i, _i, _vp, _vp, _vp, _vp]),
 }
 
 
@@ -321,6 +322,12 @@ def gather_paged(layer, d_len, d_prefill, d_slots, n, capacity_rows, out_k, out_
     check(lib().uocr_b200_rswa_gather_paged(layer.ref(), _p(d_len), _p(d_prefill), _p(d_slots), n, capacity_rows,
                                              _p(out_k), _p(out_v), out_dtype, ws.h if ws else None,
                                              stream_handle(stream)))
+
+
+def gather_heads_paged(layer, d_len, d_prefill, d_slots, n, capacity_rows, out_k, out_v, ws=None, stream=None):
+    """fp32 out[n][kv_heads][capacity_rows][head_dim]: the layout of the reference's cache snapshots."""
+    check(lib().uocr_b200_rswa_gather_heads_paged(layer.ref(), _p(d_len), _p(d_prefill), _p(d_slots), n, capacity_rows,
+                                                   _p(out_k), _p(out_v), ws.h if ws else None, stream_handle(stream)))
 
 
 def append_decode_batch_f32(k, v, kbase, vbase, d_len, d_ring, d_prefill, d_slots, batch, batch_cap, window,

@@ -1003,6 +1003,26 @@ int uocr_b200_rswa_gather_paged(const uocr_b200_paged_kv* kv, const int* d_len, 
     return after_launch("gather (paged)");
 }
 
+int uocr_b200_rswa_gather_heads_paged(const uocr_b200_paged_kv* kv, const int* d_len, const int* d_prefill_len,
+                                      const int* d_slots, int n, int capacity_rows, float* out_k, float* out_v,
+                                      uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (n <= 0 || capacity_rows <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!d_len || !d_prefill_len || !d_slots || !out_k || !out_v) return fail(UOCR_B200_ERR_INVALID, "gather_heads_paged: null pointer");
+    if (!aligned16(out_k) || !aligned16(out_v)) return fail(UOCR_B200_ERR_INVALID, "gather_heads_paged: outputs must be 16-byte aligned");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    dim3 grid(capacity_rows, n);
+    uint8_t* ok = reinterpret_cast<uint8_t*>(out_k);
+    uint8_t* ov = reinterpret_cast<uint8_t*>(out_v);
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_gather_paged_kernel<BF16, true, true><<<grid, 160, 0, st>>>(pv, d_len, d_prefill_len, d_slots, capacity_rows, ok, ov, status);
+    else
+        rswa_gather_paged_kernel<F32, false, true><<<grid, 160, 0, st>>>(pv, d_len, d_prefill_len, d_slots, capacity_rows, ok, ov, status);
+    return after_launch("gather (paged, head-major)");
+}
+
 }  // extern "C"
 
 // =================================================================================================

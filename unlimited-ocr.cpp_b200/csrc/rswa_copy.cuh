@@ -232,8 +232,9 @@ __global__ void __launch_bounds__(256) rswa_ring_fill_kernel(
 }
 
 // Gather: logical row s of slot d_slots[i] -> out[i][s][:]; rows >= len are zero-filled.
+// HEAD_MAJOR: out[i][head][s][:] instead (the layout of the reference's exported cache snapshots).
 // grid = (capacity_rows, n); one thread per 16-byte pool chunk.
-template <typename KV, bool WIDEN>
+template <typename KV, bool WIDEN, bool HEAD_MAJOR = false>
 __global__ void __launch_bounds__(256) rswa_gather_paged_kernel(
     PagedView pv, const int* __restrict__ d_len, const int* __restrict__ d_prefill_len,
     const int* __restrict__ d_slots, int capacity_rows, uint8_t* __restrict__ out_k,
@@ -265,23 +266,25 @@ __global__ void __launch_bounds__(256) rswa_gather_paged_kernel(
     }
     for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
         const int e0 = c * EPC;
+        const int head = e0 / hd, d = e0 - head * hd;
         uint4 kw = make_uint4(0, 0, 0, 0), vw = kw;
         if (blk >= 0) {
-            const int head = e0 / hd, d = e0 - head * hd;
             const size_t src = ((((size_t)blk * pv.kv_heads + head) * kBlockTokens + off) * hd + d) * KV::kBytes;
             kw = *reinterpret_cast<const uint4*>(pv.k_pool + src);
             vw = *reinterpret_cast<const uint4*>(pv.v_pool + src);
         }
+        const size_t dst = HEAD_MAJOR ? ((((size_t)i * pv.kv_heads + head) * capacity_rows + s) * hd + d) * OUT_B
+                                      : out_row + (size_t)e0 * OUT_B;
         if constexpr (WIDEN && EPC == 8) {
-            float4* ko = reinterpret_cast<float4*>(out_k + out_row + (size_t)e0 * 4);
-            float4* vo = reinterpret_cast<float4*>(out_v + out_row + (size_t)e0 * 4);
+            float4* ko = reinterpret_cast<float4*>(out_k + dst);
+            float4* vo = reinterpret_cast<float4*>(out_v + dst);
             ko[0] = make_float4(bf16_lo(kw.x), bf16_hi(kw.x), bf16_lo(kw.y), bf16_hi(kw.y));
             ko[1] = make_float4(bf16_lo(kw.z), bf16_hi(kw.z), bf16_lo(kw.w), bf16_hi(kw.w));
             vo[0] = make_float4(bf16_lo(vw.x), bf16_hi(vw.x), bf16_lo(vw.y), bf16_hi(vw.y));
             vo[1] = make_float4(bf16_lo(vw.z), bf16_hi(vw.z), bf16_lo(vw.w), bf16_hi(vw.w));
         } else {
-            *reinterpret_cast<uint4*>(out_k + out_row + (size_t)e0 * OUT_B) = kw;
-            *reinterpret_cast<uint4*>(out_v + out_row + (size_t)e0 * OUT_B) = vw;
+            *reinterpret_cast<uint4*>(out_k + dst) = kw;
+            *reinterpret_cast<uint4*>(out_v + dst) = vw;
         }
     }
 }

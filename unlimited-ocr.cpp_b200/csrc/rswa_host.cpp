@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstring>
 #include <ctime>
+#include <map>
 
 namespace uocr {
 
@@ -823,6 +824,9 @@ struct PagedBatchKV::Impl {
     int pf_cap = 0, pf_nv = 0, pf_nt = 0;
     std::vector<uocr_b200_prefill_tile> pf_tiles;
     int ws_rows = 0;
+    // snapshot export: manifest entries written so far, per directory (tensor name -> "file/shape" json)
+    std::map<std::string, std::map<std::string, std::string>> manifests;
+    std::map<std::string, std::map<std::string, long long>> manifest_ints;
 
     std::size_t block_bytes() const {
         return static_cast<std::size_t>(cfg.kv_heads) * UOCR_B200_BLOCK_TOKENS * cfg.head_dim *
@@ -1143,6 +1147,70 @@ void PagedBatchKV::windowed_prefill_layer(int layer, const float* q, const float
         abi_ok(uocr_b200_rswa_ring_fill_paged(view, s.text_k, s.text_v, s.text_blocks, t_slots, t_pos, t_b0, t_len, s.d_prefill,
                                               d_len(layer), d_ring_pos(layer), nt, s.cfg.window, s.ws, stream),
                "windowed prefill: ring fill");
+}
+
+void PagedBatchKV::export_snapshot(const std::string& dir, int slot, const std::string& tag, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(slot >= 0 && slot < s.cfg.slots && s.slot[slot].bound, "export_snapshot: slot not admitted");
+    UOCR_CHECK(tag == "prefill" || tag == "final", "export_snapshot: tag must be \"prefill\" or \"final\"");
+    const int cap = s.cfg.max_prefix_tokens + s.cfg.window, kvh = s.cfg.kv_heads, hd = s.cfg.head_dim;
+    const std::size_t elems = static_cast<std::size_t>(kvh) * cap * hd;
+    float *dk = nullptr, *dv = nullptr;
+    int* d_slot = nullptr;
+    cuda_ok(cudaMalloc(&dk, elems * sizeof(float)), "snapshot K buffer");
+    cudaError_t e = cudaMalloc(&dv, elems * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&d_slot, sizeof(int));
+    std::vector<float> hk(elems), hv(elems);
+    std::vector<int> lens(static_cast<std::size_t>(s.cfg.layers), 0);
+    std::string err;
+    auto write_bin = [&](const std::string& name, const std::vector<float>& full, int len) {
+        // full is [kvh][cap][hd]; the file keeps the first `len` rows of every head
+        FILE* f = std::fopen((dir + "/" + name + ".bin").c_str(), "wb");
+        if (!f) { err = "cannot write " + dir + "/" + name + ".bin"; return; }
+        for (int h = 0; h < kvh && err.empty(); ++h)
+            if (len > 0 && std::fwrite(full.data() + static_cast<std::size_t>(h) * cap * hd, sizeof(float),
+                                       static_cast<std::size_t>(len) * hd, f) != static_cast<std::size_t>(len) * hd)
+                err = "short write to " + dir + "/" + name + ".bin";
+        std::fclose(f);
+        s.manifests[dir][name] = "{\"file\": \"" + name + ".bin\", \"shape\": [" + std::to_string(kvh) + ", " +
+                                 std::to_string(len) + ", " + std::to_string(hd) + "], \"dtype\": \"<f4\"}";
+    };
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_slot, &slot, sizeof(int), cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemcpy2DAsync(lens.data(), sizeof(int), s.d_len + slot, sizeof(int) * s.cfg.slots, sizeof(int),
+                                                s.cfg.layers, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    for (int l = 0; l < s.cfg.layers && e == cudaSuccess && err.empty(); ++l) {
+        const int rc = uocr_b200_rswa_gather_heads_paged(&s.view[l], d_len(l), s.d_prefill, d_slot, 1, cap, dk, dv, s.ws, stream);
+        if (rc != UOCR_B200_OK) { err = std::string("gather: ") + uocr_b200_last_error(); break; }
+        e = cudaMemcpyAsync(hk.data(), dk, elems * sizeof(float), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(hv.data(), dv, elems * sizeof(float), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) break;
+        write_bin(tag + "_k_" + std::to_string(l), hk, lens[l]);
+        if (err.empty()) write_bin(tag + "_v_" + std::to_string(l), hv, lens[l]);
+    }
+    cudaFree(dk);
+    if (dv) cudaFree(dv);
+    if (d_slot) cudaFree(d_slot);
+    cuda_ok(e, "export_snapshot");
+    if (!err.empty()) UOCR_THROW("export_snapshot: " + err);
+    auto& ints = s.manifest_ints[dir];
+    ints["window"] = s.cfg.window;
+    ints["cache_layers"] = s.cfg.layers;
+    ints["kv_heads"] = kvh;
+    ints["head_dim"] = hd;
+    ints[tag + "_cache_len"] = lens[0];
+    FILE* f = std::fopen((dir + "/manifest.json").c_str(), "w");
+    if (!f) UOCR_THROW("export_snapshot: cannot write " + dir + "/manifest.json");
+    std::fprintf(f, "{\n");
+    for (const auto& kv : ints) std::fprintf(f, "  \"%s\": %lld,\n", kv.first.c_str(), kv.second);
+    std::fprintf(f, "  \"tensors\": {\n");
+    std::size_t i = 0;
+    const auto& tensors = s.manifests[dir];
+    for (const auto& kv : tensors)
+        std::fprintf(f, "    \"%s\": %s%s\n", kv.first.c_str(), kv.second.c_str(), ++i < tensors.size() ? "," : "");
+    std::fprintf(f, "  }\n}\n");
+    std::fclose(f);
 }
 
 void PagedBatchKV::attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total,

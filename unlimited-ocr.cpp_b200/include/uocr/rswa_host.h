@@ -419,6 +419,15 @@ public:
     // Logical fp32 view of `n` slots: out[i] is [max_prefix_tokens + window][kv_heads*head_dim].
     void gather(int layer, const int* d_slots, int n, float* out_k, float* out_v, cudaStream_t stream = nullptr);
 
+    // Cache snapshot of one slot in the reference's on-disk alignment format (written by
+    // tools/reference/export_reference.py:21-26,110-117,155-160; read by tools/compare_reference.cpp:25-36,
+    // 219-241): per layer `<tag>_k_<l>.bin` and `<tag>_v_<l>.bin`, raw little-endian fp32 of shape
+    // [kv_heads, len, head_dim] (logical slot order: prefix, then ring slots), and `manifest.json` with
+    // one {"file","shape","dtype":"<f4"} entry per tensor plus "window", "cache_layers", "kv_heads",
+    // "head_dim" and "<tag>_cache_len".  tag is "prefill" or "final"; a second call with another tag into
+    // the same directory extends the manifest.  Synchronises the stream and writes files: not capturable.
+    void export_snapshot(const std::string& dir, int slot, const std::string& tag, cudaStream_t stream = nullptr);
+
     const BlockManager& blocks() const;
     const std::vector<int>& table_row(int slot) const;  // host copy of the slot's block ids (-1 = unused)
     int device_status(cudaStream_t stream = nullptr);   // synchronises; 0 = no kernel recorded a fault
