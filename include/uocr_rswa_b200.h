@@ -82,6 +82,14 @@ UOCR_B200_API int uocr_b200_workspace_status(uocr_b200_workspace* ws, uocr_b200_
 UOCR_B200_API int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled);
 UOCR_B200_API int uocr_b200_workspace_last_kernel_ms(uocr_b200_workspace* ws, float* ms);
 
+/* Output type of every attention entry point that takes this workspace (the split-KV family, the
+ * fused decode steps and the tensor-core prefill): UOCR_B200_F32 (default, the reference's
+ * interface) or UOCR_B200_BF16, in which case `out` is read as uint16 bf16 [rows][heads*head_dim]
+ * (round-to-nearest-even on the raw bits, include/uocr/common.h:56-64) -- the input the o-projection
+ * GEMM that follows the path (src/engine/gpu_decoder.cu:997) reads at half the bytes.  The setting
+ * is read when a call is issued (and frozen into captured graphs). */
+UOCR_B200_API int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int dtype);
+
 /* Opt-in launch overlap for uocr_b200_rswa_decode_step_paged calls that use this workspace.  When
  * enabled, the step is launched with programmatic stream serialization: its prologue (planning from
  * the layer's cursors, block-table reads, the first KV tiles) may run while the preceding kernel in

@@ -339,6 +339,43 @@ def test_fused_decode_step_with_rope(orc, b, dtype_name, hd, theta):
     assert pb.ws.status() == 0
 
 
+def test_bf16_attention_output(orc, b):
+    # workspace option: results written as bf16 (RNE) for the o-projection.  Separate and fused calls, an
+    # item merged from several partials (long rows) and rows written directly; against RNE(oracle).
+    import torch
+    slots, W, P, kvh, hd = 6, 64, 600, 10, 128
+    pb = PagedBatch(orc, slots, 1, kvh, hd, W, b.BF16, [P, P, 40, P, 0, P], prefix_keys=["d", "d", "e", "d", "f", "d"], seed=23)
+    pb.write_prefixes()
+    pb.ws.set_out_dtype(b.BF16)
+    rows = [5, 1, 4, 0, 2, 3]
+    ds = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    for t in range(4):
+        k, v, q = pb.step_inputs(t, 0, rows)
+        out = torch.full((slots, kvh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dq = torch.from_numpy(q).cuda()
+        if t % 2:
+            pb.append(0, k, v, rows)
+            b.attention_batch_paged(pb.layer[0], dq, pb.d_len[0], pb.d_prefill, ds, slots, kvh, out, pb.ws)
+        else:
+            b.decode_step_paged(pb.layer[0], dq, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), pb.d_len[0],
+                                pb.d_ring[0], pb.d_prefill, ds, slots, W, kvh, out, pb.ws)
+            for i, s in enumerate(rows):
+                pb.cache[s].append_decode(0, k[i], v[i])
+        got = out.float().cpu().numpy()
+        want = np.stack([pb.cache[s].attention(0, q[i:i + 1], pb.cache[s].len(0) - 1, kvh, False)[0]
+                         for i, s in enumerate(rows)])
+        assert np.isfinite(got).all()
+        exact = got == synth.round_bf16(want)
+        assert exact.mean() > 0.99                                       # fp32 reassociation flips a rounding now and then
+        # never more than half a bf16 ulp (<= |x| / 256) off, plus the fp32 difference that caused a flip
+        assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -8 + 2e-6).all()
+    pb.ws.set_out_dtype(b.F32)
+    k, v, q = pb.step_inputs(9, 0, rows)
+    got, want = pb.step_fused(0, k, v, q, rows)
+    assert_attention_close(got, want, *TIGHT)
+    assert pb.ws.status() == 0
+
+
 def test_fused_step_graph_replay(orc, b):
     import torch
     slots, W, P, kvh, hd = 4, 16, 9, 2, 64

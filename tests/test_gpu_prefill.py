@@ -136,3 +136,31 @@ def test_prefill_tensor_core_real_geometry(orc, b):
     # 10 heads x 128, prefixes and prompts spanning several 128-row / 128-key tiles, window shorter than prompts
     run_prefill_case(orc, b, b.BF16, 10, 128, 10, 160, prefixes=[272, 48, 656], text_lens=[300, 130, 64], seed=92,
                      engine="tc")
+
+
+def test_prefill_tensor_core_bf16_output(orc, b):
+    # the workspace's bf16 output option on the tcgen05 path: same rows as fp32, rounded to nearest even
+    import torch
+    kvh = heads = 2
+    hd, W, P, T = 128, 48, 40, 150
+    pb = PagedBatch(orc, 1, 1, kvh, hd, W, b.BF16, [P], heads=heads, seed=31)
+    pb.write_prefixes()
+    ws = b.Workspace(256)
+    nb = ceil_div(T, 16)
+    text_k = torch.zeros((nb, kvh, 16, hd), dtype=torch.bfloat16, device="cuda")
+    text_v = torch.zeros_like(text_k)
+    k = pb.rnd(synth.normal(31, 51, (T, kvh * hd)))
+    v = pb.rnd(synth.normal(31, 52, (T, kvh * hd)))
+    q = synth.normal(31, 53, (P + T, heads * hd))
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    pos = np.arange(T, dtype=np.int32)
+    b.text_scatter_paged(pb.layer[0], text_k, text_v, nb, d(k), d(v), d(pos), d(np.zeros(T, np.int32)), T, ws)
+    tiles = b.make_prefill_tiles([(0, P, 0, 0, 0, 0), (P, T, 0, 1, 0, 0)])
+    out32 = torch.full((P + T, heads * hd), float("nan"), device="cuda")
+    b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles, W, heads, out32, ws)
+    ws.set_out_dtype(b.BF16)
+    out16 = torch.full((P + T, heads * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles, W, heads, out16, ws)
+    a, c = out32.cpu().numpy(), out16.float().cpu().numpy()
+    assert np.isfinite(a).all() and np.array_equal(c, synth.round_bf16(a))  # same kernel, same fp32 values, RNE
+    assert ws.status() == 0

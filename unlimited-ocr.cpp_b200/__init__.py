@@ -69,6 +69,7 @@ _SIGS = {
     "uocr_b200_workspace_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "uocr_b200_workspace_set_timing": (_i, [_vp, _i]),
     "uocr_b200_workspace_set_overlap": (_i, [_vp, _i]),
+    "uocr_b200_workspace_set_out_dtype": (_i, [_vp, _i]),
     "uocr_b200_workspace_calibrate": (_i, [_vp, _i, _vp]),
     "uocr_b200_workspace_split_shares": (_i, [_vp, _vp, _i]),
     "uocr_b200_workspace_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
@@ -174,6 +175,10 @@ class Workspace:
 
     def set_timing(self, enabled: bool) -> None:
         check(lib().uocr_b200_workspace_set_timing(self.h, 1 if enabled else 0))
+
+    def set_out_dtype(self, dtype: int) -> None:
+        """F32 (default) or BF16: type of the `out` tensor of every attention call using this workspace."""
+        check(lib().uocr_b200_workspace_set_out_dtype(self.h, dtype))
 
     def set_overlap(self, enabled: bool) -> None:
         check(lib().uocr_b200_workspace_set_overlap(self.h, 1 if enabled else 0))

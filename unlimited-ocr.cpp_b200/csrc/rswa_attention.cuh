@@ -60,6 +60,7 @@ struct PlanParams {
 struct AttnParams {
     const float* q;
     float* out;
+    int out_bf16;  // 1: `out` holds bf16 [rows][heads * head_dim] (round-to-nearest-even on the raw bits), else fp32
     const uint8_t* k_base;
     const uint8_t* v_base;
     const uint8_t* k_text;  // text prefill: second pool (same block layout) holding the window tokens
@@ -713,7 +714,12 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
 #pragma unroll
                 for (int i = 0; i < (HD + 31) / 32; ++i) {
                     const int d = lane + 32 * i;
-                    if (d < HD) out_item[d] = o[i] * inv;
+                    if (d < HD) {
+                        if (p.out_bf16)
+                            reinterpret_cast<uint16_t*>(p.out)[(size_t)item * HD + d] = (uint16_t)f32_to_bf16_bits(o[i] * inv);
+                        else
+                            out_item[d] = o[i] * inv;
+                    }
                 }
             }
             pend_n = 0;
@@ -948,10 +954,16 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
                         for (int cp = 0; cp < CPL; ++cp) {
                             const int d0 = (g + 32 * cp) * EPC;
 #pragma unroll
-                            for (int e = 0; e < EPC; e += 4)
-                                *reinterpret_cast<float4*>(out_item + d0 + e) =
-                                    make_float4(acc[cp * EPC + e] * mul, acc[cp * EPC + e + 1] * mul,
-                                                acc[cp * EPC + e + 2] * mul, acc[cp * EPC + e + 3] * mul);
+                            for (int e = 0; e < EPC; e += 4) {
+                                if (p.out_bf16)
+                                    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)cur_item * HD + d0 + e) =
+                                        make_uint2(pack_bf16x2(acc[cp * EPC + e] * mul, acc[cp * EPC + e + 1] * mul),
+                                                   pack_bf16x2(acc[cp * EPC + e + 2] * mul, acc[cp * EPC + e + 3] * mul));
+                                else
+                                    *reinterpret_cast<float4*>(out_item + d0 + e) =
+                                        make_float4(acc[cp * EPC + e] * mul, acc[cp * EPC + e + 1] * mul,
+                                                    acc[cp * EPC + e + 2] * mul, acc[cp * EPC + e + 3] * mul);
+                            }
                         }
                     }
                 } else {

@@ -111,6 +111,7 @@ struct uocr_b200_workspace {
     int* claim = nullptr;                 // device, [2][kMaxCtas]
     int calibrated_ctas = 0;      // 0: even split
     unsigned seq = 0;             // launches issued; its low bit picks the claim array
+    bool out_bf16 = false;  // attention results are written as bf16 instead of fp32
     bool timing = false;
     bool overlap = false;  // fused decode step may start its prologue before the preceding kernel ends
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -299,6 +300,13 @@ int uocr_b200_workspace_split_shares(const uocr_b200_workspace* ws, int* out_fra
     return m;
 }
 
+int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int dtype) {
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_set_out_dtype: null workspace");
+    if (dtype != UOCR_B200_F32 && dtype != UOCR_B200_BF16) return fail(UOCR_B200_ERR_UNSUPPORTED, "workspace_set_out_dtype: fp32 or bf16");
+    ws->out_bf16 = dtype == UOCR_B200_BF16;
+    return UOCR_B200_OK;
+}
+
 int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled) {
     if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_set_overlap: null workspace");
     ws->overlap = enabled != 0;
@@ -472,6 +480,7 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     AttnParams ap{};
     ap.q = c.q;
     ap.out = c.out;
+    ap.out_bf16 = ws->out_bf16 ? 1 : 0;
     ap.k_base = static_cast<const uint8_t*>(c.k_base);
     ap.v_base = static_cast<const uint8_t*>(c.v_base);
     ap.k_text = static_cast<const uint8_t*>(c.k_text);
@@ -518,7 +527,7 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     c.plan.rs = ws->rs;
     c.plan.info = ws->info;
     c.plan.out = c.fused ? nullptr : c.out;
-    c.plan.out_row_elems = c.heads * c.head_dim;
+    c.plan.out_row_elems = c.heads * c.head_dim / (ws->out_bf16 ? 2 : 1);  // zero-filled as 32-bit words
     ap.plan = c.plan;
 
     int warps = 0;
@@ -889,6 +898,7 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     PrefillParams pp{};
     pp.q = q;
     pp.out = out;
+    pp.out_bf16 = ws->out_bf16 ? 1 : 0;
     pp.k_pool = pv.k_pool;
     pp.v_pool = pv.v_pool;
     pp.k_text = static_cast<const uint8_t*>(text_k_pool);

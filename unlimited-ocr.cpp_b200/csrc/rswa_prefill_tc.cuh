@@ -50,6 +50,7 @@ struct PrefillTile {
 struct PrefillParams {
     const float* q;
     float* out;
+    int out_bf16;  // 1: `out` holds bf16 rows (round-to-nearest-even), else fp32
     const uint8_t* k_pool;
     const uint8_t* v_pool;
     const uint8_t* k_text;
@@ -485,9 +486,15 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
 #pragma unroll 4
                 for (int k = 0; k < 16; ++k) {
                     const int row = warp * 16 + k;
-                    if (row < t.rows)
-                        reinterpret_cast<float4*>(p.out + ((size_t)(t.row0 + row) * p.heads + head) * kTcTile)[lane] =
-                            so[row * 32 + (lane ^ (row & 31))];
+                    if (row < t.rows) {
+                        const float4 o4 = so[row * 32 + (lane ^ (row & 31))];
+                        const size_t at = ((size_t)(t.row0 + row) * p.heads + head) * kTcTile;
+                        if (p.out_bf16)
+                            reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + at)[lane] =
+                                make_uint2(pack_bf16x2(o4.x, o4.y), pack_bf16x2(o4.z, o4.w));
+                        else
+                            reinterpret_cast<float4*>(p.out + at)[lane] = o4;
+                    }
                 }
             }
         }
