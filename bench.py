@@ -223,9 +223,10 @@ class DecodeWorkload:
         self.d_ring = torch.zeros((L, B), dtype=torch.int32, device="cuda")
         self.set_positions(self.pos0)
         self.d_positions = torch.from_numpy((plen + self.pos0).astype(np.int32)).cuda()  # rotary positions (--rope)
-        self.q = torch.randn((L, B, self.row), generator=g, device="cuda")
-        self.k = torch.randn((L, B, self.row), generator=g, device="cuda")
-        self.v = torch.randn((L, B, self.row), generator=g, device="cuda")
+        # q, k, v of a layer sit next to each other so that the end-to-end step can bring the inputs of
+        # several layers over in one copy
+        self.qkv = torch.randn((L, 3, B, self.row), generator=g, device="cuda")
+        self.q, self.k, self.v = self.qkv[:, 0], self.qkv[:, 1], self.qkv[:, 2]
         self.out = torch.zeros((L, B, self.row), device="cuda")
         self.ws = pkg.Workspace(B)
         self.ws.set_overlap(overlap)  # consecutive launches belong to different layers: overlap is safe
@@ -244,22 +245,25 @@ class DecodeWorkload:
         self.d_len.copy_(torch.from_numpy(np.tile(ln.astype(np.int32), (self.L, 1))))
         self.d_ring.copy_(torch.from_numpy(np.tile(rp.astype(np.int32), (self.L, 1))))
 
-    def step_plain(self, per_layer_hook=None):
+    def layer_step(self, l):
         p = self.pkg
+        if self.fused and self.rope:
+            p.decode_step_rope_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_positions, 10000.0,
+                                     self.d_len[l], self.d_ring[l], self.d_prefill, self.d_slots, self.B,
+                                     CFG["window"], CFG["heads"], self.out[l], self.ws)
+        elif self.fused:
+            p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
+                                self.ws)
+        else:
+            p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
+                                        self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
+            p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots,
+                                    self.B, CFG["heads"], self.out[l], self.ws)
+
+    def step_plain(self, per_layer_hook=None):
         for l in range(self.L):
-            if self.fused and self.rope:
-                p.decode_step_rope_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_positions, 10000.0,
-                                         self.d_len[l], self.d_ring[l], self.d_prefill, self.d_slots, self.B,
-                                         CFG["window"], CFG["heads"], self.out[l], self.ws)
-            elif self.fused:
-                p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
-                                    self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
-                                    self.ws)
-            else:
-                p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
-                                            self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
-                p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots,
-                                        self.B, CFG["heads"], self.out[l], self.ws)
+            self.layer_step(l)
             if per_layer_hook:
                 per_layer_hook(l)
 
@@ -278,37 +282,38 @@ class DecodeWorkload:
         self.graph.replay()
         self.steps_done += 1
 
-    def capture_e2e(self, hq, hk, hv, hout):
-        """One graph for a whole step fed from pinned host memory: three streams, layer-pipelined."""
-        torch, p = self.torch, self.pkg
+    def capture_e2e(self, hqkv, hout, chunks=(1, 3, 8)):
+        """One graph for a whole step fed from pinned host memory, three streams.  The inputs come over in
+        a few copies of growing size (layer 0 alone, so that compute starts early; the rest behind the
+        kernels of the layers before them); every layer's result goes back as soon as its kernel is done.
+        Few cross-stream waits keep the kernels of one chunk back to back on the compute stream."""
+        torch = self.torch
+        assert sum(chunks) == self.L
         h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             main = torch.cuda.current_stream()
             h2d.wait_stream(main)
             d2h.wait_stream(main)
-            for l in range(self.L):
-                with torch.cuda.stream(h2d):
-                    self.q[l].copy_(hq[l], non_blocking=True)
-                    self.k[l].copy_(hk[l], non_blocking=True)
-                    self.v[l].copy_(hv[l], non_blocking=True)
-                    ready = torch.cuda.Event()
-                    ready.record(h2d)
-                main.wait_event(ready)
-                if self.fused:
-                    p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
-                                        self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
-                                        self.ws)
-                else:
-                    p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
-                                                self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
-                    p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots,
-                                            self.B, CFG["heads"], self.out[l], self.ws)
-                done = torch.cuda.Event()
-                done.record(main)
-                d2h.wait_event(done)
-                with torch.cuda.stream(d2h):
-                    hout[l].copy_(self.out[l], non_blocking=True)
+            ready, l0 = [], 0
+            with torch.cuda.stream(h2d):
+                for n in chunks:
+                    self.qkv[l0:l0 + n].copy_(hqkv[l0:l0 + n], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(h2d)
+                    ready.append(ev)
+                    l0 += n
+            l0 = 0
+            for ci, n in enumerate(chunks):
+                main.wait_event(ready[ci])
+                for l in range(l0, l0 + n):
+                    self.layer_step(l)
+                    done = torch.cuda.Event()
+                    done.record(main)
+                    d2h.wait_event(done)
+                    with torch.cuda.stream(d2h):
+                        hout[l].copy_(self.out[l], non_blocking=True)
+                l0 += n
             main.wait_stream(h2d)
             main.wait_stream(d2h)
         return g
@@ -374,10 +379,12 @@ def run_ours(args, rank, world):
 
     # ---- e2e: the same step from HOST buffers (pinned): per layer, H2D of q/k/v on a copy stream, the
     # fused kernel on the compute stream, D2H of out on a third stream -- all captured in one graph so
-    # the copies of layer l+1 overlap the kernel of layer l; the caller reads the result every step ----
-    hq, hk, hv = (torch.randn(wl.q.shape).pin_memory() for _ in range(3))
+    # the copies of later layers overlap the kernels of earlier ones; the caller reads the result every step ----
+    hqkv = torch.randn(wl.qkv.shape).pin_memory()
     hout = torch.empty(wl.out.shape).pin_memory()
-    e2e_graph = wl.capture_e2e(hq, hk, hv, hout)
+    chunks = tuple(int(x) for x in os.environ.get("UOCR_E2E_CHUNKS", "1,3,8").split(",")) if CFG["layers"] == 12 \
+        else (1,) * CFG["layers"]
+    e2e_graph = wl.capture_e2e(hqkv, hout, chunks)
     for _ in range(2):
         e2e_graph.replay()
     barrier()
@@ -390,7 +397,7 @@ def run_ours(args, rank, world):
     barrier()
     e2e_ms = e0.elapsed_time(e1)
     e2e_ms = ranks.max_over_ranks(e2e_ms)
-    h2d = int(hq.numel() * 4 * 3)
+    h2d = int(hqkv.numel() * 4)
     d2h = int(hout.numel() * 4)
 
     cpu = None
