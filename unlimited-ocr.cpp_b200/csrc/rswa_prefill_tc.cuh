@@ -272,21 +272,23 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
     alpha = tc_exp2(m_run - m_safe);
     float lsum = 0.f;
-    uint32_t hi[32], lo[32];
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-        float pr[2];
+    for (int qq = 0; qq < 2; ++qq) {  // 32 keys at a time: their 16 hi words, then their 16 lo words, over their own columns
+        uint32_t pk[32];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int key = h * 64 + 2 * e + u;
-            const bool valid = FULL || (key >= vlo && key < vhi);
-            pr[u] = valid ? tc_exp2(__uint_as_float(s[2 * e + u]) - m_safe) : 0.f;
-            lsum += pr[u];
+        for (int e = 0; e < 16; ++e) {
+            float pr[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int key = h * 64 + qq * 32 + 2 * e + u;
+                const bool valid = FULL || (key >= vlo && key < vhi);
+                pr[u] = valid ? tc_exp2(__uint_as_float(s[qq * 32 + 2 * e + u]) - m_safe) : 0.f;
+                lsum += pr[u];
+            }
+            tc_split2(pr[0], pr[1], pk[e], pk[16 + e]);
         }
-        tc_split2(pr[0], pr[1], hi[e], lo[e]);
+        tc_st32(tS + h * 64 + qq * 32, pk);
     }
-    tc_st32(tS + h * 64, hi);
-    tc_st32(tS + h * 64 + 32, lo);
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     TC_TRACE(tstep >= 0, tstep, 4);
     l_run = l_run * alpha + lsum;
@@ -593,12 +595,12 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 TC_TRACE(true, n, 12);
                 const uint64_t stage = (uint64_t)((n & 1) * (kTcStageBytes >> 4));
                 const uint32_t tP = tmem + (n & 1) * 128, tO = tmem + 256 + (n & 1) * 128;
-                // P: 16 keys = 8 TMEM columns per MMA; each 64-key half holds its hi words, then its lo words.
+                // P: 16 keys = 8 TMEM columns per MMA; every 32 keys hold their 16 hi words, then their 16 lo words.
                 tc_mma_ts<false>(tO, tP, dV[0] + stage, idesc_o);
 #pragma unroll
                 for (int u = 1; u < 16; ++u) {
                     const int hp = u >> 3, j = u & 7;
-                    tc_mma_ts<true>(tO, tP + (j >> 2) * 64 + hp * 32 + (j & 3) * 8, dV[j] + stage, idesc_o);
+                    tc_mma_ts<true>(tO, tP + (j >> 1) * 32 + hp * 16 + (j & 1) * 8, dV[j] + stage, idesc_o);
                 }
                 tc_commit(o_full(n & 1));
                 tc_commit(v_free(n & 1));
