@@ -493,7 +493,8 @@ def run_prefill(args, rank, world):
     (prompts longer than W wrap).  Per layer: scatter of the vision K/V into the prefix blocks and of
     the text K/V into the text pool, attention (vision rows causal over the prefix; text rows over
     prefix + window) on the tcgen05 kernel, ring fill.  Reports prefill tokens/s and TFLOP/s
-    (4*D*H = 5120 flop per attended (query, key) pair).  Parity of this path: tests/test_gpu_prefill.py."""
+    (4*D*H = 5120 flop per attended (query, key) pair).  Tensor-core pass: vision scatter; text scatter + ring
+    fill + cursor publication in one kernel; attention.  Parity of this path: tests/test_gpu_prefill.py."""
     if rank != 0:
         return
     import torch
@@ -552,8 +553,10 @@ def run_prefill(args, rank, world):
     def layer_pass(l, tc=True):
         pkg.write_prefill_ragged_paged(layers[l], k[:nv], v[:nv], v_slots, v_pos, nv, ws)
         if tc:
-            pkg.text_scatter_paged(layers[l], text_k, text_v, text_blocks, k[nv:], v[nv:], t_pos, t_b0, nt, ws)
+            pkg.text_scatter_fill_paged(layers[l], text_k, text_v, text_blocks, k[nv:], v[nv:], t_slots, t_pos, t_b0, t_len,
+                                        d_prefill, d_len[l], d_ring[l], nt, W, ws)
             pkg.prefill_attention_tc(layers[l], text_k, text_v, text_blocks, q, d_prefill, tiles, W, H, out, ws)
+            return
         else:
             pkg.attention_ragged_paged(layers[l], q[:nv], d_prefill, v_slots, v_pos, nv, H, out[:nv], ws)
             pkg.prefill_text_paged(layers[l], text_k, text_v, text_blocks, q[nv:], k[nv:], v[nv:], d_prefill, t_slots,

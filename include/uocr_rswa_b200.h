@@ -258,6 +258,17 @@ UOCR_B200_API int uocr_b200_rswa_text_scatter_paged(
     const float* k, const float* v, const int* d_pos, const int* d_text_block0, int total,
     uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* uocr_b200_rswa_text_scatter_paged and uocr_b200_rswa_ring_fill_paged in one pass over the fp32 rows:
+ * every row goes to the text pool, the last min(T, window) rows of each request also straight to
+ * their ring slots, and the cursors are published -- the same final state without reading the text
+ * pool back.  For callers that attend through uocr_b200_rswa_prefill_attention_tc, which reads the
+ * prefix blocks and the text pool but neither the ring nor the cursors, so the call may come first. */
+UOCR_B200_API int uocr_b200_rswa_text_scatter_fill_paged(
+    const uocr_b200_paged_kv* kv, void* text_k_pool, void* text_v_pool, int text_blocks,
+    const float* k, const float* v, const int* d_slots, const int* d_pos, const int* d_text_block0,
+    const int* d_text_len, const int* d_prefill_len, int* d_len, int* d_ring_pos, int total,
+    int window, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
 /* Ragged prefill attention on the tcgen05 tensor cores (bf16 KV, head_dim 128).  The caller
  * describes the packed query rows as tiles of at most 128 consecutive positions of one request
  * (host array, copied to the device by this call):

@@ -82,6 +82,7 @@ _SIGS = {
     "uocr_b200_rswa_attention_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_prefill_text_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_text_scatter_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 4 + [_i, _vp, _vp]),
+    "uocr_b200_rswa_text_scatter_fill_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 9 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_prefill_attention_tc": (_i, [C.POINTER(PagedKV), _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_ring_fill_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_decode_step_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
@@ -256,6 +257,15 @@ def text_scatter_paged(layer, text_k, text_v, text_blocks, k, v, d_pos, d_block0
     check(lib().uocr_b200_rswa_text_scatter_paged(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(k), _p(v),
                                                    _p(d_pos), _p(d_block0), total, ws.h if ws else None,
                                                    stream_handle(stream)))
+
+
+def text_scatter_fill_paged(layer, text_k, text_v, text_blocks, k, v, d_slots, d_pos, d_block0, d_text_len, d_prefill,
+                            d_len, d_ring, total, window, ws=None, stream=None):
+    """text scatter + ring fill + cursor publication in one pass."""
+    check(lib().uocr_b200_rswa_text_scatter_fill_paged(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(k), _p(v),
+                                                        _p(d_slots), _p(d_pos), _p(d_block0), _p(d_text_len), _p(d_prefill),
+                                                        _p(d_len), _p(d_ring), total, window, ws.h if ws else None,
+                                                        stream_handle(stream)))
 
 
 def prefill_attention_tc(layer, text_k, text_v, text_blocks, q, d_prefill, tiles, window, heads, out, ws, stream=None):

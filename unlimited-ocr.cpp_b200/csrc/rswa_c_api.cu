@@ -825,6 +825,37 @@ int uocr_b200_rswa_text_scatter_paged(const uocr_b200_paged_kv* kv, void* text_k
     return after_launch("text scatter");
 }
 
+int uocr_b200_rswa_text_scatter_fill_paged(const uocr_b200_paged_kv* kv, void* text_k_pool, void* text_v_pool, int text_blocks,
+                                           const float* k, const float* v, const int* d_slots, const int* d_pos,
+                                           const int* d_text_block0, const int* d_text_len, const int* d_prefill_len,
+                                           int* d_len, int* d_ring_pos, int total, int window, uocr_b200_workspace* ws,
+                                           uocr_b200_stream_t stream) {
+    if (total <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    if (int rc = paged_view(kv, &pv)) return rc;
+    if (!text_k_pool || !text_v_pool || text_blocks <= 0 || !k || !v || !d_slots || !d_pos || !d_text_block0 || !d_text_len ||
+        !d_prefill_len || !d_len || !d_ring_pos)
+        return fail(UOCR_B200_ERR_INVALID, "text_scatter_fill_paged: null pointer");
+    if (!aligned16(text_k_pool) || !aligned16(text_v_pool) || !aligned16(k) || !aligned16(v))
+        return fail(UOCR_B200_ERR_INVALID, "text_scatter_fill_paged: pointers must be 16-byte aligned");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "text_scatter_fill_paged: window must be positive");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    PagedView text = pv;
+    text.k_pool = static_cast<uint8_t*>(text_k_pool);
+    text.v_pool = static_cast<uint8_t*>(text_v_pool);
+    text.table = nullptr;
+    text.table_stride = 0;
+    text.num_blocks = text_blocks;
+    int* status = ws ? ws->status : nullptr;
+    if (kv->dtype == UOCR_B200_BF16)
+        rswa_scatter_text_fill_kernel<BF16><<<total, 160, 0, st>>>(pv, text, k, v, d_slots, d_pos, d_text_block0, d_text_len,
+                                                                   d_prefill_len, d_len, d_ring_pos, window, status);
+    else
+        rswa_scatter_text_fill_kernel<F32><<<total, 160, 0, st>>>(pv, text, k, v, d_slots, d_pos, d_text_block0, d_text_len,
+                                                                  d_prefill_len, d_len, d_ring_pos, window, status);
+    return after_launch("text scatter + ring fill");
+}
+
 // Tensor map of a K or V pool seen as a [rows][128] bf16 matrix, fetched in boxes of 16 rows x 64
 // elements (one 16-token block of one head, one 128-byte half of each row) with the 128-byte swizzle
 // the tensor-core operand layout uses.  Rows at or beyond `rows` read as zeros.

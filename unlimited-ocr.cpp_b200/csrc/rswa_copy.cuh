@@ -231,6 +231,70 @@ __global__ void __launch_bounds__(256) rswa_ring_fill_kernel(
     }
 }
 
+// Text scatter and ring fill in one pass over the fp32 rows: row t goes to the text pool (as
+// rswa_scatter_text_kernel) and, when it is one of its request's last min(T, window) tokens, also
+// straight to ring slot (pos mod window); the request's last row publishes the cursors.  Same final
+// state as the two kernels above run one after the other, without reading the text pool back.
+template <typename KV>
+__global__ void __launch_bounds__(160) rswa_scatter_text_fill_kernel(
+    PagedView pv, PagedView text, const float* __restrict__ k, const float* __restrict__ v,
+    const int* __restrict__ d_slots, const int* __restrict__ d_pos, const int* __restrict__ d_text_block0,
+    const int* __restrict__ d_text_len, const int* __restrict__ d_prefill_len, int* __restrict__ d_len,
+    int* __restrict__ d_ring_pos, int window, int* __restrict__ status) {
+    constexpr int EPC = KV::kPerChunk;
+    const int t = blockIdx.x;
+    const int slot = d_slots[t], i = d_pos[t], T = d_text_len[t];
+    const int pfx = d_prefill_len[slot];
+    if (i == T - 1 && threadIdx.x == 0) {
+        d_len[slot] = pfx + min(T, window);
+        d_ring_pos[slot] = T < window ? 0 : (T - window) % window;
+    }
+    const int tok = d_text_block0[t] * kBlockTokens + i;
+    const int tblk = tok / kBlockTokens, toff = tok & (kBlockTokens - 1);
+    const bool text_ok = tok >= 0 && tblk < text.num_blocks;
+    int rblk = -1, roff = 0;
+    if (i >= T - window) {  // not overwritten by a later token of the same request
+        const int r = i % window;
+        const int idx = (pfx + kBlockTokens - 1) / kBlockTokens + r / kBlockTokens;
+        if (idx < pv.table_stride) rblk = pv.table[(size_t)slot * pv.table_stride + idx];
+        if (rblk < 0 || rblk >= pv.num_blocks) {
+            if (threadIdx.x == 0 && status) atomicOr(status, kStatusBadBlock);
+            rblk = -1;
+        }
+        roff = r & (kBlockTokens - 1);
+    }
+    if (!text_ok && threadIdx.x == 0 && status) atomicOr(status, kStatusBadBlock);
+    const int hd = pv.head_dim, chunks = pv.kv_heads * hd / EPC;
+    const float* ksrc = k + (size_t)t * pv.kv_heads * hd;
+    const float* vsrc = v + (size_t)t * pv.kv_heads * hd;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const int e0 = c * EPC;
+        const int head = e0 / hd, d = e0 - head * hd;
+        uint4 kw, vw;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(ksrc + e0));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(vsrc + e0));
+        if constexpr (EPC == 8) {
+            const float4 a2 = __ldg(reinterpret_cast<const float4*>(ksrc + e0 + 4));
+            const float4 b2 = __ldg(reinterpret_cast<const float4*>(vsrc + e0 + 4));
+            kw = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(a2.x, a2.y), pack_bf16x2(a2.z, a2.w));
+            vw = make_uint4(pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w), pack_bf16x2(b2.x, b2.y), pack_bf16x2(b2.z, b2.w));
+        } else {
+            kw = make_uint4(__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w));
+            vw = make_uint4(__float_as_uint(b.x), __float_as_uint(b.y), __float_as_uint(b.z), __float_as_uint(b.w));
+        }
+        if (text_ok) {
+            const size_t dst = ((((size_t)tblk * pv.kv_heads + head) * kBlockTokens + toff) * hd + d) * KV::kBytes;
+            *reinterpret_cast<uint4*>(text.k_pool + dst) = kw;
+            *reinterpret_cast<uint4*>(text.v_pool + dst) = vw;
+        }
+        if (rblk >= 0) {
+            const size_t dst = ((((size_t)rblk * pv.kv_heads + head) * kBlockTokens + roff) * hd + d) * KV::kBytes;
+            *reinterpret_cast<uint4*>(pv.k_pool + dst) = kw;
+            *reinterpret_cast<uint4*>(pv.v_pool + dst) = vw;
+        }
+    }
+}
+
 // Gather: logical row s of slot d_slots[i] -> out[i][s][:]; rows >= len are zero-filled.
 // HEAD_MAJOR: out[i][head][s][:] instead (the layout of the reference's exported cache snapshots).
 // grid = (capacity_rows, n); one thread per 16-byte pool chunk.

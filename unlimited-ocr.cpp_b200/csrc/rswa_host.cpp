@@ -1120,9 +1120,10 @@ void PagedBatchKV::windowed_prefill_layer(int layer, const float* q, const float
         abi_ok(uocr_b200_rswa_write_prefill_ragged_paged(view, k, v, v_slots, v_pos, nv, s.ws, stream), "windowed prefill: prefix scatter");
     const bool tensor_cores = s.cfg.dtype == DType::BF16 && s.cfg.head_dim == 128;
     if (tensor_cores) {
-        if (nt > 0)
-            abi_ok(uocr_b200_rswa_text_scatter_paged(view, s.text_k, s.text_v, s.text_blocks, kt, vt, t_pos, t_b0, nt, s.ws, stream),
-                   "windowed prefill: text scatter");
+        if (nt > 0)  // text pool, ring blocks and cursors in one pass; the attention below reads none of the latter two
+            abi_ok(uocr_b200_rswa_text_scatter_fill_paged(view, s.text_k, s.text_v, s.text_blocks, kt, vt, t_slots, t_pos, t_b0, t_len,
+                                                          s.d_prefill, d_len(layer), d_ring_pos(layer), nt, s.cfg.window, s.ws, stream),
+                   "windowed prefill: text scatter + ring fill");
         abi_ok(uocr_b200_rswa_prefill_attention_tc(view, s.text_k, s.text_v, s.text_blocks, q, s.d_prefill, s.pf_tiles.data(),
                                                    static_cast<int>(s.pf_tiles.size()), s.cfg.window, heads, out, s.ws, stream),
                "windowed prefill: attention");
@@ -1143,7 +1144,7 @@ void PagedBatchKV::windowed_prefill_layer(int layer, const float* q, const float
                    "windowed prefill: text attention");
         }
     }
-    if (nt > 0)
+    if (nt > 0 && !tensor_cores)
         abi_ok(uocr_b200_rswa_ring_fill_paged(view, s.text_k, s.text_v, s.text_blocks, t_slots, t_pos, t_b0, t_len, s.d_prefill,
                                               d_len(layer), d_ring_pos(layer), nt, s.cfg.window, s.ws, stream),
                "windowed prefill: ring fill");
