@@ -278,7 +278,10 @@ UOCR_B200_API int uocr_b200_rswa_text_scatter_fill_paged(
  *           the semantics of uocr_b200_rswa_prefill_text_paged.
  * K/V must already be in the pools (uocr_b200_rswa_write_prefill_ragged_paged for the fixed
  * region, uocr_b200_rswa_text_scatter_paged for the text).  Same results as the CUDA-core entry
- * points within the attention tolerance. */
+ * points within the attention tolerance.  The call sorts the tiles (longest first), copies them from
+ * pageable host memory and encodes tensor maps on the host, so it cannot be part of a stream capture
+ * (ragged prefill shapes change from call to call anyway); unwritten rows of the pools that fall
+ * into a fetched block must hold finite values (they are masked, but a NaN times zero is a NaN). */
 typedef struct {
     int32_t row0;   /* first packed row of the tile */
     int32_t rows;   /* 1..128 */
