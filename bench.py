@@ -245,21 +245,22 @@ class DecodeWorkload:
         self.d_len.copy_(torch.from_numpy(np.tile(ln.astype(np.int32), (self.L, 1))))
         self.d_ring.copy_(torch.from_numpy(np.tile(rp.astype(np.int32), (self.L, 1))))
 
-    def layer_step(self, l):
+    def layer_step(self, l, out=None):
         p = self.pkg
+        out = self.out[l] if out is None else out
         if self.fused and self.rope:
             p.decode_step_rope_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_positions, 10000.0,
                                      self.d_len[l], self.d_ring[l], self.d_prefill, self.d_slots, self.B,
-                                     CFG["window"], CFG["heads"], self.out[l], self.ws)
+                                     CFG["window"], CFG["heads"], out, self.ws)
         elif self.fused:
             p.decode_step_paged(self.layers[l], self.q[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
-                                self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], self.out[l],
+                                self.d_prefill, self.d_slots, self.B, CFG["window"], CFG["heads"], out,
                                 self.ws)
         else:
             p.append_decode_batch_paged(self.layers[l], self.k[l], self.v[l], self.d_len[l], self.d_ring[l],
                                         self.d_prefill, self.d_slots, self.B, CFG["window"], self.ws)
             p.attention_batch_paged(self.layers[l], self.q[l], self.d_len[l], self.d_prefill, self.d_slots,
-                                    self.B, CFG["heads"], self.out[l], self.ws)
+                                    self.B, CFG["heads"], out, self.ws)
 
     def step_plain(self, per_layer_hook=None):
         for l in range(self.L):
@@ -282,7 +283,7 @@ class DecodeWorkload:
         self.graph.replay()
         self.steps_done += 1
 
-    def capture_e2e(self, hqkv, hout, chunks=(1, 3, 8)):
+    def capture_e2e(self, hqkv, hout, chunks=(1, 3, 8), mapped_out=False):
         """One graph for a whole step fed from pinned host memory, three streams.  The inputs come over in
         a few copies of growing size (layer 0 alone, so that compute starts early; the rest behind the
         kernels of the layers before them); every layer's result goes back as soon as its kernel is done.
@@ -307,6 +308,11 @@ class DecodeWorkload:
             for ci, n in enumerate(chunks):
                 main.wait_event(ready[ci])
                 for l in range(l0, l0 + n):
+                    if mapped_out:
+                        # the kernel stores the layer's result straight into the caller's pinned (mapped)
+                        # host buffer: no copy node, no cross-stream edge behind the kernel
+                        self.layer_step(l, hout[l])
+                        continue
                     self.layer_step(l)
                     done = torch.cuda.Event()
                     done.record(main)
@@ -384,7 +390,7 @@ def run_ours(args, rank, world):
     hout = torch.empty(wl.out.shape).pin_memory()
     chunks = tuple(int(x) for x in os.environ.get("UOCR_E2E_CHUNKS", "1,3,8").split(",")) if CFG["layers"] == 12 \
         else (1,) * CFG["layers"]
-    e2e_graph = wl.capture_e2e(hqkv, hout, chunks)
+    e2e_graph = wl.capture_e2e(hqkv, hout, chunks, mapped_out=(args.e2e_out == "mapped"))
     for _ in range(2):
         e2e_graph.replay()
     barrier()
@@ -645,6 +651,9 @@ def main():
     ap.add_argument("--rope", action="store_true",
                     help="fused step with the rotary embedding folded in (q, k un-rotated; one position per row)")
     ap.add_argument("--weighted", action="store_true", help="SM-weighted split (calibrates per-SM streaming rates first)")
+    ap.add_argument("--e2e-out", default="copy", choices=["copy", "mapped"],
+                    help="end-to-end step: results return by one device-to-host copy per layer, or the kernels "
+                         "store them straight into the pinned host buffer")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch the fused steps without programmatic dependent launch")
     ap.add_argument("--seqs", type=int, default=None, help="profiling aid only: sequences per GPU (not a bench number)")

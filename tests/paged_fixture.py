@@ -138,15 +138,24 @@ class PagedBatch:
                          for i, s in enumerate(row_slots)])
         return got, want
 
-    def step_fused(self, layer, k, v, q, row_slots):
-        """append + attention in one launch (decode_step_paged); oracle advanced alongside."""
+    def step_fused(self, layer, k, v, q, row_slots, host_out=False):
+        """append + attention in one launch (decode_step_paged); oracle advanced alongside.  With
+        `host_out` the kernel stores the result straight into pinned (device-mapped) host memory."""
         torch = self.torch
         dk, dv, dq = (torch.from_numpy(x).cuda() for x in (k, v, q))
         ds = torch.tensor(row_slots, dtype=torch.int32, device="cuda")
-        out = torch.full((len(row_slots), self.heads * self.hd), float("nan"), device="cuda")
+        shape = (len(row_slots), self.heads * self.hd)
+        if host_out:
+            out = torch.full(shape, float("nan")).pin_memory()
+        else:
+            out = torch.full(shape, float("nan"), device="cuda")
         self.b.decode_step_paged(self.layer[layer], dq, dk, dv, self.d_len[layer], self.d_ring[layer],
                                  self.d_prefill, ds, len(row_slots), self.W, self.heads, out, self.ws)
-        got = out.cpu().numpy()
+        if host_out:
+            torch.cuda.synchronize()
+            got = out.numpy().copy()
+        else:
+            got = out.cpu().numpy()
         want = []
         for i, s in enumerate(row_slots):
             self.cache[s].append_decode(layer, k[i], v[i])

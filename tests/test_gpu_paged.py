@@ -264,6 +264,21 @@ def test_fused_decode_step_real_geometry_and_mixed_calls(orc, b):
     assert pb.ws.status() == 0
 
 
+def test_fused_decode_step_stores_into_pinned_host_output(orc, b):
+    # `out` may be any device-accessible address: pinned host memory receives the same values, from
+    # rows written directly by one warp and from rows merged out of partials alike
+    slots, W, P = 6, 64, 273
+    pb = PagedBatch(orc, slots, 1, 10, 128, W, b.BF16, [P] * slots, prefix_keys=["doc"] * slots, seed=79)
+    pb.write_prefixes()
+    rows = [5, 3, 1, 0, 2, 4]
+    for t in range(W + 4):
+        k, v, q = pb.step_inputs(t, 0, rows)
+        got, want = pb.step_fused(0, k, v, q, rows, host_out=(t % 2 == 0))
+        assert_attention_close(got, want, *TIGHT)
+    pb.check_logical_view(0)
+    assert pb.ws.status() == 0
+
+
 @pytest.mark.parametrize("slots,P,W", [(24, 1600, 64), (5, 273, 48)])
 def test_sm_weighted_split(orc, b, slots, P, W):
     # calibrated workspace: every CTA claims the share measured for its SM.  The large case has enough

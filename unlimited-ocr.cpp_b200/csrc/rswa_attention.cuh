@@ -100,12 +100,16 @@ struct AttnParams {
     int* d_len;
     int* d_ring_pos;
     int* done_ctas;
+    int* planned_ctas;  // CTAs that have built their plan from the pre-append cursors, zero between launches
 };
 
 // -------------------------------------------------------------------------------------------------
 // plan: per-row attended ranges and the prefix sum of unit counts
 // -------------------------------------------------------------------------------------------------
-__device__ __forceinline__ int plan_row(const PlanParams& p, int r, RowInfo& ri) {
+// `next_len` / `next_ring` (decode step only, may be null): the cursor values the step leaves behind for
+// this row's slot, -1 where the reference's append leaves the cursor as it is.
+__device__ __forceinline__ int plan_row(const PlanParams& p, int r, RowInfo& ri, int* next_len = nullptr,
+                                        int* next_ring = nullptr) {
     int slot, len;
     ri.aux = -1;
     if (p.mode == kPlanBatch) {
@@ -132,13 +136,21 @@ __device__ __forceinline__ int plan_row(const PlanParams& p, int r, RowInfo& ri)
         slot = p.d_slots[r];
         const int pfx = p.d_prefill_len[slot];
         const int cur = p.d_len[slot];
-        int row;
+        int row, nl = -1, nr = -1;
         if (cur < pfx + p.window) {
             row = cur;
             len = cur + 1;
+            nl = cur + 1;
+            if (cur + 1 >= pfx + p.window) nr = 0;
         } else {
-            row = pfx + p.d_ring_pos[slot];
+            const int ring = p.d_ring_pos[slot];
+            row = pfx + ring;
             len = cur;
+            nr = (ring + 1) % p.window;
+        }
+        if (next_len) {
+            *next_len = nl;
+            *next_ring = nr;
         }
         const int rr = row - pfx;
         ri.aux = rr >= 0 ? ((((pfx + kBlockTokens - 1) / kBlockTokens + rr / kBlockTokens) << 4) | (rr & 15)) : -2;
@@ -159,7 +171,8 @@ __device__ __forceinline__ int plan_row(const PlanParams& p, int r, RowInfo& ri)
 
 // Block-wide: fills rs[0..rows] and info[0..rows) (global or shared memory).  `scratch` = 33 ints
 // of shared memory.
-__device__ __forceinline__ void plan_all_rows(const PlanParams& p, int* rs, RowInfo* info, int* scratch) {
+__device__ __forceinline__ void plan_all_rows(const PlanParams& p, int* rs, RowInfo* info, int* scratch,
+                                              int* next_len = nullptr, int* next_ring = nullptr) {
     int* warp_sums = scratch;
     int* carry_s = scratch + 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -171,7 +184,7 @@ __device__ __forceinline__ void plan_all_rows(const PlanParams& p, int* rs, RowI
         int units = 0;
         if (r < p.rows) {
             RowInfo ri;
-            units = plan_row(p, r, ri);
+            units = next_len ? plan_row(p, r, ri, next_len + r, next_ring + r) : plan_row(p, r, ri);
             info[r] = ri;
             if (units == 0 && p.out)
                 for (int i = 0; i < p.out_row_elems; ++i) p.out[(size_t)r * p.out_row_elems + i] = 0.f;
@@ -475,16 +488,31 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
     // ---- the plan: global (made by rswa_plan_kernel) or built here in shared memory ----------------
     const int* rs = p.rs;
     const RowInfo* info = p.info;
+    int planner_ticket = -1;  // fused step, thread 0: how many CTAs had planned before this one
+    const int* next_len = nullptr;
+    const int* next_ring = nullptr;
     if constexpr (FUSED) {
         uint8_t* plan_base = smem + bar_bytes + (size_t)warps * (kRing * TILE) + (size_t)warps * kPendMax * sizeof(int);
         RowInfo* info_s = reinterpret_cast<RowInfo*>(plan_base);
         int* rs_s = reinterpret_cast<int*>(plan_base + sizeof(RowInfo) * p.rows);
         int* scratch = rs_s + p.rows + 1;
-        plan_all_rows(p.plan, rs_s, info_s, scratch);
+        int* next_len_s = scratch + 33;
+        int* next_ring_s = next_len_s + p.rows;
+        plan_all_rows(p.plan, rs_s, info_s, scratch, next_len_s, next_ring_s);
         if (weighted && threadIdx.x == 0) s_cta = resolve_claim(first_claim, want, p.claim, p.status);
         __syncthreads();
+        // The cursors move as soon as every CTA has planned from their old values.  Thread 0 announces
+        // this CTA's plan; the answer is looked at once the first tiles are on their way, and the warp
+        // that learns it was the last planner stores the new cursors (nobody reads them again in this
+        // launch), which keeps the publication off the tail of the launch.
+        if (threadIdx.x == 0) {
+            __threadfence();
+            planner_ticket = atomicAdd(p.planned_ctas, 1);
+        }
         rs = rs_s;
         info = info_s;
+        next_len = next_len_s;
+        next_ring = next_ring_s;
     } else {
         if (weighted) {
             if (threadIdx.x == 0) s_cta = resolve_claim(first_claim, want, p.claim, p.status);
@@ -640,6 +668,23 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             dep_synced = true;
         };
 
+        // Fused step, warp 0: if this CTA was the last to plan, store the cursors the step leaves behind.
+        bool publish_checked = false;
+        auto publish_cursors = [&]() {
+            if constexpr (FUSED) {
+                if (warp != 0 || publish_checked) return;
+                publish_checked = true;
+                if (!__shfl_sync(FULL, planner_ticket == (int)gridDim.x - 1, 0)) return;
+                if (lane == 0) *p.planned_ctas = 0;  // ready for the next launch
+                __threadfence();  // every other CTA's cursor reads precede its announcement
+                for (int r = lane; r < p.rows; r += 32) {
+                    const int slot = info[r].slot;
+                    if (next_len[r] >= 0) p.d_len[slot] = next_len[r];
+                    if (next_ring[r] >= 0) p.d_ring_pos[slot] = next_ring[r];
+                }
+            }
+        };
+
         // ---- arrivals: whoever completes an item's set of partials merges them ------------------------
         auto flush_arrivals = [&]() {
             if (pend_n == 0) return;
@@ -743,6 +788,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             build_desc(0);
 #pragma unroll
             for (int s = 0; s < kRing; ++s) issue_next();
+            publish_cursors();
             // everything up to here read only this layer's own cursors, table and pool
             dependency_sync();
             TRACE(2);
@@ -1002,11 +1048,12 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             piece = -1;
         }
         TRACE(4);
+        publish_cursors();  // a warp without a piece gets here without having looked
         if (!gave_up) flush_arrivals();
     }
 
     TRACE(5);
-    // ---- the last CTA to finish re-arms the scratch counters; fused step: it publishes the cursors ----
+    // ---- the last CTA to finish re-arms the scratch counters ------------------------------------------
     {
         __shared__ int is_last;
         if constexpr (FUSED) {
@@ -1031,22 +1078,8 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
         }
         if constexpr (FUSED) {
             __syncthreads();
-            if (is_last) {
-                if (weighted)
-                    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
-                // every CTA has planned from the old cursors by now; nobody reads them again in this launch
-                for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
-                    const int slot = p.plan.d_slots[r];
-                    const int pfx = p.plan.d_prefill_len[slot];
-                    const int cur = p.d_len[slot];
-                    if (cur < pfx + p.plan.window) {
-                        p.d_len[slot] = cur + 1;
-                        if (cur + 1 >= pfx + p.plan.window) p.d_ring_pos[slot] = 0;
-                    } else {
-                        p.d_ring_pos[slot] = (p.d_ring_pos[slot] + 1) % p.plan.window;
-                    }
-                }
-            }
+            if (is_last && weighted)
+                for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
         }
     }
     TRACE(6);

@@ -100,6 +100,7 @@ struct uocr_b200_workspace {
     int* counters = nullptr;   // [pieces_max] arrival counters, zero between launches
     int* done_ctas = nullptr;  // CTAs that have finished, zero between launches
     int* dyn_next = nullptr;   // next dynamic piece to hand out, zero between launches
+    int* planned_ctas = nullptr;  // fused step: CTAs that have planned from the old cursors, zero between launches
     int dyn_cap = 0;           // dynamic pieces the scratch is sized for (0: static split only)
     int pieces_max = 0;
     PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
@@ -177,6 +178,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
     ws->done_ctas = ws->counters + ws->pieces_max;
     ws->dyn_next = ws->done_ctas + 1;
+    ws->planned_ctas = ws->done_ctas + 2;
     ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
     ws->claim = reinterpret_cast<int*>(ws->base + o_split);
     *out = ws;
@@ -377,7 +379,7 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
                    bool overlap = false) {
     using M = TileMap<KV, HD>;
     constexpr int per_warp = kRing * M::kTileBytes;
-    const int plan_bytes = FUSED ? (int)(sizeof(RowInfo) * ap.rows + sizeof(int) * (ap.rows + 1 + 33) + 128) : 0;
+    const int plan_bytes = FUSED ? (int)(sizeof(RowInfo) * ap.rows + sizeof(int) * (3 * ap.rows + 1 + 33) + 128) : 0;
     const int budget = (di.smem_optin < 200 * 1024 ? di.smem_optin : 200 * 1024) - 1024 - plan_bytes -
                        kMaxWarpsPerCta * kPendMax * (int)sizeof(int);
     int warps = budget / per_warp;
@@ -507,6 +509,7 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.d_len = c.d_len_rw;
     ap.d_ring_pos = c.d_ring_rw;
     ap.done_ctas = ws->done_ctas;
+    ap.planned_ctas = ws->planned_ctas;
     if (c.rope_pos) {
         ap.rope_pos = c.rope_pos;
         // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
@@ -1134,6 +1137,7 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     view.counters = reinterpret_cast<int*>(base + kNaCnt);
     view.done_ctas = view.counters + kNoAllocMaxWarps;
     view.dyn_next = view.done_ctas + 1;
+    view.planned_ctas = view.done_ctas + 2;
     view.dyn_cap = 0;  // the built-in scratch holds one piece per warp: static split only
     view.pieces_max = kNoAllocMaxWarps;
 
