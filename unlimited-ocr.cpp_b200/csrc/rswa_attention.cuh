@@ -100,6 +100,7 @@ struct AttnParams {
     int* d_len;
     int* d_ring_pos;
     int* done_ctas;
+    int trace_half;     // instrumented builds only: which half of the timeline array this launch writes
     int* planned_ctas;  // CTAs that have built their plan from the pre-append cursors, zero between launches
 };
 
@@ -371,9 +372,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #define UOCR_FFMA2 1
 #endif
 #ifdef UOCR_TRACE
-__device__ unsigned long long g_trace[8 * 4096];
+__device__ unsigned long long g_trace[2 * 8 * 4096];  // two halves: consecutive (overlapping) launches alternate
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { const int tw_ = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if ((threadIdx.x & 31) == 0 && tw_ < 4096) { g_trace[tw_ * 8 + (slot)] = gtime(); if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_trace[tw_ * 8 + 7] = sm; } } } while (0)
+#define TRACE(slot) do { const int tw_ = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if ((threadIdx.x & 31) == 0 && tw_ < 4096) { unsigned long long* tr_ = g_trace + (size_t)(p.trace_half & 1) * 8 * 4096; tr_[tw_ * 8 + (slot)] = gtime(); if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); tr_[tw_ * 8 + 7] = sm; } } } while (0)
 #else
 #define TRACE(slot) do {} while (0)
 #endif
@@ -703,12 +704,10 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
                 my_wf = pm.of(my_s0);
                 my_wl = pm.of(my_s0 + n - 1);
                 const int old = atomicAdd(p.counters + my_wf, 1);
-                if (old == my_wl - my_wf) {
-                    my_last = true;
-                    p.counters[my_wf] = 0;  // ready for the next launch
-                }
+                my_last = (old == my_wl - my_wf);
             }
-            unsigned todo = __ballot_sync(FULL, my_last);
+            const unsigned all_todo = __ballot_sync(FULL, my_last);
+            unsigned todo = all_todo;
             if (todo) __threadfence();  // the other arrivers' partials are visible after their arrivals
             while (todo) {
                 const int src = __ffs(todo) - 1;
@@ -717,39 +716,88 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
                 const int wf = __shfl_sync(FULL, my_wf, src);
                 const int wl = __shfl_sync(FULL, my_wl, src);
                 const long long s0 = __shfl_sync(FULL, my_s0, src);
-                // merge, lanes in parallel over the partials: (max, sum) first, then the accumulators
                 float* out_item = p.out + (size_t)item * HD;
                 const bool wf_second = pm.start(wf) < s0;  // the item is piece wf's second segment
-                float mall = -INFINITY;
-                for (int w0 = wf; w0 <= wl; w0 += 32) {
-                    const int w = w0 + lane;
-                    const float mi = w <= wl ? __ldcg(p.part_ml + 2 * (2 * w + (w == wf && wf_second ? 1 : 0))) : -INFINITY;
-                    mall = fmaxf(mall, mi);
-                }
+                constexpr int NK = (HD + 31) / 32;
+                float o[NK];
 #pragma unroll
-                for (int d = 16; d >= 1; d >>= 1) mall = fmaxf(mall, __shfl_xor_sync(FULL, mall, d));
-                const float mall_safe = (mall == -INFINITY) ? 0.f : mall;
+                for (int i = 0; i < NK; ++i) o[i] = 0.f;
                 float lall = 0.f;
-                float o[(HD + 31) / 32];
-#pragma unroll
-                for (int i = 0; i < (HD + 31) / 32; ++i) o[i] = 0.f;
-                for (int w0 = wf; w0 <= wl; w0 += 32) {
-                    const int w = w0 + lane;
-                    const int slot_w = 2 * w + (w == wf && wf_second ? 1 : 0);
-                    float wg = 0.f;
-                    if (w <= wl) {
-                        wg = fast_exp2(__ldcg(p.part_ml + 2 * slot_w) - mall_safe);
-                        lall += __ldcg(p.part_ml + 2 * slot_w + 1) * wg;
+                const int n_part = wl - wf + 1;
+                if (n_part <= 32) {
+                    // The usual case.  Lane i holds (max, sum) of partial i; the accumulators come in batches
+                    // of kBatch partials whose loads are all issued before any of them is used, the first
+                    // batch together with the (max, sum) loads: a merge costs about one round trip to L2 per
+                    // batch instead of one per partial (the last arriver's merge ends the launch).
+                    constexpr int kBatch = NK > 4 ? 4 : 8;
+                    const int slot_l = 2 * (wf + lane) + ((lane == 0 && wf_second) ? 1 : 0);
+                    float mi = -INFINITY, li = 0.f;
+                    if (lane < n_part) {
+                        mi = __ldcg(p.part_ml + 2 * slot_l);
+                        li = __ldcg(p.part_ml + 2 * slot_l + 1);
                     }
-                    const int cnt = min(32, wl - w0 + 1);
-                    for (int i = 0; i < cnt; ++i) {
-                        const float wi = __shfl_sync(FULL, wg, i);
-                        const int si = __shfl_sync(FULL, slot_w, i);
-                        const float* pa = p.part_acc + (size_t)si * HD;
+                    float tmp[kBatch][NK];
+                    auto load_batch = [&](int b0) {
 #pragma unroll
-                        for (int kk = 0; kk < (HD + 31) / 32; ++kk) {
-                            const int d = lane + 32 * kk;
-                            if (d < HD) o[kk] = fmaf(__ldcg(pa + d), wi, o[kk]);
+                        for (int i = 0; i < kBatch; ++i) {
+                            const int w = wf + b0 + i;
+                            const int si = 2 * w + ((b0 + i == 0 && wf_second) ? 1 : 0);
+                            const float* pa = p.part_acc + (size_t)si * HD;
+#pragma unroll
+                            for (int kk = 0; kk < NK; ++kk) {
+                                const int d = lane + 32 * kk;
+                                tmp[i][kk] = (b0 + i < n_part && d < HD) ? __ldcg(pa + d) : 0.f;
+                            }
+                        }
+                    };
+                    load_batch(0);
+                    float mall = mi;
+#pragma unroll
+                    for (int d = 16; d >= 1; d >>= 1) mall = fmaxf(mall, __shfl_xor_sync(FULL, mall, d));
+                    const float mall_safe = (mall == -INFINITY) ? 0.f : mall;
+                    const float wg = lane < n_part ? fast_exp2(mi - mall_safe) : 0.f;
+                    lall = li * wg;
+                    for (int b0 = 0;;) {
+#pragma unroll
+                        for (int i = 0; i < kBatch; ++i) {
+                            const float wi = __shfl_sync(FULL, wg, (b0 + i) & 31);
+#pragma unroll
+                            for (int kk = 0; kk < NK; ++kk) o[kk] = fmaf(tmp[i][kk], wi, o[kk]);
+                        }
+                        b0 += kBatch;
+                        if (b0 >= n_part) break;
+                        load_batch(b0);
+                    }
+                } else {
+                    // an item cut into more than 32 pieces (few rows on many warps): (max, sum) first, then the
+                    // accumulators one partial at a time
+                    float mall = -INFINITY;
+                    for (int w0 = wf; w0 <= wl; w0 += 32) {
+                        const int w = w0 + lane;
+                        const float mi = w <= wl ? __ldcg(p.part_ml + 2 * (2 * w + (w == wf && wf_second ? 1 : 0))) : -INFINITY;
+                        mall = fmaxf(mall, mi);
+                    }
+#pragma unroll
+                    for (int d = 16; d >= 1; d >>= 1) mall = fmaxf(mall, __shfl_xor_sync(FULL, mall, d));
+                    const float mall_safe = (mall == -INFINITY) ? 0.f : mall;
+                    for (int w0 = wf; w0 <= wl; w0 += 32) {
+                        const int w = w0 + lane;
+                        const int slot_w = 2 * w + (w == wf && wf_second ? 1 : 0);
+                        float wg = 0.f;
+                        if (w <= wl) {
+                            wg = fast_exp2(__ldcg(p.part_ml + 2 * slot_w) - mall_safe);
+                            lall += __ldcg(p.part_ml + 2 * slot_w + 1) * wg;
+                        }
+                        const int cnt = min(32, wl - w0 + 1);
+                        for (int i = 0; i < cnt; ++i) {
+                            const float wi = __shfl_sync(FULL, wg, i);
+                            const int si = __shfl_sync(FULL, slot_w, i);
+                            const float* pa = p.part_acc + (size_t)si * HD;
+#pragma unroll
+                            for (int kk = 0; kk < NK; ++kk) {
+                                const int d = lane + 32 * kk;
+                                if (d < HD) o[kk] = fmaf(__ldcg(pa + d), wi, o[kk]);
+                            }
                         }
                     }
                 }
@@ -757,7 +805,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
                 for (int d = 16; d >= 1; d >>= 1) lall += __shfl_xor_sync(FULL, lall, d);
                 const float inv = lall > 0.f ? 1.f / lall : 0.f;
 #pragma unroll
-                for (int i = 0; i < (HD + 31) / 32; ++i) {
+                for (int i = 0; i < NK; ++i) {
                     const int d = lane + 32 * i;
                     if (d < HD) {
                         if (p.out_bf16)
@@ -767,6 +815,9 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
                     }
                 }
             }
+            // the counters of the merged items go back to zero for the next launch (after the merges: a store
+            // ahead of the fence above would make that fence wait for it)
+            if (my_last) p.counters[my_wf] = 0;
             pend_n = 0;
             __syncwarp();
         };
@@ -1053,15 +1104,16 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
     }
 
     TRACE(5);
-    // ---- the last CTA to finish re-arms the scratch counters ------------------------------------------
-    {
-        __shared__ int is_last;
-        if constexpr (FUSED) {
-            if (!dep_synced) {
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            }
+    // ---- the last CTA to finish re-arms the hand-out counter and the claims; a launch that uses neither
+    //      (even split, no dynamic pieces) has nothing to re-arm and its CTAs leave without the round trip ----
+    if constexpr (FUSED) {
+        if (!dep_synced) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         }
+    }
+    if (weighted || p.dyn_cap > 0) {
+        __shared__ int is_last;
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();
@@ -1070,17 +1122,11 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             if (is_last) {
                 *p.done_ctas = 0;
                 *p.dyn_next = 0;
-                if constexpr (!FUSED) {
-                    if (weighted)
-                        for (int i = 0; i < (int)gridDim.x; ++i) p.claim[i] = 0;
-                }
             }
         }
-        if constexpr (FUSED) {
-            __syncthreads();
-            if (is_last && weighted)
-                for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
-        }
+        __syncthreads();
+        if (is_last && weighted)
+            for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
     }
     TRACE(6);
 }

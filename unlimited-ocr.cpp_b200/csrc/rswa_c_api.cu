@@ -510,6 +510,8 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.d_ring_pos = c.d_ring_rw;
     ap.done_ctas = ws->done_ctas;
     ap.planned_ctas = ws->planned_ctas;
+    static int launch_seq = 0;
+    ap.trace_half = launch_seq++ & 1;
     if (c.rope_pos) {
         ap.rope_pos = c.rope_pos;
         // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
@@ -1170,8 +1172,29 @@ extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_tc_cta_tra
 #endif
 
 #ifdef UOCR_TRACE
+// instrumented builds: shares of the weighted split straight from per-SM rates (0 = SM not present)
+extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_set_split(uocr_b200_workspace* ws, const double* rate_by_smid) {
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+    int c = 0;
+    double total = 0, run = 0;
+    for (int sm = 0; sm < uocr_b200::kMaxSmid; ++sm) total += rate_by_smid[sm];
+    for (int sm = 0; sm < uocr_b200::kMaxSmid; ++sm) {
+        ws->slot_of_smid[sm] = 255;
+        if (rate_by_smid[sm] <= 0 || c >= di->sms) continue;
+        ws->slot_of_smid[sm] = (uint8_t)c;
+        run += rate_by_smid[sm];
+        ws->cta_frac[++c] = (int)std::llround(run / total * (double)(1 << 20));
+    }
+    if (c != di->sms) return -1;
+    ws->cta_frac[0] = 0;
+    ws->cta_frac[c] = 1 << 20;
+    cudaMemset(ws->claim, 0, sizeof(int) * 2 * uocr_b200::kMaxCtas);
+    ws->calibrated_ctas = c;
+    return 0;
+}
 extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_trace(unsigned long long* out, int n) {
     cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_trace, sizeof(unsigned long long) * n);
+    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_trace, sizeof(unsigned long long) * n);  // n <= 2 * 8 * 4096
 }
 #endif
