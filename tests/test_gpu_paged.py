@@ -391,6 +391,76 @@ def test_bf16_attention_output(orc, b):
     assert pb.ws.status() == 0
 
 
+def test_fused_decode_step_overlapped_launches(orc, b):
+    # the step of every layer queued back to back with launch overlap enabled (each kernel may become
+    # resident while its predecessor drains): outputs, pool contents and cursors still equal the oracle
+    import torch
+    slots, layers, W, P, kvh, hd = 12, 4, 80, 273, 10, 128
+    pb = PagedBatch(orc, slots, layers, kvh, hd, W, b.BF16, [P] * slots, prefix_keys=["doc"] * slots, seed=83)
+    pb.write_prefixes()
+    pb.ws.set_overlap(True)
+    rows = [7, 3, 11, 0, 5, 9, 1, 10, 2, 8, 4, 6]
+    ds = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    for t in range(W + 6):
+        ins = [pb.step_inputs(t, l, rows) for l in range(layers)]
+        dev = [[torch.from_numpy(x).cuda() for x in kvq] for kvq in ins]
+        outs = [torch.full((slots, kvh * hd), float("nan"), device="cuda") for _ in range(layers)]
+        torch.cuda.synchronize()
+        for l in range(layers):  # no host synchronisation between the launches
+            dk, dv, dq = dev[l]
+            b.decode_step_paged(pb.layer[l], dq, dk, dv, pb.d_len[l], pb.d_ring[l], pb.d_prefill, ds, slots, W,
+                                kvh, outs[l], pb.ws)
+        torch.cuda.synchronize()
+        check = t in (0, 1, W - 1, W, W + 5) or t % 9 == 0
+        for l in range(layers):
+            k, v, q = ins[l]
+            want = []
+            for i, s in enumerate(rows):
+                pb.cache[s].append_decode(l, k[i], v[i])
+                if check:
+                    want.append(pb.cache[s].attention(l, q[i:i + 1], pb.cache[s].len(l) - 1, kvh, False)[0])
+            if check:
+                assert_attention_close(outs[l].cpu().numpy(), np.stack(want), *TIGHT)
+    for l in range(layers):
+        pb.check_logical_view(l)
+    assert pb.ws.status() == 0
+
+
+def test_fused_decode_step_overlapped_launches_full_grid(orc, b):
+    # enough units that every warp of every CTA holds a piece: the overlapped launch then trims the share
+    # of its last CTA (the one that starts late); results must not depend on how the line is cut
+    import torch
+    slots, layers, W, P, kvh, hd = 64, 2, 32, 512, 10, 128
+    pb = PagedBatch(orc, slots, layers, kvh, hd, W, b.BF16, [P] * slots, prefix_keys=["doc"] * slots, seed=84)
+    pb.write_prefixes()
+    pb.ws.set_overlap(True)
+    rows = list(range(slots))[::-1]
+    ds = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    for t in range(W + 3):
+        ins = [pb.step_inputs(t, l, rows) for l in range(layers)]
+        dev = [[torch.from_numpy(x).cuda() for x in kvq] for kvq in ins]
+        outs = [torch.full((slots, kvh * hd), float("nan"), device="cuda") for _ in range(layers)]
+        torch.cuda.synchronize()
+        for l in range(layers):
+            dk, dv, dq = dev[l]
+            b.decode_step_paged(pb.layer[l], dq, dk, dv, pb.d_len[l], pb.d_ring[l], pb.d_prefill, ds, slots, W,
+                                kvh, outs[l], pb.ws)
+        torch.cuda.synchronize()
+        check = t in (0, W - 1, W, W + 2)
+        for l in range(layers):
+            k, v, q = ins[l]
+            want = []
+            for i, s in enumerate(rows):
+                pb.cache[s].append_decode(l, k[i], v[i])
+                if check:
+                    want.append(pb.cache[s].attention(l, q[i:i + 1], pb.cache[s].len(l) - 1, kvh, False)[0])
+            if check:
+                assert_attention_close(outs[l].cpu().numpy(), np.stack(want), *TIGHT)
+    for l in range(layers):
+        pb.check_logical_view(l)
+    assert pb.ws.status() == 0
+
+
 def test_fused_step_graph_replay(orc, b):
     import torch
     slots, W, P, kvh, hd = 4, 16, 9, 2, 64

@@ -100,6 +100,7 @@ struct AttnParams {
     int* d_len;
     int* d_ring_pos;
     int* done_ctas;
+    int late_cta;       // overlapped launches, even split: sixteenths of a share the last CTA's warps give up (0: none)
     int trace_half;     // instrumented builds only: which half of the timeline array this launch writes
     int* planned_ctas;  // CTAs that have built their plan from the pre-append cursors, zero between launches
 };
@@ -270,25 +271,42 @@ struct PieceMap {
     int ns, nd, chunk;
     const int* frac;  // weighted split: cumulative CTA shares scaled to 1 << 20 (kernel parameter space); else null
     int wpc;          // warps per CTA (weighted split: piece k belongs to CTA k / wpc)
+    // Even split under launch overlap: the warps of the last CTA carry (16 - late) / 16 of a share.  CTAs of
+    // an overlapped launch move in as their predecessor's CTAs leave, in block order, so the last block starts
+    // several microseconds after the others (it cannot hide its prologue) and would finish last by as much.
+    int late;
+    long long wtot;   // sum of the piece weights (16 each, 16 - late for the last CTA's)
+    __device__ __forceinline__ long long weight_before(int k) const {
+        const int n1 = ns - wpc;
+        return k <= n1 ? 16LL * k : 16LL * n1 + (long long)(16 - late) * (k - n1);
+    }
     // first unit of CTA c's share (weighted split only; u1 < 2^26, so the product fits 64 bits with room)
     __device__ __forceinline__ int bound(int c) const { return (int)((u1 * (long long)frac[c]) >> 20); }
     __device__ __forceinline__ long long start(int k) const {
         if (k >= ns) return u1 + (long long)(k - ns) * chunk;
-        if (frac == nullptr) return ((long long)k * u1) / ns;
+        if (frac == nullptr) return late ? (u1 * weight_before(k)) / wtot : ((long long)k * u1) / ns;
         const int c = k / wpc, j = k - c * wpc;
         const int b0 = bound(c);
         return b0 + (j * (bound(c + 1) - b0)) / wpc;
     }
     __device__ __forceinline__ long long end(int k) const {
         if (k >= ns) return u1 + (long long)(k - ns + 1) * chunk;
-        if (frac == nullptr) return ((long long)(k + 1) * u1) / ns;
+        if (frac == nullptr) return late ? (u1 * weight_before(k + 1)) / wtot : ((long long)(k + 1) * u1) / ns;
         const int c = k / wpc, j = k - c * wpc;
         const int b0 = bound(c);
         return b0 + ((j + 1) * (bound(c + 1) - b0)) / wpc;
     }
     __device__ __forceinline__ int of(long long u) const {
         if (u >= u1) return ns + (int)((u - u1) / chunk);
-        if (frac == nullptr) return (int)(((u + 1) * ns - 1) / u1);
+        if (frac == nullptr) {
+            if (!late) return (int)(((u + 1) * ns - 1) / u1);
+            // the last piece whose weight prefix w satisfies floor(u1 * w / wtot) <= u
+            const long long a = ((u + 1) * wtot - 1) / u1;
+            const int n1 = ns - wpc;
+            if (a < 16LL * n1) return (int)(a / 16);
+            const int k = n1 + (int)((a - 16LL * n1) / (16 - late));
+            return k < ns ? k : ns - 1;
+        }
         // the CTA owning unit v: start from the even split's answer, the shares move it by a step or two
         const int v = (int)u, n = ns / wpc;
         int lo = (int)(((long long)v * n) / u1);
@@ -316,17 +334,24 @@ __device__ __forceinline__ bool weighted_split_ok(long long total, int total_war
     return total >= 8LL * total_warps && total < (1LL << 26);
 }
 
-__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int dyn_cap, const int* frac, int wpc) {
+__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int dyn_cap, const int* frac, int wpc,
+                                                   int late = 0) {
     PieceMap m;
     m.total = total;
     m.frac = frac;
     m.wpc = wpc;
+    m.late = 0;
+    m.wtot = 0;
     m.chunk = kDynChunk;
     m.nd = 0;
     if (kDynShare > 0 && dyn_cap > 0 && total >= 8LL * total_warps)
         m.nd = (int)min((long long)dyn_cap, total / (max(kDynShare, 1) * kDynChunk));
     m.u1 = total - (long long)m.nd * kDynChunk;
     m.ns = (int)min((long long)total_warps, m.u1);
+    if (late > 0 && frac == nullptr && m.ns == total_warps && m.ns > wpc && weighted_split_ok(total, total_warps)) {
+        m.late = min(late, 12);
+        m.wtot = 16LL * m.ns - (long long)m.late * wpc;
+    }
     return m;
 }
 
@@ -525,7 +550,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
     const bool use_split = weighted && weighted_split_ok(total, p.total_warps);
     TRACE(1);
     const int gw = (weighted ? s_cta : (int)blockIdx.x) * warps + warp;
-    const PieceMap pm = make_piece_map(total, p.total_warps, p.dyn_cap, use_split ? p.cta_frac : nullptr, warps);
+    const PieceMap pm = make_piece_map(total, p.total_warps, p.dyn_cap, use_split ? p.cta_frac : nullptr, warps, p.late_cta);
     int piece = gw < pm.ns ? gw : -1;  // the warp's static piece; dynamic ones follow
     int n_units = 0;
     long long u0 = 0;

@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -372,6 +373,16 @@ struct AttnCall {
     float rope_theta = 0.f;
 };
 
+// Share the last CTA of an overlapped launch gives up, in sixteenths (UOCR_LATE_CTA overrides; measurement aid).
+int late_cta_sixteenths() {
+    static const int v = [] {
+        const char* e = std::getenv("UOCR_LATE_CTA");
+        const int x = e ? std::atoi(e) : 3;
+        return x < 0 ? 0 : (x > 12 ? 12 : x);
+    }();
+    return v;
+}
+
 constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
 
 template <typename KV, int HD, bool PAGED, bool FUSED, bool ROPE = false>
@@ -510,6 +521,7 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.d_ring_pos = c.d_ring_rw;
     ap.done_ctas = ws->done_ctas;
     ap.planned_ctas = ws->planned_ctas;
+    ap.late_cta = (c.fused && ws->overlap) ? late_cta_sixteenths() : 0;
     static int launch_seq = 0;
     ap.trace_half = launch_seq++ & 1;
     if (c.rope_pos) {
