@@ -888,6 +888,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
             if (it == 0) TRACE(3);
             if (it == n_units - 4) TRACE(6);  // four units left: the pace of the tail shows between here and the end
+            if (it == n_units - 4) TRACE(6);  // four units left: the pace of the tail shows between here and the end
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) {  // the new K row replaces whatever the ring slot held
                     const int off = (int)((meta >> kMetaPatchOffShift) & 15);
