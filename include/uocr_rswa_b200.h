@@ -96,7 +96,11 @@ UOCR_B200_API int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int
  * the stream is still finishing; it waits for that kernel before reading q / k / v and before
  * touching scratch.  Enable it only where the preceding kernel does not write THIS layer's cursors,
  * block table or pool (true between the layers of a decoder, whose predecessor is another layer's
- * work); leave it off otherwise, e.g. directly after a prefill of the same layer.  Default: off. */
+ * work); leave it off otherwise, e.g. directly after a prefill of the same layer.  Default: off.
+ * With overlap on, the CTAs of a launch move in as the CTAs of the preceding launch leave, so the
+ * last block starts several microseconds after the rest; when every warp holds work it is given
+ * 13/16 of an even share (environment variable UOCR_LATE_CTA = 0..12 sixteenths to give up, read
+ * once; a measurement aid).  Results do not depend on how the work is cut. */
 UOCR_B200_API int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled);
 
 /* Opt-in SM-weighted split for the attention kernels that use this workspace (no reference
