@@ -50,8 +50,26 @@ def load_pkg():
     return mod
 
 
+def _global_shard(rank: int):
+    """Strong-scaling workloads: positions and prefix ids are drawn once for the whole job; sequences are
+    ordered by prefix (affinity first: a GPU then holds as few distinct prefixes as possible, one copy of
+    each) and dealt to the ranks in contiguous, near-equal shards.  Returns (positions, prefix ids) of
+    this rank's sequences."""
+    import synth
+    total, n = CFG["total_seqs"], len(CFG["prefixes"])
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    pos = synth.integers(CFG["seed"], 77, CFG["pos_lo"], CFG["pos_hi"], (total,)).astype(np.int64)
+    ids = synth.integers(CFG["seed"], 177, 0, n - 1, (total,)).astype(np.int64) if n > 1 else np.zeros(total, np.int64)
+    order = np.argsort(ids, kind="stable")
+    start, count = shard_sequences(total, world, rank)
+    mine = order[start:start + count]
+    return pos[mine], ids[mine]
+
+
 def draw_positions(rank: int):
     import synth
+    if CFG["total_seqs"]:
+        return _global_shard(rank)[0][:CFG["seqs"]]
     return synth.integers(CFG["seed"], 77 + rank, CFG["pos_lo"], CFG["pos_hi"], (CFG["seqs"],)).astype(np.int64)
 
 
@@ -59,6 +77,8 @@ def draw_prefix_ids(rank: int):
     """Which of the distinct prefixes each sequence of this GPU uses (uniform; one prefix -> all 0)."""
     import synth
     n = len(CFG["prefixes"])
+    if CFG["total_seqs"]:
+        return _global_shard(rank)[1][:CFG["seqs"]]
     if n == 1:
         return np.zeros(CFG["seqs"], np.int64)
     return synth.integers(CFG["seed"], 177 + rank, 0, n - 1, (CFG["seqs"],)).astype(np.int64)
