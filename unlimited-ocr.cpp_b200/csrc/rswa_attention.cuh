@@ -390,8 +390,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // -------------------------------------------------------------------------------------------------
 // attention
 // -------------------------------------------------------------------------------------------------
+// Tile slots per warp.  Two (the K and the V tile of one unit, or V(u) and K(u+1), in flight) measured
+// faster than three at every size tried (16 to 512 sequences, W = 1024 and 4096: 2-5 % per step): sixteen
+// warps per SM already hold several times the bytes in flight that the memory latency asks for, and a
+// deeper ring only lengthens the queues in front of the memory.  One slot is slower at small sizes.
 #ifndef UOCR_RING
-#define UOCR_RING 3
+#define UOCR_RING 2
 #endif
 #ifndef UOCR_FFMA2
 #define UOCR_FFMA2 1

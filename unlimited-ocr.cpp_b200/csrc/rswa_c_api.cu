@@ -395,6 +395,9 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
                        kMaxWarpsPerCta * kPendMax * (int)sizeof(int);
     int warps = budget / per_warp;
     if (warps > kMaxWarpsPerCta) warps = kMaxWarpsPerCta;
+#ifdef UOCR_WARPS_CAP  // measurement aid: fewer warps per CTA than the workspace is sized for
+    if (warps > UOCR_WARPS_CAP) warps = UOCR_WARPS_CAP;
+#endif
     if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
     // Two half-size CTAs per SM when the tiles allow it: with the overlapped launch of the fused step a
     // CTA of the next launch can then move in as soon as half an SM has drained.
