@@ -463,7 +463,11 @@ def run_ours(args, rank, world):
                      "traffic_capture_algorithmic_bytes": 279.7e6 if CFG["name"] == "cfg2" and CFG["seqs"] == 64 else None,
                      "step_gbs": bytes_layer * CFG["layers"] / (ms / args.steps * 1e-3) / 1e9},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+                "ms_per_step": e2e_ms / args.steps,
+                "how": "per step: q/k/v of all layers from pinned host memory in %s host-to-device copies behind the "
+                       "kernels, results %s, host synchronises after every step"
+                       % (len(chunks), "stored by the kernels straight into the pinned host buffer (device-mapped)"
+                          if args.e2e_out == "mapped" else "returned by one device-to-host copy per layer")},
         "gpu_launches": wl.launches_per_step * args.steps,
         "clocks": clocks,
     }
@@ -719,7 +723,7 @@ def main():
     ap.add_argument("--rope", action="store_true",
                     help="fused step with the rotary embedding folded in (q, k un-rotated; one position per row)")
     ap.add_argument("--weighted", action="store_true", help="SM-weighted split (calibrates per-SM streaming rates first)")
-    ap.add_argument("--e2e-out", default="copy", choices=["copy", "mapped"],
+    ap.add_argument("--e2e-out", default="mapped", choices=["copy", "mapped"],
                     help="end-to-end step: results return by one device-to-host copy per layer, or the kernels "
                          "store them straight into the pinned host buffer")
     ap.add_argument("--no-overlap", action="store_true",
