@@ -14,7 +14,7 @@
 //
 // The fused decode step (FUSED = true) additionally plans in shared memory from the pre-append
 // cursors, patches the freshly appended token into the tile that holds its ring slot (and writes it
-// to the pool), and lets the last CTA to finish publish the new cursors: one launch per layer.
+// to the pool), and lets the last CTA to have planned store the new cursors: one launch per layer.
 //
 // Semantics follow RSWACache::attention (src/scheduler/kv_cache.cpp:84-130): scale 1/sqrt(d),
 // softmax over the attended slots, 0 for an empty set; decode is order-independent in the slot
@@ -390,12 +390,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // -------------------------------------------------------------------------------------------------
 // attention
 // -------------------------------------------------------------------------------------------------
-// Tile slots per warp.  Two (the K and the V tile of one unit, or V(u) and K(u+1), in flight) measured
-// faster than three at every size tried (16 to 512 sequences, W = 1024 and 4096: 2-5 % per step): sixteen
-// warps per SM already hold several times the bytes in flight that the memory latency asks for, and a
-// deeper ring only lengthens the queues in front of the memory.  One slot is slower at small sizes.
+// Tile slots per warp, and how many of them are kept in flight once the loop runs.  Two in flight (the K
+// and the V tile of one unit, or V(u) and K(u+1)) measured faster than three at every size tried (16 to 512
+// sequences, W = 1024 and 4096: 2-5 % per step): sixteen warps per SM already hold several times the bytes
+// in flight that the memory latency asks for, and more only lengthens the queues in front of the memory.
+// One is slower at small sizes.  UOCR_RING slots are filled before the loop starts -- under launch overlap
+// that is while the previous launch drains and the memory has room -- and UOCR_STEADY are refilled.
 #ifndef UOCR_RING
 #define UOCR_RING 2
+#endif
+#ifndef UOCR_STEADY
+#define UOCR_STEADY 2
 #endif
 #ifndef UOCR_FFMA2
 #define UOCR_FFMA2 1
@@ -407,6 +412,7 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #else
 #define TRACE(slot) do {} while (0)
 #endif
+constexpr int kSteady = UOCR_STEADY < UOCR_RING ? UOCR_STEADY : UOCR_RING;
 constexpr int kRing = UOCR_RING;  // shared-memory tile slots per warp; tiles K(0) V(0) K(1) V(1) ... rotate through them
 
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
@@ -647,8 +653,14 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
         };
 
         auto issue_next = [&]() {
-            if (issue_seq < 2 * n_units) issue_tile(issue_seq >> 1, (issue_seq & 1) != 0);
-            ++issue_seq;
+            if (issue_seq < 2 * n_units) {
+                issue_tile(issue_seq >> 1, (issue_seq & 1) != 0);
+                ++issue_seq;
+            }
+        };
+        // after `consumed` tiles of the piece have been used: refill while fewer than kSteady are in flight
+        auto refill = [&](int consumed) {
+            if (issue_seq - consumed < kSteady) issue_next();
         };
         // ---- consumer state ---------------------------------------------------------------------
         float2 q2[PPL], acc2[PPL];
@@ -955,7 +967,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            issue_next();
+            refill(2 * it + 1);
 
             RowReduce<ITER, LPR / 2>::run(sc, lane);
             const int my_tok = (LPR >= 2 ? (g >> 1) * RPW : 0) + rg;
@@ -1045,7 +1057,7 @@ __global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            issue_next();
+            refill(2 * it + 2);
 
             // ---- end of an item (or of the piece): emit ----------------------------------------------
             const bool item_done = (meta & kMetaLast) != 0;
