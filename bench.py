@@ -716,7 +716,7 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="issue append and attention as the reference does (two entry points per layer) "
                          "instead of the fused one-launch decode step")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "churn"],
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "churn", "gather"],
                     help="cfg2 (default, headline): 64 seqs/GPU, W=1024, one shared prefix, weak scaling; "
                          "cfg4: 512 seqs in total sharded over the GPUs, W=4096, 4 prefixes, strong scaling; "
                          "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
@@ -743,7 +743,16 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     if CFG["total_seqs"]:
         CFG["seqs"] = shard_sequences(CFG["total_seqs"], world, rank)[1]
-    if args.workload == "churn":
+    if args.workload == "gather":
+        if rank == 0:
+            import torch
+            pkg = load_pkg()
+            pkg.lib()
+            print(json.dumps({"metric": "rswa_gather_batched", "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+                              "config": {"workload": "block-table gather of 256 sequences (656-token shared prefix + "
+                                                     "W=1024 ring each, bf16) in one launch"},
+                              **gather_batched_gbs(pkg, torch, reps=max(args.steps, 1) if args.steps < 500 else 10)}))
+    elif args.workload == "churn":
         run_churn(args, rank, world)
     elif args.workload == "cfg3":
         run_prefill(args, rank, world)
