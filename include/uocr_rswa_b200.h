@@ -303,9 +303,11 @@ UOCR_B200_API int uocr_b200_rswa_prefill_attention_tc(
  * uocr::cuda::rswa_append_decode_batch followed by uocr::cuda::rswa_attention_batch (the pair issued
  * at src/engine/gpu_decoder.cu:990-996), on the paged layout.  Every CTA plans from the pre-append
  * cursors, the warp that owns the tile holding a row's ring slot patches the new token into it (and
- * writes it to the pool), and the last CTA to finish publishes the new d_len / d_ring_pos.  Results
- * and final state are identical to calling the two separate entry points.  batch > 1024 falls back
- * to those two launches. */
+ * writes it to the pool), and the last CTA to have planned stores the new d_len / d_ring_pos (no CTA
+ * reads the cursors again in that launch).  Results and final state are identical to calling the
+ * two separate entry points.  batch > 1024 falls back to those two launches.  `out` may be any
+ * address the device can write, pinned (device-mapped) host memory included: the kernel then
+ * delivers the layer's result to the host without a copy of its own. */
 UOCR_B200_API int uocr_b200_rswa_decode_step_paged(
     const uocr_b200_paged_kv* kv, const float* q, const float* k, const float* v, int* d_len,
     int* d_ring_pos, const int* d_prefill_len, const int* d_slots, int batch, int window, int heads,

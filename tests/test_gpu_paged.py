@@ -264,6 +264,30 @@ def test_fused_decode_step_real_geometry_and_mixed_calls(orc, b):
     assert pb.ws.status() == 0
 
 
+@pytest.mark.parametrize("dtype_name,hd,kvh,heads", [("bf16", 256, 2, 2), ("f32", 256, 1, 4), ("bf16", 64, 2, 8),
+                                                      ("f32", 64, 4, 4), ("bf16", 32, 1, 2)])
+def test_head_dims_of_the_reference_dispatch_and_grouped_heads(orc, b, dtype_name, hd, kvh, heads):
+    # the reference instantiates its kernels for head_dim 64 / 128 / 256 (rswa_attention.cu:348-359) and maps
+    # query head h to kv head h / (heads / kv_heads): fused and separate calls, across the ring wrap
+    dtype = b.BF16 if dtype_name == "bf16" else b.F32
+    slots, W, P = 5, 32, 21
+    pb = PagedBatch(orc, slots, 1, kvh, hd, W, dtype, [P, P, 7, P, 0], prefix_keys=["a", "a", "b", "a", "c"],
+                    heads=heads, seed=hd + kvh)
+    pb.write_prefixes()
+    rows = [3, 0, 4, 1, 2]
+    for t in range(2 * W + 3):
+        k, v, q = pb.step_inputs(t, 0, rows)
+        if t % 4 == 1:
+            pb.append(0, k, v, rows)
+            got, want = pb.attend(0, q, rows)
+        else:
+            got, want = pb.step_fused(0, k, v, q, rows)
+        assert_attention_close(got, want, *tol_for(b, dtype))
+        assert_attention_close(got, want, *TIGHT)
+    pb.check_logical_view(0)
+    assert pb.ws.status() == 0
+
+
 def test_fused_decode_step_stores_into_pinned_host_output(orc, b):
     # `out` may be any device-accessible address: pinned host memory receives the same values, from
     # rows written directly by one warp and from rows merged out of partials alike
