@@ -399,6 +399,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifndef UOCR_RING
 #define UOCR_RING 2
 #endif
+#ifndef UOCR_ATTN_THREADS
+#define UOCR_ATTN_THREADS 512  // threads per CTA the attention kernel is compiled for (16 warps: 124 registers each)
+#endif
 #ifndef UOCR_STEADY
 #define UOCR_STEADY 2
 #endif
@@ -482,7 +485,7 @@ __device__ __forceinline__ void rope_chunk(const float* freq, float pos, int d0,
 }
 
 template <typename KV, int HD, bool PAGED, bool FUSED, bool ROPE = false>
-__global__ void __launch_bounds__(512, 1) rswa_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const __grid_constant__ AttnParams p) {
     static_assert(!ROPE || (FUSED && HD >= 2 * KV::kPerChunk), "rotary embedding: fused step only, a chunk must lie in one half of the head");
     using M = TileMap<KV, HD>;
     constexpr int LPR = M::kLanesPerRow, CPL = M::kChunksPerLane, RPW = M::kRowsPerLoad;

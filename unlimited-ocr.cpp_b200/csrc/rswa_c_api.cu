@@ -72,7 +72,7 @@ int device_info(const DeviceInfo** out) {
     return UOCR_B200_OK;
 }
 
-constexpr int kMaxWarpsPerCta = 16;
+constexpr int kMaxWarpsPerCta = UOCR_ATTN_THREADS / 32;
 constexpr int kMaxHeadDim = 256;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
