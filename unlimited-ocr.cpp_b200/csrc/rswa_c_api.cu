@@ -525,8 +525,12 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.done_ctas = ws->done_ctas;
     ap.planned_ctas = ws->planned_ctas;
     ap.late_cta = (c.fused && ws->overlap) ? late_cta_sixteenths() : 0;
-    static int launch_seq = 0;
+#ifdef UOCR_TRACE
+    static int launch_seq = 0;  // instrumented builds: consecutive (overlapping) launches alternate timeline halves
     ap.trace_half = launch_seq++ & 1;
+#else
+    ap.trace_half = 0;
+#endif
     if (c.rope_pos) {
         ap.rope_pos = c.rope_pos;
         // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
