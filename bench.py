@@ -627,7 +627,7 @@ def run_prefill(args, rank, world):
                    "query_tiles": int(tiles.shape[0]), "attended_pairs_per_layer": pairs},
         "roofline": {"bound": "tensor", "kernel": "rswa_prefill_tc_kernel", "achieved": tf, "unit": "TFLOP/s",
                      "peak": peaks.get("bf16_tflops"), "frac": (tf / peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
-                     "note": "useful flops only; the kernel issues 2x (hi+lo operands) and is not yet pipelined"},
+                     "note": "useful flops only; the tensor core executes 2x that (Q and P go in as bf16 hi+lo pairs)"},
         "cuda_core_path_ms_per_layer": ms_cuda_core_layer, "tensor_core_path_ms_per_layer": ms / L}))
 
 
