@@ -131,6 +131,17 @@ class Ranks:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t[0])
 
+    def gather(self, values):
+        """Every rank's list of floats, as a list of lists indexed by rank (same on all ranks)."""
+        if not self.dist:
+            return [list(values)]
+        import torch
+        dev = self.device if self.device is not None else "cpu"
+        mine = torch.tensor(list(values), dtype=torch.float64, device=dev)
+        out = [torch.zeros_like(mine) for _ in range(self.world)]
+        self.dist.all_gather(out, mine)
+        return [[float(x) for x in t.tolist()] for t in out]
+
     def close(self):
         if self.dist:
             self.dist.barrier()
@@ -345,6 +356,85 @@ class DecodeWorkload:
         return g
 
 
+def parity_check(pkg, wl, n_seqs=4):
+    """After the timed region: one more decode step of layer 0 on the device, and the same step on the CPU
+    oracle (the checker, never the thing timed) for a few sampled sequences.  The oracle caches are filled
+    with what the device holds -- read back through the block-table gather -- driven to the same cursors
+    through the reference's own calls (reset, write_prefill, append_decode), then append + attention.
+    Cursors must agree exactly, outputs within max-abs 2e-2 / rel-L2 1e-3 (bf16 KV)."""
+    import torch
+    import synth
+    from oracle import oracle
+    if wl.rope:
+        return None
+    orc = oracle.load("orc")
+    c, W, B = CFG, CFG["window"], wl.B
+    sel = sorted({int(round(x)) for x in np.linspace(0, B - 1, n_seqs)})
+    cap = int(max(c["prefixes"])) + W
+    ds = torch.tensor(sel, dtype=torch.int32, device="cuda")
+    gk = torch.empty((len(sel), cap, wl.row), device="cuda")
+    gv = torch.empty_like(gk)
+    pkg.gather_paged(wl.layers[0], wl.d_len[0], wl.d_prefill, ds, len(sel), cap, gk, gv, pkg.F32, wl.ws)
+    len0, ring0 = wl.d_len[0].cpu().numpy(), wl.d_ring[0].cpu().numpy()
+    hk, hv = gk.cpu().numpy(), gv.cpu().numpy()
+    q, k, v = (x[0].cpu().numpy() for x in (wl.q, wl.k, wl.v))
+    out = torch.full((B, wl.row), float("nan"), device="cuda")
+    wl.layer_step(0, out)
+    got = out.cpu().numpy()
+    len1, ring1 = wl.d_len[0].cpu().numpy(), wl.d_ring[0].cpu().numpy()
+    want, cursors_ok = [], True
+    for i, s_ in enumerate(sel):
+        P = int(wl.plen[s_])
+        n = int(len0[s_]) - P
+        cache = orc.Cache(1, c["kv_heads"], c["head_dim"], W)
+        cache.reset(P)
+        cache.write_prefill(0, hk[i, :P], hv[i, :P])
+        for j in range(n):
+            cache.append_decode(0, hk[i, P + j], hv[i, P + j])
+        if n == W:  # steady state: the same rows once more up to the device's ring position
+            for j in range(int(ring0[s_])):
+                cache.append_decode(0, hk[i, P + j], hv[i, P + j])
+        cache.append_decode(0, synth.round_bf16(k[s_]), synth.round_bf16(v[s_]))
+        cursors_ok &= cache.len(0) == int(len1[s_]) and cache.ring_pos(0) == int(ring1[s_])
+        want.append(cache.attention(0, q[s_:s_ + 1], cache.len(0) - 1, c["heads"], False)[0])
+    want = np.stack(want)
+    g = got[sel]
+    max_abs = float(np.abs(g - want).max())
+    rel_l2 = float(np.linalg.norm(g - want) / max(np.linalg.norm(want), 1e-30))
+    ok = bool(np.isfinite(g).all() and cursors_ok and max_abs <= 2e-2 and rel_l2 <= 1e-3)
+    assert ok, f"parity check failed: max-abs {max_abs}, rel-L2 {rel_l2}, cursors ok {cursors_ok}"
+    return {"ok": ok, "max_abs": max_abs, "rel_l2": rel_l2, "rows": len(sel), "sequences": sel, "layer": 0,
+            "window_tokens": [int(len0[x] - wl.plen[x]) for x in sel], "cursors_bit_exact": bool(cursors_ok),
+            "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-3}, "checker": "CPU oracle (restatement of RSWACache)"}
+
+
+def kernel_source_sha():
+    """Hash of the sources the dominant kernel is compiled from; ties an ncu traffic record to the code."""
+    import hashlib
+    h = hashlib.sha256()
+    for f in ("rswa_attention.cuh", "rswa_device.cuh"):
+        h.update(open(os.path.join(ROOT, "unlimited-ocr.cpp_b200", "csrc", f), "rb").read())
+    return h.hexdigest()[:16]
+
+
+def traffic_record(name="rswa_attn_kernel_fused_bf16_hd128_cfg2.md"):
+    """DRAM traffic of one launch of the dominant kernel from the committed ncu summary: a line
+    `traffic-record: kernel_sha=<hash> dram_bytes=<read+write> algorithmic_bytes=<bytes at the captured step>`.
+    Returned only while the kernel sources still hash to the recorded value; otherwise the record is stale
+    and the traffic is reported as null."""
+    import re
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        m = re.search(r"traffic-record:\s*kernel_sha=(\w+)\s+dram_bytes=([\d.e+]+)\s+algorithmic_bytes=([\d.e+]+)", open(path).read())
+    except OSError:
+        m = None
+    if not m:
+        return None, None, "no traffic record"
+    if m.group(1) != kernel_source_sha():
+        return None, None, f"stale: profiles/{name} was captured at kernel sources {m.group(1)}, now {kernel_source_sha()}"
+    return float(m.group(2)), float(m.group(3)), f"profiles/{name} @ kernel sources {m.group(1)}"
+
+
 def run_ours(args, rank, world):
     import torch
     pkg = load_pkg()
@@ -363,29 +453,39 @@ def run_ours(args, rank, world):
         ranks.barrier()
         torch.cuda.synchronize()
 
-    # ---- timed region: K whole steps (12 layers x (append + attention)), one graph launch each ----
+    # ---- timed region: K whole steps (12 layers x (append + attention)), one graph launch each.  The
+    # K-step train is timed `repeats` times in this one invocation, every time from the same cursor state
+    # (a short launch train is a thin sample: the median over the repeats is the reported value, min and
+    # max stand beside it); each repeat is bracketed by barrier + synchronize and is the MAX over ranks ----
     stream = torch.cuda.current_stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
-    barrier()
-    steps_before = wl.steps_done
-    e0.record(stream)
-    for _ in range(args.steps):
-        wl.step()
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
+    start_pos = wl.pos0 + wl.steps_done
+    rep_ms_local = []
+    for _ in range(args.repeats):
+        wl.set_positions(start_pos)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            wl.step()
+        e1.record(stream)
+        barrier()
+        rep_ms_local.append(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
-    ms = ranks.max_over_ranks(ms)
+    by_rank = ranks.gather(rep_ms_local)  # [rank][repeat]
+    rep_ms = [max(r[i] for r in by_rank) for i in range(args.repeats)]
+    ms = statistics.median(rep_ms)
+    per_rank_ms = [statistics.median(r) / args.steps for r in by_rank]
     dev_status = wl.ws.status()
     assert dev_status == 0, f"device status {dev_status}"
 
     # ---- roofline of the dominant kernel: per-launch duration of the partial-attention kernel ------
-    pos_mid = wl.pos0 + steps_before + np.arange(args.steps)[:, None] + 1  # after each timed append
+    pos_mid = start_pos + np.arange(args.steps)[:, None] + 1  # after each timed append
     bytes_layer = float(np.mean([algorithmic_bytes_per_layer(p, wl.prefix_ids) for p in pos_mid]))
+    parity = parity_check(pkg, wl) if rank == 0 and not args.no_parity_check else None
     wl.ws.set_timing(True)
     kms = []
     wl.step_plain(lambda l: kms.append(wl.ws.last_kernel_ms()))
@@ -394,6 +494,7 @@ def run_ours(args, rank, world):
         wl.step_plain(lambda l: kms.append(wl.ws.last_kernel_ms()))
         wl.steps_done += 1
     wl.ws.set_timing(False)
+    wl.set_positions(start_pos + args.steps)  # all layers back on one cursor state
     k_ms_isolated = float(np.mean(kms))  # one launch between two events on an idle stream (includes launch latency)
     # The fused step is ONE launch per layer, so the timed region is a back-to-back train of identical
     # launches of the dominant kernel: its average launch duration is the region's time per launch.
@@ -413,31 +514,48 @@ def run_ours(args, rank, world):
     e2e_graph = wl.capture_e2e(hqkv, hout, chunks, mapped_out=(args.e2e_out == "mapped"))
     for _ in range(2):
         e2e_graph.replay()
-    barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        e2e_graph.replay()
-        wl.steps_done += 1
-        stream.synchronize()  # the caller reads the step's result before the next step
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    e2e_ms = ranks.max_over_ranks(e2e_ms)
+    e2e_local = []
+    for _ in range(args.repeats):
+        wl.set_positions(start_pos)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_graph.replay()
+            stream.synchronize()  # the caller reads the step's result before the next step
+        e1.record(stream)
+        barrier()
+        e2e_local.append(e0.elapsed_time(e1))
+    e2e_by_rank = ranks.gather(e2e_local)
+    e2e_rep = [max(r[i] for r in e2e_by_rank) for i in range(args.repeats)]
+    e2e_ms = statistics.median(e2e_rep)
     h2d = int(hqkv.numel() * 4)
     d2h = int(hout.numel() * 4)
 
+    # ---- read-only streaming rate of this GPU through the same copy engine path the kernel uses (one CTA
+    # per SM, 4 KB bulk copies into shared memory): a second denominator beside the read+write copy peak ----
+    stream_read_gbs = wl.ws.stream_read_gbs() if rank == 0 else None
+
+    secondary = None
+    if rank == 0 and world == 1 and not args.no_secondary and CFG["name"] == "cfg2":
+        del e2e_graph, hqkv, hout
+        secondary = {"cfg3_ragged_prefill": prefill_record(pkg, torch, layers=2, steps=3, warmup=2),
+                     "gather_batched": gather_batched_gbs(pkg, torch, reps=5)}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(sample_seqs=16, steps=4, threads=host_threads())
+        cpu = cpu_baseline(sample_seqs=CFG["seqs"], steps=4, threads=host_threads())
     ranks.close()
     if rank != 0:
         return
+    traffic, traffic_alg, traffic_source = traffic_record() if (CFG["name"] == "cfg2" and CFG["seqs"] == 64 and not args.separate
+                                                                  and not args.rope) else (None, None, "no capture of this workload")
     seqs_all = [shard_sequences(CFG["total_seqs"], world, r)[1] for r in range(world)] if CFG["total_seqs"] \
         else [CFG["seqs"]] * world
     tokens = sum(seqs_all) * args.steps
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "repeats": args.repeats, "ms_per_step_min": min(rep_ms) / args.steps, "ms_per_step_max": max(rep_ms) / args.steps,
+        "per_rank_ms": per_rank_ms,
         "scaling": "strong" if CFG["total_seqs"] else "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "%s: batched decode, %d seqs/GPU x %d layers, 10 heads x 128, bf16 paged KV "
@@ -454,23 +572,31 @@ def run_ours(args, rank, world):
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": k_ms,
                      "kernel_ms_isolated_launch": k_ms_isolated,
+                     # one launch alone between two events (no neighbour hides its prologue): in a decoder the
+                     # neighbours are other kernels, so the drop-in figure lies between frac_isolated and frac
+                     "frac_isolated": bytes_layer / (k_ms_isolated * 1e-3) / 1e9 / peak,
                      "algorithmic_bytes_per_launch": bytes_layer,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
-                     # workload's per-layer shape (ncu capture summarised under profiles/).  The capture
-                     # sits at the workload's first steps, where a launch has 279.7 MB of algorithmic
-                     # bytes; every step appends a token per sequence, so later steps move a little more.
-                     "traffic": 284.4e6 if CFG["name"] == "cfg2" and CFG["seqs"] == 64 else None,
-                     "traffic_capture_algorithmic_bytes": 279.7e6 if CFG["name"] == "cfg2" and CFG["seqs"] == 64 else None,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the ncu
+                     # capture summarised in the file named by traffic_source (null when the kernel sources
+                     # changed since); the capture sits at the workload's first steps, hence its own byte count
+                     "traffic": traffic, "traffic_capture_algorithmic_bytes": traffic_alg, "traffic_source": traffic_source,
+                     "stream_read_gbs": stream_read_gbs,
+                     "frac_of_stream_read": (achieved / stream_read_gbs) if stream_read_gbs else None,
                      "step_gbs": bytes_layer * CFG["layers"] / (ms / args.steps * 1e-3) / 1e9},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps,
+                "ms_per_step": e2e_ms / args.steps, "ms_per_step_min": min(e2e_rep) / args.steps,
+                "ms_per_step_max": max(e2e_rep) / args.steps,
                 "how": "per step: q/k/v of all layers from pinned host memory in %s host-to-device copies behind the "
                        "kernels, results %s, host synchronises after every step"
                        % (len(chunks), "stored by the kernels straight into the pinned host buffer (device-mapped)"
                           if args.e2e_out == "mapped" else "returned by one device-to-host copy per layer")},
-        "gpu_launches": wl.launches_per_step * args.steps,
+        "gpu_launches": wl.launches_per_step * args.steps,  # per timed K-step train (there are `repeats` of them)
         "clocks": clocks,
     }
+    if parity:
+        line["parity_check"] = parity
+    if secondary:
+        line["secondary"] = secondary
     if cpu:
         line["cpu_baseline"] = cpu
     print(json.dumps(line))
@@ -497,7 +623,8 @@ def cpu_baseline(sample_seqs: int, steps: int, threads: int = 0):
     sec, used, _ = o.run_decode_bench(pl, pos, CFG["layers"], CFG["kv_heads"], CFG["head_dim"], CFG["window"],
                                       steps, threads=threads, seed=CFG["seed"])
     return {"value": sample_seqs * steps / sec, "unit": UNIT, "cores": used, "kind": kind,
-            "sample": f"first {sample_seqs} of the 64 sequences, all 12 layers, {steps} decode steps, fp32 KV "
+            "sample": f"{'all' if sample_seqs >= CFG['seqs'] else 'first'} {sample_seqs} of the {CFG['seqs']} sequences, "
+                      f"all {CFG['layers']} layers, {steps} decode steps, fp32 KV "
                       f"holding the bf16-rounded values; OpenMP over (sequence, layer) in the harness",
             "seconds": sec}
 
@@ -505,7 +632,7 @@ def cpu_baseline(sample_seqs: int, steps: int, threads: int = 0):
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    seqs = 16
+    seqs = CFG["seqs"]  # every sequence of the configuration (fp32 caches: about 10 GB of host memory for cfg2)
     steps = max(args.steps, 1)
     # warm-up steps are part of the same call (state set-up dominates); time K steps
     cpu = cpu_baseline(sample_seqs=seqs, steps=steps, threads=host_threads())
@@ -513,7 +640,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": world,
         "steps": steps, "warmup": args.warmup, "ms_per_step": cpu["seconds"] / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg2 sample on host cores: " + cpu["sample"]},
+        "config": {"workload": "cfg2 on host cores: " + cpu["sample"]},
         "cpu_baseline": cpu,
         "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -531,10 +658,16 @@ def run_prefill(args, rank, world):
     if rank != 0:
         return
     import torch
-    import synth
     pkg = load_pkg()
+    print(json.dumps(prefill_record(pkg, torch, layers=args.layers or CFG["layers"], steps=max(1, min(args.steps, 20)),
+                                    warmup=max(args.warmup, 1))))
+
+
+def prefill_record(pkg, torch, layers, steps, warmup):
+    """The cfg3 measurement as a dict (see run_prefill); `layers` < 12 gives a compact record for the default line."""
+    import synth
     c = CFG
-    S, L, W, H, D, bt = 16, args.layers or c["layers"], c["window"], c["heads"], c["head_dim"], 16
+    S, L, W, H, D, bt = 16, layers, 1024, c["heads"], c["head_dim"], 16
     row = H * D
     pv = np.array([(256, 656, 1056)[i] for i in synth.integers(c["seed"], 301, 0, 2, (S,))])
     tl = synth.integers(c["seed"], 302, 64, 2048, (S,)).astype(np.int64)
@@ -598,10 +731,9 @@ def run_prefill(args, rank, world):
                             d_ring[l], nt, W, ws)
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for _ in range(max(args.warmup, 1)):
+    for _ in range(warmup):
         layer_pass(0)
     torch.cuda.synchronize()
-    steps = max(1, min(args.steps, 20))
     e0.record()
     for _ in range(steps):
         for l in range(L):
@@ -619,16 +751,26 @@ def run_prefill(args, rank, world):
     assert ws.status() == 0
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
     tf = flops * L / (ms * 1e-3) / 1e12
-    print(json.dumps({
+    # the attention kernel alone (the dominant kernel of the pass), per layer
+    e0.record()
+    for _ in range(steps):
+        pkg.prefill_attention_tc(layers[0], text_k, text_v, text_blocks, q, d_prefill, tiles, W, H, out, ws)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_attn = e0.elapsed_time(e1) / steps
+    tf_attn = flops / (ms_attn * 1e-3) / 1e12
+    return ({
         "metric": "rswa_prefill_tokens_per_s", "value": (nv + nt) / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "ms_per_step": ms, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "cfg3: ragged prefill + ring fill, 16 seqs x %d layers, prefixes {256,656,1056}, "
                                "text U[64,2048], W=1024" % L, "vision_tokens": nv, "text_tokens": nt,
                    "query_tiles": int(tiles.shape[0]), "attended_pairs_per_layer": pairs},
-        "roofline": {"bound": "tensor", "kernel": "rswa_prefill_tc_kernel", "achieved": tf, "unit": "TFLOP/s",
-                     "peak": peaks.get("bf16_tflops"), "frac": (tf / peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
-                     "note": "useful flops only; the tensor core executes 2x that (Q and P go in as bf16 hi+lo pairs)"},
-        "cuda_core_path_ms_per_layer": ms_cuda_core_layer, "tensor_core_path_ms_per_layer": ms / L}))
+        "roofline": {"bound": "tensor", "kernel": "rswa_prefill_tc_kernel", "achieved": tf_attn, "unit": "TFLOP/s",
+                     "peak": peaks.get("bf16_tflops"), "frac": (tf_attn / peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
+                     "kernel_ms": ms_attn, "whole_pass_tflops": tf,
+                     "note": "useful flops (5120 per attended query-key pair) over the attention kernel's own time; "
+                             "whole_pass_tflops divides by the pass including the scatter kernels"},
+        "cuda_core_path_ms_per_layer": ms_cuda_core_layer, "tensor_core_path_ms_per_layer": ms / L})
 
 
 def gather_batched_gbs(pkg, torch, seqs=256, prefix=656, window=1024, reps=10):
@@ -676,14 +818,14 @@ def run_churn(args, rank, world):
     """Configuration 5: pool of 65536 blocks x 12 layers (64 GB), 1000 requests on a seeded Poisson
     schedule, 8 prefixes, W=1024; reports append and block-table gather bandwidth (algorithmic bytes:
     append reads the fp32 k, v rows and writes them as bf16; gather reads and writes len x 5120 B per
-    layer).  Table parity for this workload is asserted by tests/test_gpu_churn.py."""
+    layer).  Table parity for this workload at full size is asserted by tests/test_host_classes.py (host
+    integers only) and with device values at reduced size by tests/test_gpu_churn.py."""
     if rank != 0:
         return
     import torch
     import churn_driver
-    from oracle import oracle  # only its generic C-ABI driver class is used, on the CUDA library itself
     pkg = load_pkg()
-    host = oracle.Oracle("b200-host", path=pkg.LIB_PATH, prefix="uocr_b200")
+    host = pkg.host_classes()  # the library's own MemoryPool / BlockManager / scheduler through its C ABI
     cfg = churn_driver.ChurnConfig(layers=args.layers or 12)
     t0 = time.time()
     res = churn_driver.run(cfg, host, check=None, time_kernels=True)
@@ -712,7 +854,11 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=10,
+                    help="how many times the K-step train is timed (median reported, min / max beside it)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity-check", action="store_true", help="skip the oracle check of 4 sequences after the timed region")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the compact cfg3 / gather records of the default line")
     ap.add_argument("--separate", action="store_true",
                     help="issue append and attention as the reference does (two entry points per layer) "
                          "instead of the fused one-launch decode step")
@@ -739,6 +885,7 @@ def main():
     if args.seqs:
         CFG["seqs"] = args.seqs
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if CFG["total_seqs"]:

@@ -90,6 +90,15 @@ UOCR_B200_API int uocr_b200_workspace_last_kernel_ms(uocr_b200_workspace* ws, fl
  * is read when a call is issued (and frozen into captured graphs). */
 UOCR_B200_API int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int dtype);
 
+/* How many polls a wait for a KV tile may take before the warp gives up (default and maximum: 2^22;
+ * each poll already blocks for a hardware-defined slice).  A wait that runs out sets
+ * UOCR_B200 device status bit 2 (reported by uocr_b200_workspace_status, which also clears the
+ * scratch counters the abandoned launch left half-way); the warp lets its copies in flight land and
+ * leaves, the kernel ends normally and the results of that launch are void.  Lowering the limit is
+ * a diagnostic aid: 0 makes every wait give up at once, which exercises exactly that path without
+ * hanging anything.  Applies to the split-KV attention kernels launched with this workspace. */
+UOCR_B200_API int uocr_b200_workspace_set_wait_limit(uocr_b200_workspace* ws, unsigned polls);
+
 /* Opt-in launch overlap for uocr_b200_rswa_decode_step_paged calls that use this workspace.  When
  * enabled, the step is launched with programmatic stream serialization: its prologue (planning from
  * the layer's cursors, block-table reads, the first KV tiles) may run while the preceding kernel in
@@ -99,8 +108,7 @@ UOCR_B200_API int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int
  * work); leave it off otherwise, e.g. directly after a prefill of the same layer.  Default: off.
  * With overlap on, the CTAs of a launch move in as the CTAs of the preceding launch leave, so the
  * last block starts several microseconds after the rest; when every warp holds work it is given
- * 13/16 of an even share (environment variable UOCR_LATE_CTA = 0..12 sixteenths to give up, read
- * once; a measurement aid).  Results do not depend on how the work is cut. */
+ * 13/16 of an even share.  Results do not depend on how the work is cut. */
 UOCR_B200_API int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled);
 
 /* Opt-in SM-weighted split for the attention kernels that use this workspace (no reference
@@ -115,12 +123,18 @@ UOCR_B200_API int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int e
  * changes).  Pays off on large launches (measured +2.5..4 % on 512 sequences x W=4096, -0.7 % on 64
  * sequences x W=1024, where the claim and the uneven bounds cost more than the balance returns).
  * The shares travel in the kernel parameters: calibrate before capturing a graph.  Allocates: call
- * outside stream capture.  enabled: 0 = even split, 1 = weighted; 2 (even shares through the
- * claimed path) and 3 (shares proportional to the measured rate) exist for measurements.
+ * outside stream capture.  enabled: 0 = even split, non-zero = weighted.
  * split_shares copies the cumulative shares (scaled to 1 << 20, one more entry than SMs) to the host
  * and returns how many it wrote, 0 when off. */
 UOCR_B200_API int uocr_b200_workspace_calibrate(uocr_b200_workspace* ws, int enabled, uocr_b200_stream_t stream);
 UOCR_B200_API int uocr_b200_workspace_split_shares(const uocr_b200_workspace* ws, int* out_frac, int n);
+
+/* Measurement aid (no reference counterpart): the rate at which this GPU streams from HBM into shared
+ * memory through the path the attention kernels use -- one persistent CTA per SM, 16 warps each pulling
+ * 4 KB tiles with bulk async copies, nothing written back -- in GB/s (median of 5 runs over a 1.2 GB
+ * buffer read twice).  A read-only denominator to put beside a copy-bandwidth figure, which counts a
+ * read and a write stream.  Allocates the buffer and synchronises: call outside stream capture. */
+UOCR_B200_API int uocr_b200_workspace_stream_read_gbs(uocr_b200_workspace* ws, uocr_b200_stream_t stream, double* gbs);
 
 /* ------------------------------------------------------------------------------------------------
  * Paged KV view of ONE layer.
@@ -183,8 +197,9 @@ UOCR_B200_API int uocr_b200_rswa_write_prefill_ragged_paged(
 
 /* ================================================================================================
  * Attention.  q / out are fp32 [rows][heads*head_dim]; scale = 1/sqrt(head_dim); out = 0 for a row
- * that attends nothing.  All forms run the same split-KV kernels: a plan kernel, a persistent
- * partial-attention kernel fed by bulk async copies, and a merge kernel.
+ * that attends nothing.  All forms run the same split-KV kernels: a plan kernel (folded into the
+ * attention kernel in the fused decode steps) and a persistent attention kernel fed by bulk async
+ * copies, in which whichever warp finishes a split item last merges its partial results.
  * ============================================================================================= */
 
 /* Replaces uocr::cuda::rswa_attention_batch (include/uocr/cuda_ops.h:104-107;
@@ -342,10 +357,20 @@ UOCR_B200_API int uocr_b200_rswa_decode_step_rope_paged(
  * share the array: it still holds the previous call's contents when the next one starts (the call
  * clears the parts that have to start at zero itself), and two calls that overlap on the GPU --
  * different streams, or different host threads -- race on it.  Issue them on one stream, or
- * serialise them yourself.  Results are identical to the workspace-based entry point. */
+ * serialise them yourself.  Results are identical to the workspace-based entry point.  Arguments
+ * are checked before the array is touched, so a refused call leaves it as it was. */
 UOCR_B200_API int uocr_b200_rswa_attention_batch_paged_noalloc(
     const uocr_b200_paged_kv* kv, const float* q, const int* d_len, const int* d_prefill_len,
     const int* d_slots, int batch, int heads, float* out, uocr_b200_stream_t stream);
+
+/* Device status of the allocation-free calls (no counterpart in the reference): what
+ * uocr_b200_workspace_status is for workspace-based calls.  The kernels never trap on a bad block id,
+ * a table row that is too short or a wait that ran out: they substitute block 0 / leave the loop and
+ * set a bit of a status word that lives in the same built-in array (1 bad block id, 2 wait ran out,
+ * 4 position outside the table row).  The bits accumulate over calls until this function reads them:
+ * it synchronises `stream`, copies the word to *device_status (4 bytes into the caller's variable) and
+ * clears it.  It allocates nothing either. */
+UOCR_B200_API int uocr_b200_noalloc_status(uocr_b200_stream_t stream, int* device_status);
 
 /* ================================================================================================
  * Block-table gather: paged storage -> the reference's logical view

@@ -15,7 +15,9 @@ REF_BIN = os.path.join(ROOT, "oracle", "_ref", "ref_kv_ring_buffer_on_b200")
 HOST_API_BIN = os.path.join(BIN, "test_host_api")
 
 
-def build(ref_root="/root/reference"):
+def build(ref_root=None):
+    from oracle import oracle
+    ref_root = ref_root or oracle.reference_root()
     os.makedirs(BIN, exist_ok=True)
     subprocess.check_call([
         "nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O1", "-std=c++17",

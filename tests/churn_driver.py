@@ -45,20 +45,26 @@ def arrivals(cfg):
     return np.floor(np.cumsum(gaps)).astype(np.int64)
 
 
-def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False):
-    import torch
+def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False, device=True):
+    """`device=False` replays the bookkeeping alone (allocator, scheduler, slots, block-table rows: host
+    integers) with no KV writes, so the full-size schedule can be checked without a GPU."""
     b = load_b200()
     bt = b.BLOCK_TOKENS
     L, row, W = cfg.layers, cfg.kv_heads * cfg.head_dim, cfg.window
     rb = ceil_div(W, bt)
     stride = ceil_div(max(cfg.prefix_lens), bt) + rb
     num_blocks = cfg.prefix_arena_blocks + cfg.ring_arena_blocks
-    table = torch.full((cfg.slots, stride), -1, dtype=torch.int32, device="cuda")
-    layers = [b.PagedLayer(num_blocks, cfg.kv_heads, cfg.head_dim, b.BF16, table) for _ in range(L)]
-    d_len = torch.zeros((L, cfg.slots), dtype=torch.int32, device="cuda")
-    d_ring = torch.zeros((L, cfg.slots), dtype=torch.int32, device="cuda")
-    d_prefill = torch.zeros(cfg.slots, dtype=torch.int32, device="cuda")
-    ws = b.Workspace(max(cfg.slots, 64))
+    host_table = np.full((cfg.slots, stride), -1, np.int32)
+    host_len = np.zeros(cfg.slots, np.int64)       # tokens appended so far, per slot (closed-form cursors)
+    host_prefill = np.zeros(cfg.slots, np.int64)
+    if device:
+        import torch
+        table = torch.full((cfg.slots, stride), -1, dtype=torch.int32, device="cuda")
+        layers = [b.PagedLayer(num_blocks, cfg.kv_heads, cfg.head_dim, b.BF16, table) for _ in range(L)]
+        d_len = torch.zeros((L, cfg.slots), dtype=torch.int32, device="cuda")
+        d_ring = torch.zeros((L, cfg.slots), dtype=torch.int32, device="cuda")
+        d_prefill = torch.zeros(cfg.slots, dtype=torch.int32, device="cuda")
+        ws = b.Workspace(max(cfg.slots, 64))
 
     arr = arrivals(cfg)
     pkey = synth.integers(cfg.seed, 902, 0, len(cfg.prefix_lens) - 1, (cfg.requests,))
@@ -69,14 +75,15 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False):
     scheds = [x.Scheduler(cfg.slots, 4) for x in impls]
     free_slots = list(range(cfg.slots))  # handed out from the back, released slots reused first
     slot_of, ring_of, rows_log, mismatches = {}, {}, [], 0
-    k_in = torch.randn((L, cfg.slots, row), device="cuda")
-    v_in = torch.randn((L, cfg.slots, row), device="cuda")
     cap = max(cfg.prefix_lens) + W
-    gk = torch.empty((1, cap, row), dtype=torch.bfloat16, device="cuda")
-    gv = torch.empty_like(gk)
+    if device:
+        k_in = torch.randn((L, cfg.slots, row), device="cuda")
+        v_in = torch.randn((L, cfg.slots, row), device="cuda")
+        gk = torch.empty((1, cap, row), dtype=torch.bfloat16, device="cuda")
+        gv = torch.empty_like(gk)
     stats = dict(steps=0, append_rows=0, append_ms=0.0, gather_tokens=0, gather_ms=0.0, peak_running=0,
                  prefix_hits=0, prefix_misses=0)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if device else []
     sampled = {}
     nxt, step = 0, 0
     while nxt < cfg.requests or scheds[0].has_work():
@@ -109,10 +116,14 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False):
             r[:pb] = off // 256 + np.arange(pb)
             r[pb:pb + rb] = cfg.prefix_arena_blocks + roff // 256 + np.arange(rb)
             rows_log.append((rid, slot, r.copy()))
-            table[slot].copy_(torch.from_numpy(r))
-            d_len[:, slot] = P
-            d_ring[:, slot] = 0
-            d_prefill[slot] = P
+            host_table[slot] = r
+            host_len[slot] = 0
+            host_prefill[slot] = P
+            if device:
+                table[slot].copy_(torch.from_numpy(r))
+                d_len[:, slot] = P
+                d_ring[:, slot] = 0
+                d_prefill[slot] = P
             if oracle_caches is not None and cfg.sample_every and rid % cfg.sample_every == 0:
                 c = oracle_caches.Cache(L, cfg.kv_heads, cfg.head_dim, W)
                 c.reset(P)
@@ -124,7 +135,11 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False):
         # ---- one token per running sequence per layer ---------------------------------------------------
         run_ids = [i for i in dc] + [i for i in pf]
         stats["peak_running"] = max(stats["peak_running"], len(run_ids))
-        if run_ids:
+        for i in run_ids:
+            host_len[slot_of[i]] += 1
+        if run_ids and not device:
+            stats["append_rows"] += len(run_ids) * L
+        if run_ids and device:
             rows = torch.tensor([slot_of[i] for i in run_ids], dtype=torch.int32, device="cuda")
             n = len(run_ids)
             if time_kernels:
@@ -152,7 +167,12 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False):
                 continue
             slot = slot_of.pop(i)
             P = int(cfg.prefix_lens[pkey[i]])
-            if cfg.gather_on_finish:
+            if device:  # device cursors equal the closed form of the ring state machine for this slot
+                n_app = int(host_len[slot])
+                want_len = P + min(n_app, W)
+                want_ring = 0 if n_app < W else (n_app - W) % W
+                assert int(d_len[0, slot]) == want_len and int(d_ring[0, slot]) == want_ring
+            if cfg.gather_on_finish and device:
                 sl = torch.tensor([slot], dtype=torch.int32, device="cuda")
                 if time_kernels:
                     ev[2].record()
@@ -175,14 +195,18 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False):
                 bm.release_prefix(f"doc{pkey[i]}")
             ring_of.pop(i)
             free_slots.append(slot)
-            table[slot] = -1
+            host_table[slot] = -1
+            if device:
+                table[slot] = -1
         if check is not None and bms[0].stats() != bms[1].stats():
             mismatches += 1
         step += 1
         stats["steps"] = step
         assert step < 10_000_000
-    assert ws.status() == 0
+    if device:
+        assert ws.status() == 0
+        assert np.array_equal(table.cpu().numpy(), host_table)
     final = [bm.stats() for bm in bms]
     sched_final = [s.stats() for s in scheds]
-    return dict(stats=stats, rows=rows_log, mismatches=mismatches, final=final, sched=sched_final,
+    return dict(stats=stats, rows=rows_log, mismatches=mismatches, final=final, sched=sched_final, table=host_table,
                 row_bytes_in=row * 4 * 2, row_bytes_out=row * 2 * 2)

@@ -29,7 +29,7 @@ def test_churn_tables_bit_exact(orc, checker):
     if checker == "ref" and not oracle.available("ref"):
         pytest.skip("compiled reference not present")
     b = load_b200()
-    host = oracle.Oracle("b200-host", path=b.LIB_PATH, prefix="uocr_b200")
+    host = b.host_classes()
     chk = oracle.load(checker)
     cfg = small_cfg()
     res = churn_driver.run(cfg, host, check=chk, oracle_caches=orc)

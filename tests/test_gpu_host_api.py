@@ -25,7 +25,7 @@ def host():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     b = load_b200()
-    return oracle.Oracle("b200-host", path=b.LIB_PATH, prefix="uocr_b200")
+    return b.host_classes()
 
 
 @pytest.mark.parametrize("name", ["tiny", "tiny_gqa", "p0", "ref_cuda_case", "cfg1"])

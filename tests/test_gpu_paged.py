@@ -415,15 +415,18 @@ def test_bf16_attention_output(orc, b):
     assert pb.ws.status() == 0
 
 
-def test_fused_decode_step_overlapped_launches(orc, b):
+@pytest.mark.parametrize("slots,layers", [(12, 4), (2, 3)])
+def test_fused_decode_step_overlapped_launches(orc, b, slots, layers):
     # the step of every layer queued back to back with launch overlap enabled (each kernel may become
-    # resident while its predecessor drains): outputs, pool contents and cursors still equal the oracle
+    # resident while its predecessor drains): outputs, pool contents and cursors still equal the oracle.
+    # The two-slot case leaves most CTAs without a unit (they plan, draw their ticket and leave at once, so
+    # CTAs of the next launch move in early) and has an odd number of launches per step.
     import torch
-    slots, layers, W, P, kvh, hd = 12, 4, 80, 273, 10, 128
+    W, P, kvh, hd = 80, 273, 10, 128
     pb = PagedBatch(orc, slots, layers, kvh, hd, W, b.BF16, [P] * slots, prefix_keys=["doc"] * slots, seed=83)
     pb.write_prefixes()
     pb.ws.set_overlap(True)
-    rows = [7, 3, 11, 0, 5, 9, 1, 10, 2, 8, 4, 6]
+    rows = [7, 3, 11, 0, 5, 9, 1, 10, 2, 8, 4, 6] if slots == 12 else [1, 0]
     ds = torch.tensor(rows, dtype=torch.int32, device="cuda")
     for t in range(W + 6):
         ins = [pb.step_inputs(t, l, rows) for l in range(layers)]
@@ -514,5 +517,34 @@ def test_fused_step_graph_replay(orc, b):
             pb.cache[s].append_decode(0, kk[i], vv[i])
             want.append(pb.cache[s].attention(0, qq[i:i + 1], pb.cache[s].len(0) - 1, kvh, False)[0])
         assert_attention_close(got, np.stack(want), *TIGHT)
+    pb.check_logical_view(0)
+    assert pb.ws.status() == 0
+
+
+def test_wait_that_runs_out_is_reported_and_the_workspace_recovers(orc, b):
+    # With the poll limit at zero every tile wait gives up at once: each warp records the fact, lets the
+    # copies it has in flight land and leaves; the kernel ends normally (nothing hangs, nothing faults),
+    # the status word says the launch is void, and after the status call the same workspace serves the
+    # next launch correctly.  Long rows so that items are split over several warps and partials are in play.
+    slots, W, P = 12, 96, 400
+    pb = PagedBatch(orc, slots, 1, 10, 128, W, b.BF16, [P] * slots, prefix_keys=["doc"] * slots, seed=61)
+    pb.write_prefixes()
+    rows = list(range(slots))
+    for t in range(W + 5):
+        k, v, q = pb.step_inputs(t, 0, rows)
+        pb.append(0, k, v, rows)
+    got, want = pb.attend(0, q, rows)
+    assert_attention_close(got, want, *TIGHT)
+    pb.ws.set_wait_limit(0)
+    pb.attend(0, q, rows)  # void launch
+    assert pb.ws.status() & b.STATUS_WAIT_TIMEOUT
+    pb.ws.set_wait_limit(1 << 22)
+    assert pb.ws.status() == 0
+    for _ in range(2):
+        got, want = pb.attend(0, q, rows)
+        assert_attention_close(got, want, *TIGHT)
+    k, v, q = pb.step_inputs(W + 5, 0, rows)
+    got, want = pb.step_fused(0, k, v, q, rows)
+    assert_attention_close(got, want, *TIGHT)
     pb.check_logical_view(0)
     assert pb.ws.status() == 0

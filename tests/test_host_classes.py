@@ -15,7 +15,7 @@ from oracle import oracle
 from paged_fixture import ROOT, load_b200
 
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "rswa_golden.npz"))
-REF = "/root/reference"
+REF = oracle.reference_root()
 
 
 @pytest.fixture(scope="module")
@@ -23,7 +23,7 @@ def host():
     b = load_b200()
     if not os.path.exists(b.LIB_PATH):
         b.build()
-    return oracle.Oracle("b200-host", path=b.LIB_PATH, prefix="uocr_b200")
+    return b.host_classes()
 
 
 @pytest.mark.parametrize("key", ["pool", "pool1"])
@@ -98,3 +98,33 @@ def test_reference_unit_tests_compile_and_pass_against_this_library(tmp_path):
     obj = tmp_path / "kv.o"
     subprocess.check_call(["g++", "-std=c++17", "-c", *[f"-I{i}" for i in inc],
                            os.path.join(REF, "tests", "test_kv_ring_buffer.cpp"), "-o", str(obj)])
+
+
+@pytest.mark.parametrize("checker", ["orc", "ref"])
+def test_churn_full_size_tables_bit_exact(host, checker):
+    # The block-manager churn stress at its full size -- pool of 65536 blocks (1024 prefix ids + 64512 ring
+    # ids), 1000 requests on the seeded arrival schedule, 8 prefixes, output lengths 32..2048, W=1024 -- with
+    # the KV writes switched off: allocator offsets, every block-table row, every stats tuple and every
+    # scheduler batch of this library's host classes must equal the checker's (the compiled reference where
+    # it is present, the restatement always), the end-of-run table is empty and both arenas are free.
+    import churn_driver
+    if checker == "ref" and not oracle.available("ref"):
+        pytest.skip("compiled reference not present")
+    chk = oracle.load(checker)
+    cfg = churn_driver.ChurnConfig()
+    assert (cfg.requests, cfg.prefix_arena_blocks + cfg.ring_arena_blocks, cfg.window) == (1000, 65536, 1024)
+    res = churn_driver.run(cfg, host, check=chk, device=False)
+    assert res["mismatches"] == 0
+    assert len(res["rows"]) == cfg.requests
+    ring_blocks = cfg.window // 16
+    live = {}
+    for rid, slot, row in res["rows"]:
+        used = row[row >= 0]
+        assert used.min() >= 0 and used.max() < 65536
+        ring = row[row >= cfg.prefix_arena_blocks]
+        assert len(ring) == ring_blocks and (np.diff(ring) == 1).all()  # one contiguous first-fit allocation
+    a, c = res["final"]
+    assert a == c and a[0] == 0 and a[3] == 0 and a[7] == 0
+    assert (res["table"] == -1).all()
+    assert res["sched"][0] == res["sched"][1] and res["sched"][0][1] == cfg.requests
+    assert res["stats"]["prefix_hits"] > 0 and res["stats"]["peak_running"] > 64

@@ -35,8 +35,12 @@ def test_noalloc_matches_workspace_entry_point_twice(orc):
         want = torch.full((slots, kvh * hd), float("nan"), device="cuda")
         got = torch.full((slots, kvh * hd), float("nan"), device="cuda")
         b.attention_batch_paged(pb.layer[0], dq, pb.d_len[0], pb.d_prefill, ds, slots, kvh, want, pb.ws)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]  # the driver's own count of free device memory
         b.attention_batch_paged_noalloc(pb.layer[0], dq, pb.d_len[0], pb.d_prefill, ds, slots, kvh, got)
         torch.cuda.synchronize()
+        if call == 1:  # the first call may load the kernel's code; by the second nothing may change hands
+            assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free call changed free device memory"
         assert_attention_close(got.cpu().numpy(), want.cpu().numpy(), 2e-5, 1e-5)
         # and both agree with the CPU oracle
         ref = np.stack([pb.cache[s].attention(0, q[i:i + 1], pb.cache[s].len(0) - 1, kvh, False)[0]
@@ -48,3 +52,29 @@ def test_noalloc_matches_workspace_entry_point_twice(orc):
         b.attention_batch_paged_noalloc(pb.layer[0], dq, pb.d_len[0], pb.d_prefill, ds, 1025, kvh, got)
     assert e.value.status == 4 and "1024" in str(e.value)
     assert b.launch_count() == before
+    assert b.noalloc_status() == 0  # nothing was recorded by the calls above
+
+
+def test_noalloc_reports_device_status(orc):
+    # A block id outside the pool is never dereferenced: the kernel reads block 0 instead and records the
+    # fact.  A caller of the allocation-free entry point has no workspace to ask, so the word lives in the
+    # built-in array and uocr_b200_noalloc_status reads (and clears) it.  A refused call leaves it alone.
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    b = load_b200()
+    pb = PagedBatch(orc, 2, 1, 2, 16, 16, b.BF16, [4, 4], seed=5)
+    q = torch.zeros((2, 32), device="cuda")
+    out = torch.zeros((2, 32), device="cuda")
+    ds = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    b.noalloc_status()  # start from a clean word whatever ran before
+    tbl = pb.table.clone()
+    tbl[0, 0] = pb.num_blocks + 5
+    poisoned = b.PagedLayer(pb.num_blocks, 2, 16, b.BF16, tbl)
+    b.attention_batch_paged_noalloc(poisoned, q, pb.d_len[0], pb.d_prefill, ds, 2, 2, out)
+    with pytest.raises(b.Error):  # heads not a multiple of kv_heads: refused before the array is touched
+        b.attention_batch_paged_noalloc(pb.layer[0], q, pb.d_len[0], pb.d_prefill, ds, 2, 3, out)
+    assert b.noalloc_status() & b.STATUS_BAD_BLOCK
+    assert b.noalloc_status() == 0  # reading clears it
+    b.attention_batch_paged_noalloc(pb.layer[0], q, pb.d_len[0], pb.d_prefill, ds, 2, 2, out)
+    assert b.noalloc_status() == 0

@@ -69,9 +69,12 @@ _SIGS = {
     "uocr_b200_workspace_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "uocr_b200_workspace_set_timing": (_i, [_vp, _i]),
     "uocr_b200_workspace_set_overlap": (_i, [_vp, _i]),
+    "uocr_b200_workspace_set_wait_limit": (_i, [_vp, C.c_uint]),
+    "uocr_b200_noalloc_status": (_i, [_vp, C.POINTER(_i)]),
     "uocr_b200_workspace_set_out_dtype": (_i, [_vp, _i]),
     "uocr_b200_workspace_calibrate": (_i, [_vp, _i, _vp]),
     "uocr_b200_workspace_split_shares": (_i, [_vp, _vp, _i]),
+    "uocr_b200_workspace_stream_read_gbs": (_i, [_vp, _vp, C.POINTER(C.c_double)]),
     "uocr_b200_workspace_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
     "uocr_b200_rswa_append_decode_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
@@ -184,9 +187,19 @@ class Workspace:
     def set_overlap(self, enabled: bool) -> None:
         check(lib().uocr_b200_workspace_set_overlap(self.h, 1 if enabled else 0))
 
+    def set_wait_limit(self, polls: int) -> None:
+        """Polls a tile wait may take before the warp gives up (0: every wait gives up at once)."""
+        check(lib().uocr_b200_workspace_set_wait_limit(self.h, polls))
+
     def calibrate(self, enabled: bool = True, stream=None) -> None:
         """SM-weighted split for the attention kernels of this workspace (measures per-SM streaming rates)."""
         check(lib().uocr_b200_workspace_calibrate(self.h, int(enabled), stream_handle(stream)))
+
+    def stream_read_gbs(self, stream=None) -> float:
+        """Read-only HBM -> shared-memory streaming rate of this GPU in GB/s (bulk copies, one CTA per SM)."""
+        v = C.c_double(0)
+        check(lib().uocr_b200_workspace_stream_read_gbs(self.h, stream_handle(stream), C.byref(v)))
+        return v.value
 
     def split_shares(self):
         """Cumulative per-SM shares scaled to 1 << 20 (empty list: even split)."""
@@ -209,6 +222,21 @@ class Workspace:
             self.close()
         except Exception:
             pass
+
+
+def host_classes():
+    """ctypes table + object wrappers over this library's host classes (MemoryPool, BlockManager,
+    ContinuousBatchScheduler, RSWACache): see host_classes.py."""
+    import importlib.util
+    import sys
+    name = "uocr_b200_host_classes"
+    if name not in sys.modules:
+        spec = importlib.util.spec_from_file_location(name, os.path.join(HERE, "host_classes.py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+    lib()  # a missing library is an error
+    return sys.modules[name].FunctionTable(LIB_PATH, "uocr_b200")
 
 
 def launch_count() -> int:
@@ -314,6 +342,13 @@ def attention_batch_paged_noalloc(layer, q, d_len, d_prefill, d_slots, batch, he
     check(lib().uocr_b200_rswa_attention_batch_paged_noalloc(layer.ref(), _p(q), _p(d_len), _p(d_prefill),
                                                               _p(d_slots), batch, heads, _p(out),
                                                               stream_handle(stream)))
+
+
+def noalloc_status(stream=None) -> int:
+    """Reads and clears the device status word of the allocation-free calls (synchronises the stream)."""
+    v = _i(0)
+    check(lib().uocr_b200_noalloc_status(stream_handle(stream), C.byref(v)))
+    return v.value
 
 
 def write_prefill_ragged_paged(layer, k, v, d_slots, d_pos, total, ws=None, stream=None):

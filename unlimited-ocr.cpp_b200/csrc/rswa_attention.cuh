@@ -77,9 +77,8 @@ struct AttnParams {
     float* part_acc;  // [2 * pieces][head_dim]
     float* part_ml;   // [2 * pieces][2]  (max in log2 domain, sum)
     int* counters;    // [pieces] arrival counters, zero between launches
-    int* dyn_next;    // next dynamic piece to hand out, zero between launches
-    int dyn_cap;      // most dynamic pieces the scratch can hold (0 = static split only)
     int* status;
+    uint32_t wait_limit;  // polls a tile wait may take before the warp gives up (kWaitLimit unless a test lowers it)
     int total_warps;
     // SM-weighted split (cta_frac null: even split).  A CTA takes the share measured for the SM it
     // runs on; `claim` (zero between launches) makes sure every share is taken exactly once even if
@@ -99,10 +98,11 @@ struct AttnParams {
     const float* v_new;
     int* d_len;
     int* d_ring_pos;
-    int* done_ctas;
+    int* done_ctas;     // weighted split: CTAs that have finished (the last one re-arms the claims), zero between launches
     int late_cta;       // overlapped launches, even split: sixteenths of a share the last CTA's warps give up (0: none)
     int trace_half;     // instrumented builds only: which half of the timeline array this launch writes
-    int* planned_ctas;  // CTAs that have built their plan from the pre-append cursors, zero between launches
+    int* planned_ctas;  // ticket counter: CTAs that have built their plan from the pre-append cursors; wraps to zero
+                        // with the last ticket of a launch (atomicInc), so nothing has to reset it
 };
 
 // -------------------------------------------------------------------------------------------------
@@ -261,14 +261,11 @@ __device__ __forceinline__ void cursor_next(UnitCursor& c, const int* rs, const 
     c.info = info[c.r];
 }
 
-// How the unit line [0, total) is cut into pieces.  The first `ns` pieces are static, one per warp,
-// and cover [0, u1) evenly; the remaining `nd` pieces of `chunk` units each cover [u1, total) and are
-// handed out at run time (one atomic per piece) to whichever warps finish early: SMs differ by
-// +-15 % in how fast they stream, and a purely static split makes everybody wait for the slowest.
-// Every piece is non-empty and pieces are consecutive, so an item spans pieces of(first)..of(last).
+// How the unit line [0, total) is cut into pieces: one piece per warp of the persistent grid, consecutive
+// and non-empty, so an item spans pieces of(first unit) .. of(last unit).
 struct PieceMap {
-    long long total, u1;
-    int ns, nd, chunk;
+    long long total;
+    int ns;           // number of pieces: min(total warps, total units)
     const int* frac;  // weighted split: cumulative CTA shares scaled to 1 << 20 (kernel parameter space); else null
     int wpc;          // warps per CTA (weighted split: piece k belongs to CTA k / wpc)
     // Even split under launch overlap: the warps of the last CTA carry (16 - late) / 16 of a share.  CTAs of
@@ -280,28 +277,20 @@ struct PieceMap {
         const int n1 = ns - wpc;
         return k <= n1 ? 16LL * k : 16LL * n1 + (long long)(16 - late) * (k - n1);
     }
-    // first unit of CTA c's share (weighted split only; u1 < 2^26, so the product fits 64 bits with room)
-    __device__ __forceinline__ int bound(int c) const { return (int)((u1 * (long long)frac[c]) >> 20); }
+    // first unit of CTA c's share (weighted split only; total < 2^26, so the product fits 64 bits with room)
+    __device__ __forceinline__ int bound(int c) const { return (int)((total * (long long)frac[c]) >> 20); }
     __device__ __forceinline__ long long start(int k) const {
-        if (k >= ns) return u1 + (long long)(k - ns) * chunk;
-        if (frac == nullptr) return late ? (u1 * weight_before(k)) / wtot : ((long long)k * u1) / ns;
+        if (frac == nullptr) return late ? (total * weight_before(k)) / wtot : ((long long)k * total) / ns;
         const int c = k / wpc, j = k - c * wpc;
         const int b0 = bound(c);
         return b0 + (j * (bound(c + 1) - b0)) / wpc;
     }
-    __device__ __forceinline__ long long end(int k) const {
-        if (k >= ns) return u1 + (long long)(k - ns + 1) * chunk;
-        if (frac == nullptr) return late ? (u1 * weight_before(k + 1)) / wtot : ((long long)(k + 1) * u1) / ns;
-        const int c = k / wpc, j = k - c * wpc;
-        const int b0 = bound(c);
-        return b0 + ((j + 1) * (bound(c + 1) - b0)) / wpc;
-    }
+    __device__ __forceinline__ long long end(int k) const { return k + 1 < ns ? start(k + 1) : total; }
     __device__ __forceinline__ int of(long long u) const {
-        if (u >= u1) return ns + (int)((u - u1) / chunk);
         if (frac == nullptr) {
-            if (!late) return (int)(((u + 1) * ns - 1) / u1);
-            // the last piece whose weight prefix w satisfies floor(u1 * w / wtot) <= u
-            const long long a = ((u + 1) * wtot - 1) / u1;
+            if (!late) return (int)(((u + 1) * ns - 1) / total);
+            // the last piece whose weight prefix w satisfies floor(total * w / wtot) <= u
+            const long long a = ((u + 1) * wtot - 1) / total;
             const int n1 = ns - wpc;
             if (a < 16LL * n1) return (int)(a / 16);
             const int k = n1 + (int)((a - 16LL * n1) / (16 - late));
@@ -309,7 +298,7 @@ struct PieceMap {
         }
         // the CTA owning unit v: start from the even split's answer, the shares move it by a step or two
         const int v = (int)u, n = ns / wpc;
-        int lo = (int)(((long long)v * n) / u1);
+        int lo = (int)(((long long)v * n) / total);
         int b0 = bound(lo), b1 = bound(lo + 1);
         while (lo > 0 && b0 > v) { --lo; b1 = b0; b0 = bound(lo); }
         while (lo < n - 1 && b1 <= v) { ++lo; b0 = b1; b1 = bound(lo + 1); }
@@ -317,16 +306,7 @@ struct PieceMap {
     }
 };
 
-#ifndef UOCR_DYN_CHUNK
-#define UOCR_DYN_CHUNK 4
-#endif
-#ifndef UOCR_DYN_SHARE
-#define UOCR_DYN_SHARE 0
-#endif
-constexpr int kDynChunk = UOCR_DYN_CHUNK;  // units per dynamic piece
-constexpr int kDynShare = UOCR_DYN_SHARE;  // 1/kDynShare of the units are handed out dynamically (0: none)
-constexpr int kDynPerWarp = 4;    // scratch is sized for this many dynamic pieces per warp
-constexpr int kPendMax = 32;      // per-warp list of partial segments awaiting their arrival
+constexpr int kPendMax = 4;  // per-warp list of partial segments awaiting their arrival (a piece leaves at most two)
 
 // Whether the weighted split applies to a launch: enough units that no piece can be empty (the shares
 // differ by tens of percent at most) and few enough that the bounds fit 32-bit arithmetic.
@@ -334,20 +314,14 @@ __device__ __forceinline__ bool weighted_split_ok(long long total, int total_war
     return total >= 8LL * total_warps && total < (1LL << 26);
 }
 
-__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int dyn_cap, const int* frac, int wpc,
-                                                   int late = 0) {
+__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, const int* frac, int wpc, int late = 0) {
     PieceMap m;
     m.total = total;
     m.frac = frac;
     m.wpc = wpc;
     m.late = 0;
     m.wtot = 0;
-    m.chunk = kDynChunk;
-    m.nd = 0;
-    if (kDynShare > 0 && dyn_cap > 0 && total >= 8LL * total_warps)
-        m.nd = (int)min((long long)dyn_cap, total / (max(kDynShare, 1) * kDynChunk));
-    m.u1 = total - (long long)m.nd * kDynChunk;
-    m.ns = (int)min((long long)total_warps, m.u1);
+    m.ns = (int)min((long long)total_warps, total);
     if (late > 0 && frac == nullptr && m.ns == total_warps && m.ns > wpc && weighted_split_ok(total, total_warps)) {
         m.late = min(late, 12);
         m.wtot = 16LL * m.ns - (long long)m.late * wpc;
@@ -544,9 +518,12 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         // this CTA's plan; the answer is looked at once the first tiles are on their way, and the warp
         // that learns it was the last planner stores the new cursors (nobody reads them again in this
         // launch), which keeps the publication off the tail of the launch.
+        // The counter wraps to zero with the launch's last ticket, so it needs no reset; a CTA of the next
+        // (overlapped) launch cannot draw before every ticket of this one is taken, because a CTA releases
+        // its dependents only after warp 0 has looked at its own ticket (see dependency_sync below).
         if (threadIdx.x == 0) {
             __threadfence();
-            planner_ticket = atomicAdd(p.planned_ctas, 1);
+            planner_ticket = (int)atomicInc(reinterpret_cast<unsigned*>(p.planned_ctas), gridDim.x - 1);
         }
         rs = rs_s;
         info = info_s;
@@ -563,14 +540,15 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
     const bool use_split = weighted && weighted_split_ok(total, p.total_warps);
     TRACE(1);
     const int gw = (weighted ? s_cta : (int)blockIdx.x) * warps + warp;
-    const PieceMap pm = make_piece_map(total, p.total_warps, p.dyn_cap, use_split ? p.cta_frac : nullptr, warps, p.late_cta);
-    int piece = gw < pm.ns ? gw : -1;  // the warp's static piece; dynamic ones follow
+    const PieceMap pm = make_piece_map(total, p.total_warps, use_split ? p.cta_frac : nullptr, warps, p.late_cta);
+    const int piece = gw < pm.ns ? gw : -1;  // this warp's piece of the unit line (-1: more warps than units)
     int n_units = 0;
     long long u0 = 0;
     int* pend = reinterpret_cast<int*>(smem + bar_bytes + (size_t)warps * (kRing * TILE)) + warp * kPendMax;
     int pend_n = 0;
     bool gave_up = false, dep_synced = false;
     int issue_slot = 0, issue_seq = 0;  // issue_seq: position in the piece's tile sequence (unit = seq / 2, V if odd)
+    int consumed = 0;                   // tiles of that sequence whose arrival has been waited for
     int use_slot = 0;                   // slot holding the next tile to consume
     uint32_t phases = 0;                // one phase bit per slot
 
@@ -662,8 +640,8 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             }
         };
         // after `consumed` tiles of the piece have been used: refill while fewer than kSteady are in flight
-        auto refill = [&](int consumed) {
-            if (issue_seq - consumed < kSteady) issue_next();
+        auto refill = [&](int used) {
+            if (issue_seq - used < kSteady) issue_next();
         };
         // ---- consumer state ---------------------------------------------------------------------
         float2 q2[PPL], acc2[PPL];
@@ -703,11 +681,14 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         // Before the first read of q / k_new / v_new and before any access to the shared scratch, a
         // launch that was allowed to overlap its predecessor in the stream waits for it, then lets the
         // next launch begin its own prologue.  Both instructions are no-ops for an ordinary launch.
+        // Only warp 0 releases the dependents, and only after publish_cursors() has consumed the ticket
+        // its thread 0 drew: when the next launch's first CTA starts, every ticket of this launch has
+        // been drawn, so the two launches never mix their tickets in the shared counter.
         auto dependency_sync = [&]() {
             if constexpr (FUSED) {
                 if (!dep_synced) {
                     asm volatile("griddepcontrol.wait;" ::: "memory");
-                    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+                    if (warp == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
                 }
             }
             dep_synced = true;
@@ -720,7 +701,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
                 if (warp != 0 || publish_checked) return;
                 publish_checked = true;
                 if (!__shfl_sync(FULL, planner_ticket == (int)gridDim.x - 1, 0)) return;
-                if (lane == 0) *p.planned_ctas = 0;  // ready for the next launch
                 __threadfence();  // every other CTA's cursor reads precede its announcement
                 for (int r = lane; r < p.rows; r += 32) {
                     const int slot = info[r].slot;
@@ -866,17 +846,8 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             __syncwarp();
         };
 
-        // ---- pieces: the static one first, then dynamic ones until none are left ----------------------
-        for (;;) {
-            if (piece < 0) {
-                if (pm.nd == 0 || gave_up) break;
-                dependency_sync();  // the hand-out counter is scratch shared with the previous launch
-                int k = 0;
-                if (lane == 0) k = atomicAdd(p.dyn_next, 1);
-                k = __shfl_sync(FULL, k, 0);
-                if (k >= pm.nd) break;
-                piece = pm.ns + k;
-            }
+        // ---- this warp's piece of the unit line -----------------------------------------------------------
+        if (piece >= 0) {
             u0 = pm.start(piece);
             n_units = (int)(pm.end(piece) - u0);
             issue_seq = 0;
@@ -902,11 +873,11 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
 
             // ---- scores: q . k for the 16 tokens of the tile -----------------------------------
             uint8_t* ktile = my_tiles + use_slot * TILE;
-            if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status)) { gave_up = true; break; }
+            if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status, p.wait_limit)) { gave_up = true; break; }
             phases ^= 1u << use_slot;
             use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
+            ++consumed;
             if (it == 0) TRACE(3);
-            if (it == n_units - 4) TRACE(6);  // four units left: the pace of the tail shows between here and the end
             if (it == n_units - 4) TRACE(6);  // four units left: the pace of the tail shows between here and the end
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) {  // the new K row replaces whatever the ring slot held
@@ -992,9 +963,10 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
 
             // ---- acc += p . v ----------------------------------------------------------------------
             uint8_t* vtile = my_tiles + use_slot * TILE;
-            if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status)) { gave_up = true; break; }
+            if (!mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, p.status, p.wait_limit)) { gave_up = true; break; }
             phases ^= 1u << use_slot;
             use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
+            ++consumed;
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) {
                     const int off = (int)((meta >> kMetaPatchOffShift) & 15);
@@ -1141,37 +1113,43 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             }
         }
 
-            if (gave_up) break;
-            piece = -1;
         }
         TRACE(4);
         publish_cursors();  // a warp without a piece gets here without having looked
-        if (!gave_up) flush_arrivals();
+        if (!gave_up) {
+            flush_arrivals();
+        } else {
+            // A wait ran out (the status word says so and the launch's results are void).  Tiles issued and not
+            // yet consumed may still be on their way into this warp's slots: see them land before the CTA exits
+            // and its shared memory is handed to another CTA.  These waits keep the full limit.
+            for (int t = consumed; t < issue_seq; ++t) {
+                mbar_wait_bounded(bar0 + 8 * use_slot, (phases >> use_slot) & 1u, nullptr);
+                phases ^= 1u << use_slot;
+                use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
+            }
+        }
     }
 
     TRACE(5);
-    // ---- the last CTA to finish re-arms the hand-out counter and the claims; a launch that uses neither
-    //      (even split, no dynamic pieces) has nothing to re-arm and its CTAs leave without the round trip ----
+    // ---- weighted split: the last CTA to finish re-arms the claims; with the even split there is nothing to
+    //      re-arm and the CTAs leave without the round trip ----
     if constexpr (FUSED) {
         if (!dep_synced) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            if (warp == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         }
     }
-    if (weighted || p.dyn_cap > 0) {
+    if (weighted) {
         __shared__ int is_last;
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();
             const int old = atomicAdd(p.done_ctas, 1);
             is_last = (old == (int)gridDim.x - 1);
-            if (is_last) {
-                *p.done_ctas = 0;
-                *p.dyn_next = 0;
-            }
+            if (is_last) *p.done_ctas = 0;
         }
         __syncthreads();
-        if (is_last && weighted)
+        if (is_last)
             for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
     }
 }

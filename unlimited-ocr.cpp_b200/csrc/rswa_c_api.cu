@@ -99,11 +99,10 @@ struct uocr_b200_workspace {
     float* part_acc = nullptr;
     float* part_ml = nullptr;
     int* counters = nullptr;   // [pieces_max] arrival counters, zero between launches
-    int* done_ctas = nullptr;  // CTAs that have finished, zero between launches
-    int* dyn_next = nullptr;   // next dynamic piece to hand out, zero between launches
-    int* planned_ctas = nullptr;  // fused step: CTAs that have planned from the old cursors, zero between launches
-    int dyn_cap = 0;           // dynamic pieces the scratch is sized for (0: static split only)
+    int* done_ctas = nullptr;  // weighted split: CTAs that have finished, zero between launches
+    int* planned_ctas = nullptr;  // fused step: ticket counter of CTAs that have planned; wraps to zero by itself
     int pieces_max = 0;
+    uint32_t wait_limit = kWaitLimit;  // polls a tile wait may take (uocr_b200_workspace_set_wait_limit)
     PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
     int tiles_cap = 0;
     // SM-weighted split (uocr_b200_workspace_calibrate): cumulative shares, SM id -> share, and two
@@ -151,8 +150,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_status = 0;
     const size_t o_rs = up(256);
     const size_t o_info = o_rs + up(sizeof(int) * (size_t)(max_rows + 1));
-    ws->dyn_cap = kDynShare > 0 ? ws->total_warps_max * kDynPerWarp : 0;
-    ws->pieces_max = ws->total_warps_max + ws->dyn_cap;
+    ws->pieces_max = ws->total_warps_max;
     const size_t o_acc = o_info + up(sizeof(RowInfo) * (size_t)max_rows);
     const size_t o_ml = o_acc + up(sizeof(float) * 2 * (size_t)ws->pieces_max * kMaxHeadDim);
     const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->pieces_max);
@@ -178,8 +176,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->part_ml = reinterpret_cast<float*>(ws->base + o_ml);
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
     ws->done_ctas = ws->counters + ws->pieces_max;
-    ws->dyn_next = ws->done_ctas + 1;
-    ws->planned_ctas = ws->done_ctas + 2;
+    ws->planned_ctas = ws->done_ctas + 1;
     ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
     ws->claim = reinterpret_cast<int*>(ws->base + o_split);
     *out = ws;
@@ -273,13 +270,11 @@ int uocr_b200_workspace_calibrate(uocr_b200_workspace* ws, int enabled, uocr_b20
     std::vector<double> sorted_rate(rate);
     std::sort(sorted_rate.begin(), sorted_rate.end());
     const double mean = sorted_rate[sorted_rate.size() / 2];
-    if (enabled != 3)
-        for (double& r : rate) r = mean * std::sqrt(r / mean);
+    for (double& r : rate) r = mean * std::sqrt(r / mean);
     std::vector<int> frac(kMaxCtas + 1, 0);
     double total = 0, run = 0;
     for (double& r : rate) {  // keep every share within [0.5, 2] of the mean: pieces must not become empty
-        r = std::min(std::max(r, 0.5 * mean), 2.0 * mean);  // (enabled == 3, diagnostic: proportional shares)
-        if (enabled == 2) r = mean;  // diagnostic: even shares through the SM-mapped, claimed path
+        r = std::min(std::max(r, 0.5 * mean), 2.0 * mean);
         total += r;
     }
     for (int c = 0; c < ctas; ++c) {
@@ -295,6 +290,48 @@ int uocr_b200_workspace_calibrate(uocr_b200_workspace* ws, int enabled, uocr_b20
     return UOCR_B200_OK;
 }
 
+int uocr_b200_workspace_stream_read_gbs(uocr_b200_workspace* ws, uocr_b200_stream_t stream, double* gbs) {
+    if (!ws || !gbs) return fail(UOCR_B200_ERR_INVALID, "workspace_stream_read_gbs: null argument");
+    const DeviceInfo* di = nullptr;
+    if (int rc = device_info(&di)) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // one CTA per SM, each walking its own 8 MB (the whole buffer, 1.2 GB, is far larger than L2) twice
+    constexpr int kTilesPerCta = 2048, kPasses = 2, kRuns = 5, warps = 16;
+    const int ctas = di->sms;
+    const size_t bytes = (size_t)ctas * kTilesPerCta * kCalTile;
+    uint8_t* buf = nullptr;
+    unsigned long long* d_out = nullptr;
+    CHECK_CUDA(cudaMalloc(&buf, bytes), "streaming buffer");
+    cudaError_t e = cudaMalloc(&d_out, sizeof(unsigned long long) * 2 * ctas);
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    if (e == cudaSuccess) e = cudaEventCreate(&ev[0]);
+    if (e == cudaSuccess) e = cudaEventCreate(&ev[1]);
+    const int smem = ((warps * kCalRing * 8 + 127) & ~127) + warps * kCalRing * kCalTile;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rswa_calibrate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaMemsetAsync(buf, 0, bytes, st);
+    std::vector<float> ms;
+    for (int r = 0; r < kRuns + 1 && e == cudaSuccess; ++r) {
+        CalibrateParams cp{buf, kTilesPerCta, kPasses, d_out, ws->status};
+        e = cudaEventRecord(ev[0], st);
+        rswa_calibrate_kernel<<<ctas, warps * 32, smem, st>>>(cp);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaEventRecord(ev[1], st);
+        if (e == cudaSuccess) e = cudaEventSynchronize(ev[1]);
+        float t = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, ev[0], ev[1]);
+        if (r > 0) ms.push_back(t);  // the first run is the warm-up
+    }
+    cudaFree(buf);
+    if (d_out) cudaFree(d_out);
+    if (ev[0]) cudaEventDestroy(ev[0]);
+    if (ev[1]) cudaEventDestroy(ev[1]);
+    if (e != cudaSuccess) return cuda_fail(e, "streaming-rate run");
+    std::sort(ms.begin(), ms.end());
+    *gbs = (double)bytes * kPasses / (ms[ms.size() / 2] * 1e-3) / 1e9;
+    return UOCR_B200_OK;
+}
+
 int uocr_b200_workspace_split_shares(const uocr_b200_workspace* ws, int* out_frac, int n) {
     if (!ws || !out_frac || n <= 0) return fail(UOCR_B200_ERR_INVALID, "workspace_split_shares: bad arguments");
     if (ws->calibrated_ctas == 0) return 0;
@@ -307,6 +344,12 @@ int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int dtype) {
     if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_set_out_dtype: null workspace");
     if (dtype != UOCR_B200_F32 && dtype != UOCR_B200_BF16) return fail(UOCR_B200_ERR_UNSUPPORTED, "workspace_set_out_dtype: fp32 or bf16");
     ws->out_bf16 = dtype == UOCR_B200_BF16;
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_workspace_set_wait_limit(uocr_b200_workspace* ws, unsigned polls) {
+    if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_set_wait_limit: null workspace");
+    ws->wait_limit = polls > kWaitLimit ? kWaitLimit : polls;
     return UOCR_B200_OK;
 }
 
@@ -373,15 +416,9 @@ struct AttnCall {
     float rope_theta = 0.f;
 };
 
-// Share the last CTA of an overlapped launch gives up, in sixteenths (UOCR_LATE_CTA overrides; measurement aid).
-int late_cta_sixteenths() {
-    static const int v = [] {
-        const char* e = std::getenv("UOCR_LATE_CTA");
-        const int x = e ? std::atoi(e) : 3;
-        return x < 0 ? 0 : (x > 12 ? 12 : x);
-    }();
-    return v;
-}
+// Share the last CTA of an overlapped launch gives up, in sixteenths: it starts 8-12 us after the others
+// (of a launch of ~50 us), and 3/16 measured best among 0..6.
+constexpr int kLateCtaSixteenths = 3;
 
 constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
 
@@ -395,24 +432,9 @@ int launch_partial(const AttnParams& ap, const DeviceInfo& di, int* warps_used, 
                        kMaxWarpsPerCta * kPendMax * (int)sizeof(int);
     int warps = budget / per_warp;
     if (warps > kMaxWarpsPerCta) warps = kMaxWarpsPerCta;
-#ifdef UOCR_WARPS_CAP  // measurement aid: fewer warps per CTA than the workspace is sized for
-    if (warps > UOCR_WARPS_CAP) warps = UOCR_WARPS_CAP;
-#endif
     if (warps < 1) return fail(UOCR_B200_ERR_UNSUPPORTED, "tile does not fit in shared memory");
-    // Two half-size CTAs per SM when the tiles allow it: with the overlapped launch of the fused step a
-    // CTA of the next launch can then move in as soon as half an SM has drained.
-    int ctas = 1;
-#ifdef UOCR_TWO_CTAS_PER_SM  // measured: no gain over one CTA per SM on cfg2 / cfg4
-    if (warps >= 16) {
-        const int half_budget = budget / 2 - 1024 - plan_bytes / 2;
-        const int w2 = half_budget / per_warp;
-        if (w2 >= 8) {
-            warps = 8;
-            ctas = 2;
-        }
-    }
-#endif
-    *warps_used = warps * ctas;
+    constexpr int ctas = 1;  // one persistent CTA per SM
+    *warps_used = warps;
     if (dry) return UOCR_B200_OK;
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     const int smem = bar_bytes + warps * per_warp + warps * kPendMax * (int)sizeof(int) + plan_bytes;
@@ -524,7 +546,8 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.d_ring_pos = c.d_ring_rw;
     ap.done_ctas = ws->done_ctas;
     ap.planned_ctas = ws->planned_ctas;
-    ap.late_cta = (c.fused && ws->overlap) ? late_cta_sixteenths() : 0;
+    ap.late_cta = (c.fused && ws->overlap) ? kLateCtaSixteenths : 0;
+    ap.wait_limit = ws->wait_limit;
 #ifdef UOCR_TRACE
     static int launch_seq = 0;  // instrumented builds: consecutive (overlapping) launches alternate timeline halves
     ap.trace_half = launch_seq++ & 1;
@@ -536,8 +559,6 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
         // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
         for (int i = 0; i < c.head_dim / 2; ++i) ap.rope_freq[i] = std::pow(c.rope_theta, -2.0f * i / static_cast<float>(c.head_dim));
     }
-    ap.dyn_next = ws->dyn_next;
-    ap.dyn_cap = ws->dyn_cap;
     if (ws->calibrated_ctas == di->sms) {
         ap.split_ctas = ws->calibrated_ctas;
         std::memcpy(ap.cta_frac, ws->cta_frac, sizeof(ap.cta_frac));
@@ -1120,31 +1141,48 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 unsigned char* g_noalloc_ptr[64] = {nullptr};  // device address of the array, per device ordinal
 
+// Device address of the built-in scratch on the current device (looked up once per device).
+int noalloc_base(unsigned char** base, int* dev_out) {
+    int dev = 0;
+    CHECK_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(UOCR_B200_ERR_NO_DEVICE, "device ordinal out of range");
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        CHECK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
+        g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    *base = g_noalloc_ptr[dev];
+    if (dev_out) *dev_out = dev;
+    return UOCR_B200_OK;
+}
+
 }  // namespace
 
 extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     const uocr_b200_paged_kv* kv, const float* q, const int* d_len, const int* d_prefill_len,
     const int* d_slots, int batch, int heads, float* out, uocr_b200_stream_t stream) {
     if (batch <= 0) return UOCR_B200_OK;
+    // every argument is checked before the shared array is touched
     if (!d_len || !d_slots || !d_prefill_len) return fail(UOCR_B200_ERR_INVALID, "attention_batch_paged_noalloc: null index array");
     if (batch > kNoAllocMaxRows)
         return fail(UOCR_B200_ERR_WORKSPACE, "attention_batch_paged_noalloc: batch exceeds the built-in scratch (max 1024 rows)");
-    if (kv && kv->head_dim > kNoAllocMaxHeadDim)
+    AttnCall c;
+    if (int rc = fill_paged(c, kv)) return rc;
+    if (!kv->k_pool || !kv->v_pool || !q || !out) return fail(UOCR_B200_ERR_INVALID, "attention_batch_paged_noalloc: null pointer");
+    if (kv->head_dim > kNoAllocMaxHeadDim)
         return fail(UOCR_B200_ERR_WORKSPACE, "attention_batch_paged_noalloc: head_dim exceeds the built-in scratch (max 128)");
+    if (!head_dim_ok(kv->head_dim, kv->dtype)) return fail(UOCR_B200_ERR_UNSUPPORTED, "attention_batch_paged_noalloc: unsupported head_dim");
+    if (heads <= 0 || kv->kv_heads <= 0 || heads % kv->kv_heads != 0)
+        return fail(UOCR_B200_ERR_INVALID, "attention_batch_paged_noalloc: heads must be a positive multiple of kv_heads");
     const DeviceInfo* di = nullptr;
     if (int rc = device_info(&di)) return rc;
     if (di->sms > kNoAllocMaxSms)
         return fail(UOCR_B200_ERR_WORKSPACE, "attention_batch_paged_noalloc: device has more SMs than the built-in scratch covers (max 160)");
 
     // one-time set-up per device: resolve the device address of the static array
+    unsigned char* base = nullptr;
     int dev = 0;
-    CHECK_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
-    if (!g_noalloc_ptr[dev]) {
-        void* p = nullptr;
-        CHECK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
-        g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
-    }
-    unsigned char* base = g_noalloc_ptr[dev];
+    if (int rc = noalloc_base(&base, &dev)) return rc;
 
     uocr_b200_workspace view;  // a view over the static array; owns nothing
     view.device = dev;
@@ -1157,63 +1195,30 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     view.part_ml = reinterpret_cast<float*>(base + kNaMl);
     view.counters = reinterpret_cast<int*>(base + kNaCnt);
     view.done_ctas = view.counters + kNoAllocMaxWarps;
-    view.dyn_next = view.done_ctas + 1;
-    view.planned_ctas = view.done_ctas + 2;
-    view.dyn_cap = 0;  // the built-in scratch holds one piece per warp: static split only
+    view.planned_ctas = view.done_ctas + 1;
     view.pieces_max = kNoAllocMaxWarps;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    // two parts of the scratch must start at zero: the status word and the arrival counters of the
-    // split items (the kernel returns them to zero itself, but an earlier call that was cut short
-    // could have left some behind); everything else is rewritten before it is read
-    CHECK_CUDA(cudaMemsetAsync(view.status, 0, sizeof(int), st), "scratch status clear");
+    // One part of the scratch must start at zero: the arrival counters of the split items (the kernel
+    // returns them to zero itself, but an earlier call that was cut short could have left some behind).
+    // Everything else is rewritten before it is read.  The status word is NOT cleared here: faults
+    // accumulate until uocr_b200_noalloc_status reads them.
     CHECK_CUDA(cudaMemsetAsync(view.counters, 0, kNaCntBytes, st), "scratch counter clear");
 
-    AttnCall c;
-    if (int rc = fill_paged(c, kv)) return rc;
     c.rows = batch; c.heads = heads; c.q = q; c.out = out;
     c.plan.mode = kPlanBatch; c.plan.d_slots = d_slots; c.plan.d_len = d_len; c.plan.d_prefill_len = d_prefill_len;
     return run_attention(c, &view, st);
 }
 
-#ifdef UOCR_TC_TRACE
-extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_tc_trace(unsigned long long* out, int n) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_tc_trace, sizeof(unsigned long long) * n);
+extern "C" int uocr_b200_noalloc_status(uocr_b200_stream_t stream, int* device_status) {
+    if (!device_status) return fail(UOCR_B200_ERR_INVALID, "noalloc_status: null argument");
+    unsigned char* base = nullptr;
+    if (int rc = noalloc_base(&base, nullptr)) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int v = 0;
+    CHECK_CUDA(cudaMemcpyAsync(&v, base + kNaStatus, sizeof(int), cudaMemcpyDeviceToHost, st), "noalloc status D2H");
+    CHECK_CUDA(cudaMemsetAsync(base + kNaStatus, 0, sizeof(int), st), "noalloc status clear");
+    CHECK_CUDA(cudaStreamSynchronize(st), "noalloc status sync");
+    *device_status = v;
+    return UOCR_B200_OK;
 }
-#endif
-
-#ifdef UOCR_TC_TRACE
-extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_tc_cta_trace(unsigned long long* out, int n) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_tc_cta, sizeof(unsigned long long) * n);
-}
-#endif
-
-#ifdef UOCR_TRACE
-// instrumented builds: shares of the weighted split straight from per-SM rates (0 = SM not present)
-extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_set_split(uocr_b200_workspace* ws, const double* rate_by_smid) {
-    const DeviceInfo* di = nullptr;
-    if (int rc = device_info(&di)) return rc;
-    int c = 0;
-    double total = 0, run = 0;
-    for (int sm = 0; sm < uocr_b200::kMaxSmid; ++sm) total += rate_by_smid[sm];
-    for (int sm = 0; sm < uocr_b200::kMaxSmid; ++sm) {
-        ws->slot_of_smid[sm] = 255;
-        if (rate_by_smid[sm] <= 0 || c >= di->sms) continue;
-        ws->slot_of_smid[sm] = (uint8_t)c;
-        run += rate_by_smid[sm];
-        ws->cta_frac[++c] = (int)std::llround(run / total * (double)(1 << 20));
-    }
-    if (c != di->sms) return -1;
-    ws->cta_frac[0] = 0;
-    ws->cta_frac[c] = 1 << 20;
-    cudaMemset(ws->claim, 0, sizeof(int) * 2 * uocr_b200::kMaxCtas);
-    ws->calibrated_ctas = c;
-    return 0;
-}
-extern "C" __attribute__((visibility("default"))) int uocr_b200_debug_trace(unsigned long long* out, int n) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, uocr_b200::g_trace, sizeof(unsigned long long) * n);  // n <= 2 * 8 * 4096
-}
-#endif

@@ -51,12 +51,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Bounded wait: gives up after kWaitLimit polls (each poll already blocks for a hardware-defined
-// slice), records the fact and lets the caller leave the loop instead of spinning forever.
+// Bounded wait: gives up after `limit` polls (each poll already blocks for a hardware-defined slice),
+// records the fact and lets the caller leave its loop instead of spinning forever.  kWaitLimit is the
+// limit every kernel uses unless the workspace was told otherwise (a limit of 0 makes every wait give
+// up at once, which is how the give-up paths are exercised without hanging anything).
 constexpr uint32_t kWaitLimit = 1u << 22;
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
-    for (uint32_t it = 0; it < kWaitLimit; ++it)
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status,
+                                                  uint32_t limit = kWaitLimit) {
+    for (uint32_t it = 0; it < limit; ++it)
         if (mbar_try_wait(bar, parity)) return true;
     if (status) atomicOr(status, kStatusWaitTimeout);
     return false;
@@ -87,34 +90,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
 }
 
-// Widening a bf16 pair held in one 32-bit word.
-#ifndef UOCR_UNPACK_MODE
-#define UOCR_UNPACK_MODE 1
-#endif
+// Widening a bf16 pair held in one 32-bit word: one byte permute per element (the low half needs its
+// two bytes moved up, the high half its low bytes cleared; both are a single PRMT).
 __device__ __forceinline__ float bf16_lo(uint32_t w) {
     uint32_t r;
-#if UOCR_UNPACK_MODE == 0
-    r = w << 16;
-#elif UOCR_UNPACK_MODE == 1
     asm("prmt.b32 %0, %1, 0, 0x1044;" : "=r"(r) : "r"(w));
-#elif UOCR_UNPACK_MODE == 2
-    asm("shl.b32 %0, %1, 16;" : "=r"(r) : "r"(w));
-#elif UOCR_UNPACK_MODE == 3
-    asm("mul.lo.u32 %0, %1, 65536;" : "=r"(r) : "r"(w));
-#elif UOCR_UNPACK_MODE == 4
-    asm("mad.lo.u32 %0, %1, 65536, 0;" : "=r"(r) : "r"(w));
-#endif
     return __uint_as_float(r);
 }
 __device__ __forceinline__ float bf16_hi(uint32_t w) {
     uint32_t r;
-#if UOCR_UNPACK_MODE == 0
-    r = w & 0xffff0000u;
-#elif UOCR_UNPACK_MODE == 1
     asm("prmt.b32 %0, %1, 0, 0x3244;" : "=r"(r) : "r"(w));
-#else
-    asm("and.b32 %0, %1, 0xffff0000;" : "=r"(r) : "r"(w));
-#endif
     return __uint_as_float(r);
 }
 
