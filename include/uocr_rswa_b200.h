@@ -195,6 +195,20 @@ UOCR_B200_API int uocr_b200_rswa_write_prefill_ragged_paged(
     const uocr_b200_paged_kv* kv, const float* k, const float* v, const int* d_slots,
     const int* d_pos, int total, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* Publishes the state of `n` slots in one launch.  Replaces the per-request publication after a ragged
+ * prefill (src/engine/gpu_decoder.cu:1131-1150: len and ring_pos of every layer and prefill_len, one
+ * blocking single-int cudaMemcpy each, 2 * layers + 1 copies per request).  d_packed holds n records of
+ * 3 + table_stride int32: [slot, length, write_row, row[table_stride]]; for each record the kernel sets
+ * d_len[l][slot] = length and d_ring_pos[l][slot] = 0 for every layer l (arrays laid out
+ * [layers][slots]), d_prefill_len[slot] = length, and, when write_row != 0, the slot's block-table row.
+ * A caller stages the records of a whole admission wave in pinned memory and brings them over with one
+ * copy.  A record with length 0 and a row of -1 retires a slot: later use of it is then reported as a
+ * bad block instead of touching blocks that belong to someone else.  `ws` (may be null) receives the
+ * status bit for a record whose slot is out of range. */
+UOCR_B200_API int uocr_b200_rswa_publish_slots(
+    const int32_t* d_packed, int n, int32_t* block_table, int table_stride, int* d_len, int* d_ring_pos,
+    int* d_prefill_len, int slots, int layers, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
 /* ================================================================================================
  * Attention.  q / out are fp32 [rows][heads*head_dim]; scale = 1/sqrt(head_dim); out = 0 for a row
  * that attends nothing.  All forms run the same split-KV kernels: a plan kernel (folded into the

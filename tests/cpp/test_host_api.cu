@@ -448,6 +448,228 @@ static void test_windowed_prefill(bool tensor_cores) {
     cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dout); cudaFree(gk); cudaFree(gv); cudaFree(d_ident);
 }
 
+// ---- GpuRSWACache inside a captured graph: device cursors, device-length attention ----------------------------
+static void test_gpu_cache_graph_replay() {
+    std::printf("cuda::GpuRSWACache: captured append_decode_device + attention_devlen, replayed across the ring boundary\n");
+    const int kvh = 2, hd = 64, W = 8, P = 5, heads = 4, row = kvh * hd;
+    cuda::GpuRSWACache g(1, kvh, hd, W);
+    orc_cache* o = orc_cache_create(1, kvh, hd, W);
+    g.reset(P);
+    orc_cache_reset(o, P);
+    auto pk = rvec(P * row), pv = rvec(P * row);
+    float *dpk = dev(pk), *dpv = dev(pv);
+    g.write_prefill(0, dpk, dpv, P);
+    orc_cache_write_prefill(o, 0, pk.data(), pv.data(), P);
+    g.reset_device_state(P);
+    float *dk, *dv, *dq, *dout;
+    cudaMalloc(&dk, row * 4); cudaMalloc(&dv, row * 4); cudaMalloc(&dq, heads * hd * 4); cudaMalloc(&dout, heads * hd * 4);
+    cudaStream_t st;
+    cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    // one plain step first (kernel attributes, and the same call sequence the graph will hold)
+    auto step_inputs = [&](std::vector<float>& k, std::vector<float>& v, std::vector<float>& q) {
+        k = rvec(row); v = rvec(row); q = rvec(heads * hd);
+        cudaMemcpyAsync(dk, k.data(), row * 4, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(dv, v.data(), row * 4, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(dq, q.data(), heads * hd * 4, cudaMemcpyHostToDevice, st);
+        cudaStreamSynchronize(st);
+    };
+    std::vector<float> k, v, q;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    bool threw = false;
+    try { g.keys(0, st); } catch (const Error&) { threw = true; }  // a snapshot inside capture is refused
+    EXPECT(threw);
+    g.append_decode_device(0, dk, dv, st);
+    g.attention_devlen(0, dq, 1, 0, dout, heads, false, st);
+    EXPECT(cudaStreamEndCapture(st, &graph) == cudaSuccess);
+    EXPECT(cudaGraphInstantiate(&exec, graph, nullptr, nullptr, 0) == cudaSuccess);
+    float worst = 0.f;
+    for (int t = 0; t < 3 * W + 2; ++t) {
+        step_inputs(k, v, q);
+        EXPECT(cudaGraphLaunch(exec, st) == cudaSuccess);
+        cudaStreamSynchronize(st);
+        orc_cache_append_decode(o, 0, k.data(), v.data());
+        std::vector<float> want(heads * hd);
+        orc_cache_attention(o, 0, q.data(), 1, orc_cache_len(o, 0) - 1, want.data(), heads, 0);
+        worst = std::max(worst, max_abs_diff(host(dout, heads * hd), want.data()));
+        EXPECT(host(g.len_dev(0), 1)[0] == orc_cache_len(o, 0));
+    }
+    EXPECT(worst < 2e-5f);
+    const size_t n = static_cast<size_t>(orc_cache_len(o, 0)) * row;
+    EXPECT(std::memcmp(host(g.keys(0, st), n).data(), orc_cache_keys(o, 0), n * 4) == 0);  // outside capture: allowed
+    EXPECT(std::memcmp(host(g.values(0, st), n).data(), orc_cache_values(o, 0), n * 4) == 0);
+    cudaGraphExecDestroy(exec); cudaGraphDestroy(graph); cudaStreamDestroy(st);
+    cudaFree(dpk); cudaFree(dpv); cudaFree(dk); cudaFree(dv); cudaFree(dq); cudaFree(dout);
+    orc_cache_destroy(o);
+}
+
+// ---- the reference-signature wrappers under capture: prepared scratch, never reallocated -----------------------
+static void test_free_functions_capture_and_scratch_rules() {
+    std::printf("uocr::cuda::rswa_* inside stream capture (prepared per-stream scratch)\n");
+    const int kvh = 2, heads = 2, hd = 32, W = 8, batch = 2, cap = 4 + W, row = kvh * hd;
+    std::vector<float> kb = rvec(static_cast<size_t>(batch) * cap * row), vb = rvec(kb.size());
+    float *dkb = dev(kb), *dvb = dev(vb);
+    std::vector<int> len = {7, 12}, sl = {1, 0};
+    int *d_len = dev(len), *d_slots = dev(sl);
+    auto q = rvec(batch * heads * hd);
+    float* dq = dev(q);
+    float *dout, *dref;
+    cudaMalloc(&dout, q.size() * 4); cudaMalloc(&dref, q.size() * 4);
+    cudaStream_t st;
+    cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    EXPECT(cuda::rswa_prepare(st, 64));
+    cuda::rswa_attention_batch(dq, dkb, dvb, d_len, d_slots, batch, cap, heads, kvh, hd, dref, st);  // plain call
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    cuda::rswa_attention_batch(dq, dkb, dvb, d_len, d_slots, batch, cap, heads, kvh, hd, dout, st);
+    EXPECT(cudaStreamEndCapture(st, &graph) == cudaSuccess);
+    EXPECT(cudaGraphInstantiate(&exec, graph, nullptr, nullptr, 0) == cudaSuccess);
+    // a call with more rows than were prepared launches nothing (and frees nothing): the graph stays valid
+    cudaMemset(dout, 0xff, q.size() * 4);
+    std::vector<int> many_slots(100, 0);
+    int* d_many = dev(many_slots);
+    cuda::rswa_attention_batch(dq, dkb, dvb, d_len, d_many, 100, cap, heads, kvh, hd, dout, st);  // prints the refusal
+    cudaStreamSynchronize(st);
+    auto untouched = host(dout, q.size());
+    bool all_nan = true;
+    for (float x : untouched) all_nan = all_nan && std::isnan(x);
+    EXPECT(all_nan);
+    EXPECT(cuda::rswa_prepare(st, 256));  // larger scratch for later calls; the old one stays alive for the graph
+    EXPECT(cudaGraphLaunch(exec, st) == cudaSuccess);
+    cudaStreamSynchronize(st);
+    auto a = host(dout, q.size()), b = host(dref, q.size());
+    EXPECT(std::memcmp(a.data(), b.data(), a.size() * 4) == 0);
+    // another stream gets scratch of its own
+    cudaStream_t st2;
+    cudaStreamCreateWithFlags(&st2, cudaStreamNonBlocking);
+    cudaMemsetAsync(dout, 0, q.size() * 4, st2);
+    cuda::rswa_attention_batch(dq, dkb, dvb, d_len, d_slots, batch, cap, heads, kvh, hd, dout, st2);
+    cudaStreamSynchronize(st2);
+    a = host(dout, q.size());
+    EXPECT(std::memcmp(a.data(), b.data(), a.size() * 4) == 0);
+    cudaGraphExecDestroy(exec); cudaGraphDestroy(graph); cudaStreamDestroy(st); cudaStreamDestroy(st2);
+    cudaFree(dkb); cudaFree(dvb); cudaFree(d_len); cudaFree(d_slots); cudaFree(dq); cudaFree(dout); cudaFree(dref); cudaFree(d_many);
+}
+
+// ---- admission waves, captured decode steps and the GpuDecoder-named adapter -----------------------------------
+static void test_decoder_kv_adapter_waves_and_step_graphs() {
+    std::printf("cuda::GpuDecoderKV: batch_prefill (one state upload per wave), batch_decode graphs, release\n");
+    const int L = 3, kvh = 2, hd = 32, W = 16, heads = 4, row = kvh * hd, qrow = heads * hd, slots = 4;
+    const int capacity = 40 + W;
+    cuda::GpuDecoderKV dec(L, kvh, hd, W, DType::BF16);
+    EXPECT(dec.batch_configure(slots, capacity) == true);
+    EXPECT(dec.batch_configure(slots, capacity) == false);
+    EXPECT(dec.batch_slots() == slots && dec.batch_graph_count() == 0);
+    cudaStream_t st;
+    cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    auto round = [](std::vector<float> v) { for (auto& x : v) x = bf16_to_f32(f32_to_bf16(x)); return v; };
+    // wave of three requests: prompts of 21, 7 and 33 tokens into slots 3, 0, 2 (the whole prompt is the fixed region)
+    const std::vector<int> lengths = {21, 7, 33}, pslots = {3, 0, 2};
+    std::vector<int> starts = {0, 21, 28};
+    const int total = dec.batch_prefill_begin(starts, lengths, pslots, {}, st);
+    EXPECT(total == 61);
+    orc_cache* o[slots] = {nullptr, nullptr, nullptr, nullptr};
+    for (size_t r = 0; r < lengths.size(); ++r) {
+        o[pslots[r]] = orc_cache_create(L, kvh, hd, W);
+        orc_cache_reset(o[pslots[r]], lengths[r]);
+    }
+    float *dq, *dk, *dv, *dctx;
+    cudaMalloc(&dq, (size_t)L * total * qrow * 4); cudaMalloc(&dctx, (size_t)L * total * qrow * 4);
+    cudaMalloc(&dk, (size_t)L * total * row * 4); cudaMalloc(&dv, (size_t)L * total * row * 4);
+    float worst = 0.f;
+    for (int l = 0; l < L; ++l) {
+        auto q = rvec((size_t)total * qrow), k = round(rvec((size_t)total * row)), v = round(rvec((size_t)total * row));
+        cudaMemcpyAsync(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice, st);
+        dec.attention_block_ragged(l, dq, dk, dv, dctx, total, heads, st);
+        cudaStreamSynchronize(st);
+        auto got = host(dctx, (size_t)total * qrow);
+        for (size_t r = 0; r < lengths.size(); ++r) {
+            orc_cache* c = o[pslots[r]];
+            orc_cache_write_prefill(c, l, k.data() + (size_t)starts[r] * row, v.data() + (size_t)starts[r] * row, lengths[r]);
+            std::vector<float> want((size_t)lengths[r] * qrow);
+            orc_cache_attention(c, l, q.data() + (size_t)starts[r] * qrow, lengths[r], 0, want.data(), heads, 1);
+            worst = std::max(worst, max_abs_diff(want, got.data() + (size_t)starts[r] * qrow));
+        }
+    }
+    EXPECT(worst < 2e-5f);
+    // decode: batch of 3, fixed activation buffers [L][batch][row], one graph per batch size
+    const int batch = 3;
+    const std::vector<int> order = {2, 3, 0};
+    cuda::PagedBatchKV::StepIO io;
+    io.q = dq; io.k = dk; io.v = dv; io.out = dctx; io.heads = heads;
+    io.q_layer_stride = (long long)batch * qrow; io.kv_layer_stride = (long long)batch * row; io.out_layer_stride = (long long)batch * qrow;
+    worst = 0.f;
+    for (int t = 0; t < 2 * W + 3; ++t) {
+        auto q = rvec((size_t)L * batch * qrow), k = round(rvec((size_t)L * batch * row)), v = round(rvec((size_t)L * batch * row));
+        cudaMemcpyAsync(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice, st);
+        dec.batch_decode({}, order, io, false, st);
+        cudaStreamSynchronize(st);
+        auto got = host(dctx, (size_t)L * batch * qrow);
+        for (int l = 0; l < L; ++l)
+            for (int r = 0; r < batch; ++r) {
+                orc_cache* c = o[order[r]];
+                orc_cache_append_decode(c, l, k.data() + ((size_t)l * batch + r) * row, v.data() + ((size_t)l * batch + r) * row);
+                std::vector<float> want(qrow);
+                orc_cache_attention(c, l, q.data() + ((size_t)l * batch + r) * qrow, 1, orc_cache_len(c, l) - 1, want.data(), heads, 0);
+                worst = std::max(worst, max_abs_diff(want, got.data() + ((size_t)l * batch + r) * qrow));
+            }
+    }
+    EXPECT(worst < 2e-5f);
+    EXPECT(dec.batch_graph_count() == 1);  // captured once, replayed across the warm-up -> ring boundary
+    // cursors and contents after the replays, bit for bit
+    const int cap = capacity;
+    std::vector<int> ident = {0, 1, 2, 3};
+    int* d_ident = dev(ident);
+    float *gk, *gv;
+    cudaMalloc(&gk, (size_t)slots * cap * row * 4); cudaMalloc(&gv, (size_t)slots * cap * row * 4);
+    for (int l = 0; l < L; ++l) {
+        dec.kv().gather(l, d_ident, slots, gk, gv, st);
+        cudaStreamSynchronize(st);
+        auto hk = host(gk, (size_t)slots * cap * row), hv = host(gv, (size_t)slots * cap * row);
+        auto dl = host(dec.kv().d_len(l), slots), dr = host(dec.kv().d_ring_pos(l), slots);
+        for (int sl : {0, 2, 3}) {
+            const size_t n = (size_t)orc_cache_len(o[sl], l) * row;
+            EXPECT(dl[sl] == orc_cache_len(o[sl], l) && dr[sl] == orc_cache_ring_pos(o[sl], l));
+            EXPECT(std::memcmp(hk.data() + (size_t)sl * cap * row, orc_cache_keys(o[sl], l), n * 4) == 0);
+            EXPECT(std::memcmp(hv.data() + (size_t)sl * cap * row, orc_cache_values(o[sl], l), n * 4) == 0);
+        }
+    }
+    // a second batch size gets its own graph; release poisons the slot's device row
+    dec.batch_decode({}, {3, 0}, io, false, st);
+    EXPECT(dec.batch_graph_count() == 2);
+    dec.batch_release(2, st);
+    cudaStreamSynchronize(st);
+    auto row2 = host(dec.kv().layer_view(0).block_table + 2 * dec.kv().layer_view(0).table_stride, dec.kv().layer_view(0).table_stride);
+    bool all_minus_one = true;
+    for (int x : row2) all_minus_one = all_minus_one && x == -1;
+    EXPECT(all_minus_one);
+    EXPECT(host(dec.kv().d_len(1), slots)[2] == 0 && host(dec.kv().d_prefill_len(), slots)[2] == 0);
+    EXPECT(dec.kv().device_status(st) == 0);
+    dec.batch_decode({}, order, io, false, st);  // slot 2 is stale now: flagged, not obeyed
+    EXPECT((dec.kv().device_status(st) & 1) != 0);
+    // an all-or-nothing wave: the second request cannot be placed, the first is rolled back
+    const auto before = dec.kv().blocks().stats();
+    bool threw = false;
+    try {
+        dec.kv().admit_wave({{2, "docX", 8}, {1, "docY", capacity}}, st);  // prefix longer than configured
+    } catch (const Error&) { threw = true; }
+    EXPECT(threw);
+    const auto after = dec.kv().blocks().stats();
+    EXPECT(before.live_prefixes == after.live_prefixes && before.ring_live_bytes == after.ring_live_bytes);
+    // a new shape reallocates and drops the captured graphs (src/engine/gpu_decoder.cu:929-931)
+    EXPECT(dec.batch_configure(slots + 1, capacity) == true);
+    EXPECT(dec.batch_graph_count() == 0);
+    for (int sl : {0, 2, 3}) orc_cache_destroy(o[sl]);
+    cudaStreamDestroy(st);
+    cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dctx); cudaFree(gk); cudaFree(gv); cudaFree(d_ident);
+}
+
 int main() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -461,6 +683,9 @@ int main() {
         test_paged_batch_kv();
         test_windowed_prefill(false);
         test_windowed_prefill(true);
+        test_gpu_cache_graph_replay();
+        test_free_functions_capture_and_scratch_rules();
+        test_decoder_kv_adapter_waves_and_step_graphs();
     } catch (const std::exception& e) {
         std::printf("  EXCEPTION: %s\n", e.what());
         ++g_fail;

@@ -81,6 +81,7 @@ _SIGS = {
     "uocr_b200_rswa_append_decode_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 6 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_write_prefill_ragged_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "uocr_b200_rswa_write_prefill_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _vp, _vp]),
+    "uocr_b200_rswa_publish_slots": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_f32": (_i, [_vp] * 5 + [_i] * 5 + [_vp, _vp, _vp]),
     "uocr_b200_rswa_attention_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_prefill_text_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),

@@ -706,6 +706,18 @@ int uocr_b200_rswa_write_prefill_ragged_paged(const uocr_b200_paged_kv* kv, cons
     return after_launch("prefill scatter (paged)");
 }
 
+// ---- slot state publication ---------------------------------------------------------------------------
+int uocr_b200_rswa_publish_slots(const int32_t* d_packed, int n, int32_t* block_table, int table_stride, int* d_len,
+                                 int* d_ring_pos, int* d_prefill_len, int slots, int layers, uocr_b200_workspace* ws,
+                                 uocr_b200_stream_t stream) {
+    if (n <= 0) return UOCR_B200_OK;
+    if (!d_packed || !block_table || !d_len || !d_ring_pos || !d_prefill_len) return fail(UOCR_B200_ERR_INVALID, "publish_slots: null pointer");
+    if (table_stride <= 0 || slots <= 0 || layers <= 0) return fail(UOCR_B200_ERR_INVALID, "publish_slots: bad geometry");
+    rswa_publish_slots_kernel<<<n, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        d_packed, block_table, table_stride, d_len, d_ring_pos, d_prefill_len, slots, layers, ws ? ws->status : nullptr);
+    return after_launch("slot state publication");
+}
+
 // ---- attention ----------------------------------------------------------------------------------------
 int uocr_b200_rswa_attention_batch_f32(const float* q, const float* kbase, const float* vbase, const int* d_len,
                                        const int* d_slots, int batch, int batch_cap, int heads, int kv_heads,

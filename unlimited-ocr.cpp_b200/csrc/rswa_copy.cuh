@@ -174,6 +174,28 @@ __global__ void __launch_bounds__(256) rswa_scatter_paged_kernel(
     store_row_paged<KV>(pv, blk, pos & (kBlockTokens - 1), k + src, v + src);
 }
 
+// Slot state publication: record i of `packed` is [slot, fixed-region length, write_row, row[table_stride]].
+// One CTA per record stores the slot's block-table row (when write_row != 0), len = length and
+// ring_pos = 0 for every layer, and prefill_len = length -- what the reference does with 2 * layers + 1
+// blocking single-int copies per request after a prefill (src/engine/gpu_decoder.cu:1131-1150).
+__global__ void __launch_bounds__(128) rswa_publish_slots_kernel(
+    const int32_t* __restrict__ packed, int32_t* __restrict__ table, int table_stride, int* __restrict__ d_len,
+    int* __restrict__ d_ring_pos, int* __restrict__ d_prefill_len, int slots, int layers, int* __restrict__ status) {
+    const int32_t* rec = packed + (size_t)blockIdx.x * (3 + table_stride);
+    const int slot = rec[0], length = rec[1];
+    if (slot < 0 || slot >= slots || length < 0) {
+        if (threadIdx.x == 0 && status) atomicOr(status, kStatusBadSlot);
+        return;
+    }
+    if (rec[2])
+        for (int i = threadIdx.x; i < table_stride; i += blockDim.x) table[(size_t)slot * table_stride + i] = rec[3 + i];
+    for (int l = threadIdx.x; l < layers; l += blockDim.x) {
+        d_len[(size_t)l * slots + slot] = length;
+        d_ring_pos[(size_t)l * slots + slot] = 0;
+    }
+    if (threadIdx.x == 0) d_prefill_len[slot] = length;
+}
+
 // Text prefill scatter: packed row t (fp32) -> text pool token d_text_block0[t]*16 + d_pos[t].
 template <typename KV>
 __global__ void __launch_bounds__(256) rswa_scatter_text_kernel(

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <ctime>
 #include <map>
+#include <mutex>
 
 namespace uocr {
 
@@ -22,6 +23,10 @@ inline void abi_ok(int rc, const char* what) {
 }
 inline int blocks_for(int tokens) { return (tokens + UOCR_B200_BLOCK_TOKENS - 1) / UOCR_B200_BLOCK_TOKENS; }
 inline double cpu_seconds() { return static_cast<double>(::clock()) / CLOCKS_PER_SEC; }
+inline bool stream_is_capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    return cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
+}
 
 }  // namespace
 
@@ -521,6 +526,15 @@ public:
                                               q_start, heads, causal ? 1 : 0, d_out, ws, st), "attention");
     }
 
+    // The same attention over the DEVICE cursors: nothing of the host shadow is frozen into the launch.
+    void attention_devlen_dev(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads, bool causal,
+                              cudaStream_t st) {
+        UOCR_CHECK(!host_dirty[layer], "attention_devlen: pending host edits (mutable_keys/values) must be flushed outside capture");
+        UOCR_CHECK(seq <= ws_rows(), "attention_devlen: more query rows than the cache's workspace holds");
+        abi_ok(uocr_b200_rswa_attention_paged(&view[layer], 0, d_q, 0, d_len + layer, 0, d_prefill, seq, q_start, heads,
+                                              causal ? 1 : 0, d_out, ws, st), "attention_devlen");
+    }
+
     int ws_rows_ = 0;
     int ws_rows() { return ws_rows_ ? ws_rows_ : std::max(alloc_rows, 64); }
     void grow_workspace(int rows) {
@@ -689,17 +703,23 @@ void GpuRSWACache::attention(int layer, const float* d_q, int seq, int q_start, 
                              cudaStream_t stream) const {
     s_->attention_dev(layer, d_q, seq, q_start, d_out, heads, causal, stream);
 }
+void GpuRSWACache::attention_devlen(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads,
+                                    bool causal, cudaStream_t stream) const {
+    s_->attention_devlen_dev(layer, d_q, seq, q_start, d_out, heads, causal, stream);
+}
 int GpuRSWACache::len(int layer) const { return s_->len[layer]; }
 int GpuRSWACache::prefill_len() const { return s_->prefill_len; }
 int GpuRSWACache::window() const { return s_->window; }
 int GpuRSWACache::capacity() const { return s_->capacity; }
 int GpuRSWACache::num_layers() const { return s_->layers; }
-const float* GpuRSWACache::keys(int layer) const {
-    s_->gather_dev(layer, nullptr);
+const float* GpuRSWACache::keys(int layer, cudaStream_t stream) const {
+    UOCR_CHECK(!stream_is_capturing(stream), "GpuRSWACache::keys: a snapshot cannot be taken inside stream capture; use attention_devlen");
+    s_->gather_dev(layer, stream);
     return s_->d_stage_a;
 }
-const float* GpuRSWACache::values(int layer) const {
-    s_->gather_dev(layer, nullptr);
+const float* GpuRSWACache::values(int layer, cudaStream_t stream) const {
+    UOCR_CHECK(!stream_is_capturing(stream), "GpuRSWACache::values: a snapshot cannot be taken inside stream capture; use attention_devlen");
+    s_->gather_dev(layer, stream);
     return s_->d_stage_b;
 }
 
@@ -708,29 +728,57 @@ const float* GpuRSWACache::values(int layer) const {
 // =================================================================================================
 namespace {
 
-uocr_b200_workspace* default_workspace(int rows) {
-    struct Slot {
-        uocr_b200_workspace* ws = nullptr;
-        int rows = 0;
-    };
-    static Slot per_device[64];
+// One workspace per (device, stream), never freed or moved once a launch may have used it.
+struct StreamScratch {
+    uocr_b200_workspace* ws = nullptr;
+    int rows = 0;
+};
+std::mutex g_scratch_mutex;
+std::map<std::pair<int, cudaStream_t>, StreamScratch> g_scratch;
+std::vector<uocr_b200_workspace*> g_retired;  // superseded by a larger one; kept alive for captured graphs
+
+constexpr int kDefaultScratchRows = 4096;
+
+bool prepare_scratch(cudaStream_t stream, int rows) {
     int dev = 0;
-    cudaGetDevice(&dev);
-    Slot& s = per_device[dev & 63];
-    if (!s.ws || rows > s.rows) {
-        if (s.ws) {
-            cudaDeviceSynchronize();
-            uocr_b200_workspace_destroy(s.ws);
-            s.ws = nullptr;
-        }
-        const int want = std::max(rows, 4096);
-        if (uocr_b200_workspace_create(want, &s.ws) != UOCR_B200_OK) {
-            std::fprintf(stderr, "uocr::cuda: workspace: %s\n", uocr_b200_last_error());
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    StreamScratch& s = g_scratch[{dev, stream}];
+    if (s.ws && rows <= s.rows) return true;
+    if (stream_is_capturing(stream)) {
+        std::fprintf(stderr, "uocr::cuda: no scratch for %d rows on this stream and the stream is capturing: call "
+                             "rswa_prepare(stream, max_rows) before the capture begins\n", rows);
+        return false;
+    }
+    uocr_b200_workspace* fresh = nullptr;
+    if (uocr_b200_workspace_create(rows, &fresh) != UOCR_B200_OK) {
+        std::fprintf(stderr, "uocr::cuda: workspace: %s\n", uocr_b200_last_error());
+        return false;
+    }
+    if (s.ws) g_retired.push_back(s.ws);
+    s.ws = fresh;
+    s.rows = rows;
+    return true;
+}
+
+// The workspace of `stream` for a call with `rows` query rows; null (nothing may be launched) when the
+// prepared one is too small or none exists and none can be made now.
+uocr_b200_workspace* default_workspace(cudaStream_t stream, int rows) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_scratch_mutex);
+        auto it = g_scratch.find({dev, stream});
+        if (it != g_scratch.end() && it->second.ws) {
+            if (rows <= it->second.rows) return it->second.ws;
+            std::fprintf(stderr, "uocr::cuda: %d query rows exceed the %d this stream's scratch was prepared for: call "
+                                 "rswa_prepare(stream, max_rows) first (outside stream capture)\n", rows, it->second.rows);
             return nullptr;
         }
-        s.rows = want;
     }
-    return s.ws;
+    if (!prepare_scratch(stream, std::max(rows, kDefaultScratchRows))) return nullptr;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    return g_scratch[{dev, stream}].ws;
 }
 
 // CUDA-side failures are reported, not thrown, like the reference's wrappers (gpu_cache.cu:10-18).
@@ -740,21 +788,31 @@ void report(int rc, const char* what) {
 
 }  // namespace
 
+bool rswa_prepare(cudaStream_t stream, int max_rows) { return max_rows > 0 && prepare_scratch(stream, max_rows); }
+
 void rswa_attention_decode(const float* q, const float* kcache, const float* vcache, int kv_len, int heads,
                            int kv_heads, int head_dim, float* out, cudaStream_t stream) {
+    uocr_b200_workspace* ws = default_workspace(stream, 1);
+    if (!ws) return;
     report(uocr_b200_rswa_attention_f32(q, kcache, vcache, kv_len, nullptr, 1, 0, heads, kv_heads, head_dim, 0, out,
-                                        default_workspace(1), stream), "rswa_attention_decode");
+                                        ws, stream), "rswa_attention_decode");
 }
 void rswa_attention(const float* q, const float* kcache, const float* vcache, int kv_len, int seq, int q_start,
                     int heads, int kv_heads, int head_dim, bool causal, float* out, cudaStream_t stream) {
+    if (seq <= 0) return;
+    uocr_b200_workspace* ws = default_workspace(stream, seq);
+    if (!ws) return;
     report(uocr_b200_rswa_attention_f32(q, kcache, vcache, kv_len, nullptr, seq, q_start, heads, kv_heads, head_dim,
-                                        causal ? 1 : 0, out, default_workspace(seq), stream), "rswa_attention");
+                                        causal ? 1 : 0, out, ws, stream), "rswa_attention");
 }
 void rswa_attention_devlen(const float* q, const float* kcache, const float* vcache, const int* d_len, int seq,
                            int q_start, int heads, int kv_heads, int head_dim, bool causal, float* out,
                            cudaStream_t stream) {
+    if (seq <= 0) return;
+    uocr_b200_workspace* ws = default_workspace(stream, seq);
+    if (!ws) return;
     report(uocr_b200_rswa_attention_f32(q, kcache, vcache, 0, d_len, seq, q_start, heads, kv_heads, head_dim,
-                                        causal ? 1 : 0, out, default_workspace(seq), stream), "rswa_attention_devlen");
+                                        causal ? 1 : 0, out, ws, stream), "rswa_attention_devlen");
 }
 void rswa_append_decode(const float* k, const float* v, float* kcache, float* vcache, int* d_len, int* d_ring_pos,
                         int prefill_len, int window, int kv_heads, int head_dim, cudaStream_t stream) {
@@ -772,8 +830,10 @@ void rswa_attention_batch(const float* q, const float* kcache_base, const float*
                           const int* d_slots, int batch, int batch_cap, int heads, int kv_heads, int head_dim,
                           float* out, cudaStream_t stream) {
     if (batch <= 0) return;
+    uocr_b200_workspace* ws = default_workspace(stream, batch);
+    if (!ws) return;
     report(uocr_b200_rswa_attention_batch_f32(q, kcache_base, vcache_base, d_len, d_slots, batch, batch_cap, heads,
-                                              kv_heads, head_dim, out, default_workspace(batch), stream),
+                                              kv_heads, head_dim, out, ws, stream),
            "rswa_attention_batch");
 }
 void rswa_write_prefill_ragged(const float* k, const float* v, float* kcache_base, float* vcache_base,
@@ -786,8 +846,10 @@ void rswa_attention_ragged(const float* q, const float* kcache_base, const float
                            const int* d_pos, int total, int batch_cap, int heads, int kv_heads, int head_dim,
                            float* out, cudaStream_t stream) {
     if (total <= 0) return;
+    uocr_b200_workspace* ws = default_workspace(stream, total);
+    if (!ws) return;
     report(uocr_b200_rswa_attention_ragged_f32(q, kcache_base, vcache_base, d_slots, d_pos, total, batch_cap, heads,
-                                               kv_heads, head_dim, out, default_workspace(total), stream),
+                                               kv_heads, head_dim, out, ws, stream),
            "rswa_attention_ragged");
 }
 
@@ -803,8 +865,20 @@ struct PagedBatchKV::Impl {
     int* d_len = nullptr;      // [layers][slots]
     int* d_ring = nullptr;     // [layers][slots]
     int* d_prefill = nullptr;  // [slots]
-    int* d_state_stage = nullptr;  // packed upload target, see publish()
-    int* h_state_stage = nullptr;  // pinned
+    // packed slot-state records ([slot, length, write_row, row[stride]] each): two pinned staging buffers
+    // used alternately, each with its device twin and an event recorded behind the copy that reads it
+    int* h_stage[2] = {nullptr, nullptr};
+    int* d_stage[2] = {nullptr, nullptr};
+    cudaEvent_t stage_done[2] = {nullptr, nullptr};
+    bool stage_used[2] = {false, false};
+    int stage_next = 0;
+    // captured decode steps, one per batch size
+    struct StepGraph {
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        StepIO io;
+    };
+    std::map<int, StepGraph> step_graphs;
     uocr_b200_workspace* ws = nullptr;
     std::vector<uocr_b200_paged_kv> view;
     struct SlotState {
@@ -841,8 +915,15 @@ struct PagedBatchKV::Impl {
         if (d_len) cudaFree(d_len);
         if (d_ring) cudaFree(d_ring);
         if (d_prefill) cudaFree(d_prefill);
-        if (d_state_stage) cudaFree(d_state_stage);
-        if (h_state_stage) cudaFreeHost(h_state_stage);
+        drop_graphs();
+        for (int i = 0; i < 2; ++i) {
+            if (d_stage[i]) cudaFree(d_stage[i]);
+            if (h_stage[i]) cudaFreeHost(h_stage[i]);
+            if (stage_done[i]) cudaEventDestroy(stage_done[i]);
+            d_stage[i] = h_stage[i] = nullptr;
+            stage_done[i] = nullptr;
+            stage_used[i] = false;
+        }
         if (text_k) cudaFree(text_k);
         if (text_v) cudaFree(text_v);
         if (d_pf) cudaFree(d_pf);
@@ -850,9 +931,36 @@ struct PagedBatchKV::Impl {
         d_pf = nullptr;
         text_blocks_cap = text_blocks = pf_cap = pf_nv = pf_nt = 0;
         pf_tiles.clear();
-        d_table = nullptr; d_len = d_ring = d_prefill = d_state_stage = nullptr; h_state_stage = nullptr;
+        d_table = nullptr; d_len = d_ring = d_prefill = nullptr;
         if (ws) uocr_b200_workspace_destroy(ws);
         ws = nullptr;
+    }
+    void drop_graphs() {
+        for (auto& kv : step_graphs) {
+            if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+            if (kv.second.graph) cudaGraphDestroy(kv.second.graph);
+        }
+        step_graphs.clear();
+    }
+    int record_ints() const { return 3 + stride; }
+    // Brings `n` staged records over with one copy and applies them with one kernel, both on `stream`.
+    // `fill(i, rec)` writes record i into pinned memory.  No host synchronisation unless both staging
+    // buffers are still being read by earlier copies.
+    template <typename Fill>
+    void publish(int n, Fill fill, cudaStream_t stream) {
+        if (n <= 0) return;
+        UOCR_CHECK(n <= cfg.slots, "PagedBatchKV: more slot records than slots");
+        const int b = stage_next;
+        stage_next ^= 1;
+        if (stage_used[b]) cuda_ok(cudaEventSynchronize(stage_done[b]), "slot state staging");
+        const int ri = record_ints();
+        for (int i = 0; i < n; ++i) fill(i, h_stage[b] + static_cast<std::size_t>(i) * ri);
+        cuda_ok(cudaMemcpyAsync(d_stage[b], h_stage[b], sizeof(int) * static_cast<std::size_t>(n) * ri, cudaMemcpyHostToDevice,
+                                stream), "slot state H2D");
+        cuda_ok(cudaEventRecord(stage_done[b], stream), "slot state event");
+        stage_used[b] = true;
+        abi_ok(uocr_b200_rswa_publish_slots(d_stage[b], n, d_table, stride, d_len, d_ring, d_prefill, cfg.slots, cfg.layers, ws,
+                                            stream), "slot state publication");
     }
     ~Impl() { free_all(); }
 };
@@ -893,7 +1001,12 @@ bool PagedBatchKV::configure(const Config& c) {
         cuda_ok(cudaMalloc(&s.d_len, sizeof(int) * c.layers * c.slots), "batch len");
         cuda_ok(cudaMalloc(&s.d_ring, sizeof(int) * c.layers * c.slots), "batch ring");
         cuda_ok(cudaMalloc(&s.d_prefill, sizeof(int) * c.slots), "batch prefill");
-        cuda_ok(cudaMallocHost(&s.h_state_stage, sizeof(int) * (2 * c.layers + s.stride)), "state stage");
+        for (int i = 0; i < 2; ++i) {
+            const std::size_t bytes = sizeof(int) * static_cast<std::size_t>(c.slots) * (3 + s.stride);
+            cuda_ok(cudaMallocHost(&s.h_stage[i], bytes), "slot state staging (pinned)");
+            cuda_ok(cudaMalloc(&s.d_stage[i], bytes), "slot state staging (device)");
+            cuda_ok(cudaEventCreateWithFlags(&s.stage_done[i], cudaEventDisableTiming), "slot state event");
+        }
         s.ws_rows = std::max(c.slots, 4096);
         abi_ok(uocr_b200_workspace_create(s.ws_rows, &s.ws), "batch workspace");
         s.view.assign(static_cast<std::size_t>(c.layers), uocr_b200_paged_kv{});
@@ -928,62 +1041,89 @@ bool PagedBatchKV::configure(const Config& c) {
 void PagedBatchKV::publish_prefill_state(int slot, int prefix_len, cudaStream_t stream) {
     Impl& s = *p_;
     UOCR_CHECK(slot >= 0 && slot < s.cfg.slots, "PagedBatchKV: slot out of range");
-    // one strided 2-D copy per cursor array instead of 2*layers+1 single-int copies
-    int* lens = s.h_state_stage;
-    int* zeros = s.h_state_stage + s.cfg.layers;
-    for (int l = 0; l < s.cfg.layers; ++l) {
-        lens[l] = prefix_len;
-        zeros[l] = 0;
-    }
-    cuda_ok(cudaMemcpy2DAsync(s.d_len + slot, sizeof(int) * s.cfg.slots, lens, sizeof(int), sizeof(int),
-                              s.cfg.layers, cudaMemcpyHostToDevice, stream), "publish len");
-    cuda_ok(cudaMemcpy2DAsync(s.d_ring + slot, sizeof(int) * s.cfg.slots, zeros, sizeof(int), sizeof(int),
-                              s.cfg.layers, cudaMemcpyHostToDevice, stream), "publish ring");
-    cuda_ok(cudaMemcpyAsync(s.d_prefill + slot, lens, sizeof(int), cudaMemcpyHostToDevice, stream),
-            "publish prefill");
-    cuda_ok(cudaStreamSynchronize(stream), "publish sync");
+    UOCR_CHECK(prefix_len >= 0, "PagedBatchKV: negative prefix length");
+    s.publish(1, [&](int, int* rec) {
+        rec[0] = slot;
+        rec[1] = prefix_len;
+        rec[2] = 0;  // the table row stays as it is
+    }, stream);
     s.slot[slot].prefix_len = prefix_len;
 }
 
-PagedBatchKV::Admission PagedBatchKV::admit(int slot, const std::string& doc_key, int prefix_len, cudaStream_t stream) {
-    Impl& s = *p_;
-    UOCR_CHECK(slot >= 0 && slot < s.cfg.slots, "PagedBatchKV: slot out of range");
-    UOCR_CHECK(!s.slot[slot].bound, "PagedBatchKV: slot already bound");
-    UOCR_CHECK(prefix_len >= 0 && prefix_len <= s.cfg.max_prefix_tokens, "PagedBatchKV: prefix longer than configured");
-    Admission a;
-    a.slot = slot;
-    const int pb = blocks_for(prefix_len), rb = blocks_for(s.cfg.window);
-    std::vector<int>& row = s.rows[slot];
-    std::fill(row.begin(), row.end(), -1);
-    if (pb > 0) {
-        const std::size_t live_before = s.bm->live_prefixes();
-        PrefixEntry* e = s.bm->acquire_prefix(doc_key, prefix_len, static_cast<std::size_t>(pb) * 256);  // throws when exhausted
-        UOCR_CHECK(e->prefill_len == prefix_len, "PagedBatchKV: doc_key reused with a different prefix length");
-        a.prefix_is_new = s.bm->live_prefixes() != live_before;
-        a.prefix_refcount = e->refcount;
-        for (int i = 0; i < pb; ++i) row[static_cast<std::size_t>(i)] = static_cast<int>(e->offset / 256) + i;
-    }
-    const i64 roff = s.bm->allocate_ring(static_cast<std::size_t>(rb) * 256);
-    if (roff < 0) {
-        if (pb > 0) s.bm->release_prefix(doc_key);
-        UOCR_THROW("ring pool exhausted");
-    }
-    for (int i = 0; i < rb; ++i)
-        row[static_cast<std::size_t>(pb + i)] = s.cfg.prefix_arena_blocks + static_cast<int>(roff / 256) + i;
-    Impl::SlotState& st = s.slot[slot];
-    st.bound = true;
-    st.key = doc_key;
-    st.has_prefix = pb > 0;
-    st.ring_off = roff;
-    int* row_stage = s.h_state_stage + 2 * s.cfg.layers;
-    std::memcpy(row_stage, row.data(), sizeof(int) * s.stride);
-    cuda_ok(cudaMemcpyAsync(s.d_table + static_cast<std::size_t>(slot) * s.stride, row_stage,
-                            sizeof(int) * s.stride, cudaMemcpyHostToDevice, stream), "table row H2D");
-    publish_prefill_state(slot, prefix_len, stream);
-    return a;
+void PagedBatchKV::set_overlap(bool enabled) {
+    UOCR_CHECK(p_->ws != nullptr, "PagedBatchKV: not configured");
+    abi_ok(uocr_b200_workspace_set_overlap(p_->ws, enabled ? 1 : 0), "set_overlap");
 }
 
-void PagedBatchKV::release(int slot) {
+std::vector<PagedBatchKV::Admission> PagedBatchKV::admit_wave(const std::vector<WaveItem>& items, cudaStream_t stream) {
+    Impl& s = *p_;
+    std::vector<Admission> out;
+    out.reserve(items.size());
+    const int rb = blocks_for(s.cfg.window);
+    std::size_t done = 0;
+    auto unbind = [&](int slot) {  // host-side undo of one admission of this wave
+        Impl::SlotState& st = s.slot[slot];
+        s.bm->free_ring(st.ring_off, static_cast<std::size_t>(rb) * 256);
+        if (st.has_prefix) s.bm->release_prefix(st.key);
+        st = Impl::SlotState{};
+        std::fill(s.rows[slot].begin(), s.rows[slot].end(), -1);
+    };
+    try {
+        for (; done < items.size(); ++done) {
+            const WaveItem& it = items[done];
+            UOCR_CHECK(it.slot >= 0 && it.slot < s.cfg.slots, "PagedBatchKV: slot out of range");
+            UOCR_CHECK(!s.slot[it.slot].bound, "PagedBatchKV: slot already bound");
+            UOCR_CHECK(it.prefix_len >= 0 && it.prefix_len <= s.cfg.max_prefix_tokens, "PagedBatchKV: prefix longer than configured");
+            Admission a;
+            a.slot = it.slot;
+            const int pb = blocks_for(it.prefix_len);
+            std::vector<int>& row = s.rows[it.slot];
+            std::fill(row.begin(), row.end(), -1);
+            if (pb > 0) {
+                const std::size_t live_before = s.bm->live_prefixes();
+                PrefixEntry* e = s.bm->acquire_prefix(it.doc_key, it.prefix_len, static_cast<std::size_t>(pb) * 256);  // throws when exhausted
+                if (e->prefill_len != it.prefix_len) {
+                    s.bm->release_prefix(it.doc_key);
+                    UOCR_THROW("PagedBatchKV: doc_key reused with a different prefix length");
+                }
+                a.prefix_is_new = s.bm->live_prefixes() != live_before;
+                a.prefix_refcount = e->refcount;
+                for (int i = 0; i < pb; ++i) row[static_cast<std::size_t>(i)] = static_cast<int>(e->offset / 256) + i;
+            }
+            const i64 roff = s.bm->allocate_ring(static_cast<std::size_t>(rb) * 256);
+            if (roff < 0) {
+                if (pb > 0) s.bm->release_prefix(it.doc_key);
+                std::fill(row.begin(), row.end(), -1);
+                UOCR_THROW("ring pool exhausted");
+            }
+            for (int i = 0; i < rb; ++i)
+                row[static_cast<std::size_t>(pb + i)] = s.cfg.prefix_arena_blocks + static_cast<int>(roff / 256) + i;
+            Impl::SlotState& st = s.slot[it.slot];
+            st.bound = true;
+            st.key = it.doc_key;
+            st.has_prefix = pb > 0;
+            st.ring_off = roff;
+            st.prefix_len = it.prefix_len;
+            out.push_back(a);
+        }
+    } catch (...) {
+        for (std::size_t i = 0; i < done; ++i) unbind(items[i].slot);
+        throw;
+    }
+    s.publish(static_cast<int>(items.size()), [&](int i, int* rec) {
+        rec[0] = items[static_cast<std::size_t>(i)].slot;
+        rec[1] = items[static_cast<std::size_t>(i)].prefix_len;
+        rec[2] = 1;
+        std::memcpy(rec + 3, s.rows[items[static_cast<std::size_t>(i)].slot].data(), sizeof(int) * s.stride);
+    }, stream);
+    return out;
+}
+
+PagedBatchKV::Admission PagedBatchKV::admit(int slot, const std::string& doc_key, int prefix_len, cudaStream_t stream) {
+    return admit_wave({WaveItem{slot, doc_key, prefix_len}}, stream)[0];
+}
+
+void PagedBatchKV::release(int slot, cudaStream_t stream) {
     Impl& s = *p_;
     UOCR_CHECK(slot >= 0 && slot < s.cfg.slots, "PagedBatchKV: slot out of range");
     Impl::SlotState& st = s.slot[slot];
@@ -992,7 +1132,65 @@ void PagedBatchKV::release(int slot) {
     if (st.has_prefix) s.bm->release_prefix(st.key);
     st = Impl::SlotState{};
     std::fill(s.rows[slot].begin(), s.rows[slot].end(), -1);
+    s.publish(1, [&](int, int* rec) {  // device row <- -1, cursors <- 0: stale use is flagged, not obeyed
+        rec[0] = slot;
+        rec[1] = 0;
+        rec[2] = 1;
+        std::fill(rec + 3, rec + 3 + s.stride, -1);
+    }, stream);
 }
+
+bool PagedBatchKV::capture_step(int batch, const StepIO& io, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(batch > 0 && batch <= s.cfg.slots, "capture_step: invalid batch size");
+    UOCR_CHECK(io.q && io.k && io.v && io.out && io.d_slots && io.heads > 0, "capture_step: incomplete buffer description");
+    UOCR_CHECK(stream != nullptr, "capture_step: needs a stream of its own (the legacy default stream cannot be captured)");
+    auto it = s.step_graphs.find(batch);
+    if (it != s.step_graphs.end()) {
+        const StepIO& o = it->second.io;
+        const bool same = o.q == io.q && o.k == io.k && o.v == io.v && o.out == io.out && o.d_slots == io.d_slots &&
+                          o.q_layer_stride == io.q_layer_stride && o.kv_layer_stride == io.kv_layer_stride &&
+                          o.out_layer_stride == io.out_layer_stride && o.heads == io.heads && o.d_positions == io.d_positions &&
+                          o.rope_theta == io.rope_theta;
+        if (same) return false;
+        cudaGraphExecDestroy(it->second.exec);
+        cudaGraphDestroy(it->second.graph);
+        s.step_graphs.erase(it);
+    }
+    Impl::StepGraph g;
+    g.io = io;
+    cuda_ok(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "begin step capture");
+    try {
+        for (int l = 0; l < s.cfg.layers; ++l) {
+            const float* q = io.q + static_cast<std::size_t>(l) * io.q_layer_stride;
+            const float* k = io.k + static_cast<std::size_t>(l) * io.kv_layer_stride;
+            const float* v = io.v + static_cast<std::size_t>(l) * io.kv_layer_stride;
+            float* out = io.out + static_cast<std::size_t>(l) * io.out_layer_stride;
+            if (io.d_positions)
+                decode_step_rope(l, q, k, v, io.d_positions, io.rope_theta, io.d_slots, batch, io.heads, out, stream);
+            else
+                decode_step(l, q, k, v, io.d_slots, batch, io.heads, out, stream);
+        }
+    } catch (...) {
+        cudaGraph_t broken = nullptr;
+        cudaStreamEndCapture(stream, &broken);
+        if (broken) cudaGraphDestroy(broken);
+        throw;
+    }
+    cuda_ok(cudaStreamEndCapture(stream, &g.graph), "end step capture");
+    cuda_ok(cudaGraphInstantiate(&g.exec, g.graph, nullptr, nullptr, 0), "instantiate step graph");
+    s.step_graphs[batch] = g;
+    return true;
+}
+
+void PagedBatchKV::replay_step(int batch, cudaStream_t stream) {
+    auto it = p_->step_graphs.find(batch);
+    UOCR_CHECK(it != p_->step_graphs.end(), "replay_step: no graph captured for this batch size");
+    cuda_ok(cudaGraphLaunch(it->second.exec, stream), "step graph launch");
+}
+
+int PagedBatchKV::step_graph_count() const { return static_cast<int>(p_->step_graphs.size()); }
+void PagedBatchKV::drop_step_graphs() { p_->drop_graphs(); }
 
 void PagedBatchKV::append_decode_batch(int layer, const float* k, const float* v, const int* d_slots, int batch,
                                        cudaStream_t stream) {
@@ -1232,6 +1430,149 @@ int PagedBatchKV::device_status(cudaStream_t stream) {
     abi_ok(uocr_b200_workspace_status(p_->ws, stream, &v), "device_status");
     return v;
 }
+
+// =================================================================================================
+// GpuDecoderKV -- KV half of GpuDecoder's continuous-batching interface (gpu_decoder.h:69-87)
+// =================================================================================================
+struct GpuDecoderKV::Impl {
+    int layers = 0, kv_heads = 0, head_dim = 0, window = 0;
+    DType dtype = DType::BF16;
+    PagedBatchKV kv;
+    int slots = 0, capacity = 0;
+    int* d_batch_slots = nullptr;  // [slots] row -> slot of the current decode batch
+    int* d_positions = nullptr;    // [slots] positions of the current decode batch (rotary step only)
+    int* d_row_slot = nullptr;     // ragged prefill: packed row -> slot
+    int* d_row_pos = nullptr;      // ragged prefill: packed row -> position inside its request
+    int ragged_cap = 0;
+    unsigned long long anon = 0;   // requests without a doc_key get a key of their own
+
+    void free_index_arrays() {
+        for (int** p : {&d_batch_slots, &d_positions, &d_row_slot, &d_row_pos}) {
+            if (*p) cudaFree(*p);
+            *p = nullptr;
+        }
+        ragged_cap = 0;
+    }
+    ~Impl() { free_index_arrays(); }
+};
+
+GpuDecoderKV::GpuDecoderKV(int num_layers, int kv_heads, int head_dim, int window, DType dtype) : p_(new Impl) {
+    UOCR_CHECK(num_layers > 0 && kv_heads > 0 && head_dim > 0 && window > 0, "GpuDecoderKV: bad geometry");
+    p_->layers = num_layers;
+    p_->kv_heads = kv_heads;
+    p_->head_dim = head_dim;
+    p_->window = window;
+    p_->dtype = dtype;
+}
+GpuDecoderKV::~GpuDecoderKV() = default;
+PagedBatchKV& GpuDecoderKV::kv() { return p_->kv; }
+int GpuDecoderKV::batch_slots() const { return p_->slots; }
+int GpuDecoderKV::batch_graph_count() const { return p_->slots ? p_->kv.step_graph_count() : 0; }
+const int* GpuDecoderKV::d_batch_slots() const { return p_->d_batch_slots; }
+
+bool GpuDecoderKV::batch_configure(int slots, int capacity) {
+    Impl& s = *p_;
+    UOCR_CHECK(slots > 0 && capacity > s.window, "batch_configure: invalid shape");
+    PagedBatchKV::Config c;
+    c.slots = slots;
+    c.layers = s.layers;
+    c.kv_heads = s.kv_heads;
+    c.head_dim = s.head_dim;
+    c.window = s.window;
+    c.dtype = s.dtype;
+    c.max_prefix_tokens = capacity - s.window;  // the reference sizes every slot for the longest prompt + window
+    c.prefix_arena_blocks = slots * blocks_for(c.max_prefix_tokens);  // worst case: no two requests share a prefix
+    c.ring_arena_blocks = slots * blocks_for(s.window);
+    const bool fresh = s.kv.configure(c);
+    if (fresh || slots != s.slots) {
+        s.free_index_arrays();
+        cuda_ok(cudaMalloc(&s.d_batch_slots, sizeof(int) * slots), "batch slots");
+        cuda_ok(cudaMalloc(&s.d_positions, sizeof(int) * slots), "batch positions");
+    }
+    s.slots = slots;
+    s.capacity = capacity;
+    return fresh;
+}
+
+int GpuDecoderKV::batch_prefill_begin(const std::vector<int>& starts, const std::vector<int>& lengths,
+                                      const std::vector<int>& slots, const std::vector<std::string>& doc_keys,
+                                      cudaStream_t stream) {
+    Impl& s = *p_;
+    const int requests = static_cast<int>(lengths.size());
+    UOCR_CHECK(requests > 0, "batch_prefill_embeds: no requests");
+    UOCR_CHECK(static_cast<int>(starts.size()) == requests && static_cast<int>(slots.size()) == requests,
+               "batch_prefill_embeds: array size mismatch");
+    UOCR_CHECK(doc_keys.empty() || static_cast<int>(doc_keys.size()) == requests, "batch_prefill_embeds: doc_keys size mismatch");
+    int total = 0;
+    std::vector<PagedBatchKV::WaveItem> wave;
+    for (int r = 0; r < requests; ++r) {
+        UOCR_CHECK(lengths[r] > 0, "batch_prefill_embeds: empty prompt");
+        UOCR_CHECK(starts[r] == total, "batch_prefill_embeds: non-contiguous starts");
+        UOCR_CHECK(slots[r] >= 0 && slots[r] < s.slots, "batch_prefill_embeds: slot out of range");
+        total += lengths[r];
+        const std::string key = (!doc_keys.empty() && !doc_keys[r].empty()) ? doc_keys[r] : "#request" + std::to_string(s.anon++);
+        wave.push_back({slots[r], key, lengths[r]});
+    }
+    s.kv.admit_wave(wave, stream);  // table rows + len = prefill = prompt length, ring_pos = 0: one upload
+    std::vector<int> idx(static_cast<std::size_t>(2 * total));
+    for (int r = 0; r < requests; ++r)
+        for (int p = 0; p < lengths[r]; ++p) {
+            idx[static_cast<std::size_t>(starts[r] + p)] = slots[r];
+            idx[static_cast<std::size_t>(total + starts[r] + p)] = p;
+        }
+    if (total > s.ragged_cap) {
+        if (s.d_row_slot) cudaFree(s.d_row_slot);
+        s.d_row_slot = nullptr;
+        cuda_ok(cudaMalloc(&s.d_row_slot, sizeof(int) * 2 * static_cast<std::size_t>(total)), "ragged row index");
+        s.ragged_cap = total;
+    }
+    s.d_row_pos = nullptr;
+    // pageable source: the copy has staged `idx` when the call returns
+    cuda_ok(cudaMemcpyAsync(s.d_row_slot, idx.data(), sizeof(int) * idx.size(), cudaMemcpyHostToDevice, stream), "ragged index H2D");
+    return total;
+}
+
+void GpuDecoderKV::attention_block_ragged(int li, const float* q, const float* k, const float* v, float* ctx, int total,
+                                          int heads, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(s.d_row_slot != nullptr && total > 0 && total <= s.ragged_cap, "attention_block_ragged: call batch_prefill_begin first");
+    const int* row_slot = s.d_row_slot;
+    const int* row_pos = s.d_row_slot + total;  // second half of the array staged by batch_prefill_begin
+    s.kv.write_prefill_ragged(li, k, v, row_slot, row_pos, total, stream);
+    s.kv.attention_ragged(li, q, row_slot, row_pos, total, heads, ctx, stream);
+}
+
+void GpuDecoderKV::batch_decode_begin(const std::vector<int>& slots, cudaStream_t stream) {
+    Impl& s = *p_;
+    const int batch = static_cast<int>(slots.size());
+    UOCR_CHECK(batch > 0 && batch <= s.slots, "batch_decode size out of range");
+    cuda_ok(cudaMemcpyAsync(s.d_batch_slots, slots.data(), sizeof(int) * batch, cudaMemcpyHostToDevice, stream), "batch slots");
+}
+
+void GpuDecoderKV::attention_block_batch(int li, const float* q, const float* k, const float* v, float* ctx, int batch,
+                                         int heads, cudaStream_t stream) {
+    Impl& s = *p_;
+    UOCR_CHECK(batch > 0 && batch <= s.slots, "batch_decode size out of range");
+    s.kv.decode_step(li, q, k, v, s.d_batch_slots, batch, heads, ctx, stream);  // append + attention, one launch
+}
+
+void GpuDecoderKV::batch_decode(const std::vector<int>& positions, const std::vector<int>& slots,
+                                const PagedBatchKV::StepIO& io, bool fold_rope, cudaStream_t stream) {
+    Impl& s = *p_;
+    const int batch = static_cast<int>(slots.size());
+    UOCR_CHECK(batch > 0 && batch <= s.slots, "batch_decode size out of range");
+    UOCR_CHECK(!fold_rope || static_cast<int>(positions.size()) == batch, "positions size mismatch");
+    cuda_ok(cudaMemcpyAsync(s.d_batch_slots, slots.data(), sizeof(int) * batch, cudaMemcpyHostToDevice, stream), "batch slots");
+    if (fold_rope)
+        cuda_ok(cudaMemcpyAsync(s.d_positions, positions.data(), sizeof(int) * batch, cudaMemcpyHostToDevice, stream), "batch pos");
+    PagedBatchKV::StepIO fixed = io;
+    fixed.d_slots = s.d_batch_slots;
+    fixed.d_positions = fold_rope ? s.d_positions : nullptr;
+    s.kv.capture_step(batch, fixed, stream);  // no-op when this batch size was captured on these buffers
+    s.kv.replay_step(batch, stream);
+}
+
+void GpuDecoderKV::batch_release(int slot, cudaStream_t stream) { p_->kv.release(slot, stream); }
 
 }  // namespace cuda
 }  // namespace uocr

@@ -301,25 +301,46 @@ public:
     void reset_device_state(int prefill_len, cudaStream_t stream = nullptr);
     void append_decode_device(int layer, const float* d_k, const float* d_v, cudaStream_t stream = nullptr);
     const int* len_dev(int layer) const;
+    // Attention over the length this object's HOST cursor holds (the reference's host-cursor path,
+    // src/kernels/cuda/gpu_cache.cu:141-145).  The length is frozen into the launch: inside a captured
+    // graph use attention_devlen instead.
     void attention(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads, bool causal,
                    cudaStream_t stream = nullptr) const;
+    // Attention over the DEVICE length len_dev(layer): the call to pair with append_decode_device inside a
+    // captured decode graph.  It stands in for the reference's graph call site, which passes
+    // keys(layer) / values(layer) and len_dev(layer) to rswa_attention_devlen
+    // (src/engine/gpu_decoder.cu:502-505): here the cache is paged, so the attention reads the blocks
+    // directly instead of a contiguous view, and a replayed graph sees every appended token.
+    void attention_devlen(int layer, const float* d_q, int seq, int q_start, float* d_out, int heads, bool causal,
+                          cudaStream_t stream = nullptr) const;
 
     int len(int layer) const;
     int prefill_len() const;
     int window() const;
     int capacity() const;
     int num_layers() const;
-    // Device pointers to the logical fp32 view [capacity][kv_heads*head_dim], refreshed by a gather;
-    // valid until the next call on this object.
-    const float* keys(int layer) const;
-    const float* values(int layer) const;
+    // Device pointers to the logical fp32 view [capacity][kv_heads*head_dim]: a SNAPSHOT made by a
+    // block-table gather launched on `stream` when the call is made, valid until the next call on this
+    // object.  Not for use inside stream capture (a replayed graph would attend over the snapshot taken
+    // at capture time): the call throws uocr::Error when `stream` is capturing.
+    const float* keys(int layer, cudaStream_t stream = nullptr) const;
+    const float* values(int layer, cudaStream_t stream = nullptr) const;
 
 private:
     std::unique_ptr<detail::PagedSeqStore> s_;
 };
 
-// The reference's eight R-SWA entry points, same signatures (contiguous fp32 caches).  Scratch comes
-// from a per-device workspace created on first use: make the first call outside graph capture.
+// The reference's eight R-SWA entry points, same signatures (contiguous fp32 caches).  The reference's
+// kernels need no scratch; the split-KV kernels here do, and the attention wrappers take it from a
+// workspace kept per (device, stream): two streams never share scratch, and a workspace, once handed to
+// a launch, is never freed or moved (a captured graph keeps pointing into it).  rswa_prepare creates the
+// workspace of a stream for up to `max_rows` query rows per call (packed prefill tokens or batch rows);
+// without it the first attention call on a stream prepares 4096 rows itself, which allocates and so must
+// not happen inside stream capture -- a call that finds no workspace while its stream is capturing, or
+// that has more rows than were prepared, launches nothing and reports the error on stderr like the
+// reference's wrappers do for CUDA errors.  A later rswa_prepare with a larger count adds a larger
+// workspace for subsequent calls and leaves the old one in place.  Returns false when it failed.
+UOCR_HOST_API bool rswa_prepare(cudaStream_t stream, int max_rows);
 UOCR_HOST_API void rswa_attention_decode(const float* q, const float* kcache, const float* vcache, int kv_len,
                                          int heads, int kv_heads, int head_dim, float* out, cudaStream_t stream = nullptr);
 UOCR_HOST_API void rswa_attention(const float* q, const float* kcache, const float* vcache, int kv_len, int seq,
@@ -376,12 +397,57 @@ public:
     bool configure(const Config& cfg);
     const Config& config() const;
 
-    // Binds a slot to a document prefix (shared by doc_key, refcounted) and a private ring; uploads the
-    // slot's table row and publishes len = P, ring_pos = 0, prefill = P for every layer in one copy.
+    // Binds a slot to a document prefix (shared by doc_key, refcounted) and a private ring and publishes
+    // its table row, len = P, ring_pos = 0 and prefill = P for every layer.
     Admission admit(int slot, const std::string& doc_key, int prefix_len, cudaStream_t stream = nullptr);
-    void release(int slot);  // frees the ring, drops the prefix reference
+    // A whole admission wave at once: the table rows and cursors of every admitted slot are staged in one
+    // pinned buffer, brought over by ONE copy and applied by one kernel on `stream`; no host
+    // synchronisation (the staging buffers alternate and are guarded by events).  Replaces the
+    // 2 * layers + 1 blocking copies per request of src/engine/gpu_decoder.cu:1131-1150.  All-or-nothing:
+    // if a request cannot be placed (arena exhausted) the earlier ones of the wave are rolled back and
+    // the call throws.
+    struct WaveItem {
+        int slot = -1;
+        std::string doc_key;
+        int prefix_len = 0;
+    };
+    std::vector<Admission> admit_wave(const std::vector<WaveItem>& items, cudaStream_t stream = nullptr);
+    // Frees the ring and drops the prefix reference.  The slot's device table row is overwritten with -1
+    // and its cursors with 0 by a kernel queued on `stream`, so a stale use of the slot is reported as a bad
+    // block instead of touching blocks that may already belong to another sequence.  Ordering is the
+    // caller's: issue the release on the stream that carried the slot's last launch (the blocks may be
+    // handed out again by the next admit, whose own writes are queued behind the release on that stream),
+    // and drop or re-stage captured graphs whose row -> slot map still names the slot.
+    void release(int slot, cudaStream_t stream = nullptr);
     // Engine-style state publication after a ragged prefill (src/engine/gpu_decoder.cu:1131-1150).
     void publish_prefill_state(int slot, int prefix_len, cudaStream_t stream = nullptr);
+    // Launch overlap between the fused steps of consecutive layers (uocr_b200_workspace_set_overlap).
+    void set_overlap(bool enabled);
+
+    // The decode step of all layers as one CUDA graph per batch size, as GpuDecoder::capture_batch_graph /
+    // batch_decode keep one per observed batch size (src/engine/gpu_decoder.cu:746-772,1210-1213).  The
+    // graph holds layers x decode_step (or decode_step_rope when d_positions is set) on FIXED buffers: layer l
+    // reads q + l * q_layer_stride, k / v + l * kv_layer_stride and writes out + l * out_layer_stride
+    // (strides in floats); d_slots (and d_positions) are device arrays the caller refreshes before a replay.
+    // capture_step returns true when it captured (false: a graph for this batch size and these buffers
+    // exists already); graphs are dropped when configure() reallocates, as the reference invalidates its
+    // batch graphs (:929-931).  Cursors live on the device, so one graph replays across the warm-up ->
+    // ring boundary.
+    struct StepIO {
+        const float* q = nullptr;
+        const float* k = nullptr;
+        const float* v = nullptr;
+        float* out = nullptr;
+        long long q_layer_stride = 0, kv_layer_stride = 0, out_layer_stride = 0;
+        const int* d_slots = nullptr;
+        int heads = 0;
+        const int* d_positions = nullptr;  // non-null: rotary embedding folded into the step
+        float rope_theta = 10000.f;
+    };
+    bool capture_step(int batch, const StepIO& io, cudaStream_t stream);
+    void replay_step(int batch, cudaStream_t stream);
+    int step_graph_count() const;
+    void drop_step_graphs();
 
     // Per-layer calls; every pointer is a device pointer, d_slots maps batch rows to slots.
     void append_decode_batch(int layer, const float* k, const float* v, const int* d_slots, int batch,
@@ -435,6 +501,64 @@ public:
     int* d_len(int layer) const;
     int* d_ring_pos(int layer) const;
     int* d_prefill_len() const;
+
+private:
+    struct Impl;
+    std::unique_ptr<Impl> p_;
+};
+
+// ------------------------------------------------------------------------------------------------
+// GpuDecoderKV: the KV half of GpuDecoder's continuous-batching interface under the reference's own
+// method names (include/uocr/gpu_decoder.h:69-87, src/engine/gpu_decoder.cu:904-1213), over a
+// PagedBatchKV.  A decoder keeps its projections, rotary embedding, MoE and lm_head and replaces the
+// KV members (gpu_decoder.h:246-258) and the three attention call sites by calls on this object:
+//
+//   batch_configure(slots, capacity)                    gpu_decoder.cu:904-970
+//   batch_prefill_begin(starts, lengths, slots)         the index staging of batch_prefill_embeds (:1106-1127)
+//                                                       and its state publication (:1131-1150), in one copy
+//   attention_block_ragged(li, q, k, v, ctx, total)     the KV body of :1025-1052 (scatter, ragged attention)
+//   batch_decode_begin(slots)                           the row -> slot staging of batch_decode (:1199-1200)
+//   attention_block_batch(li, q, k, v, ctx, batch)      the KV body of :972-1003 (append, batched attention)
+//   batch_decode(positions, slots, io, stream)          the captured form: one graph per batch size (:1210-1213)
+//   batch_slots(), batch_graph_count()                  gpu_decoder.h:85-87
+//
+// As in the reference, a request's whole first prefill becomes its fixed region (len = prefill = prompt
+// length, ring_pos = 0) and `capacity` is the longest prompt plus the window.  New here: requests that
+// name the same doc_key share the physical prefix blocks, and a slot only holds ceil(P / 16) + W / 16
+// blocks instead of `capacity` rows.
+// ------------------------------------------------------------------------------------------------
+class UOCR_HOST_API GpuDecoderKV {
+public:
+    GpuDecoderKV(int num_layers, int kv_heads, int head_dim, int window, DType dtype = DType::BF16);
+    ~GpuDecoderKV();
+    GpuDecoderKV(const GpuDecoderKV&) = delete;
+    GpuDecoderKV& operator=(const GpuDecoderKV&) = delete;
+
+    // Returns true when device buffers were (re)allocated (captured graphs are dropped then).
+    bool batch_configure(int slots, int capacity);
+    int batch_slots() const;
+    int batch_graph_count() const;
+
+    // Request r owns packed rows [starts[r], starts[r] + lengths[r]) and cache slot slots[r]; doc_keys[r]
+    // (optional) names a shareable prefix.  Admits the slots (one packed state upload for the wave) and
+    // stages the row -> slot and row -> position arrays.  Returns the packed row count.
+    int batch_prefill_begin(const std::vector<int>& starts, const std::vector<int>& lengths, const std::vector<int>& slots,
+                            const std::vector<std::string>& doc_keys = {}, cudaStream_t stream = nullptr);
+    void attention_block_ragged(int li, const float* q, const float* k, const float* v, float* ctx, int total, int heads,
+                                cudaStream_t stream = nullptr);
+    void batch_decode_begin(const std::vector<int>& slots, cudaStream_t stream = nullptr);
+    void attention_block_batch(int li, const float* q, const float* k, const float* v, float* ctx, int batch, int heads,
+                               cudaStream_t stream = nullptr);
+    // All layers of a decode step on fixed activation buffers, replaying a graph captured on first use for
+    // this batch size (io.d_slots / io.d_positions are ignored: the staged arrays of this object are used).
+    // With a positive rope_theta in `io` the rotary embedding is folded into the step and `positions` are
+    // staged as well; otherwise they are not needed by the KV half.
+    void batch_decode(const std::vector<int>& positions, const std::vector<int>& slots, const PagedBatchKV::StepIO& io,
+                      bool fold_rope, cudaStream_t stream);
+    void batch_release(int slot, cudaStream_t stream = nullptr);
+
+    PagedBatchKV& kv();
+    const int* d_batch_slots() const;  // [batch] row -> slot, as staged by the last *_begin / batch_decode
 
 private:
     struct Impl;
