@@ -382,6 +382,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifndef UOCR_FFMA2
 #define UOCR_FFMA2 1
 #endif
+#ifndef UOCR_L2_HINTS
+#define UOCR_L2_HINTS 3  // bit 0: ring tiles evict-first, bit 1: fixed-region tiles evict-last
+#endif
+#ifndef UOCR_ARRIVE_RELEASE
+#define UOCR_ARRIVE_RELEASE 1
+#endif
 #ifdef UOCR_TRACE
 __device__ unsigned long long g_trace[2 * 8 * 4096];  // two halves: consecutive (overlapping) launches alternate
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
@@ -416,6 +422,7 @@ constexpr uint32_t kMetaText = 1u << 11;        // tile comes from the text pool
 constexpr uint32_t kMetaPatch = 1u << 12;       // fused step: the new token lands in this tile
 constexpr int kMetaPatchOffShift = 13;          // bits 13-16
 constexpr int kMetaHeadShift = 17;              // bits 17-31 kv head (row-mode addressing)
+constexpr uint32_t kMetaFixed = 1u << 17;       // paged addressing: tile of the fixed (possibly shared) region
 
 template <typename KV>
 __device__ __forceinline__ void unpack2(const uint4& w, float2 (&f)[KV::kPerChunk / 2]) {
@@ -571,6 +578,7 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
                 uint32_t m = 0;
                 if (c.j < npb) {
                     valid = min(kBlockTokens, c.info.pe - c.j * kBlockTokens);
+                    if constexpr (PAGED) m |= kMetaFixed;
                 } else {
                     int lead = 0;
                     if constexpr (PAGED && !FUSED) lead = p.k_text != nullptr ? (c.info.aux & 15) : 0;
@@ -609,6 +617,9 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             }
         };
 
+#if UOCR_L2_HINTS
+        const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+#endif
         // ---- producer side: tiles K(0) V(0) K(1) V(1) ... rotate through the kRing slots -------------
         auto issue_tile = [&](int unit, bool is_v) {
             const uint32_t tile = __shfl_sync(FULL, d_tile, unit - desc_base);
@@ -619,7 +630,16 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
                 if (lane == 0) {
                     const uint8_t* base = (meta & kMetaText) ? (is_v ? p.v_text : p.k_text) : (is_v ? p.v_base : p.k_base);
                     mbar_arrive_expect_tx(bar, TILE);
+#if UOCR_L2_HINTS
+                    // ring tiles are read once per launch: first out of L2; tiles of the fixed region are
+                    // re-read by every sequence that shares the prefix: last out
+                    if ((meta & kMetaFixed) ? (UOCR_L2_HINTS & 2) : (UOCR_L2_HINTS & 1))
+                        bulk_copy_g2s_hint(dst, base + (size_t)tile * TILE, TILE, bar, (meta & kMetaFixed) ? pol_keep : pol_stream);
+                    else
+                        bulk_copy_g2s(dst, base + (size_t)tile * TILE, TILE, bar);
+#else
                     bulk_copy_g2s(dst, base + (size_t)tile * TILE, TILE, bar);
+#endif
                 }
             } else {
                 const int nvalid = (int)(meta & kMetaValidMask);
@@ -713,7 +733,9 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         // ---- arrivals: whoever completes an item's set of partials merges them ------------------------
         auto flush_arrivals = [&]() {
             if (pend_n == 0) return;
+#if !UOCR_ARRIVE_RELEASE
             __threadfence();  // this warp's partial stores are visible before its arrivals
+#endif
             __syncwarp();
             // every lane arrives for one pending segment (the atomics overlap), then the warp merges the
             // items for which one of its arrivals was the last
@@ -727,12 +749,21 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
                 my_s0 = (long long)rs[r] + (long long)h * n;
                 my_wf = pm.of(my_s0);
                 my_wl = pm.of(my_s0 + n - 1);
+#if UOCR_ARRIVE_RELEASE
+                int old;  // release: the warp's partial stores (ordered before this by the barrier above); acquire: the other arrivers' partials
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + my_wf) : "memory");
+#else
                 const int old = atomicAdd(p.counters + my_wf, 1);
+#endif
                 my_last = (old == my_wl - my_wf);
             }
             const unsigned all_todo = __ballot_sync(FULL, my_last);
             unsigned todo = all_todo;
+#if !UOCR_ARRIVE_RELEASE
             if (todo) __threadfence();  // the other arrivers' partials are visible after their arrivals
+#else
+            __syncwarp();  // the arriving lane's acquire covers the loads the whole warp issues next
+#endif
             while (todo) {
                 const int src = __ffs(todo) - 1;
                 todo &= todo - 1;

@@ -418,7 +418,10 @@ struct AttnCall {
 
 // Share the last CTA of an overlapped launch gives up, in sixteenths: it starts 8-12 us after the others
 // (of a launch of ~50 us), and 3/16 measured best among 0..6.
-constexpr int kLateCtaSixteenths = 3;
+#ifndef UOCR_LATE_SIXTEENTHS
+#define UOCR_LATE_SIXTEENTHS 3
+#endif
+constexpr int kLateCtaSixteenths = UOCR_LATE_SIXTEENTHS;
 
 constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
 

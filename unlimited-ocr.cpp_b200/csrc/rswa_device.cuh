@@ -76,6 +76,26 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
         : "memory");
 }
 
+// The same copy with an L2 eviction policy for the lines it brings in (createpolicy word in `policy`).
+__device__ __forceinline__ void bulk_copy_g2s_hint(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
+                                                   uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+            "r"(dst),
+        "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
 // ---------------------------------------------------------------------------------------------
 // bf16 on raw bits (round-to-nearest-even exactly as the reference's host helper does:
 // add 0x7fff + lsb, shift; NaN is not special-cased -- include/uocr/common.h:56-64)
