@@ -262,7 +262,7 @@ class DecodeWorkload:
         self.ws = pkg.Workspace(B)
         self.ws.set_overlap(overlap)  # consecutive launches belong to different layers: overlap is safe
         if weighted:
-            self.ws.calibrate(int(os.environ.get("UOCR_SPLIT_MODE", "1")))  # per-SM shares from a measured streaming rate instead of an even split
+            self.ws.calibrate(True)  # per-SM shares from a measured streaming rate instead of an even split
         self.graph = None
         self.launches_per_step = 0
         self.steps_done = 0
@@ -435,6 +435,19 @@ def traffic_record(name="rswa_attn_kernel_fused_bf16_hd128_cfg2.md"):
     return float(m.group(2)), float(m.group(3)), f"profiles/{name} @ kernel sources {m.group(1)}"
 
 
+def workload_config(world):
+    """The workload both arms run (the GPU arm and the reference's CPU code): same dict in both lines."""
+    return {"workload": "%s: batched decode, %d seqs/GPU x %d layers, 10 heads x 128, bf16 paged KV "
+                        "(16-token blocks), shared prefixes %s, W=%d, pos~U[%d,%d]"
+                        % (CFG["name"], CFG["seqs"], CFG["layers"], list(CFG["prefixes"]), CFG["window"],
+                           CFG["pos_lo"], CFG["pos_hi"]),
+            "seqs_per_gpu": CFG["seqs"], "layers": CFG["layers"], "window": CFG["window"],
+            "prefixes": list(CFG["prefixes"]),
+            "l2_policy": "inputs larger than L2: the KV every step streams is resident and far larger than the "
+                         "126 MB L2 (bf16 pools on the GPU, fp32 caches on the host arm)",
+            "parallelism": f"replicas x{world} (sequences shard by request, no collective)"}
+
+
 def run_ours(args, rank, world):
     import torch
     pkg = load_pkg()
@@ -509,8 +522,7 @@ def run_ours(args, rank, world):
     # the copies of later layers overlap the kernels of earlier ones; the caller reads the result every step ----
     hqkv = torch.randn(wl.qkv.shape).pin_memory()
     hout = torch.empty(wl.out.shape).pin_memory()
-    chunks = tuple(int(x) for x in os.environ.get("UOCR_E2E_CHUNKS", "1,3,8").split(",")) if CFG["layers"] == 12 \
-        else (1,) * CFG["layers"]
+    chunks = (1, 3, 8) if CFG["layers"] == 12 else (1,) * CFG["layers"]
     e2e_graph = wl.capture_e2e(hqkv, hout, chunks, mapped_out=(args.e2e_out == "mapped"))
     for _ in range(2):
         e2e_graph.replay()
@@ -542,7 +554,10 @@ def run_ours(args, rank, world):
                      "gather_batched": gather_batched_gbs(pkg, torch, reps=5)}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(sample_seqs=CFG["seqs"], steps=4, threads=host_threads())
+        # cfg2: every sequence (fp32 caches of 64 sequences are about 10 GB of host memory); the W=4096
+        # configuration would need hundreds of GB, so a sample of 8 sequences stands for it
+        cpu = cpu_baseline(sample_seqs=CFG["seqs"] if CFG["name"] == "cfg2" else min(8, CFG["seqs"]), steps=4,
+                           threads=host_threads())
     ranks.close()
     if rank != 0:
         return
@@ -558,16 +573,10 @@ def run_ours(args, rank, world):
         "per_rank_ms": per_rank_ms,
         "scaling": "strong" if CFG["total_seqs"] else "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "%s: batched decode, %d seqs/GPU x %d layers, 10 heads x 128, bf16 paged KV "
-                               "(16-token blocks), shared prefixes %s, W=%d, pos~U[%d,%d]"
-                               % (CFG["name"], CFG["seqs"], CFG["layers"], list(CFG["prefixes"]), CFG["window"],
-                                  CFG["pos_lo"], CFG["pos_hi"]),
-                   "seqs_per_gpu": CFG["seqs"], "layers": CFG["layers"], "window": CFG["window"],
-                   "prefixes": list(CFG["prefixes"]),
-                   "kv_resident_gb": round(wl.num_blocks * 81920 * CFG["layers"] / 1e9, 2),
-                   "l2_policy": "inputs larger than L2 (resident KV pool vs 126 MB L2)", "step": ("cuda graph of 12 x (append; plan; attention)" if args.separate else
-                            "cuda graph of 12 fused decode-step launches (append + attention in one kernel)"),
-                   "parallelism": f"replicas x{world} (sequences shard by request, no collective)"},
+        "config": workload_config(world),
+        "run": {"kv_resident_gb": round(wl.num_blocks * 81920 * CFG["layers"] / 1e9, 2),
+                "step": ("cuda graph of %d x (append; plan; attention)" % CFG["layers"] if args.separate else
+                         "cuda graph of %d fused decode-step launches (append + attention in one kernel)" % CFG["layers"])},
         "roofline": {"bound": "hbm", "kernel": "rswa_attn_kernel<BF16,128,paged,%s>" % ("separate" if args.separate else "fused"), "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "kernel_ms": k_ms,
@@ -640,7 +649,8 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": world,
         "steps": steps, "warmup": args.warmup, "ms_per_step": cpu["seconds"] / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg2 on host cores: " + cpu["sample"]},
+        "config": workload_config(world),
+        "run": {"how": "the reference's RSWACache on host cores (rank 0 only): " + cpu["sample"]},
         "cpu_baseline": cpu,
         "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }

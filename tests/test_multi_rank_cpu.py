@@ -16,11 +16,12 @@ WORKER = textwrap.dedent("""
     r = bench.Ranks(rank, world, backend="gloo")
     r.barrier()
     slow = r.max_over_ranks(10.0 + 5.0 * rank)           # rank 1 is the slow one
+    by_rank = r.gather([1.0 + rank, 2.0 + rank, 3.0 + rank])  # per-repeat times of every rank, seen by all
     start, n = bench.shard_sequences(513, world, rank)
     bench.CFG["seqs"] = 8
     pos = bench.draw_positions(rank).tolist()
     r.close()
-    print(json.dumps({"rank": rank, "slow": slow, "start": start, "n": n, "pos": pos}))
+    print(json.dumps({"rank": rank, "slow": slow, "start": start, "n": n, "pos": pos, "by_rank": by_rank}))
 """) % ROOT
 
 
@@ -39,6 +40,7 @@ def test_two_gloo_ranks(tmp_path):
     assert outs[0]["slow"] == outs[1]["slow"] == 15.0          # MAX over ranks, seen by every rank
     assert (outs[0]["start"], outs[0]["n"]) == (0, 257) and (outs[1]["start"], outs[1]["n"]) == (257, 256)
     assert outs[0]["pos"] != outs[1]["pos"]                     # every replica draws its own workload
+    assert outs[0]["by_rank"] == outs[1]["by_rank"] == [[1.0, 2.0, 3.0], [2.0, 3.0, 4.0]]
     import bench
     assert bench.aggregate_tokens_per_s([64, 64], 10, 20.0) == 64000.0
     assert [bench.shard_sequences(512, 8, r)[1] for r in range(8)] == [64] * 8

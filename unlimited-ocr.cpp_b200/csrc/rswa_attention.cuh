@@ -379,15 +379,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifndef UOCR_STEADY
 #define UOCR_STEADY 2
 #endif
-#ifndef UOCR_FFMA2
-#define UOCR_FFMA2 1
-#endif
-#ifndef UOCR_L2_HINTS
-#define UOCR_L2_HINTS 3  // bit 0: ring tiles evict-first, bit 1: fixed-region tiles evict-last
-#endif
-#ifndef UOCR_ARRIVE_RELEASE
-#define UOCR_ARRIVE_RELEASE 1
-#endif
 #ifdef UOCR_TRACE
 __device__ unsigned long long g_trace[2 * 8 * 4096];  // two halves: consecutive (overlapping) launches alternate
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
@@ -398,20 +389,9 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 constexpr int kSteady = UOCR_STEADY < UOCR_RING ? UOCR_STEADY : UOCR_RING;
 constexpr int kRing = UOCR_RING;  // shared-memory tile slots per warp; tiles K(0) V(0) K(1) V(1) ... rotate through them
 
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-#if UOCR_FFMA2
-    return __ffma2_rn(a, b, c);
-#else
-    return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
-#endif
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-#if UOCR_FFMA2
-    return __fmul2_rn(a, b);
-#else
-    return make_float2(a.x * b.x, a.y * b.y);
-#endif
-}
+// packed fp32x2 arithmetic: one instruction per two lanes of the dot products and accumulators
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 
 // Unit descriptor bits (one 32-bit word per unit, built 32 units at a time, one per lane).
 constexpr uint32_t kMetaValidMask = 0x1f;       // bits 0-4   tokens [skip, valid) of the tile are attended
@@ -617,9 +597,7 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             }
         };
 
-#if UOCR_L2_HINTS
         const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
-#endif
         // ---- producer side: tiles K(0) V(0) K(1) V(1) ... rotate through the kRing slots -------------
         auto issue_tile = [&](int unit, bool is_v) {
             const uint32_t tile = __shfl_sync(FULL, d_tile, unit - desc_base);
@@ -630,16 +608,9 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
                 if (lane == 0) {
                     const uint8_t* base = (meta & kMetaText) ? (is_v ? p.v_text : p.k_text) : (is_v ? p.v_base : p.k_base);
                     mbar_arrive_expect_tx(bar, TILE);
-#if UOCR_L2_HINTS
                     // ring tiles are read once per launch: first out of L2; tiles of the fixed region are
                     // re-read by every sequence that shares the prefix: last out
-                    if ((meta & kMetaFixed) ? (UOCR_L2_HINTS & 2) : (UOCR_L2_HINTS & 1))
-                        bulk_copy_g2s_hint(dst, base + (size_t)tile * TILE, TILE, bar, (meta & kMetaFixed) ? pol_keep : pol_stream);
-                    else
-                        bulk_copy_g2s(dst, base + (size_t)tile * TILE, TILE, bar);
-#else
-                    bulk_copy_g2s(dst, base + (size_t)tile * TILE, TILE, bar);
-#endif
+                    bulk_copy_g2s_hint(dst, base + (size_t)tile * TILE, TILE, bar, (meta & kMetaFixed) ? pol_keep : pol_stream);
                 }
             } else {
                 const int nvalid = (int)(meta & kMetaValidMask);
@@ -733,10 +704,7 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         // ---- arrivals: whoever completes an item's set of partials merges them ------------------------
         auto flush_arrivals = [&]() {
             if (pend_n == 0) return;
-#if !UOCR_ARRIVE_RELEASE
-            __threadfence();  // this warp's partial stores are visible before its arrivals
-#endif
-            __syncwarp();
+            __syncwarp();  // orders the partial stores of every lane before the arriving lanes' releases
             // every lane arrives for one pending segment (the atomics overlap), then the warp merges the
             // items for which one of its arrivals was the last
             int my_item = -1, my_wf = 0, my_wl = 0;
@@ -749,21 +717,13 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
                 my_s0 = (long long)rs[r] + (long long)h * n;
                 my_wf = pm.of(my_s0);
                 my_wl = pm.of(my_s0 + n - 1);
-#if UOCR_ARRIVE_RELEASE
                 int old;  // release: the warp's partial stores (ordered before this by the barrier above); acquire: the other arrivers' partials
                 asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + my_wf) : "memory");
-#else
-                const int old = atomicAdd(p.counters + my_wf, 1);
-#endif
                 my_last = (old == my_wl - my_wf);
             }
             const unsigned all_todo = __ballot_sync(FULL, my_last);
             unsigned todo = all_todo;
-#if !UOCR_ARRIVE_RELEASE
-            if (todo) __threadfence();  // the other arrivers' partials are visible after their arrivals
-#else
             __syncwarp();  // the arriving lane's acquire covers the loads the whole warp issues next
-#endif
             while (todo) {
                 const int src = __ffs(todo) - 1;
                 todo &= todo - 1;

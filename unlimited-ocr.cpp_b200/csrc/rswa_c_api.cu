@@ -418,10 +418,7 @@ struct AttnCall {
 
 // Share the last CTA of an overlapped launch gives up, in sixteenths: it starts 8-12 us after the others
 // (of a launch of ~50 us), and 3/16 measured best among 0..6.
-#ifndef UOCR_LATE_SIXTEENTHS
-#define UOCR_LATE_SIXTEENTHS 3
-#endif
-constexpr int kLateCtaSixteenths = UOCR_LATE_SIXTEENTHS;
+constexpr int kLateCtaSixteenths = 3;
 
 constexpr int kFusedMaxRows = 1024;  // the fused step plans in shared memory
 

@@ -181,37 +181,6 @@ constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchan
 constexpr int kTcSmemBytes = 6 * kTcTileBytes + 256 + kTcExchangeBytes + 1024;  // Qhi Qlo K[2] V[2], barriers, exchange, alignment slack
 constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;                            // one K tile + one V tile
 
-// Optional timeline of the first CTAs (cycle stamps per key tile and role), compiled in with -DUOCR_TC_TRACE.
-#ifdef UOCR_TC_TRACE
-#ifndef UOCR_TC_TRACE_FIRST
-#define UOCR_TC_TRACE_FIRST 0  // first traced query tile (blockIdx.x), head 0
-#endif
-constexpr int kTcTraceCtas = 64, kTcTraceSteps = 24, kTcTraceSlots = 16;
-__device__ unsigned long long g_tc_trace[kTcTraceCtas * kTcTraceSteps * kTcTraceSlots];
-__device__ __forceinline__ void tc_trace(int step, int slot) {
-    const int cta = (int)blockIdx.x - UOCR_TC_TRACE_FIRST;
-    if (blockIdx.y == 0 && cta >= 0 && cta < kTcTraceCtas && step < kTcTraceSteps)
-        g_tc_trace[(cta * kTcTraceSteps + step) * kTcTraceSlots + slot] = clock64();
-}
-#define TC_TRACE(cond, step, slot) do { if (cond) tc_trace(step, slot); } while (0)
-// per CTA: start and end (global nanosecond timer), SM id, key tiles walked
-constexpr int kTcTraceCtaRows = 8192;
-__device__ unsigned long long g_tc_cta[kTcTraceCtaRows * 8];
-__device__ __forceinline__ void tc_trace_cta(int field, unsigned long long v) {
-    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
-    if (cta < kTcTraceCtaRows) g_tc_cta[cta * 8 + field] = v;
-}
-__device__ __forceinline__ unsigned long long tc_globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TC_TRACE_CTA(field, value) do { if (threadIdx.x == 0) tc_trace_cta(field, value); } while (0)
-#else
-#define TC_TRACE(cond, step, slot) do { } while (0)
-#define TC_TRACE_CTA(field, value) do { } while (0)
-#endif
-
 // 64 consecutive TMEM columns of this thread's lane into registers: two loads, one wait.  The wait
 // and the empty statement after it name the registers so that no use can be scheduled before them.
 #define UOCR_R32(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7]), \
@@ -254,10 +223,9 @@ __device__ __forceinline__ bool softmax_sync(uint32_t bar, uint32_t parity, int*
 template <bool FULL>
 __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
                                                 uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_run, float& l_run,
-                                                float& alpha, int tstep) {
+                                                float& alpha) {
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
-    TC_TRACE(tstep >= 0, tstep, 2);
     float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < 64; ++j) {
@@ -267,7 +235,6 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     *my_max = mx;
     // also: both halves of S are in registers from here on, P may overwrite them
     if (!pair_sync(pair_bar, pair_parity, status)) return false;
-    TC_TRACE(tstep >= 0, tstep, 3);
     const float m_new = fmaxf(m_run, fmaxf(mx, *other_max));
     const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
     alpha = tc_exp2(m_run - m_safe);
@@ -290,7 +257,6 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
         tc_st32(tS + h * 64 + qq * 32, pk);
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    TC_TRACE(tstep >= 0, tstep, 4);
     l_run = l_run * alpha + lsum;
     m_run = m_new;
     return true;
@@ -329,14 +295,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const PrefillTile t = p.tiles[blockIdx.x];
     const int head = blockIdx.y, kvh = head / p.group;
-#ifdef UOCR_TC_TRACE
-    TC_TRACE_CTA(0, tc_globaltimer());
-    {
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        TC_TRACE_CTA(2, smid);
-    }
-#endif
 
     if (tid == 0) {
 #pragma unroll
@@ -364,9 +322,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-#ifdef UOCR_TC_TRACE
-    TC_TRACE_CTA(4, tc_globaltimer());
-#endif
 
     // ---- key tiles this query tile can see (uniform over the CTA) ------------------------------------
     const int pfx = max(p.d_prefill_len[t.slot], 0);
@@ -412,9 +367,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
             mbar_arrive(q_full);
-#ifdef UOCR_TC_TRACE
-            TC_TRACE_CTA(5, tc_globaltimer());
-#endif
         }
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         float acc[64];
@@ -430,20 +382,17 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
             const int vlo = text ? tlo - t0 : -(1 << 30);
             const int vhi = (text ? thi : phi) - t0;
-            const int tstep = tid == 0 ? n : -1;
-            TC_TRACE(tstep >= 0, tstep, 0);
             // warp-uniform outcome: the TMEM instructions below need the whole warp
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            TC_TRACE(tstep >= 0, tstep, 1);
             const uint32_t tS = tmem + lane_base + b * 128;
             float* my_max = xmax + (b * 2 + h) * 128 + r;
             const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
             float alpha = 1.f;
             if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
-                ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha, tstep);
+                ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
             else
-                ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha, tstep);
+                ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
             if (!ok) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full(b));
@@ -451,10 +400,8 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 const int k = n - 1;
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                TC_TRACE(tstep >= 0, tstep, 5);
                 tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
                 folded = n;
-                TC_TRACE(tstep >= 0, tstep, 6);
             }
             alpha_prev = alpha;
         }
@@ -465,9 +412,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
             }
         }
-#ifdef UOCR_TC_TRACE
-        TC_TRACE_CTA(6, tc_globaltimer());
-#endif
         // ---- row sum over both key halves, then this thread's 64 dims of the row ------------------------
         // (after a wait that ran out the partner warp may be elsewhere: no rendezvous then, zeros out)
         xsum[h * 128 + r] = l_run;
@@ -500,9 +444,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 }
             }
         }
-#ifdef UOCR_TC_TRACE
-        TC_TRACE_CTA(7, tc_globaltimer());
-#endif
     } else if (warp == 8 || warp == 10) {
         // ================= producer warps: warp 8 feeds K, warp 10 feeds V ============================
         // lane = (64-dim half, block of the tile); K runs further ahead than V because its stage is
@@ -537,7 +478,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 }
                 map = is_v ? &maps.v : &maps.k;
             }
-            TC_TRACE(lane == 0, n, 14 + is_v);
             if (lane == 0) mbar_arrive_expect_tx(full, kTcTileBytes);
             __syncwarp();
             const uint32_t dst = smem_addr(sKV) + b * kTcStageBytes + is_v * kTcTileBytes + half * kTcHalfBytes + blk_i * 2048;
@@ -575,7 +515,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             };
             bool ok = mbar_wait_bounded(q_full, 0, p.status);
             for (int n = 0; n < n_steps && ok; ++n) {
-                TC_TRACE(true, n, 8);
                 if (n == 0) {
                     if (!mbar_wait_bounded(k_full(0), 0, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -584,15 +523,11 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 if (n + 1 < n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
                     if (!mbar_wait_bounded(k_full((n + 1) & 1), (uint32_t)((n + 1) >> 1) & 1u, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    TC_TRACE(true, n, 9);
                     issue_qk(n + 1);
-                    TC_TRACE(true, n, 10);
                 }
                 if (!mbar_wait_bounded(v_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
-                TC_TRACE(true, n, 11);
                 if (!mbar_wait_bounded(p_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                TC_TRACE(true, n, 12);
                 const uint64_t stage = (uint64_t)((n & 1) * (kTcStageBytes >> 4));
                 const uint32_t tP = tmem + (n & 1) * 128, tO = tmem + 256 + (n & 1) * 128;
                 // P: 16 keys = 8 TMEM columns per MMA; every 32 keys hold their 16 hi words, then their 16 lo words.
@@ -604,7 +539,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 }
                 tc_commit(o_full(n & 1));
                 tc_commit(v_free(n & 1));
-                TC_TRACE(true, n, 13);
             }
             // every MMA issued above has finished before the TMEM is released
             tc_commit(drained);
@@ -615,10 +549,6 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-#ifdef UOCR_TC_TRACE
-    TC_TRACE_CTA(1, tc_globaltimer());
-    TC_TRACE_CTA(3, (unsigned long long)n_steps);
-#endif
     if (warp == 9) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
