@@ -50,27 +50,75 @@ def load_pkg():
     return mod
 
 
-def _global_shard(rank: int):
-    """Strong-scaling workloads: positions and prefix ids are drawn once for the whole job; sequences are
-    ordered by prefix (affinity first: a GPU then holds as few distinct prefixes as possible, one copy of
-    each) and dealt to the ranks in contiguous, near-equal shards.  Returns (positions, prefix ids) of
-    this rank's sequences."""
+def strong_plan(world: int):
+    """Strong-scaling workloads: positions and prefix ids are drawn once for the whole job and the sequences
+    are dealt to the ranks.  Returns (positions, prefix ids, order, bounds): rank r owns order[bounds[r]:bounds[r+1]]."""
     import synth
     total, n = CFG["total_seqs"], len(CFG["prefixes"])
-    world = int(os.environ.get("WORLD_SIZE", 1))
     pos = synth.integers(CFG["seed"], 77, CFG["pos_lo"], CFG["pos_hi"], (total,)).astype(np.int64)
     ids = synth.integers(CFG["seed"], 177, 0, n - 1, (total,)).astype(np.int64) if n > 1 else np.zeros(total, np.int64)
-    order = np.argsort(ids, kind="stable")
-    start, count = shard_sequences(total, world, rank)
-    mine = order[start:start + count]
+    order, bounds = balanced_shards(ids, np.minimum(pos, CFG["window"]), total, world)
+    return pos, ids, order, bounds
+
+
+def _global_shard(rank: int):
+    """(positions, prefix ids) of this rank's sequences."""
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    pos, ids, order, bounds = strong_plan(world)
+    mine = order[bounds[rank]:bounds[rank + 1]]
     return pos[mine], ids[mine]
+
+
+def balanced_shards(ids, load, total, world, balance=True):
+    """Contiguous shards of the prefix-sorted sequence order for a strong-scaling job (requests are
+    independent, so any partition is valid).  Affinity first: the order is sorted by prefix id, so a rank
+    holds as few distinct prefixes as possible, one copy of each.  Then bytes: `load` is the window tokens
+    a sequence streams per step; the shard boundaries are put where the cumulated load of the groups' mean
+    crosses multiples of total / world (a rank whose sequences have long windows gets a few sequences
+    fewer), and inside every prefix group the sequences are dealt to the shards that cut the group largest
+    first, each to the segment whose mean load is lowest.  With balance=False: equal counts, no dealing."""
+    order = np.argsort(ids, kind="stable")
+    if not balance or world == 1:
+        return order, [shard_sequences(total, world, r)[0] for r in range(world)] + [total]
+    load = np.asarray(load, np.float64)
+    gmean = np.zeros(total)
+    for g in set(ids.tolist()):
+        gmean[ids == g] = load[ids == g].mean()
+    cum = np.concatenate([[0.0], np.cumsum(gmean[order])])
+    bounds = [0]
+    for r in range(1, world):
+        b = int(np.argmin(np.abs(cum - r * cum[-1] / world)))
+        bounds.append(min(max(b, bounds[-1] + 1), total - (world - r)))
+    bounds.append(total)
+    out = order.copy()
+    g0 = 0
+    while g0 < total:
+        g1 = g0
+        while g1 < total and ids[order[g1]] == ids[order[g0]]:
+            g1 += 1
+        cuts = sorted({g0, g1} | {b for b in bounds if g0 < b < g1})
+        segs = list(zip(cuts, cuts[1:]))
+        members = sorted(order[g0:g1].tolist(), key=lambda i: (-load[i], i))
+        fill = [[] for _ in segs]
+        sums = [0.0] * len(segs)
+        for i in members:
+            open_ = [k for k, (a, b) in enumerate(segs) if len(fill[k]) < b - a]
+            k = min(open_, key=lambda k: (sums[k] / (segs[k][1] - segs[k][0]), k))
+            fill[k].append(i)
+            sums[k] += load[i]
+        for (a, b), f in zip(segs, fill):
+            out[a:b] = f
+        g0 = g1
+    return out, bounds
 
 
 def draw_positions(rank: int):
     import synth
     if CFG["total_seqs"]:
         return _global_shard(rank)[0][:CFG["seqs"]]
-    return synth.integers(CFG["seed"], 77 + rank, CFG["pos_lo"], CFG["pos_hi"], (CFG["seqs"],)).astype(np.int64)
+    # weak scaling: every replica gets the SAME positions (the work per GPU is fixed exactly as the GPU count
+    # grows; only the random KV contents differ by rank), so the slowest rank is a slower GPU, not a longer job
+    return synth.integers(CFG["seed"], 77, CFG["pos_lo"], CFG["pos_hi"], (CFG["seqs"],)).astype(np.int64)
 
 
 def draw_prefix_ids(rank: int):
@@ -81,7 +129,7 @@ def draw_prefix_ids(rank: int):
         return _global_shard(rank)[1][:CFG["seqs"]]
     if n == 1:
         return np.zeros(CFG["seqs"], np.int64)
-    return synth.integers(CFG["seed"], 177 + rank, 0, n - 1, (CFG["seqs"],)).astype(np.int64)
+    return synth.integers(CFG["seed"], 177, 0, n - 1, (CFG["seqs"],)).astype(np.int64)
 
 
 def algorithmic_bytes_per_layer(pos_after_append: np.ndarray, prefix_ids: np.ndarray) -> float:
@@ -563,8 +611,11 @@ def run_ours(args, rank, world):
         return
     traffic, traffic_alg, traffic_source = traffic_record() if (CFG["name"] == "cfg2" and CFG["seqs"] == 64 and not args.separate
                                                                   and not args.rope) else (None, None, "no capture of this workload")
-    seqs_all = [shard_sequences(CFG["total_seqs"], world, r)[1] for r in range(world)] if CFG["total_seqs"] \
-        else [CFG["seqs"]] * world
+    if CFG["total_seqs"]:
+        bounds = strong_plan(world)[3]
+        seqs_all = [bounds[r + 1] - bounds[r] for r in range(world)]
+    else:
+        seqs_all = [CFG["seqs"]] * world
     tokens = sum(seqs_all) * args.steps
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -899,7 +950,8 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if CFG["total_seqs"]:
-        CFG["seqs"] = shard_sequences(CFG["total_seqs"], world, rank)[1]
+        bounds = strong_plan(world)[3]
+        CFG["seqs"] = bounds[rank + 1] - bounds[rank]
     if args.workload == "gather":
         if rank == 0:
             import torch

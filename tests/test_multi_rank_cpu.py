@@ -39,8 +39,35 @@ def test_two_gloo_ranks(tmp_path):
     outs.sort(key=lambda d: d["rank"])
     assert outs[0]["slow"] == outs[1]["slow"] == 15.0          # MAX over ranks, seen by every rank
     assert (outs[0]["start"], outs[0]["n"]) == (0, 257) and (outs[1]["start"], outs[1]["n"]) == (257, 256)
-    assert outs[0]["pos"] != outs[1]["pos"]                     # every replica draws its own workload
+    assert outs[0]["pos"] == outs[1]["pos"]                     # weak scaling: the same work on every replica
     assert outs[0]["by_rank"] == outs[1]["by_rank"] == [[1.0, 2.0, 3.0], [2.0, 3.0, 4.0]]
     import bench
     assert bench.aggregate_tokens_per_s([64, 64], 10, 20.0) == 64000.0
     assert [bench.shard_sequences(512, 8, r)[1] for r in range(8)] == [64] * 8
+
+
+def test_strong_scaling_shards_keep_prefix_affinity_and_balance_bytes():
+    # 512 sequences, 4 prefixes, W = 4096 dealt to 8 ranks: every sequence lands on exactly one rank, a rank
+    # holds at most two distinct prefixes, and the window tokens per rank are within 1.5 % of the mean (the
+    # plain equal-count split of the prefix-sorted order is several percent off)
+    import numpy as np
+    import bench
+    import synth
+    total, world, W = 512, 8, 4096
+    pos = synth.integers(1234, 77, 1, 16384, (total,)).astype(np.int64)
+    ids = synth.integers(1234, 177, 0, 3, (total,)).astype(np.int64)
+    load = np.minimum(pos, W)
+    spreads = {}
+    for balance in (False, True):
+        order, bounds = bench.balanced_shards(ids, load, total, world, balance=balance)
+        assert sorted(order.tolist()) == list(range(total)) and bounds[0] == 0 and bounds[-1] == total
+        per_rank = []
+        for r in range(world):
+            mine = order[bounds[r]:bounds[r + 1]]
+            assert len(mine) >= 1 and len(set(ids[mine].tolist())) <= 2
+            per_rank.append(int(load[mine].sum()))
+        spreads[balance] = max(per_rank) / (sum(per_rank) / world) - 1.0
+    assert spreads[True] < 0.015 < spreads[False]
+    for w in (1, 2, 4):
+        order, bounds = bench.balanced_shards(ids, load, total, w)
+        assert sorted(order.tolist()) == list(range(total)) and len(bounds) == w + 1
