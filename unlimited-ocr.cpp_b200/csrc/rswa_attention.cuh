@@ -10,7 +10,9 @@
 // consumes tiles with 16-byte shared loads, warp-shuffle reductions and an online softmax in the
 // exp2 domain.  A piece that covers a whole (row, head) item writes the output directly; otherwise
 // the warp leaves an un-normalised partial (max, sum, accumulator) in scratch, bumps the item's
-// arrival counter, and the last arriver merges (no warp ever waits for another).
+// arrival counter, and the last arriver merges (no warp ever waits for another).  Every tile copy
+// names an L2 eviction policy: ring tiles are read once per launch and leave L2 first, tiles of the
+// fixed region are re-read by every sequence sharing the prefix and leave last.
 //
 // The fused decode step (FUSED = true) additionally plans in shared memory from the pre-append
 // cursors, patches the freshly appended token into the tile that holds its ring slot (and writes it
@@ -100,7 +102,6 @@ struct AttnParams {
     int* d_ring_pos;
     int* done_ctas;     // weighted split: CTAs that have finished (the last one re-arms the claims), zero between launches
     int late_cta;       // overlapped launches, even split: sixteenths of a share the last CTA's warps give up (0: none)
-    int trace_half;     // instrumented builds only: which half of the timeline array this launch writes
     int* planned_ctas;  // ticket counter: CTAs that have built their plan from the pre-append cursors; wraps to zero
                         // with the last ticket of a launch (atomicInc), so nothing has to reset it
 };
@@ -306,6 +307,10 @@ struct PieceMap {
     }
 };
 
+#ifndef UOCR_MIN_PIECE_UNITS
+#define UOCR_MIN_PIECE_UNITS 1
+#endif
+constexpr int kMinPieceUnits = UOCR_MIN_PIECE_UNITS;
 constexpr int kPendMax = 4;  // per-warp list of partial segments awaiting their arrival (a piece leaves at most two)
 
 // Whether the weighted split applies to a launch: enough units that no piece can be empty (the shares
@@ -321,7 +326,9 @@ __device__ __forceinline__ PieceMap make_piece_map(long long total, int total_wa
     m.wpc = wpc;
     m.late = 0;
     m.wtot = 0;
-    m.ns = (int)min((long long)total_warps, total);
+    // Small launches: a piece is at least kMinPieceUnits units long, so that an item is not cut into more
+    // partial results than the memory system can use in parallelism.
+    m.ns = (int)min((long long)total_warps, max(1LL, total / kMinPieceUnits));
     if (late > 0 && frac == nullptr && m.ns == total_warps && m.ns > wpc && weighted_split_ok(total, total_warps)) {
         m.late = min(late, 12);
         m.wtot = 16LL * m.ns - (long long)m.late * wpc;
@@ -378,13 +385,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #endif
 #ifndef UOCR_STEADY
 #define UOCR_STEADY 2
-#endif
-#ifdef UOCR_TRACE
-__device__ unsigned long long g_trace[2 * 8 * 4096];  // two halves: consecutive (overlapping) launches alternate
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { const int tw_ = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if ((threadIdx.x & 31) == 0 && tw_ < 4096) { unsigned long long* tr_ = g_trace + (size_t)(p.trace_half & 1) * 8 * 4096; tr_[tw_ * 8 + (slot)] = gtime(); if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); tr_[tw_ * 8 + 7] = sm; } } } while (0)
-#else
-#define TRACE(slot) do {} while (0)
 #endif
 constexpr int kSteady = UOCR_STEADY < UOCR_RING ? UOCR_STEADY : UOCR_RING;
 constexpr int kRing = UOCR_RING;  // shared-memory tile slots per warp; tiles K(0) V(0) K(1) V(1) ... rotate through them
@@ -458,7 +458,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
     extern __shared__ __align__(128) uint8_t smem[];
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    TRACE(0);
 
     // ---- which share of the unit line this CTA takes -------------------------------------------------
     __shared__ int s_cta;
@@ -525,10 +524,12 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
 
     const long long total = rs[p.rows];
     const bool use_split = weighted && weighted_split_ok(total, p.total_warps);
-    TRACE(1);
     const int gw = (weighted ? s_cta : (int)blockIdx.x) * warps + warp;
     const PieceMap pm = make_piece_map(total, p.total_warps, use_split ? p.cta_frac : nullptr, warps, p.late_cta);
-    const int piece = gw < pm.ns ? gw : -1;  // this warp's piece of the unit line (-1: more warps than units)
+    // When there are fewer pieces than warps they are spread over the SMs (warp-major numbering) instead of
+    // filling the first CTAs; otherwise CTA c owns pieces c * warps .. (the late-CTA shares rely on that).
+    const int gw_spread = warp * (int)gridDim.x + (int)blockIdx.x;
+    const int piece = pm.ns == p.total_warps ? gw : (gw_spread < pm.ns ? gw_spread : -1);
     int n_units = 0;
     long long u0 = 0;
     int* pend = reinterpret_cast<int*>(smem + bar_bytes + (size_t)warps * (kRing * TILE)) + warp * kPendMax;
@@ -848,7 +849,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             publish_cursors();
             // everything up to here read only this layer's own cursors, table and pool
             dependency_sync();
-            TRACE(2);
             uint32_t cur_item = __shfl_sync(FULL, d_item, 0);
             load_q(cur_item);
             bool first_segment = true;
@@ -868,8 +868,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
             phases ^= 1u << use_slot;
             use_slot = use_slot == kRing - 1 ? 0 : use_slot + 1;
             ++consumed;
-            if (it == 0) TRACE(3);
-            if (it == n_units - 4) TRACE(6);  // four units left: the pace of the tail shows between here and the end
             if constexpr (FUSED) {
                 if (meta & kMetaPatch) {  // the new K row replaces whatever the ring slot held
                     const int off = (int)((meta >> kMetaPatchOffShift) & 15);
@@ -1105,7 +1103,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         }
 
         }
-        TRACE(4);
         publish_cursors();  // a warp without a piece gets here without having looked
         if (!gave_up) {
             flush_arrivals();
@@ -1121,7 +1118,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         }
     }
 
-    TRACE(5);
     // ---- weighted split: the last CTA to finish re-arms the claims; with the even split there is nothing to
     //      re-arm and the CTAs leave without the round trip ----
     if constexpr (FUSED) {

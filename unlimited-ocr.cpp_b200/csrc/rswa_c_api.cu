@@ -548,12 +548,6 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.planned_ctas = ws->planned_ctas;
     ap.late_cta = (c.fused && ws->overlap) ? kLateCtaSixteenths : 0;
     ap.wait_limit = ws->wait_limit;
-#ifdef UOCR_TRACE
-    static int launch_seq = 0;  // instrumented builds: consecutive (overlapping) launches alternate timeline halves
-    ap.trace_half = launch_seq++ & 1;
-#else
-    ap.trace_half = 0;
-#endif
     if (c.rope_pos) {
         ap.rope_pos = c.rope_pos;
         // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
