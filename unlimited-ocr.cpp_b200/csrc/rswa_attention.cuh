@@ -307,10 +307,6 @@ struct PieceMap {
     }
 };
 
-#ifndef UOCR_MIN_PIECE_UNITS
-#define UOCR_MIN_PIECE_UNITS 1
-#endif
-constexpr int kMinPieceUnits = UOCR_MIN_PIECE_UNITS;
 constexpr int kPendMax = 4;  // per-warp list of partial segments awaiting their arrival (a piece leaves at most two)
 
 // Whether the weighted split applies to a launch: enough units that no piece can be empty (the shares
@@ -326,9 +322,7 @@ __device__ __forceinline__ PieceMap make_piece_map(long long total, int total_wa
     m.wpc = wpc;
     m.late = 0;
     m.wtot = 0;
-    // Small launches: a piece is at least kMinPieceUnits units long, so that an item is not cut into more
-    // partial results than the memory system can use in parallelism.
-    m.ns = (int)min((long long)total_warps, max(1LL, total / kMinPieceUnits));
+    m.ns = (int)min((long long)total_warps, total);
     if (late > 0 && frac == nullptr && m.ns == total_warps && m.ns > wpc && weighted_split_ok(total, total_warps)) {
         m.late = min(late, 12);
         m.wtot = 16LL * m.ns - (long long)m.late * wpc;
