@@ -670,6 +670,41 @@ static void test_decoder_kv_adapter_waves_and_step_graphs() {
     cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dctx); cudaFree(gk); cudaFree(gv); cudaFree(d_ident);
 }
 
+// ---- a packed prefill larger than the attention scratch is served in chunks -------------------------------------
+static void test_large_ragged_prefill_is_chunked() {
+    std::printf("cuda::GpuDecoderKV: ragged prefill of 4300 rows (scratch holds 4096 per call)\n");
+    const int L = 1, kvh = 1, hd = 32, W = 16, heads = 2, row = kvh * hd, qrow = heads * hd;
+    const int total = 4300;
+    cuda::GpuDecoderKV dec(L, kvh, hd, W, DType::BF16);
+    dec.batch_configure(2, total + W);
+    cudaStream_t st;
+    cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    EXPECT(dec.batch_prefill_begin({0, 4000}, {4000, 300}, {1, 0}, {}, st) == total);
+    auto round = [](std::vector<float> v) { for (auto& x : v) x = bf16_to_f32(f32_to_bf16(x)); return v; };
+    auto q = rvec((size_t)total * qrow), k = round(rvec((size_t)total * row)), v = round(rvec((size_t)total * row));
+    float *dq = dev(q), *dk = dev(k), *dv = dev(v), *dctx;
+    cudaMalloc(&dctx, (size_t)total * qrow * 4);
+    cudaMemset(dctx, 0xff, (size_t)total * qrow * 4);
+    dec.attention_block_ragged(0, dq, dk, dv, dctx, total, heads, st);
+    cudaStreamSynchronize(st);
+    auto got = host(dctx, (size_t)total * qrow);
+    float worst = 0.f;
+    const int starts[2] = {0, 4000}, lens[2] = {4000, 300};
+    for (int r = 0; r < 2; ++r) {
+        orc_cache* c = orc_cache_create(L, kvh, hd, W);
+        orc_cache_reset(c, lens[r]);
+        orc_cache_write_prefill(c, 0, k.data() + (size_t)starts[r] * row, v.data() + (size_t)starts[r] * row, lens[r]);
+        std::vector<float> want((size_t)lens[r] * qrow);
+        orc_cache_attention(c, 0, q.data() + (size_t)starts[r] * qrow, lens[r], 0, want.data(), heads, 1);
+        worst = std::max(worst, max_abs_diff(want, got.data() + (size_t)starts[r] * qrow));
+        orc_cache_destroy(c);
+    }
+    EXPECT(worst < 2e-5f);
+    EXPECT(dec.kv().device_status(st) == 0);
+    cudaStreamDestroy(st);
+    cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dctx);
+}
+
 int main() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -686,6 +721,7 @@ int main() {
         test_gpu_cache_graph_replay();
         test_free_functions_capture_and_scratch_rules();
         test_decoder_kv_adapter_waves_and_step_graphs();
+        test_large_ragged_prefill_is_chunked();
     } catch (const std::exception& e) {
         std::printf("  EXCEPTION: %s\n", e.what());
         ++g_fail;

@@ -1415,9 +1415,12 @@ void PagedBatchKV::export_snapshot(const std::string& dir, int slot, const std::
 void PagedBatchKV::attention_ragged(int layer, const float* q, const int* d_row_slots, const int* d_pos, int total,
                                     int heads, float* out, cudaStream_t stream) {
     Impl& s = *p_;
-    UOCR_CHECK(total <= 4096 || total <= s.cfg.slots, "attention_ragged: more packed rows than the workspace holds (4096)");
-    abi_ok(uocr_b200_rswa_attention_ragged_paged(&s.view[layer], q, s.d_prefill, d_row_slots, d_pos, total, heads, out,
-                                                 s.ws, stream), "attention_ragged");
+    const std::size_t qrow = static_cast<std::size_t>(heads) * s.cfg.head_dim;
+    for (int a = 0; a < total; a += s.ws_rows) {  // the split-KV scratch holds ws_rows query rows per call; rows are independent
+        const int n = std::min(s.ws_rows, total - a);
+        abi_ok(uocr_b200_rswa_attention_ragged_paged(&s.view[layer], q + a * qrow, s.d_prefill, d_row_slots + a, d_pos + a, n,
+                                                     heads, out + a * qrow, s.ws, stream), "attention_ragged");
+    }
 }
 void PagedBatchKV::gather(int layer, const int* d_slots, int n, float* out_k, float* out_v, cudaStream_t stream) {
     Impl& s = *p_;
