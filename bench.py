@@ -645,6 +645,7 @@ def run_ours(args, rank, world):
                      "step_gbs": bytes_layer * CFG["layers"] / (ms / args.steps * 1e-3) / 1e9},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps, "ms_per_step_min": min(e2e_rep) / args.steps,
+                "per_rank_ms": [statistics.median(r) / args.steps for r in e2e_by_rank],
                 "ms_per_step_max": max(e2e_rep) / args.steps,
                 "how": "per step: q/k/v of all layers from pinned host memory in %s host-to-device copies behind the "
                        "kernels, results %s, host synchronises after every step"
