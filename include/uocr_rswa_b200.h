@@ -179,6 +179,19 @@ UOCR_B200_API int uocr_b200_rswa_append_decode_batch_paged(
     const int* d_prefill_len, const int* d_slots, int batch, int window,
     uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
+/* The paged append above for ALL layers of a step in one launch.  No single reference call does this:
+ * the reference appends inside its layer loop (src/engine/gpu_decoder.cu:990-993), where the K/V rows
+ * of layer l+1 do not exist before layer l is done; in a decoder the append is part of the fused step
+ * below.  This form is for callers that hold the rows of every layer at once -- importing a cache,
+ * replaying a trace, the block-manager churn workload -- for whom `layers` launches of a few megabytes
+ * each are bound by launch latency.  kv_layers[0..layers) describe pools of one geometry behind one
+ * block table (1..32 layers per call); layer l reads its rows at k / v + l * kv_layer_stride (floats) and
+ * its cursors at d_len / d_ring_pos + l * cursor_layer_stride (ints).  Same result as `layers` calls. */
+UOCR_B200_API int uocr_b200_rswa_append_decode_batch_paged_layers(
+    const uocr_b200_paged_kv* kv_layers, int layers, const float* k, const float* v, long long kv_layer_stride,
+    int* d_len, int* d_ring_pos, long long cursor_layer_stride, const int* d_prefill_len, const int* d_slots,
+    int batch, int window, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+
 /* ================================================================================================
  * Prefill scatter
  * ============================================================================================= */
@@ -397,6 +410,15 @@ UOCR_B200_API int uocr_b200_rswa_gather_paged(
     const uocr_b200_paged_kv* kv, const int* d_len, const int* d_prefill_len, const int* d_slots,
     int n, int capacity_rows, void* out_k, void* out_v, int out_dtype, uocr_b200_workspace* ws,
     uocr_b200_stream_t stream);
+
+/* uocr_b200_rswa_gather_paged for ALL layers in one launch (no reference counterpart; same reason as the
+ * all-layer append: retiring one sequence is `layers` launches of 10-25 MB otherwise).  Layer l reads its
+ * cursors at d_len + l * cursor_layer_stride (ints) and writes its views at
+ * out_k / out_v + l * out_layer_stride_bytes.  Same result as `layers` calls. */
+UOCR_B200_API int uocr_b200_rswa_gather_paged_layers(
+    const uocr_b200_paged_kv* kv_layers, int layers, const int* d_len, long long cursor_layer_stride,
+    const int* d_prefill_len, const int* d_slots, int n, int capacity_rows, void* out_k, void* out_v,
+    long long out_layer_stride_bytes, int out_dtype, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
 
 /* The same view in the layout of the reference's cache snapshots (tools/reference/export_reference.py:
  * 110-117, read back by tools/compare_reference.cpp:219-241): fp32 out[i][kv_head][s][head_dim], rows

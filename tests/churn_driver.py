@@ -34,6 +34,7 @@ class ChurnConfig:
         self.seed = 1234
         self.sample_every = 0      # value-check every n-th request against an oracle cache (0 = off)
         self.gather_on_finish = True
+        self.all_layer_launches = False  # append / gather of every layer in one launch instead of one per layer
         self.__dict__.update(kw)
 
 
@@ -81,6 +82,9 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False, device=Tr
         v_in = torch.randn((L, cfg.slots, row), device="cuda")
         gk = torch.empty((1, cap, row), dtype=torch.bfloat16, device="cuda")
         gv = torch.empty_like(gk)
+        if cfg.all_layer_launches:
+            gk_all = torch.empty((L, 1, cap, row), dtype=torch.bfloat16, device="cuda")
+            gv_all = torch.empty_like(gk_all)
     stats = dict(steps=0, append_rows=0, append_ms=0.0, gather_tokens=0, gather_ms=0.0, peak_running=0,
                  prefix_hits=0, prefix_misses=0)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if device else []
@@ -144,8 +148,11 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False, device=Tr
             n = len(run_ids)
             if time_kernels:
                 ev[0].record()
-            for l in range(L):
-                b.append_decode_batch_paged(layers[l], k_in[l], v_in[l], d_len[l], d_ring[l], d_prefill, rows, n, W, ws)
+            if cfg.all_layer_launches:  # one launch for the append of every layer
+                b.append_decode_batch_paged_layers(layers, k_in, v_in, d_len, d_ring, d_prefill, rows, n, W, ws)
+            else:
+                for l in range(L):
+                    b.append_decode_batch_paged(layers[l], k_in[l], v_in[l], d_len[l], d_ring[l], d_prefill, rows, n, W, ws)
             if time_kernels:
                 ev[1].record()
                 ev[1].synchronize()
@@ -176,7 +183,9 @@ def run(cfg, impl, check=None, oracle_caches=None, time_kernels=False, device=Tr
                 sl = torch.tensor([slot], dtype=torch.int32, device="cuda")
                 if time_kernels:
                     ev[2].record()
-                for l in range(L if (time_kernels or i in sampled) else 1):
+                if cfg.all_layer_launches and i not in sampled:
+                    b.gather_paged_layers(layers, d_len, d_prefill, sl, 1, cap, gk_all, gv_all, b.BF16, ws)
+                for l in range(0 if (cfg.all_layer_launches and i not in sampled) else (L if (time_kernels or i in sampled) else 1)):
                     b.gather_paged(layers[l], d_len[l], d_prefill, sl, 1, cap, gk, gv, b.BF16, ws)
                     if i in sampled:
                         c = sampled[i]

@@ -548,3 +548,47 @@ def test_wait_that_runs_out_is_reported_and_the_workspace_recovers(orc, b):
     assert_attention_close(got, want, *TIGHT)
     pb.check_logical_view(0)
     assert pb.ws.status() == 0
+
+
+@pytest.mark.parametrize("dtype_name", ["bf16", "f32"])
+def test_all_layer_append_and_gather_equal_the_per_layer_calls(orc, b, dtype_name):
+    # one launch for every layer of an append step / of a gather: same cursors, same pool contents, same
+    # views as one call per layer, and as the oracle; steps alternate between the two forms, rows permuted,
+    # one slot lagging, across the ring wrap
+    import torch
+    dtype = b.BF16 if dtype_name == "bf16" else b.F32
+    slots, L, W, kvh, hd = 5, 3, 32, 2, 32
+    P = [21, 21, 7, 0, 16]
+    pb = PagedBatch(orc, slots, L, kvh, hd, W, dtype, P, prefix_keys=["a", "a", "b", "c", "d"], seed=314)
+    pb.write_prefixes()
+    for t in range(2 * W + 5):
+        rows = [3, 0, 4, 1, 2] if t % 3 else [0, 1, 2, 4]
+        kv = [pb.step_inputs(t, l, rows) for l in range(L)]
+        if t % 2:
+            k = torch.from_numpy(np.stack([x[0] for x in kv])).cuda()
+            v = torch.from_numpy(np.stack([x[1] for x in kv])).cuda()
+            ds = torch.tensor(rows, dtype=torch.int32, device="cuda")
+            b.append_decode_batch_paged_layers(pb.layer, k, v, pb.d_len, pb.d_ring, pb.d_prefill, ds, len(rows), W, pb.ws)
+            for l in range(L):
+                for i, s in enumerate(rows):
+                    pb.cache[s].append_decode(l, kv[l][0][i], kv[l][1][i])
+        else:
+            for l in range(L):
+                pb.append(l, kv[l][0], kv[l][1], rows)
+    for l in range(L):
+        pb.check_logical_view(l)
+    cap = max(P) + W
+    ds = torch.tensor([4, 2, 0], dtype=torch.int32, device="cuda")
+    for out_dtype, tdt in ((b.F32, torch.float32), (dtype, torch.bfloat16 if dtype == b.BF16 else torch.float32)):
+        ak = torch.full((L, 3, cap, pb.row), float("nan"), dtype=tdt, device="cuda")
+        av = torch.full_like(ak, float("nan"))
+        b.gather_paged_layers(pb.layer, pb.d_len, pb.d_prefill, ds, 3, cap, ak, av, out_dtype, pb.ws)
+        for l in range(L):
+            ok = torch.full((3, cap, pb.row), float("nan"), dtype=tdt, device="cuda")
+            ov = torch.full_like(ok, float("nan"))
+            b.gather_paged(pb.layer[l], pb.d_len[l], pb.d_prefill, ds, 3, cap, ok, ov, out_dtype, pb.ws)
+            assert torch.equal(ak[l], ok) and torch.equal(av[l], ov)
+    with pytest.raises(b.Error):  # layers behind different block tables cannot share a launch
+        other = b.PagedLayer(pb.num_blocks, kvh, hd, dtype, pb.table.clone())
+        b.gather_paged_layers([pb.layer[0], other], pb.d_len, pb.d_prefill, ds, 3, cap, ak, av, b.F32, pb.ws)
+    assert pb.ws.status() == 0

@@ -79,6 +79,10 @@ _SIGS = {
     "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
     "uocr_b200_rswa_append_decode_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "uocr_b200_rswa_append_decode_batch_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 6 + [_i, _i, _vp, _vp]),
+    "uocr_b200_rswa_append_decode_batch_paged_layers": (_i, [_vp, _i, _vp, _vp, C.c_longlong, _vp, _vp, C.c_longlong, _vp, _vp,
+                                                              _i, _i, _vp, _vp]),
+    "uocr_b200_rswa_gather_paged_layers": (_i, [_vp, _i, _vp, C.c_longlong, _vp, _vp, _i, _i, _vp, _vp, C.c_longlong, _i,
+                                                 _vp, _vp]),
     "uocr_b200_rswa_write_prefill_ragged_f32": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
     "uocr_b200_rswa_write_prefill_ragged_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [_i, _vp, _vp]),
     "uocr_b200_rswa_publish_slots": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp]),
@@ -268,6 +272,28 @@ def append_decode_batch_paged(layer, k, v, d_len, d_ring, d_prefill, d_slots, ba
     check(lib().uocr_b200_rswa_append_decode_batch_paged(layer.ref(), _p(k), _p(v), _p(d_len), _p(d_ring),
                                                           _p(d_prefill), _p(d_slots), batch, window,
                                                           ws.h if ws else None, stream_handle(stream)))
+
+
+def layer_array(layers):
+    """Contiguous array of uocr_b200_paged_kv for the entry points that take several layers at once."""
+    arr = (PagedKV * len(layers))()
+    for i, lay in enumerate(layers):
+        arr[i] = lay.desc
+    return arr
+
+
+def append_decode_batch_paged_layers(layers, k, v, d_len, d_ring, d_prefill, d_slots, batch, window, ws=None, stream=None):
+    """All layers of an append step in one launch: k, v are [L][rows >= batch][row], d_len / d_ring [L][slots]."""
+    check(lib().uocr_b200_rswa_append_decode_batch_paged_layers(
+        layer_array(layers), len(layers), _p(k), _p(v), k.stride(0), _p(d_len), _p(d_ring), d_len.stride(0), _p(d_prefill),
+        _p(d_slots), batch, window, ws.h if ws else None, stream_handle(stream)))
+
+
+def gather_paged_layers(layers, d_len, d_prefill, d_slots, n, capacity_rows, out_k, out_v, out_dtype, ws=None, stream=None):
+    """All layers of a gather in one launch: out_k, out_v are [L][n][capacity_rows][row], d_len [L][slots]."""
+    check(lib().uocr_b200_rswa_gather_paged_layers(
+        layer_array(layers), len(layers), _p(d_len), d_len.stride(0), _p(d_prefill), _p(d_slots), n, capacity_rows,
+        _p(out_k), _p(out_v), out_k.stride(0) * out_k.element_size(), out_dtype, ws.h if ws else None, stream_handle(stream)))
 
 
 def attention_batch_paged(layer, q, d_len, d_prefill, d_slots, batch, heads, out, ws, stream=None):

@@ -669,6 +669,71 @@ int uocr_b200_rswa_append_decode_batch_paged(const uocr_b200_paged_kv* kv, const
     return after_launch("append (paged)");
 }
 
+// Checks that `layers` views describe pools of one geometry behind one block table and collects the pools.
+static int collect_layers(const uocr_b200_paged_kv* kv, int layers, PagedView* pv, LayerPools* pools, const char* who) {
+    if (!kv || layers <= 0 || layers > kMaxLayersPerLaunch)
+        return fail(UOCR_B200_ERR_INVALID, std::string(who) + ": 1..32 layers per call");
+    if (int rc = paged_view(&kv[0], pv)) return rc;
+    for (int l = 0; l < layers; ++l) {
+        PagedView one;
+        if (int rc = paged_view(&kv[l], &one)) return rc;
+        if (kv[l].dtype != kv[0].dtype || one.table != pv->table || one.table_stride != pv->table_stride ||
+            one.num_blocks != pv->num_blocks || one.kv_heads != pv->kv_heads || one.head_dim != pv->head_dim)
+            return fail(UOCR_B200_ERR_INVALID, std::string(who) + ": the layers must share block table, geometry and dtype");
+        pools->k[l] = one.k_pool;
+        pools->v[l] = one.v_pool;
+    }
+    return UOCR_B200_OK;
+}
+
+int uocr_b200_rswa_append_decode_batch_paged_layers(const uocr_b200_paged_kv* kv_layers, int layers, const float* k,
+                                                    const float* v, long long kv_layer_stride, int* d_len, int* d_ring_pos,
+                                                    long long cursor_layer_stride, const int* d_prefill_len,
+                                                    const int* d_slots, int batch, int window, uocr_b200_workspace* ws,
+                                                    uocr_b200_stream_t stream) {
+    if (batch <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    LayerPools pools{};
+    if (int rc = collect_layers(kv_layers, layers, &pv, &pools, "append_decode_batch_paged_layers")) return rc;
+    if (!k || !v || !d_len || !d_ring_pos || !d_prefill_len || !d_slots) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_paged_layers: null pointer");
+    if (!aligned16(k) || !aligned16(v) || (kv_layer_stride & 3)) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_paged_layers: k/v and the layer stride must be 16-byte aligned");
+    if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "append_decode_batch_paged_layers: window must be positive");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    const dim3 grid(batch, 1, layers);
+    if (kv_layers[0].dtype == UOCR_B200_BF16)
+        rswa_append_paged_layers_kernel<BF16><<<grid, 256, 0, st>>>(pv, pools, k, v, kv_layer_stride, d_len, d_ring_pos, cursor_layer_stride, d_prefill_len, d_slots, window, status);
+    else
+        rswa_append_paged_layers_kernel<F32><<<grid, 256, 0, st>>>(pv, pools, k, v, kv_layer_stride, d_len, d_ring_pos, cursor_layer_stride, d_prefill_len, d_slots, window, status);
+    return after_launch("append (paged, all layers)");
+}
+
+int uocr_b200_rswa_gather_paged_layers(const uocr_b200_paged_kv* kv_layers, int layers, const int* d_len,
+                                       long long cursor_layer_stride, const int* d_prefill_len, const int* d_slots, int n,
+                                       int capacity_rows, void* out_k, void* out_v, long long out_layer_stride_bytes,
+                                       int out_dtype, uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    if (n <= 0 || capacity_rows <= 0) return UOCR_B200_OK;
+    PagedView pv;
+    LayerPools pools{};
+    if (int rc = collect_layers(kv_layers, layers, &pv, &pools, "gather_paged_layers")) return rc;
+    if (!d_len || !d_prefill_len || !d_slots || !out_k || !out_v) return fail(UOCR_B200_ERR_INVALID, "gather_paged_layers: null pointer");
+    if (!aligned16(out_k) || !aligned16(out_v) || (out_layer_stride_bytes & 15)) return fail(UOCR_B200_ERR_INVALID, "gather_paged_layers: outputs and the layer stride must be 16-byte aligned");
+    const int dtype = kv_layers[0].dtype;
+    if (out_dtype != UOCR_B200_F32 && out_dtype != dtype) return fail(UOCR_B200_ERR_UNSUPPORTED, "gather_paged_layers: out_dtype must be fp32 or the pool dtype");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int* status = ws ? ws->status : nullptr;
+    const dim3 grid(capacity_rows, n, layers);
+    uint8_t* ok = static_cast<uint8_t*>(out_k);
+    uint8_t* ov = static_cast<uint8_t*>(out_v);
+    if (dtype == UOCR_B200_BF16 && out_dtype == UOCR_B200_F32)
+        rswa_gather_paged_layers_kernel<BF16, true><<<grid, 160, 0, st>>>(pv, pools, d_len, cursor_layer_stride, d_prefill_len, d_slots, capacity_rows, ok, ov, out_layer_stride_bytes, status);
+    else if (dtype == UOCR_B200_BF16)
+        rswa_gather_paged_layers_kernel<BF16, false><<<grid, 160, 0, st>>>(pv, pools, d_len, cursor_layer_stride, d_prefill_len, d_slots, capacity_rows, ok, ov, out_layer_stride_bytes, status);
+    else
+        rswa_gather_paged_layers_kernel<F32, false><<<grid, 160, 0, st>>>(pv, pools, d_len, cursor_layer_stride, d_prefill_len, d_slots, capacity_rows, ok, ov, out_layer_stride_bytes, status);
+    return after_launch("gather (paged, all layers)");
+}
+
 // ---- prefill scatter --------------------------------------------------------------------------------
 int uocr_b200_rswa_write_prefill_ragged_f32(const float* k, const float* v, float* kbase, float* vbase,
                                             const int* d_slots, const int* d_pos, int total, int batch_cap,

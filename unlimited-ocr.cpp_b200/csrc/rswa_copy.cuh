@@ -128,11 +128,18 @@ __device__ __forceinline__ void store_row_paged(const PagedView& pv, int blk, in
     }
 }
 
+// Pools of several layers for the kernels that serve all layers of a step in one launch (blockIdx.z = layer).
+constexpr int kMaxLayersPerLaunch = 32;
+struct LayerPools {
+    uint8_t* k[kMaxLayersPerLaunch];
+    uint8_t* v[kMaxLayersPerLaunch];
+};
+
 template <typename KV>
-__global__ void __launch_bounds__(256) rswa_append_paged_kernel(
-    PagedView pv, const float* __restrict__ k, const float* __restrict__ v, int* __restrict__ d_len,
-    int* __restrict__ d_ring_pos, const int* __restrict__ d_prefill_len,
-    const int* __restrict__ d_slots, int window, int* __restrict__ status) {
+__device__ __forceinline__ void append_paged_row(const PagedView& pv, const float* __restrict__ k, const float* __restrict__ v,
+                                                 int* __restrict__ d_len, int* __restrict__ d_ring_pos,
+                                                 const int* __restrict__ d_prefill_len, const int* __restrict__ d_slots,
+                                                 int window, int* __restrict__ status) {
     __shared__ int s_blk, s_off;
     const int b = blockIdx.x;
     if (threadIdx.x == 0) {
@@ -155,6 +162,28 @@ __global__ void __launch_bounds__(256) rswa_append_paged_kernel(
     if (s_blk < 0) return;
     const size_t src = (size_t)b * pv.kv_heads * pv.head_dim;
     store_row_paged<KV>(pv, s_blk, s_off, k + src, v + src);
+}
+
+template <typename KV>
+__global__ void __launch_bounds__(256) rswa_append_paged_kernel(
+    PagedView pv, const float* __restrict__ k, const float* __restrict__ v, int* __restrict__ d_len,
+    int* __restrict__ d_ring_pos, const int* __restrict__ d_prefill_len,
+    const int* __restrict__ d_slots, int window, int* __restrict__ status) {
+    append_paged_row<KV>(pv, k, v, d_len, d_ring_pos, d_prefill_len, d_slots, window, status);
+}
+
+// The same append for every layer of a step in one launch: grid (batch, 1, layers); layer z reads its rows
+// at k / v + z * kv_layer_stride and its cursors at d_len / d_ring_pos + z * cursor_layer_stride.
+template <typename KV>
+__global__ void __launch_bounds__(256) rswa_append_paged_layers_kernel(
+    PagedView pv, const LayerPools pools, const float* __restrict__ k, const float* __restrict__ v,
+    long long kv_layer_stride, int* __restrict__ d_len, int* __restrict__ d_ring_pos, long long cursor_layer_stride,
+    const int* __restrict__ d_prefill_len, const int* __restrict__ d_slots, int window, int* __restrict__ status) {
+    const int z = blockIdx.z;
+    pv.k_pool = pools.k[z];
+    pv.v_pool = pools.v[z];
+    append_paged_row<KV>(pv, k + z * kv_layer_stride, v + z * kv_layer_stride, d_len + z * cursor_layer_stride,
+                         d_ring_pos + z * cursor_layer_stride, d_prefill_len, d_slots, window, status);
 }
 
 template <typename KV>
@@ -320,11 +349,11 @@ __global__ void __launch_bounds__(160) rswa_scatter_text_fill_kernel(
 // Gather: logical row s of slot d_slots[i] -> out[i][s][:]; rows >= len are zero-filled.
 // HEAD_MAJOR: out[i][head][s][:] instead (the layout of the reference's exported cache snapshots).
 // grid = (capacity_rows, n); one thread per 16-byte pool chunk.
-template <typename KV, bool WIDEN, bool HEAD_MAJOR = false>
-__global__ void __launch_bounds__(256) rswa_gather_paged_kernel(
-    PagedView pv, const int* __restrict__ d_len, const int* __restrict__ d_prefill_len,
-    const int* __restrict__ d_slots, int capacity_rows, uint8_t* __restrict__ out_k,
-    uint8_t* __restrict__ out_v, int* __restrict__ status) {
+template <typename KV, bool WIDEN, bool HEAD_MAJOR>
+__device__ __forceinline__ void gather_paged_row(const PagedView& pv, const int* __restrict__ d_len,
+                                                 const int* __restrict__ d_prefill_len, const int* __restrict__ d_slots,
+                                                 int capacity_rows, uint8_t* __restrict__ out_k, uint8_t* __restrict__ out_v,
+                                                 int* __restrict__ status) {
     constexpr int EPC = KV::kPerChunk;
     constexpr int OUT_B = WIDEN ? 4 : KV::kBytes;
     const int s = blockIdx.x, i = blockIdx.y;
@@ -373,6 +402,28 @@ __global__ void __launch_bounds__(256) rswa_gather_paged_kernel(
             *reinterpret_cast<uint4*>(out_v + dst) = vw;
         }
     }
+}
+
+template <typename KV, bool WIDEN, bool HEAD_MAJOR = false>
+__global__ void __launch_bounds__(256) rswa_gather_paged_kernel(
+    PagedView pv, const int* __restrict__ d_len, const int* __restrict__ d_prefill_len,
+    const int* __restrict__ d_slots, int capacity_rows, uint8_t* __restrict__ out_k,
+    uint8_t* __restrict__ out_v, int* __restrict__ status) {
+    gather_paged_row<KV, WIDEN, HEAD_MAJOR>(pv, d_len, d_prefill_len, d_slots, capacity_rows, out_k, out_v, status);
+}
+
+// The same gather for every layer in one launch: grid (capacity_rows, n, layers); layer z reads its cursors at
+// d_len + z * cursor_layer_stride and writes its views at out_k / out_v + z * out_layer_stride_bytes.
+template <typename KV, bool WIDEN>
+__global__ void __launch_bounds__(256) rswa_gather_paged_layers_kernel(
+    PagedView pv, const LayerPools pools, const int* __restrict__ d_len, long long cursor_layer_stride,
+    const int* __restrict__ d_prefill_len, const int* __restrict__ d_slots, int capacity_rows,
+    uint8_t* __restrict__ out_k, uint8_t* __restrict__ out_v, long long out_layer_stride_bytes, int* __restrict__ status) {
+    const int z = blockIdx.z;
+    pv.k_pool = pools.k[z];
+    pv.v_pool = pools.v[z];
+    gather_paged_row<KV, WIDEN, false>(pv, d_len + z * cursor_layer_stride, d_prefill_len, d_slots, capacity_rows,
+                                       out_k + z * out_layer_stride_bytes, out_v + z * out_layer_stride_bytes, status);
 }
 
 }  // namespace uocr_b200
