@@ -592,3 +592,37 @@ def test_all_layer_append_and_gather_equal_the_per_layer_calls(orc, b, dtype_nam
         other = b.PagedLayer(pb.num_blocks, kvh, hd, dtype, pb.table.clone())
         b.gather_paged_layers([pb.layer[0], other], pb.d_len, pb.d_prefill, ds, 3, cap, ak, av, b.F32, pb.ws)
     assert pb.ws.status() == 0
+
+
+def test_stream_read_rate_and_slot_publication(orc, b):
+    # the library's own read-only streaming measurement returns a plausible HBM rate, and the packed slot
+    # publication writes exactly the rows and cursors its records name (and flags a slot out of range)
+    import ctypes as C
+    import torch
+    ws = b.Workspace(64)
+    gbs = ws.stream_read_gbs()
+    assert 1000.0 < gbs < 20000.0
+    slots, layers, stride = 6, 3, 5
+    table = torch.full((slots, stride), 7, dtype=torch.int32, device="cuda")
+    d_len = torch.full((layers, slots), 9, dtype=torch.int32, device="cuda")
+    d_ring = torch.full((layers, slots), 9, dtype=torch.int32, device="cuda")
+    d_prefill = torch.full((slots,), 9, dtype=torch.int32, device="cuda")
+    rec = np.array([[4, 33, 1, 10, 11, 12, -1, -1],     # slot 4: length 33, row written
+                    [1, 5, 0, 99, 99, 99, 99, 99],       # slot 1: cursors only, row untouched
+                    [2, 0, 1, -1, -1, -1, -1, -1]],      # slot 2: retired
+                   dtype=np.int32)
+    d_rec = torch.from_numpy(rec).cuda()
+    b.check(b.lib().uocr_b200_rswa_publish_slots(d_rec.data_ptr(), 3, table.data_ptr(), stride, d_len.data_ptr(),
+                                                 d_ring.data_ptr(), d_prefill.data_ptr(), slots, layers, ws.h,
+                                                 b.stream_handle()))
+    t, ln, rg, pf = (x.cpu().numpy() for x in (table, d_len, d_ring, d_prefill))
+    assert t[4].tolist() == [10, 11, 12, -1, -1] and t[1].tolist() == [7] * 5 and t[2].tolist() == [-1] * 5
+    assert (ln[:, 4] == 33).all() and (ln[:, 1] == 5).all() and (ln[:, 2] == 0).all() and (ln[:, [0, 3, 5]] == 9).all()
+    assert (rg[:, [4, 1, 2]] == 0).all() and (rg[:, [0, 3, 5]] == 9).all()
+    assert pf.tolist() == [9, 5, 0, 9, 33, 9]
+    assert ws.status() == 0
+    bad = torch.tensor([[slots, 1, 0, 0, 0, 0, 0, 0]], dtype=torch.int32, device="cuda")
+    b.check(b.lib().uocr_b200_rswa_publish_slots(bad.data_ptr(), 1, table.data_ptr(), stride, d_len.data_ptr(),
+                                                 d_ring.data_ptr(), d_prefill.data_ptr(), slots, layers, ws.h,
+                                                 b.stream_handle()))
+    assert ws.status() & b.STATUS_BAD_SLOT
