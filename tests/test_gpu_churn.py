@@ -21,8 +21,8 @@ def small_cfg(**kw):
     return churn_driver.ChurnConfig(**base)
 
 
-@pytest.mark.parametrize("checker", ["orc", "ref"])
-def test_churn_tables_bit_exact(orc, checker):
+@pytest.mark.parametrize("checker,all_layers", [("orc", False), ("ref", False), ("orc", True)])
+def test_churn_tables_bit_exact(orc, checker, all_layers):
     import torch
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
@@ -31,7 +31,7 @@ def test_churn_tables_bit_exact(orc, checker):
     b = load_b200()
     host = b.host_classes()
     chk = oracle.load(checker)
-    cfg = small_cfg()
+    cfg = small_cfg(all_layer_launches=all_layers)  # appends (and unsampled gathers) of every layer in one launch
     res = churn_driver.run(cfg, host, check=chk, oracle_caches=orc)
     assert res["mismatches"] == 0
     assert len(res["rows"]) == cfg.requests
