@@ -1444,13 +1444,12 @@ struct GpuDecoderKV::Impl {
     int slots = 0, capacity = 0;
     int* d_batch_slots = nullptr;  // [slots] row -> slot of the current decode batch
     int* d_positions = nullptr;    // [slots] positions of the current decode batch (rotary step only)
-    int* d_row_slot = nullptr;     // ragged prefill: packed row -> slot
-    int* d_row_pos = nullptr;      // ragged prefill: packed row -> position inside its request
-    int ragged_cap = 0;
+    int* d_row_slot = nullptr;     // ragged prefill: [packed row -> slot][packed row -> position inside its request]
+    int ragged_cap = 0;            // packed rows the array above holds (it is 2 * ragged_cap ints long)
     unsigned long long anon = 0;   // requests without a doc_key get a key of their own
 
     void free_index_arrays() {
-        for (int** p : {&d_batch_slots, &d_positions, &d_row_slot, &d_row_pos}) {
+        for (int** p : {&d_batch_slots, &d_positions, &d_row_slot}) {
             if (*p) cudaFree(*p);
             *p = nullptr;
         }
@@ -1529,7 +1528,6 @@ int GpuDecoderKV::batch_prefill_begin(const std::vector<int>& starts, const std:
         cuda_ok(cudaMalloc(&s.d_row_slot, sizeof(int) * 2 * static_cast<std::size_t>(total)), "ragged row index");
         s.ragged_cap = total;
     }
-    s.d_row_pos = nullptr;
     // pageable source: the copy has staged `idx` when the call returns
     cuda_ok(cudaMemcpyAsync(s.d_row_slot, idx.data(), sizeof(int) * idx.size(), cudaMemcpyHostToDevice, stream), "ragged index H2D");
     return total;
