@@ -264,7 +264,7 @@ class ClockSampler:
 class DecodeWorkload:
     """Device state of the cfg2 workload on the current GPU, driven through the C ABI."""
 
-    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True, weighted: bool = False,
+    def __init__(self, pkg, rank: int, fused: bool = True, overlap: bool = True,
                  rope: bool = False):
         self.rope = rope
         import torch
@@ -309,8 +309,6 @@ class DecodeWorkload:
         self.out = torch.zeros((L, B, self.row), device="cuda")
         self.ws = pkg.Workspace(B)
         self.ws.set_overlap(overlap)  # consecutive launches belong to different layers: overlap is safe
-        if weighted:
-            self.ws.calibrate(True)  # per-SM shares from a measured streaming rate instead of an even split
         self.graph = None
         self.launches_per_step = 0
         self.steps_done = 0
@@ -503,7 +501,7 @@ def run_ours(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     ranks = Ranks(rank, world, "nccl", torch.device("cuda", local))
-    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap, weighted=args.weighted,
+    wl = DecodeWorkload(pkg, rank, fused=not args.separate, overlap=not args.no_overlap,
                         rope=args.rope)
     wl.capture()
     for _ in range(max(args.warmup - 1, 0)):
@@ -937,7 +935,6 @@ def main():
                          "churn: block-manager churn on a 65536-block pool (append + gather GB/s)")
     ap.add_argument("--rope", action="store_true",
                     help="fused step with the rotary embedding folded in (q, k un-rotated; one position per row)")
-    ap.add_argument("--weighted", action="store_true", help="SM-weighted split (calibrates per-SM streaming rates first)")
     ap.add_argument("--e2e-out", default="mapped", choices=["copy", "mapped"],
                     help="end-to-end step: results return by one device-to-host copy per layer, or the kernels "
                          "store them straight into the pinned host buffer")

@@ -111,24 +111,6 @@ UOCR_B200_API int uocr_b200_workspace_set_wait_limit(uocr_b200_workspace* ws, un
  * 13/16 of an even share.  Results do not depend on how the work is cut. */
 UOCR_B200_API int uocr_b200_workspace_set_overlap(uocr_b200_workspace* ws, int enabled);
 
-/* Opt-in SM-weighted split for the attention kernels that use this workspace (no reference
- * counterpart).  The SMs of one GPU do not stream from HBM at the same rate; with the default even
- * split a launch ends with its slowest SMs.  Calibration runs a short streaming kernel (one CTA per
- * SM, 2 MB each walked four times, 6 launches, ~0.3 GB of temporary device memory) on `stream`,
- * synchronises, and keeps per-SM shares (the square root of the measured rate ratio: the attention
- * kernel is only partly bound by the SM's streaming rate).  Afterwards every persistent CTA takes the
- * share measured for the SM it runs on, claimed with one atomic so that each share is processed
- * exactly once wherever the CTAs land; launches with fewer than 8 units per warp keep the even split.
- * Results stay within the attention tolerance (only the order in which partial results are merged
- * changes).  Pays off on large launches (measured +2.5..4 % on 512 sequences x W=4096, -0.7 % on 64
- * sequences x W=1024, where the claim and the uneven bounds cost more than the balance returns).
- * The shares travel in the kernel parameters: calibrate before capturing a graph.  Allocates: call
- * outside stream capture.  enabled: 0 = even split, non-zero = weighted.
- * split_shares copies the cumulative shares (scaled to 1 << 20, one more entry than SMs) to the host
- * and returns how many it wrote, 0 when off. */
-UOCR_B200_API int uocr_b200_workspace_calibrate(uocr_b200_workspace* ws, int enabled, uocr_b200_stream_t stream);
-UOCR_B200_API int uocr_b200_workspace_split_shares(const uocr_b200_workspace* ws, int* out_frac, int n);
-
 /* Measurement aid (no reference counterpart): the rate at which this GPU streams from HBM into shared
  * memory through the path the attention kernels use -- one persistent CTA per SM, 16 warps each pulling
  * 4 KB tiles with bulk async copies, nothing written back -- in GB/s (median of 5 runs over a 1.2 GB

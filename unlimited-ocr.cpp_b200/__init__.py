@@ -72,8 +72,6 @@ _SIGS = {
     "uocr_b200_workspace_set_wait_limit": (_i, [_vp, C.c_uint]),
     "uocr_b200_noalloc_status": (_i, [_vp, C.POINTER(_i)]),
     "uocr_b200_workspace_set_out_dtype": (_i, [_vp, _i]),
-    "uocr_b200_workspace_calibrate": (_i, [_vp, _i, _vp]),
-    "uocr_b200_workspace_split_shares": (_i, [_vp, _vp, _i]),
     "uocr_b200_workspace_stream_read_gbs": (_i, [_vp, _vp, C.POINTER(C.c_double)]),
     "uocr_b200_workspace_last_kernel_ms": (_i, [_vp, C.POINTER(C.c_float)]),
     "uocr_b200_rswa_append_decode_batch_f32": (_i, [_vp] * 8 + [_i] * 5 + [_vp]),
@@ -196,21 +194,11 @@ class Workspace:
         """Polls a tile wait may take before the warp gives up (0: every wait gives up at once)."""
         check(lib().uocr_b200_workspace_set_wait_limit(self.h, polls))
 
-    def calibrate(self, enabled: bool = True, stream=None) -> None:
-        """SM-weighted split for the attention kernels of this workspace (measures per-SM streaming rates)."""
-        check(lib().uocr_b200_workspace_calibrate(self.h, int(enabled), stream_handle(stream)))
-
     def stream_read_gbs(self, stream=None) -> float:
         """Read-only HBM -> shared-memory streaming rate of this GPU in GB/s (bulk copies, one CTA per SM)."""
         v = C.c_double(0)
         check(lib().uocr_b200_workspace_stream_read_gbs(self.h, stream_handle(stream), C.byref(v)))
         return v.value
-
-    def split_shares(self):
-        """Cumulative per-SM shares scaled to 1 << 20 (empty list: even split)."""
-        buf = (C.c_int * 161)()
-        n = lib().uocr_b200_workspace_split_shares(self.h, buf, 161)
-        return [buf[i] for i in range(max(n, 0))]
 
     def last_kernel_ms(self) -> float:
         v = C.c_float(0)

@@ -24,7 +24,6 @@
 // RSWACache::append_decode (src/scheduler/kv_cache.cpp:54-82).
 #pragma once
 
-#include "rswa_calibrate.cuh"
 #include "rswa_device.cuh"
 
 namespace uocr_b200 {
@@ -82,14 +81,6 @@ struct AttnParams {
     int* status;
     uint32_t wait_limit;  // polls a tile wait may take before the warp gives up (kWaitLimit unless a test lowers it)
     int total_warps;
-    // SM-weighted split (cta_frac null: even split).  A CTA takes the share measured for the SM it
-    // runs on; `claim` (zero between launches) makes sure every share is taken exactly once even if
-    // two CTAs land on one SM.
-    // The table travels in the kernel parameters (constant bank: no global load before the claim).
-    int split_ctas;                        // 0: even split
-    int cta_frac[kMaxCtas + 1];            // cumulative shares scaled to 1 << 20
-    uint8_t slot_of_smid[kMaxSmid];        // share index of an SM id, 255 if it was never seen
-    int* claim;                            // [ctas]
     // fused decode step with rotary embedding: q and the new k row are rotated on the fly
     // (uocr::cuda::rope, src/kernels/cuda/rope_fused.cu:12-40; src/kernels/cpu_ops.cpp:157-180)
     const int* rope_pos;    // [rows] position of each batch row
@@ -100,7 +91,6 @@ struct AttnParams {
     const float* v_new;
     int* d_len;
     int* d_ring_pos;
-    int* done_ctas;     // weighted split: CTAs that have finished (the last one re-arms the claims), zero between launches
     int late_cta;       // overlapped launches, even split: sixteenths of a share the last CTA's warps give up (0: none)
     int* planned_ctas;  // ticket counter: CTAs that have built their plan from the pre-append cursors; wraps to zero
                         // with the last ticket of a launch (atomicInc), so nothing has to reset it
@@ -267,8 +257,7 @@ __device__ __forceinline__ void cursor_next(UnitCursor& c, const int* rs, const 
 struct PieceMap {
     long long total;
     int ns;           // number of pieces: min(total warps, total units)
-    const int* frac;  // weighted split: cumulative CTA shares scaled to 1 << 20 (kernel parameter space); else null
-    int wpc;          // warps per CTA (weighted split: piece k belongs to CTA k / wpc)
+    int wpc;          // warps per CTA
     // Even split under launch overlap: the warps of the last CTA carry (16 - late) / 16 of a share.  CTAs of
     // an overlapped launch move in as their predecessor's CTAs leave, in block order, so the last block starts
     // several microseconds after the others (it cannot hide its prologue) and would finish last by as much.
@@ -278,52 +267,37 @@ struct PieceMap {
         const int n1 = ns - wpc;
         return k <= n1 ? 16LL * k : 16LL * n1 + (long long)(16 - late) * (k - n1);
     }
-    // first unit of CTA c's share (weighted split only; total < 2^26, so the product fits 64 bits with room)
-    __device__ __forceinline__ int bound(int c) const { return (int)((total * (long long)frac[c]) >> 20); }
     __device__ __forceinline__ long long start(int k) const {
-        if (frac == nullptr) return late ? (total * weight_before(k)) / wtot : ((long long)k * total) / ns;
-        const int c = k / wpc, j = k - c * wpc;
-        const int b0 = bound(c);
-        return b0 + (j * (bound(c + 1) - b0)) / wpc;
+        return late ? (total * weight_before(k)) / wtot : ((long long)k * total) / ns;
     }
     __device__ __forceinline__ long long end(int k) const { return k + 1 < ns ? start(k + 1) : total; }
     __device__ __forceinline__ int of(long long u) const {
-        if (frac == nullptr) {
-            if (!late) return (int)(((u + 1) * ns - 1) / total);
-            // the last piece whose weight prefix w satisfies floor(total * w / wtot) <= u
-            const long long a = ((u + 1) * wtot - 1) / total;
-            const int n1 = ns - wpc;
-            if (a < 16LL * n1) return (int)(a / 16);
-            const int k = n1 + (int)((a - 16LL * n1) / (16 - late));
-            return k < ns ? k : ns - 1;
-        }
-        // the CTA owning unit v: start from the even split's answer, the shares move it by a step or two
-        const int v = (int)u, n = ns / wpc;
-        int lo = (int)(((long long)v * n) / total);
-        int b0 = bound(lo), b1 = bound(lo + 1);
-        while (lo > 0 && b0 > v) { --lo; b1 = b0; b0 = bound(lo); }
-        while (lo < n - 1 && b1 <= v) { ++lo; b0 = b1; b1 = bound(lo + 1); }
-        return lo * wpc + ((v - b0 + 1) * wpc - 1) / (b1 - b0);
+        if (!late) return (int)(((u + 1) * ns - 1) / total);
+        // the last piece whose weight prefix w satisfies floor(total * w / wtot) <= u
+        const long long a = ((u + 1) * wtot - 1) / total;
+        const int n1 = ns - wpc;
+        if (a < 16LL * n1) return (int)(a / 16);
+        const int k = n1 + (int)((a - 16LL * n1) / (16 - late));
+        return k < ns ? k : ns - 1;
     }
 };
 
 constexpr int kPendMax = 4;  // per-warp list of partial segments awaiting their arrival (a piece leaves at most two)
 
-// Whether the weighted split applies to a launch: enough units that no piece can be empty (the shares
-// differ by tens of percent at most) and few enough that the bounds fit 32-bit arithmetic.
-__device__ __forceinline__ bool weighted_split_ok(long long total, int total_warps) {
+// Whether the uneven (late-CTA) split applies to a launch: enough units that no piece can be empty and few
+// enough that the bounds fit the arithmetic.
+__device__ __forceinline__ bool uneven_split_ok(long long total, int total_warps) {
     return total >= 8LL * total_warps && total < (1LL << 26);
 }
 
-__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, const int* frac, int wpc, int late = 0) {
+__device__ __forceinline__ PieceMap make_piece_map(long long total, int total_warps, int wpc, int late = 0) {
     PieceMap m;
     m.total = total;
-    m.frac = frac;
     m.wpc = wpc;
     m.late = 0;
     m.wtot = 0;
     m.ns = (int)min((long long)total_warps, total);
-    if (late > 0 && frac == nullptr && m.ns == total_warps && m.ns > wpc && weighted_split_ok(total, total_warps)) {
+    if (late > 0 && m.ns == total_warps && m.ns > wpc && uneven_split_ok(total, total_warps)) {
         m.late = min(late, 12);
         m.wtot = 16LL * m.ns - (long long)m.late * wpc;
     }
@@ -411,19 +385,6 @@ __device__ __forceinline__ void unpack2(const uint4& w, float2 (&f)[KV::kPerChun
     }
 }
 
-// Weighted split: which share this CTA processes.  `first` is the answer to the claim of the share
-// measured for this CTA's SM (`want`); if somebody else holds it, take the next free one.
-__device__ __forceinline__ int resolve_claim(int first, int want, int* claim, int* status) {
-    if (first == 0) return want;
-    const int n = (int)gridDim.x;
-    for (int i = 1; i < n; ++i) {
-        const int c = want + i < n ? want + i : want + i - n;
-        if (atomicAdd(claim + c, 1) == 0) return c;
-    }
-    atomicOr(status, kStatusClaim);  // cannot happen while claims are reset between launches; results are flagged
-    return blockIdx.x;
-}
-
 // Rotation of one 16-byte chunk's worth of elements (EPC of them, first dim d0) of a head row.  `own`
 // are the elements themselves, `other` the elements HD/2 away (the chunk lies in one half of the row):
 // v[i] = x0 c - x1 s, v[i + HD/2] = x0 s + x1 c with x0 the lower-half and x1 the upper-half element.
@@ -453,20 +414,7 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- which share of the unit line this CTA takes -------------------------------------------------
-    __shared__ int s_cta;
-    const bool weighted = p.split_ctas == (int)gridDim.x;
-    int first_claim = 1, want = blockIdx.x;
-    if (weighted) {
-        if (threadIdx.x == 0) {
-            unsigned smid;
-            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            const int slot = smid < (unsigned)kMaxSmid ? p.slot_of_smid[smid] : 255;
-            if (slot < (int)gridDim.x) want = slot;
-            first_claim = atomicAdd(p.claim + want, 1);  // the answer is looked at after the plan is built
-        }
-    }
-
+    // ---- this warp's tile slots and their barriers ----------------------------------------------------
     const int bar_bytes = (warps * kRing * 8 + 127) & ~127;
     uint8_t* my_tiles = smem + bar_bytes + (size_t)warp * (kRing * TILE);
     const uint32_t bar0 = smem_addr(smem) + warp * (kRing * 8);
@@ -492,7 +440,6 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         int* next_len_s = scratch + 33;
         int* next_ring_s = next_len_s + p.rows;
         plan_all_rows(p.plan, rs_s, info_s, scratch, next_len_s, next_ring_s);
-        if (weighted && threadIdx.x == 0) s_cta = resolve_claim(first_claim, want, p.claim, p.status);
         __syncthreads();
         // The cursors move as soon as every CTA has planned from their old values.  Thread 0 announces
         // this CTA's plan; the answer is looked at once the first tiles are on their way, and the warp
@@ -509,17 +456,11 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         info = info_s;
         next_len = next_len_s;
         next_ring = next_ring_s;
-    } else {
-        if (weighted) {
-            if (threadIdx.x == 0) s_cta = resolve_claim(first_claim, want, p.claim, p.status);
-            __syncthreads();
-        }
     }
 
     const long long total = rs[p.rows];
-    const bool use_split = weighted && weighted_split_ok(total, p.total_warps);
-    const int gw = (weighted ? s_cta : (int)blockIdx.x) * warps + warp;
-    const PieceMap pm = make_piece_map(total, p.total_warps, use_split ? p.cta_frac : nullptr, warps, p.late_cta);
+    const int gw = (int)blockIdx.x * warps + warp;
+    const PieceMap pm = make_piece_map(total, p.total_warps, warps, p.late_cta);
     // When there are fewer pieces than warps they are spread over the SMs (warp-major numbering) instead of
     // filling the first CTAs; otherwise CTA c owns pieces c * warps .. (the late-CTA shares rely on that).
     const int gw_spread = warp * (int)gridDim.x + (int)blockIdx.x;
@@ -1112,26 +1053,11 @@ __global__ void __launch_bounds__(UOCR_ATTN_THREADS, 1) rswa_attn_kernel(const _
         }
     }
 
-    // ---- weighted split: the last CTA to finish re-arms the claims; with the even split there is nothing to
-    //      re-arm and the CTAs leave without the round trip ----
     if constexpr (FUSED) {
         if (!dep_synced) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
             if (warp == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         }
-    }
-    if (weighted) {
-        __shared__ int is_last;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            const int old = atomicAdd(p.done_ctas, 1);
-            is_last = (old == (int)gridDim.x - 1);
-            if (is_last) *p.done_ctas = 0;
-        }
-        __syncthreads();
-        if (is_last)
-            for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) p.claim[i] = 0;
     }
 }
 

@@ -15,6 +15,7 @@
 #include "rswa_attention.cuh"
 #include "rswa_copy.cuh"
 #include "rswa_prefill_tc.cuh"
+#include "rswa_stream_read.cuh"
 #include "uocr_rswa_b200.h"
 
 using namespace uocr_b200;
@@ -99,19 +100,11 @@ struct uocr_b200_workspace {
     float* part_acc = nullptr;
     float* part_ml = nullptr;
     int* counters = nullptr;   // [pieces_max] arrival counters, zero between launches
-    int* done_ctas = nullptr;  // weighted split: CTAs that have finished, zero between launches
     int* planned_ctas = nullptr;  // fused step: ticket counter of CTAs that have planned; wraps to zero by itself
     int pieces_max = 0;
     uint32_t wait_limit = kWaitLimit;  // polls a tile wait may take (uocr_b200_workspace_set_wait_limit)
     PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
     int tiles_cap = 0;
-    // SM-weighted split (uocr_b200_workspace_calibrate): cumulative shares, SM id -> share, and two
-    // claim arrays used alternately, because a fused step may overlap the tail of its predecessor
-    int cta_frac[kMaxCtas + 1] = {0};     // host copies: they travel in the kernel parameters
-    uint8_t slot_of_smid[kMaxSmid] = {0};
-    int* claim = nullptr;                 // device, [2][kMaxCtas]
-    int calibrated_ctas = 0;      // 0: even split
-    unsigned seq = 0;             // launches issued; its low bit picks the claim array
     bool out_bf16 = false;  // attention results are written as bf16 instead of fp32
     bool timing = false;
     bool overlap = false;  // fused decode step may start its prologue before the preceding kernel ends
@@ -156,8 +149,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->pieces_max);
     const size_t o_tiles = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
     ws->tiles_cap = max_rows;
-    const size_t o_split = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
-    ws->bytes = o_split + up(sizeof(int) * (size_t)(2 * kMaxCtas));
+    ws->bytes = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -175,10 +167,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->part_acc = reinterpret_cast<float*>(ws->base + o_acc);
     ws->part_ml = reinterpret_cast<float*>(ws->base + o_ml);
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
-    ws->done_ctas = ws->counters + ws->pieces_max;
-    ws->planned_ctas = ws->done_ctas + 1;
+    ws->planned_ctas = ws->counters + ws->pieces_max;
     ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
-    ws->claim = reinterpret_cast<int*>(ws->base + o_split);
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -202,94 +192,6 @@ int uocr_b200_workspace_set_timing(uocr_b200_workspace* ws, int enabled) {
     return UOCR_B200_OK;
 }
 
-int uocr_b200_workspace_calibrate(uocr_b200_workspace* ws, int enabled, uocr_b200_stream_t stream) {
-    if (!ws) return fail(UOCR_B200_ERR_INVALID, "workspace_calibrate: null workspace");
-    if (!enabled) {
-        ws->calibrated_ctas = 0;
-        return UOCR_B200_OK;
-    }
-    const DeviceInfo* di = nullptr;
-    if (int rc = device_info(&di)) return rc;
-    const int ctas = di->sms;
-    if (ctas > kMaxCtas) return fail(UOCR_B200_ERR_UNSUPPORTED, "workspace_calibrate: more SMs than the split table holds");
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    // 2 MB per SM, walked kPasses times per run: the whole buffer (0.3 GB) is far larger than L2, so every
-    // pass streams from HBM, and a run is long (~0.2 ms) against the few microseconds by which CTAs start apart
-    constexpr int kTilesPerCta = 512, kPasses = 4, kRuns = 5, kWarm = 1;
-    constexpr int warps = 16;
-    const size_t bytes = (size_t)ctas * kTilesPerCta * kCalTile;
-    uint8_t* buf = nullptr;
-    unsigned long long* d_out = nullptr;
-    CHECK_CUDA(cudaMalloc(&buf, bytes), "calibration buffer");
-    cudaError_t e = cudaMalloc(&d_out, sizeof(unsigned long long) * 2 * ctas * kRuns);
-    if (e != cudaSuccess) {
-        cudaFree(buf);
-        return cuda_fail(e, "calibration results");
-    }
-    const int smem = ((warps * kCalRing * 8 + 127) & ~127) + warps * kCalRing * kCalTile;
-    e = cudaFuncSetAttribute(rswa_calibrate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaMemsetAsync(buf, 0, bytes, st);
-    for (int r = 0; r < kWarm + kRuns && e == cudaSuccess; ++r) {
-        CalibrateParams cp{buf, kTilesPerCta, kPasses, d_out + (size_t)2 * ctas * (r < kWarm ? 0 : r - kWarm), ws->status};
-        rswa_calibrate_kernel<<<ctas, warps * 32, smem, st>>>(cp);
-        e = cudaGetLastError();
-    }
-    std::vector<unsigned long long> h((size_t)2 * ctas * kRuns);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(h.data(), d_out, sizeof(unsigned long long) * h.size(), cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    cudaFree(buf);
-    cudaFree(d_out);
-    if (e != cudaSuccess) return cuda_fail(e, "calibration run");
-    // median duration per SM id over the runs
-    std::vector<std::vector<double>> per_sm(kMaxSmid);
-    for (int r = 0; r < kRuns; ++r)
-        for (int c = 0; c < ctas; ++c) {
-            const unsigned long long ns = h[(size_t)2 * (r * ctas + c)], smid = h[(size_t)2 * (r * ctas + c) + 1];
-            if (smid < (unsigned long long)kMaxSmid && ns > 0) per_sm[smid].push_back((double)ns);
-        }
-    // Share c belongs to the SM that ran CTA c of the last calibration launch: on an idle GPU a grid of
-    // one CTA per SM is placed the same way every time, so a CTA normally claims the share with its own
-    // index and neighbouring shares stay spread over the chip the way neighbouring CTAs are.
-    std::vector<int> slot(kMaxSmid, 255);
-    std::vector<double> rate((size_t)ctas, 0.0);
-    int covered = 0;
-    for (int c = 0; c < ctas; ++c) {
-        const unsigned long long smid = h[(size_t)2 * ((kRuns - 1) * ctas + c) + 1];
-        if (smid >= (unsigned long long)kMaxSmid || slot[smid] != 255 || per_sm[smid].empty()) continue;
-        std::sort(per_sm[smid].begin(), per_sm[smid].end());
-        slot[smid] = c;
-        rate[c] = 1.0 / per_sm[smid][per_sm[smid].size() / 2];
-        ++covered;
-    }
-    if (covered != ctas)
-        return fail(UOCR_B200_ERR_UNSUPPORTED, "workspace_calibrate: the calibration grid did not cover every SM exactly once");
-    // The attention kernel is only partly bound by the SM's streaming rate (the rest is its own
-    // instruction stream and latency): measured on the bf16 x 128 decode step, an SM that streams at
-    // 0.80 / 1.34 of the median runs its share of attention at 0.89 / 1.12 of the median speed.  The
-    // square root of the measured ratio models that; proportional shares overshoot and are slower.
-    std::vector<double> sorted_rate(rate);
-    std::sort(sorted_rate.begin(), sorted_rate.end());
-    const double mean = sorted_rate[sorted_rate.size() / 2];
-    for (double& r : rate) r = mean * std::sqrt(r / mean);
-    std::vector<int> frac(kMaxCtas + 1, 0);
-    double total = 0, run = 0;
-    for (double& r : rate) {  // keep every share within [0.5, 2] of the mean: pieces must not become empty
-        r = std::min(std::max(r, 0.5 * mean), 2.0 * mean);
-        total += r;
-    }
-    for (int c = 0; c < ctas; ++c) {
-        run += rate[c];
-        frac[c + 1] = (int)std::llround(run / total * (double)(1 << 20));
-    }
-    frac[ctas] = 1 << 20;
-    for (int c = 0; c <= kMaxCtas; ++c) ws->cta_frac[c] = frac[c];
-    for (int sm = 0; sm < kMaxSmid; ++sm) ws->slot_of_smid[sm] = (uint8_t)slot[sm];
-    CHECK_CUDA(cudaMemsetAsync(ws->claim, 0, sizeof(int) * 2 * kMaxCtas, st), "claims zero");
-    CHECK_CUDA(cudaStreamSynchronize(st), "calibration sync");
-    ws->calibrated_ctas = ctas;
-    return UOCR_B200_OK;
-}
-
 int uocr_b200_workspace_stream_read_gbs(uocr_b200_workspace* ws, uocr_b200_stream_t stream, double* gbs) {
     if (!ws || !gbs) return fail(UOCR_B200_ERR_INVALID, "workspace_stream_read_gbs: null argument");
     const DeviceInfo* di = nullptr;
@@ -298,7 +200,7 @@ int uocr_b200_workspace_stream_read_gbs(uocr_b200_workspace* ws, uocr_b200_strea
     // one CTA per SM, each walking its own 8 MB (the whole buffer, 1.2 GB, is far larger than L2) twice
     constexpr int kTilesPerCta = 2048, kPasses = 2, kRuns = 5, warps = 16;
     const int ctas = di->sms;
-    const size_t bytes = (size_t)ctas * kTilesPerCta * kCalTile;
+    const size_t bytes = (size_t)ctas * kTilesPerCta * kStreamTile;
     uint8_t* buf = nullptr;
     unsigned long long* d_out = nullptr;
     CHECK_CUDA(cudaMalloc(&buf, bytes), "streaming buffer");
@@ -306,14 +208,14 @@ int uocr_b200_workspace_stream_read_gbs(uocr_b200_workspace* ws, uocr_b200_strea
     cudaEvent_t ev[2] = {nullptr, nullptr};
     if (e == cudaSuccess) e = cudaEventCreate(&ev[0]);
     if (e == cudaSuccess) e = cudaEventCreate(&ev[1]);
-    const int smem = ((warps * kCalRing * 8 + 127) & ~127) + warps * kCalRing * kCalTile;
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(rswa_calibrate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const int smem = ((warps * kStreamRing * 8 + 127) & ~127) + warps * kStreamRing * kStreamTile;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rswa_stream_read_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess) e = cudaMemsetAsync(buf, 0, bytes, st);
     std::vector<float> ms;
     for (int r = 0; r < kRuns + 1 && e == cudaSuccess; ++r) {
-        CalibrateParams cp{buf, kTilesPerCta, kPasses, d_out, ws->status};
+        StreamReadParams cp{buf, kTilesPerCta, kPasses, d_out, ws->status};
         e = cudaEventRecord(ev[0], st);
-        rswa_calibrate_kernel<<<ctas, warps * 32, smem, st>>>(cp);
+        rswa_stream_read_kernel<<<ctas, warps * 32, smem, st>>>(cp);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (e == cudaSuccess) e = cudaGetLastError();
         if (e == cudaSuccess) e = cudaEventRecord(ev[1], st);
@@ -330,14 +232,6 @@ int uocr_b200_workspace_stream_read_gbs(uocr_b200_workspace* ws, uocr_b200_strea
     std::sort(ms.begin(), ms.end());
     *gbs = (double)bytes * kPasses / (ms[ms.size() / 2] * 1e-3) / 1e9;
     return UOCR_B200_OK;
-}
-
-int uocr_b200_workspace_split_shares(const uocr_b200_workspace* ws, int* out_frac, int n) {
-    if (!ws || !out_frac || n <= 0) return fail(UOCR_B200_ERR_INVALID, "workspace_split_shares: bad arguments");
-    if (ws->calibrated_ctas == 0) return 0;
-    const int m = std::min(n, ws->calibrated_ctas + 1);
-    std::memcpy(out_frac, ws->cta_frac, sizeof(int) * m);
-    return m;
 }
 
 int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int dtype) {
@@ -544,7 +438,6 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
     ap.v_new = c.v_new;
     ap.d_len = c.d_len_rw;
     ap.d_ring_pos = c.d_ring_rw;
-    ap.done_ctas = ws->done_ctas;
     ap.planned_ctas = ws->planned_ctas;
     ap.late_cta = (c.fused && ws->overlap) ? kLateCtaSixteenths : 0;
     ap.wait_limit = ws->wait_limit;
@@ -552,12 +445,6 @@ int run_attention(AttnCall& c, uocr_b200_workspace* ws, cudaStream_t st) {
         ap.rope_pos = c.rope_pos;
         // same float expression as the reference (src/kernels/cpu_ops.cpp:163; rope_fused.cu:22)
         for (int i = 0; i < c.head_dim / 2; ++i) ap.rope_freq[i] = std::pow(c.rope_theta, -2.0f * i / static_cast<float>(c.head_dim));
-    }
-    if (ws->calibrated_ctas == di->sms) {
-        ap.split_ctas = ws->calibrated_ctas;
-        std::memcpy(ap.cta_frac, ws->cta_frac, sizeof(ap.cta_frac));
-        std::memcpy(ap.slot_of_smid, ws->slot_of_smid, sizeof(ap.slot_of_smid));
-        ap.claim = ws->claim + (ws->seq++ & 1u) * kMaxCtas;
     }
 
     c.plan.rows = c.rows;
@@ -1265,8 +1152,7 @@ extern "C" int uocr_b200_rswa_attention_batch_paged_noalloc(
     view.part_acc = reinterpret_cast<float*>(base + kNaAcc);
     view.part_ml = reinterpret_cast<float*>(base + kNaMl);
     view.counters = reinterpret_cast<int*>(base + kNaCnt);
-    view.done_ctas = view.counters + kNoAllocMaxWarps;
-    view.planned_ctas = view.done_ctas + 1;
+    view.planned_ctas = view.counters + kNoAllocMaxWarps;
     view.pieces_max = kNoAllocMaxWarps;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

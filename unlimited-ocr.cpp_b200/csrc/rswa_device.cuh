@@ -14,7 +14,6 @@ enum : int {
     kStatusBadBlock = 1,     // block id outside [0, num_blocks)
     kStatusWaitTimeout = 2,  // an mbarrier wait ran out of iterations
     kStatusBadSlot = 4,      // logical position outside the table row
-    kStatusClaim = 8,        // weighted split: a CTA found every share already claimed
 };
 
 // ---------------------------------------------------------------------------------------------
