@@ -940,6 +940,7 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     pp.table = pv.table;
     pp.d_prefill_len = d_prefill_len;
     pp.tiles = ws->tiles;
+    pp.n_tiles = n_tiles;
     pp.table_stride = pv.table_stride;
     pp.num_blocks = pv.num_blocks;
     pp.text_blocks = text_blocks;
@@ -969,7 +970,10 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
         maps.tk = maps.k;
         maps.tv = maps.v;
     }
-    rswa_prefill_tc_kernel<<<dim3(n_tiles, heads), kTcThreads, kTcSmemBytes, st>>>(pp, maps);
+    // persistent grid: one CTA per SM walks (tile, head) items
+    const long long n_items = (long long)n_tiles * heads;
+    const int grid = (int)std::min<long long>(n_items, di->sms);
+    rswa_prefill_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, st>>>(pp, maps);
     return after_launch("tensor-core prefill attention");
 }
 

@@ -59,12 +59,15 @@ struct PrefillParams {
     const int* d_prefill_len;
     const PrefillTile* tiles;
     int table_stride, num_blocks, text_blocks;
+    int n_tiles;
     int heads, kv_heads, group, window;
     float scale_log2e;
     int* status;
 };
 
 constexpr int kTcTile = 128;             // queries per CTA, keys per step, head_dim
+constexpr uint32_t kTcColO = 256;        // TMEM columns: S/P buffers at 0 and 128, the accumulator at 256,
+constexpr uint32_t kTcColQ = 384;        // Q as bf16 pairs at 384 (hi words) and 448 (lo words)
 constexpr int kTcHalfBytes = 128 * 128;  // one 64-element-wide half of a 128x128 bf16 tile
 constexpr int kTcTileBytes = 2 * kTcHalfBytes;
 
@@ -111,15 +114,10 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
                      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
 }
 
-// A operand from TMEM (lane = row, two bf16 per 32-bit column), B from shared memory.
-template <bool ACC>
-__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
-    if (ACC)
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                     ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc) : "memory");
-    else
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                     ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc) : "memory");
+// A operand from TMEM (lane = row, two bf16 per 32-bit column), B from shared memory.  acc == 0 overwrites D.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
 }
 
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -131,6 +129,15 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 
@@ -176,10 +183,13 @@ struct PrefillMaps {
 
 
 constexpr int kTcSoftmaxThreads = 256;  // warps 0-7: warp w owns rows 32*(w%4).., key/dim half w/4
-constexpr int kTcThreads = 352;         // + warp 8 K producer, warp 9 MMA issue and TMEM owner, warp 10 V producer
+constexpr int kTcThreads = 384;         // + warp 8 K producer, 9 MMA issue and TMEM owner, 10 V producer, 11 Q producer
 constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchange (double-buffered) + row-sum exchange
-constexpr int kTcSmemBytes = 6 * kTcTileBytes + 256 + kTcExchangeBytes + 1024;  // Qhi Qlo K[2] V[2], barriers, exchange, alignment slack
-constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;                            // one K tile + one V tile
+constexpr int kTcStages = 2;                                   // depth of the K and of the V ring
+constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;           // one K tile + one V tile
+constexpr uint32_t kTcQRowBytes = 528;                         // a staged fp32 row: 512 bytes + 16, so that row-owning and row-wide accesses are conflict-free
+constexpr uint32_t kTcQStageBytes = 128 * kTcQRowBytes;
+constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + kTcQStageBytes + 256 + kTcExchangeBytes + 1024;  // K/V ring, Q / output staging, barriers, exchange, alignment slack
 
 // 64 consecutive TMEM columns of this thread's lane into registers: two loads, one wait.  The wait
 // and the empty statement after it name the registers so that no use can be scheduled before them.
@@ -215,14 +225,22 @@ __device__ __forceinline__ bool softmax_sync(uint32_t bar, uint32_t parity, int*
     return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
 }
 
+// How far a row's maximum may rise above the reference its probabilities are scaled by before the
+// reference moves (in the exp2 domain: probabilities stay below 2^8).  The O accumulator lives in TMEM
+// across key tiles; moving a row's reference means rescaling that row of it, so the reference only
+// follows the maximum in steps.
+constexpr float kTcMaxSlack = 8.f;
+
 // One key tile of the online softmax for this thread: its row, its half (64 keys) of the tile.
 // Reads S once, agrees on the row maximum with the thread that owns the other half (shared-memory
 // exchange + a 64-thread rendezvous), writes P as bf16 pairs over its own 64 columns of the S buffer:
-// 32 words of hi pairs, then 32 words of lo pairs.  FULL: every key of the tile is visible to every row of the warp.  False if the rendezvous
-// ran out of time.
+// 32 words of hi pairs, then 32 words of lo pairs.  FULL: every key of the tile is visible to every row
+// of the warp.  m_ref is the reference the row's probabilities are scaled by; alpha is the factor the
+// row's accumulator and sum take when the reference moved (1 otherwise).  False if the rendezvous ran
+// out of time.
 template <bool FULL>
 __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
-                                                uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_run, float& l_run,
+                                                uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_ref, float& l_run,
                                                 float& alpha) {
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
@@ -235,9 +253,14 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     *my_max = mx;
     // also: both halves of S are in registers from here on, P may overwrite them
     if (!pair_sync(pair_bar, pair_parity, status)) return false;
-    const float m_new = fmaxf(m_run, fmaxf(mx, *other_max));
-    const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-    alpha = tc_exp2(m_run - m_safe);
+    // both threads of the row see the same two maxima and take the same decision
+    const float m_tile = fmaxf(mx, *other_max);
+    alpha = 1.f;
+    if (m_tile > m_ref + kTcMaxSlack) {  // also the first visible key of the row (m_ref = -inf)
+        alpha = tc_exp2(m_ref - m_tile);
+        m_ref = m_tile;
+    }
+    const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
     float lsum = 0.f;
 #pragma unroll
     for (int qq = 0; qq < 2; ++qq) {  // 32 keys at a time: their 16 hi words, then their 16 lo words, over their own columns
@@ -258,43 +281,89 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     l_run = l_run * alpha + lsum;
-    m_run = m_new;
     return true;
 }
 
-// acc = acc * alpha + this thread's 64 dims of the O_tile in TMEM
-__device__ __forceinline__ void tc_fold(uint32_t tO, float alpha, float (&acc)[64]) {
+// This thread's 64 dims of its accumulator row in TMEM times alpha, in place.
+__device__ __forceinline__ void tc_rescale(uint32_t tO, float alpha) {
     uint32_t o[64];
     tc_ld64(tO, o);
+    uint32_t w[32];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) acc[j] = fmaf(acc[j], alpha, __uint_as_float(o[j]));
+    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+    tc_st32(tO, w);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(o[32 + j]) * alpha);
+    tc_st32(tO + 32, w);
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// One work item of the persistent grid: a query tile and a head, with the key tiles its rows can see.
+struct TcItem {
+    PrefillTile t;
+    int head, kvh;
+    int pfx;             // the slot's fixed-region length
+    int n_prefix_tiles;  // key tiles in the fixed region, then (text rows) in the text window from tile text_tile0
+    int text_tile0;
+    int n_steps;
+    bool valid;
+};
+
+// The j-th item of this CTA.  Items are numbered tile-major (the host orders the tiles longest first), heads
+// innermost, and dealt to the CTAs in rounds that alternate direction, so that every CTA's items add up to
+// about the same number of key tiles.  Every role of the CTA walks the same sequence.
+__device__ __forceinline__ TcItem tc_load_item(const PrefillParams& p, uint32_t j) {
+    TcItem it;
+    const long long G = gridDim.x, c = blockIdx.x;
+    const long long k = (long long)j * G + ((j & 1u) ? G - 1 - c : c);
+    it.valid = k < (long long)p.n_tiles * p.heads;
+    it.n_steps = 0;
+    if (!it.valid) return it;
+    const int ti = (int)(k / p.heads);
+    it.head = (int)(k - (long long)ti * p.heads);
+    it.kvh = it.head / p.group;
+    it.t = p.tiles[ti];
+    it.pfx = max(__ldg(p.d_prefill_len + it.t.slot), 0);
+    const int plim = it.t.kind == 0 ? min(it.t.pos0 + it.t.rows, it.pfx) : it.pfx;
+    it.n_prefix_tiles = (plim + kTcTile - 1) / kTcTile;
+    it.text_tile0 = 0;
+    int n_text_tiles = 0;
+    if (it.t.kind == 1) {
+        it.text_tile0 = max(0, it.t.pos0 - p.window + 1) / kTcTile;
+        n_text_tiles = (it.t.pos0 + it.t.rows - 1) / kTcTile - it.text_tile0 + 1;
+    }
+    it.n_steps = it.n_prefix_tiles + n_text_tiles;
+    return it;
 }
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMaps maps) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQh = base;
-    uint8_t* sQl = base + 1 * kTcTileBytes;
-    uint8_t* sKV = base + 2 * kTcTileBytes;  // stage b: K at sKV + b * kTcStageBytes, V one tile after it
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * kTcTileBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
-    float* xmax = reinterpret_cast<float*>(base + 6 * kTcTileBytes + 256);  // [step parity][half][row]
-    float* xsum = xmax + 2 * 2 * 128;                                       // [half][row]
+    uint8_t* sKV = base;                               // stage b: K at sKV + b * kTcStageBytes, V one tile after it
+    uint8_t* sQ = base + kTcStages * kTcStageBytes;    // fp32 query rows on their way to TMEM, then the output rows
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + kTcQStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 30);
+    float* xmax = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [tile parity][half][row]
+    float* xsum = xmax + 2 * 2 * 128;                                                // [half][row]
     const uint32_t bar0 = smem_addr(bars);
-    auto k_full = [&](int b) { return bar0 + (0 + b) * 8; };   // TMA bytes of K stage b have landed
-    auto k_free = [&](int b) { return bar0 + (2 + b) * 8; };   // the S MMAs reading K stage b are done
-    auto v_full = [&](int b) { return bar0 + (16 + b) * 8; };  // same for V and the O MMAs
-    auto v_free = [&](int b) { return bar0 + (18 + b) * 8; };
-    auto s_full = [&](int b) { return bar0 + (4 + b) * 8; };   // S buffer b holds Q K^T
-    auto p_full = [&](int b) { return bar0 + (6 + b) * 8; };   // all 256 softmax threads wrote their P over S buffer b
-    auto o_full = [&](int b) { return bar0 + (8 + b) * 8; };   // O_tile buffer b holds P V
-    const uint32_t q_full = bar0 + 10 * 8, drained = bar0 + 11 * 8;
-    auto pair_bar = [&](int quad) { return bar0 + (12 + quad) * 8; };  // the two softmax warps of a lane quadrant
+    // Ring and S/P barriers are indexed by the parity of the CTA's running key-tile count g; their phase is (g >> 1) & 1.
+    auto k_full = [&](uint32_t b) { return bar0 + (0 + b) * 8; };   // TMA bytes of K stage b have landed
+    auto k_free = [&](uint32_t b) { return bar0 + (2 + b) * 8; };   // the S MMAs reading K stage b are done
+    auto v_full = [&](uint32_t b) { return bar0 + (4 + b) * 8; };   // same for V and the O MMAs
+    auto v_free = [&](uint32_t b) { return bar0 + (6 + b) * 8; };
+    auto s_full = [&](uint32_t b) { return bar0 + (8 + b) * 8; };   // S buffer b holds Q K^T
+    auto p_full = [&](uint32_t b) { return bar0 + (10 + b) * 8; };  // all 256 softmax threads wrote their P over S buffer b
+    auto o_full = [&](uint32_t b) { return bar0 + (12 + b) * 8; };  // the accumulator holds the products up to a tile of parity b
+    // One phase per item:
+    const uint32_t q_landed = bar0 + 14 * 8;    // the item's query rows are in the staging area (transaction bytes)
+    const uint32_t q_full = bar0 + 15 * 8;      // all softmax threads stored their part of Q in TMEM
+    const uint32_t sq_free = bar0 + 16 * 8;     // the staging area may take the query rows of the item after next
+    const uint32_t out_staged = bar0 + 17 * 8;  // output rows staged in shared memory
+    const uint32_t drained = bar0 + 18 * 8;
+    auto pair_bar = [&](int quad) { return bar0 + (20 + quad) * 8; };  // the two softmax warps of a lane quadrant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const PrefillTile t = p.tiles[blockIdx.x];
-    const int head = blockIdx.y, kvh = head / p.group;
 
     if (tid == 0) {
 #pragma unroll
@@ -307,14 +376,16 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             mbar_init(p_full(b), kTcSoftmaxThreads);
             mbar_init(o_full(b), 1);
         }
+        mbar_init(q_landed, 1);
         mbar_init(q_full, kTcSoftmaxThreads);
+        mbar_init(sq_free, kTcSoftmaxThreads);
+        mbar_init(out_staged, kTcSoftmaxThreads);
         mbar_init(drained, 1);
 #pragma unroll
         for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
-        mbar_init(bar0 + 20 * 8, kTcSoftmaxThreads);  // output rows staged in shared memory
         mbar_init_fence();
     }
-    if (warp == 9) {  // 512 TMEM columns: S/P buffers at 0 and 128, O_tile buffers at 256 and 384
+    if (warp == 9) {  // 512 TMEM columns: S/P buffers at 0 and 128, the accumulator at 256, Q at 384
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -323,118 +394,129 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    // ---- key tiles this query tile can see (uniform over the CTA) ------------------------------------
-    const int pfx = max(p.d_prefill_len[t.slot], 0);
-    const int plim = t.kind == 0 ? min(t.pos0 + t.rows, pfx) : pfx;
-    const int n_prefix_tiles = (plim + kTcTile - 1) / kTcTile;
-    int text_tile0 = 0, n_text_tiles = 0;
-    if (t.kind == 1) {
-        text_tile0 = max(0, t.pos0 - p.window + 1) / kTcTile;
-        n_text_tiles = (t.pos0 + t.rows - 1) / kTcTile - text_tile0 + 1;
-    }
-    const int n_steps = n_prefix_tiles + n_text_tiles;
-
     if (warp < 8) {
         // ================= softmax warps ==============================================================
         const int quad = warp & 3, h = warp >> 2;  // TMEM lane quadrant; key half of S and dim half of O
         const int r = quad * 32 + lane;            // query row of the tile == TMEM lane
-        const bool live = r < t.rows;
-        const int i = t.pos0 + r;
-        const int phi = !live ? 0 : (t.kind == 0 ? min(i + 1, pfx) : pfx);  // fixed-region tokens [0, phi)
-        const int tlo = max(0, i - p.window + 1);
-        const int thi = (live && t.kind == 1) ? i + 1 : 0;                   // text tokens [tlo, thi)
-        {
-            // Q tile -> bf16 hi/lo operand tiles.  Warp w stages rows 16w..16w+15; a row (512 B) is one
-            // coalesced request of the warp, lane l holding dims 4l..4l+3, and all 16 rows are in flight
-            // together.  The 8-byte hi and lo words land in the swizzled operand layout.
-            const float s = p.scale_log2e;
-            float4 qv[16];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const int row = warp * 16 + k;
-                qv[k] = row < t.rows ? __ldg(reinterpret_cast<const float4*>(p.q + ((size_t)(t.row0 + row) * p.heads + head) * kTcTile) + lane)
-                                     : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const int row = warp * 16 + k;
-                uint2 hi, lo;
-                tc_split2(qv[k].x * s, qv[k].y * s, hi.x, lo.x);
-                tc_split2(qv[k].z * s, qv[k].w * s, hi.y, lo.y);
-                const uint32_t off = tc_tile_offset(row, lane >> 1) + (lane & 1) * 8;
-                *reinterpret_cast<uint2*>(sQh + off) = hi;
-                *reinterpret_cast<uint2*>(sQl + off) = lo;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
-            mbar_arrive(q_full);
-        }
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        float acc[64];
+        const uint32_t tO = tmem + lane_base + kTcColO + h * 64;  // this thread's 64 dims of its accumulator row
+        const float4* my_q = reinterpret_cast<const float4*>(sQ + (size_t)r * kTcQRowBytes) + h * 16;
+        // Q rows of item `it` (staged as fp32 by the Q producer) -> bf16 hi/lo A operand in TMEM: lane = row,
+        // column c of a 64-column block = dims 2c, 2c+1.  The S MMAs of the previous item must have completed
+        // (its last s_full was waited for).  Returns once every thread has read its row.
+        auto convert_q = [&](const TcItem& it, uint32_t par) -> bool {
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_landed, par, p.status))) return false;
+            const bool live = r < it.t.rows;
+            const float s = p.scale_log2e;
 #pragma unroll
-        for (int d = 0; d < 64; ++d) acc[d] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-        bool ok = true;
-        int folded = 0;  // O_tiles folded into acc so far
-        for (int n = 0; n < n_steps; ++n) {
-            const int b = n & 1;
-            const uint32_t par = (uint32_t)(n >> 1) & 1u;
-            const bool text = n >= n_prefix_tiles;
-            const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
-            const int vlo = text ? tlo - t0 : -(1 << 30);
-            const int vhi = (text ? thi : phi) - t0;
-            // warp-uniform outcome: the TMEM instructions below need the whole warp
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tS = tmem + lane_base + b * 128;
-            float* my_max = xmax + (b * 2 + h) * 128 + r;
-            const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
-            float alpha = 1.f;
-            if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
-                ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
-            else
-                ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), (uint32_t)n & 1u, p.status, m_run, l_run, alpha);
-            if (!ok) break;
+            for (int g2 = 0; g2 < 2; ++g2) {  // 32 dims at a time: 16 hi words and 16 lo words
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 v = live ? my_q[g2 * 8 + c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    tc_split2(v.x * s, v.y * s, hi[2 * c], lo[2 * c]);
+                    tc_split2(v.z * s, v.w * s, hi[2 * c + 1], lo[2 * c + 1]);
+                }
+                tc_st16(tmem + lane_base + kTcColQ + h * 32 + g2 * 16, hi);
+                tc_st16(tmem + lane_base + kTcColQ + 64 + h * 32 + g2 * 16, lo);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full(b));
-            if (n >= 1) {  // fold the previous tile's product while the tensor core works on this one
-                const int k = n - 1;
-                if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
-                folded = n;
-            }
-            alpha_prev = alpha;
+            mbar_arrive(q_full);
+            return __all_sync(0xffffffffu, mbar_wait_bounded(q_full, par, p.status));
+        };
+
+        uint32_t g = 0;    // key tiles this CTA has gone through
+        uint32_t itc = 0;  // items this CTA has gone through
+        uint32_t pp = 0;   // rendezvous of the warp pair so far
+        TcItem cur = tc_load_item(p, 0);
+        bool ok = true;
+        if (cur.valid) {
+            ok = convert_q(cur, 0);
+            if (ok) mbar_arrive(sq_free);  // the staging area can take the next item's rows
         }
-        if (ok && folded < n_steps) {
-            const int k = n_steps - 1;
-            if (__all_sync(0xffffffffu, mbar_wait_bounded(o_full(k & 1), (uint32_t)(k >> 1) & 1u, p.status))) {
+        while (cur.valid && ok) {
+            const TcItem nxt = tc_load_item(p, itc + 1);
+            const PrefillTile& t = cur.t;
+            const bool live = r < t.rows;
+            const int i = t.pos0 + r;
+            const int phi = !live ? 0 : (t.kind == 0 ? min(i + 1, cur.pfx) : cur.pfx);  // fixed-region tokens [0, phi)
+            const int tlo = max(0, i - p.window + 1);
+            const int thi = (live && t.kind == 1) ? i + 1 : 0;                           // text tokens [tlo, thi)
+            float m_ref = -INFINITY, l_run = 0.f;
+            for (int n = 0; n < cur.n_steps; ++n) {
+                const uint32_t gn = g + n, b = gn & 1u, par = (gn >> 1) & 1u;
+                const bool text = n >= cur.n_prefix_tiles;
+                const int t0 = text ? (cur.text_tile0 + n - cur.n_prefix_tiles) * kTcTile : n * kTcTile;
+                const int vlo = text ? tlo - t0 : -(1 << 30);
+                const int vhi = (text ? thi : phi) - t0;
+                // warp-uniform outcome: the TMEM instructions below need the whole warp
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tc_fold(tmem + lane_base + 256 + (k & 1) * 128 + h * 64, alpha_prev, acc);
+                const uint32_t tS = tmem + lane_base + b * 128;
+                float* my_max = xmax + (b * 2 + h) * 128 + r;
+                const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
+                float alpha = 1.f;
+                if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
+                    ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, m_ref, l_run, alpha);
+                else
+                    ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, m_ref, l_run, alpha);
+                ++pp;
+                if (!ok) break;
+                // A row whose reference moved takes the factor on its accumulator before this tile's product is
+                // added: the previous product must have landed, and this tile's P is only announced afterwards.
+                if (n >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                    const uint32_t gk = gn - 1;
+                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(gk & 1u), (gk >> 1) & 1u, p.status))) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    tc_rescale(tO, alpha);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(p_full(b));
             }
-        }
-        // ---- row sum over both key halves, then this thread's 64 dims of the row ------------------------
-        // (after a wait that ran out the partner warp may be elsewhere: no rendezvous then, zeros out)
-        xsum[h * 128 + r] = l_run;
-        if (ok) ok = pair_sync(pair_bar(quad), (uint32_t)n_steps & 1u, p.status);
-        const float l_tot = ok ? l_run + xsum[(h ^ 1) * 128 + r] : 0.f;
-        // The row goes out through shared memory (the K/V ring is idle now: every MMA has completed and
-        // every load was consumed) so that each warp writes whole 512-byte rows.  16-byte chunk c of row
-        // r sits at chunk c ^ (r % 32): conflict-free both for the row-owning writer and the row-wide reader.
-        {
-            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            float4* so = reinterpret_cast<float4*>(sKV);
+            if (!ok) break;
+            // The next item's Q goes to TMEM before this item's rows leave, so that its first scores are
+            // computed while the rows are on their way out (every S product of this item has completed).
+            if (nxt.valid) {
+                ok = convert_q(nxt, (itc + 1) & 1u);
+                if (!ok) break;
+            }
+            // ---- this thread's 64 dims of the row, the row sum over both key halves ----------------------
+            float acc[64];
 #pragma unroll
-            for (int c = 0; c < 16; ++c)
-                so[r * 32 + ((h * 16 + c) ^ (r & 31))] =
-                    make_float4(acc[4 * c] * inv, acc[4 * c + 1] * inv, acc[4 * c + 2] * inv, acc[4 * c + 3] * inv);
-            if (ok) ok = softmax_sync(bar0 + 20 * 8, 0, p.status);
-            if (ok) {
+            for (int d = 0; d < 64; ++d) acc[d] = 0.f;
+            if (cur.n_steps > 0) {
+                const uint32_t gl = g + cur.n_steps - 1;
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(gl & 1u), (gl >> 1) & 1u, p.status))) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t o[64];
+                tc_ld64(tO, o);
+#pragma unroll
+                for (int d = 0; d < 64; ++d) acc[d] = __uint_as_float(o[d]);
+                // the accumulator is read: the next item's first product may overwrite it
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            xsum[h * 128 + r] = l_run;
+            ok = pair_sync(pair_bar(quad), pp & 1u, p.status);
+            ++pp;
+            if (!ok) break;
+            const float l_tot = l_run + xsum[(h ^ 1) * 128 + r];
+            // The rows go out through the staging area so that each warp writes whole 512-byte rows.  Rows are
+            // 528 bytes apart: conflict-free both for the row-owning writer and for the row-wide reader.
+            {
+                const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+                float4* so = reinterpret_cast<float4*>(sQ + (size_t)r * kTcQRowBytes) + h * 16;
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    so[c] = make_float4(acc[4 * c] * inv, acc[4 * c + 1] * inv, acc[4 * c + 2] * inv, acc[4 * c + 3] * inv);
+                ok = softmax_sync(out_staged, itc & 1u, p.status);
+                if (!ok) break;
 #pragma unroll 4
                 for (int k = 0; k < 16; ++k) {
                     const int row = warp * 16 + k;
                     if (row < t.rows) {
-                        const float4 o4 = so[row * 32 + (lane ^ (row & 31))];
-                        const size_t at = ((size_t)(t.row0 + row) * p.heads + head) * kTcTile;
+                        const float4 o4 = reinterpret_cast<const float4*>(sQ + (size_t)row * kTcQRowBytes)[lane];
+                        const size_t at = ((size_t)(t.row0 + row) * p.heads + cur.head) * kTcTile;
                         if (p.out_bf16)
                             reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + at)[lane] =
                                 make_uint2(pack_bf16x2(o4.x, o4.y), pack_bf16x2(o4.z, o4.w));
@@ -442,51 +524,77 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                             reinterpret_cast<float4*>(p.out + at)[lane] = o4;
                     }
                 }
+                // generic-proxy accesses of the staging area before the bulk copies that refill it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(sq_free);
             }
+            g += cur.n_steps;
+            ++itc;
+            cur = nxt;
         }
     } else if (warp == 8 || warp == 10) {
         // ================= producer warps: warp 8 feeds K, warp 10 feeds V ============================
-        // lane = (64-dim half, block of the tile); K runs further ahead than V because its stage is
-        // free again as soon as the S product has read it.
+        // lane = (64-dim half, block of the tile).  The ring runs on across items, so the first tiles of the
+        // next item are fetched while the current one finishes.
         const int is_v = warp == 10 ? 1 : 0;
         const int blk_i = lane & 7, half = (lane >> 3) & 1;
-        const int prefix_blocks = (pfx + kBlockTokens - 1) / kBlockTokens;
         const int pool_rows = p.num_blocks * p.kv_heads * kBlockTokens;
         const int text_rows = p.text_blocks * p.kv_heads * kBlockTokens;
-        int issued = 0;
-        for (int n = 0; n < n_steps; ++n) {
-            const int b = n & 1;
-            const uint32_t full = is_v ? v_full(b) : k_full(b), freed = is_v ? v_free(b) : k_free(b);
-            if (n >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(freed, (uint32_t)((n >> 1) - 1) & 1u, p.status))) break;
-            const bool text = n >= n_prefix_tiles;
-            const int t0 = text ? (text_tile0 + n - n_prefix_tiles) * kTcTile : n * kTcTile;
-            const int idx = t0 / kBlockTokens + blk_i;  // block index within the request's region
-            int y;
-            const CUtensorMap* map;
-            if (text) {
-                const int blk = t.block0 + idx;
-                y = blk < p.text_blocks ? (blk * p.kv_heads + kvh) * kBlockTokens : text_rows;
-                map = is_v ? &maps.tv : &maps.tk;
-            } else {
-                y = pool_rows;
-                if (idx < prefix_blocks && idx < p.table_stride) {
-                    const int blk = __ldg(p.table + (size_t)t.slot * p.table_stride + idx);
-                    if (blk < 0 || blk >= p.num_blocks)
-                        atomicOr(p.status, kStatusBadBlock);
-                    else
-                        y = (blk * p.kv_heads + kvh) * kBlockTokens;
+        uint32_t g = 0, m = 0, issued = 0;
+        bool ok = true;
+        for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+            const int prefix_blocks = (it.pfx + kBlockTokens - 1) / kBlockTokens;
+            for (int n = 0; n < it.n_steps; ++n) {
+                const uint32_t gn = g + n, b = gn & 1u;
+                const uint32_t full = is_v ? v_full(b) : k_full(b), freed = is_v ? v_free(b) : k_free(b);
+                if (gn >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(freed, ((gn >> 1) - 1) & 1u, p.status))) { ok = false; break; }
+                const bool text = n >= it.n_prefix_tiles;
+                const int t0 = text ? (it.text_tile0 + n - it.n_prefix_tiles) * kTcTile : n * kTcTile;
+                const int idx = t0 / kBlockTokens + blk_i;  // block index within the request's region
+                int y;
+                const CUtensorMap* map;
+                if (text) {
+                    const int blk = it.t.block0 + idx;
+                    y = blk < p.text_blocks ? (blk * p.kv_heads + it.kvh) * kBlockTokens : text_rows;
+                    map = is_v ? &maps.tv : &maps.tk;
+                } else {
+                    y = pool_rows;
+                    if (idx < prefix_blocks && idx < p.table_stride) {
+                        const int blk = __ldg(p.table + (size_t)it.t.slot * p.table_stride + idx);
+                        if (blk < 0 || blk >= p.num_blocks)
+                            atomicOr(p.status, kStatusBadBlock);
+                        else
+                            y = (blk * p.kv_heads + it.kvh) * kBlockTokens;
+                    }
+                    map = is_v ? &maps.v : &maps.k;
                 }
-                map = is_v ? &maps.v : &maps.k;
+                if (lane == 0) mbar_arrive_expect_tx(full, kTcTileBytes);
+                __syncwarp();
+                const uint32_t dst = smem_addr(sKV) + b * kTcStageBytes + is_v * kTcTileBytes + half * kTcHalfBytes + blk_i * 2048;
+                if (lane < 16) tma_load_box(dst, map, half * 64, y, full);
+                issued = gn + 1;
             }
-            if (lane == 0) mbar_arrive_expect_tx(full, kTcTileBytes);
-            __syncwarp();
-            const uint32_t dst = smem_addr(sKV) + b * kTcStageBytes + is_v * kTcTileBytes + half * kTcHalfBytes + blk_i * 2048;
-            if (lane < 16) tma_load_box(dst, map, half * 64, y, full);
-            issued = n + 1;
+            g += it.n_steps;
         }
         // the last two stages may still be landing if a consumer gave up: wait for them before leaving
-        for (int n = max(0, issued - 2); n < issued; ++n)
-            mbar_wait_bounded(is_v ? v_full(n & 1) : k_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status);
+        for (uint32_t gn = issued >= 2 ? issued - 2 : 0; gn < issued; ++gn)
+            mbar_wait_bounded(is_v ? v_full(gn & 1u) : k_full(gn & 1u), (gn >> 1) & 1u, p.status);
+    } else if (warp == 11) {
+        // ================= Q producer: the item's fp32 query rows, one bulk copy per row ==============
+        // The staging area is free for item m once the rows of item m-2 have left it (and from the start for
+        // items 0 and, after its conversion, 1): one phase of sq_free per item.
+        uint32_t m = 0;
+        bool ok = true;
+        for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+            if (m >= 1 && !__all_sync(0xffffffffu, mbar_wait_bounded(sq_free, (m - 1) & 1u, p.status))) { ok = false; break; }
+            if (lane == 0) mbar_arrive_expect_tx(q_landed, (uint32_t)it.t.rows * 512u);
+            __syncwarp();
+            for (int row = lane; row < it.t.rows; row += 32)
+                bulk_copy_g2s(smem_addr(sQ) + (uint32_t)row * kTcQRowBytes,
+                              p.q + ((size_t)(it.t.row0 + row) * p.heads + it.head) * kTcTile, 512u, q_landed);
+        }
+        // rows still on their way if the consumers gave up: see them land before the CTA leaves
+        if (m >= 1) mbar_wait_bounded(q_landed, (m - 1) & 1u, ok ? p.status : nullptr);
     } else {
         // ================= MMA warp: one thread issues every tensor-core instruction ==================
         if (lane == 0) {
@@ -494,51 +602,56 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             // Every operand descriptor is fixed for the CTA's lifetime except for the stage (0/1) of
             // K and V, which only moves the address field: build them once, so that one MMA costs the
             // issuing thread one instruction and a 32-bit add.
-            uint64_t dQ[16], dK[8], dV[8];
+            uint64_t dK[8], dV[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
-                dQ[j] = tc_smem_desc(smem_addr(sQh) + koff, 16, 1024);
-                dQ[8 + j] = tc_smem_desc(smem_addr(sQl) + koff, 16, 1024);
                 dK[j] = tc_smem_desc(smem_addr(sKV) + koff, 16, 1024);
                 // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
                 dV[j] = tc_smem_desc(smem_addr(sKV) + kTcTileBytes + j * 2048, kTcHalfBytes, 1024);
             }
-            auto issue_qk = [&](int n) {  // S[n & 1] = (Qhi + Qlo) K(n)^T
-                const uint64_t stage = (uint64_t)((n & 1) * (kTcStageBytes >> 4));  // address field counts 16-byte units
-                const uint32_t tS = tmem + (n & 1) * 128;
-                tc_mma<false>(tS, dQ[0], dK[0] + stage, idesc_s);
+            auto issue_qk = [&](uint32_t gn) {  // S[gn & 1] = (Qhi + Qlo) K^T with K in ring stage gn & 1
+                const uint64_t stage = (uint64_t)((gn & 1u) * (kTcStageBytes >> 4));  // address field counts 16-byte units
+                const uint32_t tS = tmem + (gn & 1u) * 128;
+                // Q: 16 dims = 8 TMEM columns per MMA, 64 columns of hi words, then 64 of lo words
 #pragma unroll
-                for (int j = 1; j < 16; ++j) tc_mma<true>(tS, dQ[j], dK[j & 7] + stage, idesc_s);
-                tc_commit(s_full(n & 1));
-                tc_commit(k_free(n & 1));
+                for (int j = 0; j < 16; ++j) tc_mma_ts(tS, tmem + kTcColQ + 8 * j, dK[j & 7] + stage, idesc_s, (uint32_t)j);
+                tc_commit(s_full(gn & 1u));
+                tc_commit(k_free(gn & 1u));
             };
-            bool ok = mbar_wait_bounded(q_full, 0, p.status);
-            for (int n = 0; n < n_steps && ok; ++n) {
-                if (n == 0) {
-                    if (!mbar_wait_bounded(k_full(0), 0, p.status)) { ok = false; break; }
+            uint32_t g = 0, m = 0;
+            bool ok = true;
+            for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+                if (!mbar_wait_bounded(q_full, m & 1u, p.status)) { ok = false; break; }
+                for (int n = 0; n < it.n_steps; ++n) {
+                    const uint32_t gn = g + n;
+                    if (n == 0) {
+                        if (!mbar_wait_bounded(k_full(gn & 1u), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_qk(gn);
+                    }
+                    if (n + 1 < it.n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
+                        if (!mbar_wait_bounded(k_full((gn + 1) & 1u), ((gn + 1) >> 1) & 1u, p.status)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_qk(gn + 1);
+                    }
+                    if (!mbar_wait_bounded(v_full(gn & 1u), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    if (!mbar_wait_bounded(p_full(gn & 1u), (gn >> 1) & 1u, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    issue_qk(0);
-                }
-                if (n + 1 < n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
-                    if (!mbar_wait_bounded(k_full((n + 1) & 1), (uint32_t)((n + 1) >> 1) & 1u, p.status)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    issue_qk(n + 1);
-                }
-                if (!mbar_wait_bounded(v_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
-                if (!mbar_wait_bounded(p_full(n & 1), (uint32_t)(n >> 1) & 1u, p.status)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t stage = (uint64_t)((n & 1) * (kTcStageBytes >> 4));
-                const uint32_t tP = tmem + (n & 1) * 128, tO = tmem + 256 + (n & 1) * 128;
-                // P: 16 keys = 8 TMEM columns per MMA; every 32 keys hold their 16 hi words, then their 16 lo words.
-                tc_mma_ts<false>(tO, tP, dV[0] + stage, idesc_o);
+                    const uint64_t stage = (uint64_t)((gn & 1u) * (kTcStageBytes >> 4));
+                    const uint32_t tP = tmem + (gn & 1u) * 128, tO = tmem + kTcColO;
+                    // P: 16 keys = 8 TMEM columns per MMA; every 32 keys hold their 16 hi words, then their 16 lo words.
+                    // The accumulator carries over from tile to tile (the item's first product overwrites it).
+                    tc_mma_ts(tO, tP, dV[0] + stage, idesc_o, (uint32_t)n);
 #pragma unroll
-                for (int u = 1; u < 16; ++u) {
-                    const int hp = u >> 3, j = u & 7;
-                    tc_mma_ts<true>(tO, tP + (j >> 1) * 32 + hp * 16 + (j & 1) * 8, dV[j] + stage, idesc_o);
+                    for (int u = 1; u < 16; ++u) {
+                        const int hp = u >> 3, j = u & 7;
+                        tc_mma_ts(tO, tP + (j >> 1) * 32 + hp * 16 + (j & 1) * 8, dV[j] + stage, idesc_o, 1u);
+                    }
+                    tc_commit(o_full(gn & 1u));
+                    tc_commit(v_free(gn & 1u));
                 }
-                tc_commit(o_full(n & 1));
-                tc_commit(v_free(n & 1));
+                g += it.n_steps;
             }
             // every MMA issued above has finished before the TMEM is released
             tc_commit(drained);
