@@ -183,7 +183,7 @@ struct PrefillMaps {
 
 
 constexpr int kTcSoftmaxThreads = 256;  // warps 0-7: warp w owns rows 32*(w%4).., key/dim half w/4
-constexpr int kTcThreads = 384;         // + warp 8 K producer, 9 MMA issue and TMEM owner, 10 V producer, 11 Q producer
+constexpr int kTcThreads = 384;         // + warp 8 K producer, 9 S issuer and TMEM owner, 10 V producer, 11 O issuer
 constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchange (double-buffered) + row-sum exchange
 constexpr int kTcStages = 2;                                   // depth of the K and of the V ring
 constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;           // one K tile + one V tile
@@ -358,9 +358,9 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     // One phase per item:
     const uint32_t q_landed = bar0 + 14 * 8;    // the item's query rows are in the staging area (transaction bytes)
     const uint32_t q_full = bar0 + 15 * 8;      // all softmax threads stored their part of Q in TMEM
-    const uint32_t sq_free = bar0 + 16 * 8;     // the staging area may take the query rows of the item after next
+    const uint32_t sq_free = bar0 + 16 * 8;     // the staging area may take the next query rows (one phase per fetch)
     const uint32_t out_staged = bar0 + 17 * 8;  // output rows staged in shared memory
-    const uint32_t drained = bar0 + 18 * 8;
+    const uint32_t drained = bar0 + 18 * 8, drained2 = bar0 + 19 * 8;  // the issuers' last instructions have completed
     auto pair_bar = [&](int quad) { return bar0 + (20 + quad) * 8; };  // the two softmax warps of a lane quadrant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -381,6 +381,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         mbar_init(sq_free, kTcSoftmaxThreads);
         mbar_init(out_staged, kTcSoftmaxThreads);
         mbar_init(drained, 1);
+        mbar_init(drained2, 1);
 #pragma unroll
         for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
         mbar_init_fence();
@@ -426,17 +427,41 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             return __all_sync(0xffffffffu, mbar_wait_bounded(q_full, par, p.status));
         };
 
+        // The fp32 query rows of an item come into the staging area by one bulk copy per row, issued by the
+        // thread with the row's number once the area is free (every softmax thread has arrived on sq_free,
+        // thread 0 having announced the bytes before its own arrival).
+        auto announce_q = [&](const TcItem& it) {
+            if (tid == 0 && it.valid) mbar_arrive_expect_tx(q_landed, (uint32_t)it.t.rows * 512u);
+        };
+        auto fetch_q = [&](const TcItem& it, uint32_t free_par) -> bool {
+            if (!it.valid || warp >= 4) return true;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(sq_free, free_par, p.status))) return false;
+            if (tid < it.t.rows)
+                bulk_copy_g2s(smem_addr(sQ) + (uint32_t)tid * kTcQRowBytes,
+                              p.q + ((size_t)(it.t.row0 + tid) * p.heads + it.head) * kTcTile, 512u, q_landed);
+            return true;
+        };
+
         uint32_t g = 0;    // key tiles this CTA has gone through
         uint32_t itc = 0;  // items this CTA has gone through
         uint32_t pp = 0;   // rendezvous of the warp pair so far
+        uint32_t fq = 0;   // phases of sq_free so far
         TcItem cur = tc_load_item(p, 0);
+        TcItem nxt = tc_load_item(p, 1);
         bool ok = true;
         if (cur.valid) {
-            ok = convert_q(cur, 0);
-            if (ok) mbar_arrive(sq_free);  // the staging area can take the next item's rows
+            announce_q(cur);
+            mbar_arrive(sq_free);
+            ok = fetch_q(cur, fq++ & 1u);
+            if (ok) ok = convert_q(cur, 0);
+            if (ok) {  // the staging area can take the next item's rows
+                announce_q(nxt);
+                mbar_arrive(sq_free);
+                ok = fetch_q(nxt, fq++ & 1u);
+            }
         }
         while (cur.valid && ok) {
-            const TcItem nxt = tc_load_item(p, itc + 1);
+            const TcItem nxt2 = tc_load_item(p, itc + 2);
             const PrefillTile& t = cur.t;
             const bool live = r < t.rows;
             const int i = t.pos0 + r;
@@ -524,13 +549,16 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                             reinterpret_cast<float4*>(p.out + at)[lane] = o4;
                     }
                 }
-                // generic-proxy accesses of the staging area before the bulk copies that refill it
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                // the rows have left the staging area: it takes the query rows of the item after next
+                announce_q(nxt2);
                 mbar_arrive(sq_free);
+                ok = fetch_q(nxt2, fq++ & 1u);
+                if (!ok) break;
             }
             g += cur.n_steps;
             ++itc;
             cur = nxt;
+            nxt = nxt2;
         }
     } else if (warp == 8 || warp == 10) {
         // ================= producer warps: warp 8 feeds K, warp 10 feeds V ============================
@@ -579,67 +607,59 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         // the last two stages may still be landing if a consumer gave up: wait for them before leaving
         for (uint32_t gn = issued >= 2 ? issued - 2 : 0; gn < issued; ++gn)
             mbar_wait_bounded(is_v ? v_full(gn & 1u) : k_full(gn & 1u), (gn >> 1) & 1u, p.status);
-    } else if (warp == 11) {
-        // ================= Q producer: the item's fp32 query rows, one bulk copy per row ==============
-        // The staging area is free for item m once the rows of item m-2 have left it (and from the start for
-        // items 0 and, after its conversion, 1): one phase of sq_free per item.
-        uint32_t m = 0;
-        bool ok = true;
-        for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
-            if (m >= 1 && !__all_sync(0xffffffffu, mbar_wait_bounded(sq_free, (m - 1) & 1u, p.status))) { ok = false; break; }
-            if (lane == 0) mbar_arrive_expect_tx(q_landed, (uint32_t)it.t.rows * 512u);
-            __syncwarp();
-            for (int row = lane; row < it.t.rows; row += 32)
-                bulk_copy_g2s(smem_addr(sQ) + (uint32_t)row * kTcQRowBytes,
-                              p.q + ((size_t)(it.t.row0 + row) * p.heads + it.head) * kTcTile, 512u, q_landed);
-        }
-        // rows still on their way if the consumers gave up: see them land before the CTA leaves
-        if (m >= 1) mbar_wait_bounded(q_landed, (m - 1) & 1u, ok ? p.status : nullptr);
-    } else {
-        // ================= MMA warp: one thread issues every tensor-core instruction ==================
+    } else if (warp == 9) {
+        // ================= S issuer: one thread issues the Q K^T products ==============================
+        // The tensor core takes the instructions of one thread in order, and every barrier poll between two
+        // batches leaves its queue empty for a few hundred cycles; with the S and the P V products coming
+        // from two threads, one's polls are covered by the other's queued instructions.
         if (lane == 0) {
-            const uint32_t idesc_s = tc_instr_desc(false), idesc_o = tc_instr_desc(true);
-            // Every operand descriptor is fixed for the CTA's lifetime except for the stage (0/1) of
-            // K and V, which only moves the address field: build them once, so that one MMA costs the
-            // issuing thread one instruction and a 32-bit add.
-            uint64_t dK[8], dV[8];
+            const uint32_t idesc_s = tc_instr_desc(false);
+            uint64_t dK[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t koff = (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32);
-                dK[j] = tc_smem_desc(smem_addr(sKV) + koff, 16, 1024);
-                // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
-                dV[j] = tc_smem_desc(smem_addr(sKV) + kTcTileBytes + j * 2048, kTcHalfBytes, 1024);
-            }
-            auto issue_qk = [&](uint32_t gn) {  // S[gn & 1] = (Qhi + Qlo) K^T with K in ring stage gn & 1
-                const uint64_t stage = (uint64_t)((gn & 1u) * (kTcStageBytes >> 4));  // address field counts 16-byte units
-                const uint32_t tS = tmem + (gn & 1u) * 128;
-                // Q: 16 dims = 8 TMEM columns per MMA, 64 columns of hi words, then 64 of lo words
-#pragma unroll
-                for (int j = 0; j < 16; ++j) tc_mma_ts(tS, tmem + kTcColQ + 8 * j, dK[j & 7] + stage, idesc_s, (uint32_t)j);
-                tc_commit(s_full(gn & 1u));
-                tc_commit(k_free(gn & 1u));
-            };
+            for (int j = 0; j < 8; ++j)
+                dK[j] = tc_smem_desc(smem_addr(sKV) + (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32), 16, 1024);
             uint32_t g = 0, m = 0;
             bool ok = true;
             for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
                 if (!mbar_wait_bounded(q_full, m & 1u, p.status)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
-                    const uint32_t gn = g + n;
-                    if (n == 0) {
-                        if (!mbar_wait_bounded(k_full(gn & 1u), (gn >> 1) & 1u, p.status)) { ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        issue_qk(gn);
-                    }
-                    if (n + 1 < it.n_steps) {  // next tile's scores, so the softmax never waits on the tensor core
-                        if (!mbar_wait_bounded(k_full((gn + 1) & 1u), ((gn + 1) >> 1) & 1u, p.status)) { ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        issue_qk(gn + 1);
-                    }
-                    if (!mbar_wait_bounded(v_full(gn & 1u), (gn >> 1) & 1u, p.status)) { ok = false; break; }
-                    if (!mbar_wait_bounded(p_full(gn & 1u), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    const uint32_t gn = g + n, b = gn & 1u;
+                    if (!mbar_wait_bounded(k_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    // S buffer b held P of the tile two back: the product that read it must have completed
+                    if (gn >= 2 && !mbar_wait_bounded(o_full(b), ((gn >> 1) - 1) & 1u, p.status)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t stage = (uint64_t)((gn & 1u) * (kTcStageBytes >> 4));
-                    const uint32_t tP = tmem + (gn & 1u) * 128, tO = tmem + kTcColO;
+                    const uint64_t stage = (uint64_t)(b * (kTcStageBytes >> 4));  // address field counts 16-byte units
+                    const uint32_t tS = tmem + b * 128;
+                    // Q: 16 dims = 8 TMEM columns per MMA, 64 columns of hi words, then 64 of lo words
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) tc_mma_ts(tS, tmem + kTcColQ + 8 * j, dK[j & 7] + stage, idesc_s, (uint32_t)j);
+                    tc_commit(s_full(b));
+                    tc_commit(k_free(b));
+                }
+                g += it.n_steps;
+            }
+            tc_commit(drained);
+            mbar_wait_bounded(drained, 0, p.status);
+        }
+        __syncwarp();
+    } else {
+        // ================= O issuer (warp 11): one thread issues the P V products ======================
+        if (lane == 0) {
+            const uint32_t idesc_o = tc_instr_desc(true);
+            uint64_t dV[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)  // V is [key][dim]: MN-major B operand; 64-dim halves are 16 KB apart (LBO), 8-key groups 1 KB (SBO)
+                dV[j] = tc_smem_desc(smem_addr(sKV) + kTcTileBytes + j * 2048, kTcHalfBytes, 1024);
+            uint32_t g = 0, m = 0;
+            bool ok = true;
+            for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+                for (int n = 0; n < it.n_steps; ++n) {
+                    const uint32_t gn = g + n, b = gn & 1u;
+                    if (!mbar_wait_bounded(v_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    if (!mbar_wait_bounded(p_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t stage = (uint64_t)(b * (kTcStageBytes >> 4));
+                    const uint32_t tP = tmem + b * 128, tO = tmem + kTcColO;
                     // P: 16 keys = 8 TMEM columns per MMA; every 32 keys hold their 16 hi words, then their 16 lo words.
                     // The accumulator carries over from tile to tile (the item's first product overwrites it).
                     tc_mma_ts(tO, tP, dV[0] + stage, idesc_o, (uint32_t)n);
@@ -648,14 +668,14 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                         const int hp = u >> 3, j = u & 7;
                         tc_mma_ts(tO, tP + (j >> 1) * 32 + hp * 16 + (j & 1) * 8, dV[j] + stage, idesc_o, 1u);
                     }
-                    tc_commit(o_full(gn & 1u));
-                    tc_commit(v_free(gn & 1u));
+                    tc_commit(o_full(b));
+                    tc_commit(v_free(b));
                 }
                 g += it.n_steps;
             }
-            // every MMA issued above has finished before the TMEM is released
-            tc_commit(drained);
-            mbar_wait_bounded(drained, 0, p.status);
+            // every product issued above has finished before the TMEM is released
+            tc_commit(drained2);
+            mbar_wait_bounded(drained2, 0, p.status);
         }
         __syncwarp();
     }
