@@ -176,6 +176,12 @@ __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* ma
         : "memory");
 }
 
+// shared -> global bulk copy of this thread's bulk-async group.  Both addresses and the size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy_s2g(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(__cvta_generic_to_global(dst)), "r"(src), "r"(bytes)
+                 : "memory");
+}
+
 struct PrefillMaps {
     CUtensorMap k, v;    // paged pool, as a [num_blocks * kv_heads * 16][128] bf16 matrix
     CUtensorMap tk, tv;  // text pool, same shape with text_blocks
@@ -183,8 +189,9 @@ struct PrefillMaps {
 
 
 constexpr int kTcSoftmaxThreads = 256;  // warps 0-7: warp w owns rows 32*(w%4).., key/dim half w/4
-constexpr int kTcThreads = 384;         // + warp 8 K producer, 9 S issuer and TMEM owner, 10 V producer, 11 O issuer
-constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchange (double-buffered) + row-sum exchange
+constexpr int kTcHelperThreads = 128;   // warps 8-11: thread r moves row r (Q in, output out)
+constexpr int kTcThreads = 512;         // + warp 12 K producer, 13 S issuer and TMEM owner, 14 V producer, 15 O issuer
+constexpr int kTcExchangeBytes = (2 * 2 * 128 + 2 * 2 * 128) * 4;  // row-max exchange (by tile parity) + row sums (by item parity)
 constexpr int kTcStages = 2;                                   // depth of the K and of the V ring
 constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;           // one K tile + one V tile
 constexpr uint32_t kTcQRowBytes = 528;                         // a staged fp32 row: 512 bytes + 16, so that row-owning and row-wide accesses are conflict-free
@@ -336,6 +343,12 @@ __device__ __forceinline__ TcItem tc_load_item(const PrefillParams& p, uint32_t 
     return it;
 }
 
+// Register budget of the roles (setmaxnreg): the kernel starts with 65536 / 512 = 128 registers per thread; the
+// issuing / producing warps and the helper warps hand most of theirs back, the softmax warps take them.
+#define UOCR_TC_REGS_SOFTMAX 168
+#define UOCR_TC_REGS_HELPER 104
+#define UOCR_TC_REGS_ISSUE 64
+
 __global__ void __launch_bounds__(kTcThreads, 1)
 rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMaps maps) {
     extern __shared__ uint8_t smem_raw[];
@@ -345,7 +358,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + kTcQStageBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 30);
     float* xmax = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [tile parity][half][row]
-    float* xsum = xmax + 2 * 2 * 128;                                                // [half][row]
+    float* xsum = xmax + 2 * 2 * 128;                                                // [item parity][half][row]
     const uint32_t bar0 = smem_addr(bars);
     // Ring and S/P barriers are indexed by the parity of the CTA's running key-tile count g; their phase is (g >> 1) & 1.
     auto k_full = [&](uint32_t b) { return bar0 + (0 + b) * 8; };   // TMA bytes of K stage b have landed
@@ -355,12 +368,16 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     auto s_full = [&](uint32_t b) { return bar0 + (8 + b) * 8; };   // S buffer b holds Q K^T
     auto p_full = [&](uint32_t b) { return bar0 + (10 + b) * 8; };  // all 256 softmax threads wrote their P over S buffer b
     auto o_full = [&](uint32_t b) { return bar0 + (12 + b) * 8; };  // the accumulator holds the products up to a tile of parity b
-    // One phase per item:
-    const uint32_t q_landed = bar0 + 14 * 8;    // the item's query rows are in the staging area (transaction bytes)
-    const uint32_t q_full = bar0 + 15 * 8;      // all softmax threads stored their part of Q in TMEM
-    const uint32_t sq_free = bar0 + 16 * 8;     // the staging area may take the next query rows (one phase per fetch)
-    const uint32_t out_staged = bar0 + 17 * 8;  // output rows staged in shared memory
-    const uint32_t drained = bar0 + 18 * 8, drained2 = bar0 + 19 * 8;  // the issuers' last instructions have completed
+    // Per item m.  A waiter can be one item behind the arrivals of q_full and l_ready, never two, so these are
+    // indexed by m & 1 with phase (m >> 1) & 1; the others are one barrier with phase m & 1.
+    const uint32_t q_landed = bar0 + 14 * 8;                          // the item's query rows are in the staging area
+    auto q_full = [&](uint32_t m) { return bar0 + (16 + (m & 1u)) * 8; };   // Q of item m is in TMEM
+    auto l_ready = [&](uint32_t m) { return bar0 + (18 + (m & 1u)) * 8; };  // the row sums of item m are in xsum
+    const uint32_t o_read = bar0 + 15 * 8;                            // the helpers hold item m's accumulator rows in registers
+    // A parity wait only tells a phase from its neighbours, so the helpers (who do not follow the key tiles) get
+    // the end of an item's S products and of its P V products as barriers of their own, one phase per item.
+    const uint32_t s_done = bar0 + 26 * 8, o_done = bar0 + 27 * 8;
+    const uint32_t drained = bar0 + 24 * 8, drained2 = bar0 + 25 * 8; // the issuers' last instructions have completed
     auto pair_bar = [&](int quad) { return bar0 + (20 + quad) * 8; };  // the two softmax warps of a lane quadrant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -375,18 +392,20 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             mbar_init(s_full(b), 1);
             mbar_init(p_full(b), kTcSoftmaxThreads);
             mbar_init(o_full(b), 1);
+            mbar_init(q_full(b), kTcHelperThreads);
+            mbar_init(l_ready(b), kTcSoftmaxThreads);
         }
-        mbar_init(q_landed, 1);
-        mbar_init(q_full, kTcSoftmaxThreads);
-        mbar_init(sq_free, kTcSoftmaxThreads);
-        mbar_init(out_staged, kTcSoftmaxThreads);
+        mbar_init(q_landed, kTcHelperThreads);
+        mbar_init(o_read, kTcHelperThreads);
+        mbar_init(s_done, 1);
+        mbar_init(o_done, 1);
         mbar_init(drained, 1);
         mbar_init(drained2, 1);
 #pragma unroll
         for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
         mbar_init_fence();
     }
-    if (warp == 9) {  // 512 TMEM columns: S/P buffers at 0 and 128, the accumulator at 256, Q at 384
+    if (warp == 13) {  // 512 TMEM columns: S/P buffers at 0 and 128, the accumulator at 256, Q at 384
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -395,79 +414,27 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
+    // Register hand-over: every warp of a warpgroup (warps 0-3, 4-7, 8-11, 12-15) executes the same instruction.
     if (warp < 8) {
         // ================= softmax warps ==============================================================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(UOCR_TC_REGS_SOFTMAX));
         const int quad = warp & 3, h = warp >> 2;  // TMEM lane quadrant; key half of S and dim half of O
         const int r = quad * 32 + lane;            // query row of the tile == TMEM lane
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const uint32_t tO = tmem + lane_base + kTcColO + h * 64;  // this thread's 64 dims of its accumulator row
-        const float4* my_q = reinterpret_cast<const float4*>(sQ + (size_t)r * kTcQRowBytes) + h * 16;
-        // Q rows of item `it` (staged as fp32 by the Q producer) -> bf16 hi/lo A operand in TMEM: lane = row,
-        // column c of a 64-column block = dims 2c, 2c+1.  The S MMAs of the previous item must have completed
-        // (its last s_full was waited for).  Returns once every thread has read its row.
-        auto convert_q = [&](const TcItem& it, uint32_t par) -> bool {
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_landed, par, p.status))) return false;
-            const bool live = r < it.t.rows;
-            const float s = p.scale_log2e;
-#pragma unroll
-            for (int g2 = 0; g2 < 2; ++g2) {  // 32 dims at a time: 16 hi words and 16 lo words
-                uint32_t hi[16], lo[16];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float4 v = live ? my_q[g2 * 8 + c] : make_float4(0.f, 0.f, 0.f, 0.f);
-                    tc_split2(v.x * s, v.y * s, hi[2 * c], lo[2 * c]);
-                    tc_split2(v.z * s, v.w * s, hi[2 * c + 1], lo[2 * c + 1]);
-                }
-                tc_st16(tmem + lane_base + kTcColQ + h * 32 + g2 * 16, hi);
-                tc_st16(tmem + lane_base + kTcColQ + 64 + h * 32 + g2 * 16, lo);
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(q_full);
-            return __all_sync(0xffffffffu, mbar_wait_bounded(q_full, par, p.status));
-        };
-
-        // The fp32 query rows of an item come into the staging area by one bulk copy per row, issued by the
-        // thread with the row's number once the area is free (every softmax thread has arrived on sq_free,
-        // thread 0 having announced the bytes before its own arrival).
-        auto announce_q = [&](const TcItem& it) {
-            if (tid == 0 && it.valid) mbar_arrive_expect_tx(q_landed, (uint32_t)it.t.rows * 512u);
-        };
-        auto fetch_q = [&](const TcItem& it, uint32_t free_par) -> bool {
-            if (!it.valid || warp >= 4) return true;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(sq_free, free_par, p.status))) return false;
-            if (tid < it.t.rows)
-                bulk_copy_g2s(smem_addr(sQ) + (uint32_t)tid * kTcQRowBytes,
-                              p.q + ((size_t)(it.t.row0 + tid) * p.heads + it.head) * kTcTile, 512u, q_landed);
-            return true;
-        };
-
         uint32_t g = 0;    // key tiles this CTA has gone through
         uint32_t itc = 0;  // items this CTA has gone through
         uint32_t pp = 0;   // rendezvous of the warp pair so far
-        uint32_t fq = 0;   // phases of sq_free so far
-        TcItem cur = tc_load_item(p, 0);
-        TcItem nxt = tc_load_item(p, 1);
         bool ok = true;
-        if (cur.valid) {
-            announce_q(cur);
-            mbar_arrive(sq_free);
-            ok = fetch_q(cur, fq++ & 1u);
-            if (ok) ok = convert_q(cur, 0);
-            if (ok) {  // the staging area can take the next item's rows
-                announce_q(nxt);
-                mbar_arrive(sq_free);
-                ok = fetch_q(nxt, fq++ & 1u);
-            }
-        }
-        while (cur.valid && ok) {
-            const TcItem nxt2 = tc_load_item(p, itc + 2);
+        for (TcItem cur = tc_load_item(p, 0); cur.valid && ok; cur = tc_load_item(p, ++itc)) {
             const PrefillTile& t = cur.t;
             const bool live = r < t.rows;
             const int i = t.pos0 + r;
             const int phi = !live ? 0 : (t.kind == 0 ? min(i + 1, cur.pfx) : cur.pfx);  // fixed-region tokens [0, phi)
             const int tlo = max(0, i - p.window + 1);
             const int thi = (live && t.kind == 1) ? i + 1 : 0;                           // text tokens [tlo, thi)
+            // Q of this item is in TMEM: the helpers have also taken the sums of the item before last out of xsum
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_full(itc), (itc >> 1) & 1u, p.status))) { ok = false; break; }
             float m_ref = -INFINITY, l_run = 0.f;
             for (int n = 0; n < cur.n_steps; ++n) {
                 const uint32_t gn = g + n, b = gn & 1u, par = (gn >> 1) & 1u;
@@ -500,71 +467,135 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 mbar_arrive(p_full(b));
             }
             if (!ok) break;
-            // The next item's Q goes to TMEM before this item's rows leave, so that its first scores are
-            // computed while the rows are on their way out (every S product of this item has completed).
-            if (nxt.valid) {
-                ok = convert_q(nxt, (itc + 1) & 1u);
-                if (!ok) break;
-            }
-            // ---- this thread's 64 dims of the row, the row sum over both key halves ----------------------
-            float acc[64];
-#pragma unroll
-            for (int d = 0; d < 64; ++d) acc[d] = 0.f;
-            if (cur.n_steps > 0) {
-                const uint32_t gl = g + cur.n_steps - 1;
-                if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(gl & 1u), (gl >> 1) & 1u, p.status))) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t o[64];
-                tc_ld64(tO, o);
-#pragma unroll
-                for (int d = 0; d < 64; ++d) acc[d] = __uint_as_float(o[d]);
-                // the accumulator is read: the next item's first product may overwrite it
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            }
-            xsum[h * 128 + r] = l_run;
-            ok = pair_sync(pair_bar(quad), pp & 1u, p.status);
-            ++pp;
-            if (!ok) break;
-            const float l_tot = l_run + xsum[(h ^ 1) * 128 + r];
-            // The rows go out through the staging area so that each warp writes whole 512-byte rows.  Rows are
-            // 528 bytes apart: conflict-free both for the row-owning writer and for the row-wide reader.
-            {
-                const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-                float4* so = reinterpret_cast<float4*>(sQ + (size_t)r * kTcQRowBytes) + h * 16;
-#pragma unroll
-                for (int c = 0; c < 16; ++c)
-                    so[c] = make_float4(acc[4 * c] * inv, acc[4 * c + 1] * inv, acc[4 * c + 2] * inv, acc[4 * c + 3] * inv);
-                ok = softmax_sync(out_staged, itc & 1u, p.status);
-                if (!ok) break;
-#pragma unroll 4
-                for (int k = 0; k < 16; ++k) {
-                    const int row = warp * 16 + k;
-                    if (row < t.rows) {
-                        const float4 o4 = reinterpret_cast<const float4*>(sQ + (size_t)row * kTcQRowBytes)[lane];
-                        const size_t at = ((size_t)(t.row0 + row) * p.heads + cur.head) * kTcTile;
-                        if (p.out_bf16)
-                            reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + at)[lane] =
-                                make_uint2(pack_bf16x2(o4.x, o4.y), pack_bf16x2(o4.z, o4.w));
-                        else
-                            reinterpret_cast<float4*>(p.out + at)[lane] = o4;
-                    }
-                }
-                // the rows have left the staging area: it takes the query rows of the item after next
-                announce_q(nxt2);
-                mbar_arrive(sq_free);
-                ok = fetch_q(nxt2, fq++ & 1u);
-                if (!ok) break;
-            }
+            // the row's sum over this thread's key half goes to the helper that writes the row out
+            xsum[((itc & 1u) * 2 + h) * 128 + r] = l_run;
+            mbar_arrive(l_ready(itc));
             g += cur.n_steps;
-            ++itc;
+        }
+    } else if (warp < 12) {
+        // ================= helper warps: Q into TMEM, accumulator rows out ==============================
+        // Thread r owns row r of the staging area for the whole kernel: it fetches the query row into it (one
+        // bulk copy), splits the row into the bf16 hi / lo operand in TMEM, later stages the finished output
+        // row there and sends it off with one bulk store -- so the staging area needs no barrier of its own.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(UOCR_TC_REGS_HELPER));
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        uint8_t* my_row = sQ + (size_t)r * kTcQRowBytes;
+        const uint32_t my_row_s = smem_addr(my_row);
+        auto fetch_q = [&](const TcItem& it) {  // this thread's share of the arrivals on q_landed, with its row's bytes
+            if (!it.valid) return;
+            if (r < it.t.rows) {
+                mbar_arrive_expect_tx(q_landed, 512u);
+                bulk_copy_g2s(my_row_s, p.q + ((size_t)(it.t.row0 + r) * p.heads + it.head) * kTcTile, 512u, q_landed);
+            } else {
+                mbar_arrive(q_landed);
+            }
+        };
+        // Q row of item m -> TMEM (lane = row, column c of a 64-column block = dims 2c, 2c+1; hi words, then lo words)
+        auto convert_q = [&](const TcItem& it, uint32_t m) -> bool {
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_landed, m & 1u, p.status))) return false;
+            const bool live = r < it.t.rows;
+            const float s = p.scale_log2e;
+            const float4* q4 = reinterpret_cast<const float4*>(my_row);
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {  // 32 dims at a time: 16 hi words and 16 lo words
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 v = live ? q4[g4 * 8 + c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    tc_split2(v.x * s, v.y * s, hi[2 * c], lo[2 * c]);
+                    tc_split2(v.z * s, v.w * s, hi[2 * c + 1], lo[2 * c + 1]);
+                }
+                tc_st16(tmem + lane_base + kTcColQ + g4 * 16, hi);
+                tc_st16(tmem + lane_base + kTcColQ + 64 + g4 * 16, lo);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(q_full(m));
+            return true;
+        };
+
+        uint32_t g = 0, m = 0;
+        TcItem cur = tc_load_item(p, 0);
+        TcItem nxt = tc_load_item(p, 1);
+        bool ok = true;
+        if (cur.valid) {
+            fetch_q(cur);
+            ok = convert_q(cur, 0);
+            if (ok) fetch_q(nxt);
+        }
+        while (cur.valid && ok) {
+            const TcItem nxt2 = tc_load_item(p, m + 2);
+            // ---- the next item's Q, as soon as this item's last scores have left the tensor core ----------
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_done, m & 1u, p.status))) { ok = false; break; }
+            if (nxt.valid) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                ok = convert_q(nxt, m + 1);
+                if (!ok) break;
+            }
+            // ---- this item's row: accumulator / row sum -> staging area -> global -------------------------
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(l_ready(m), (m >> 1) & 1u, p.status))) { ok = false; break; }
+            const float l_tot = xsum[((m & 1u) * 2 + 0) * 128 + r] + xsum[((m & 1u) * 2 + 1) * 128 + r];
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_done, m & 1u, p.status))) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                uint32_t o[64];
+                if (cur.n_steps > 0) {
+                    tc_ld64(tmem + lane_base + kTcColO + hh * 64, o);
+                } else {
+#pragma unroll
+                    for (int d = 0; d < 64; ++d) o[d] = 0u;
+                }
+                if (hh == 1) {  // both halves are in registers: the next item's first product may overwrite the accumulator
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(o_read);
+                }
+                if (p.out_bf16) {
+                    uint4* so = reinterpret_cast<uint4*>(my_row) + hh * 8;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        so[c] = make_uint4(pack_bf16x2(__uint_as_float(o[8 * c]) * inv, __uint_as_float(o[8 * c + 1]) * inv),
+                                           pack_bf16x2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv),
+                                           pack_bf16x2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv),
+                                           pack_bf16x2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv));
+                } else {
+                    float4* so = reinterpret_cast<float4*>(my_row) + hh * 16;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        so[c] = make_float4(__uint_as_float(o[4 * c]) * inv, __uint_as_float(o[4 * c + 1]) * inv,
+                                            __uint_as_float(o[4 * c + 2]) * inv, __uint_as_float(o[4 * c + 3]) * inv);
+                }
+            }
+            // this thread's generic-proxy stores -> the bulk store's reads
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (r < cur.t.rows) {
+                const size_t at = ((size_t)(cur.t.row0 + r) * p.heads + cur.head) * kTcTile;
+                if (p.out_bf16)
+                    bulk_copy_s2g(reinterpret_cast<uint16_t*>(p.out) + at, my_row_s, 256u);
+                else
+                    bulk_copy_s2g(p.out + at, my_row_s, 512u);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            // the row has been read out of the staging area: it takes the query row of the item after next
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            fetch_q(nxt2);
+            g += cur.n_steps;
+            ++m;
             cur = nxt;
             nxt = nxt2;
         }
-    } else if (warp == 8 || warp == 10) {
-        // ================= producer warps: warp 8 feeds K, warp 10 feeds V ============================
+        // the output rows are written before the kernel ends
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(UOCR_TC_REGS_ISSUE));
+    if (warp == 12 || warp == 14) {
+        // ================= producer warps: warp 12 feeds K, warp 14 feeds V ===========================
         // lane = (64-dim half, block of the tile).  The ring runs on across items, so the first tiles of the
         // next item are fetched while the current one finishes.
-        const int is_v = warp == 10 ? 1 : 0;
+        const int is_v = warp == 14 ? 1 : 0;
         const int blk_i = lane & 7, half = (lane >> 3) & 1;
         const int pool_rows = p.num_blocks * p.kv_heads * kBlockTokens;
         const int text_rows = p.text_blocks * p.kv_heads * kBlockTokens;
@@ -607,7 +638,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         // the last two stages may still be landing if a consumer gave up: wait for them before leaving
         for (uint32_t gn = issued >= 2 ? issued - 2 : 0; gn < issued; ++gn)
             mbar_wait_bounded(is_v ? v_full(gn & 1u) : k_full(gn & 1u), (gn >> 1) & 1u, p.status);
-    } else if (warp == 9) {
+    } else if (warp == 13) {
         // ================= S issuer: one thread issues the Q K^T products ==============================
         // The tensor core takes the instructions of one thread in order, and every barrier poll between two
         // batches leaves its queue empty for a few hundred cycles; with the S and the P V products coming
@@ -621,7 +652,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             uint32_t g = 0, m = 0;
             bool ok = true;
             for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
-                if (!mbar_wait_bounded(q_full, m & 1u, p.status)) { ok = false; break; }
+                if (!mbar_wait_bounded(q_full(m), (m >> 1) & 1u, p.status)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
                     const uint32_t gn = g + n, b = gn & 1u;
                     if (!mbar_wait_bounded(k_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
@@ -636,6 +667,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                     tc_commit(s_full(b));
                     tc_commit(k_free(b));
                 }
+                tc_commit(s_done);
                 g += it.n_steps;
             }
             tc_commit(drained);
@@ -643,7 +675,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         }
         __syncwarp();
     } else {
-        // ================= O issuer (warp 11): one thread issues the P V products ======================
+        // ================= O issuer (warp 15): one thread issues the P V products ======================
         if (lane == 0) {
             const uint32_t idesc_o = tc_instr_desc(true);
             uint64_t dV[8];
@@ -653,6 +685,8 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             uint32_t g = 0, m = 0;
             bool ok = true;
             for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+                // the item's first product overwrites the accumulator: the previous item's rows must have been read
+                if (m >= 1 && !mbar_wait_bounded(o_read, (m - 1) & 1u, p.status)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
                     const uint32_t gn = g + n, b = gn & 1u;
                     if (!mbar_wait_bounded(v_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
@@ -671,6 +705,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                     tc_commit(o_full(b));
                     tc_commit(v_free(b));
                 }
+                tc_commit(o_done);
                 g += it.n_steps;
             }
             // every product issued above has finished before the TMEM is released
@@ -679,10 +714,11 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         }
         __syncwarp();
     }
+    }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 13) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
