@@ -104,6 +104,7 @@ struct uocr_b200_workspace {
     int pieces_max = 0;
     uint32_t wait_limit = kWaitLimit;  // polls a tile wait may take (uocr_b200_workspace_set_wait_limit)
     PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
+    int* tile_order = nullptr;     // [max_rows] their indices, most key tiles first
     int tiles_cap = 0;
     bool out_bf16 = false;  // attention results are written as bf16 instead of fp32
     bool timing = false;
@@ -149,7 +150,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_cnt = o_ml + up(sizeof(float) * 4 * (size_t)ws->pieces_max);
     const size_t o_tiles = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
     ws->tiles_cap = max_rows;
-    ws->bytes = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
+    const size_t o_order = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
+    ws->bytes = o_order + up(sizeof(int) * (size_t)ws->tiles_cap);
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -169,6 +171,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
     ws->planned_ctas = ws->counters + ws->pieces_max;
     ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
+    ws->tile_order = reinterpret_cast<int*>(ws->base + o_order);
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -915,19 +918,8 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     if (int rc = device_info(&di)) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     static_assert(sizeof(uocr_b200_prefill_tile) == sizeof(PrefillTile), "tile descriptor layouts must match");
-    // Longest tiles first: CTAs are handed out in index order, so the short ones fill the tail.  The
-    // prefix length lives on the device; its share of a text tile's work is taken as the same for all.
-    std::vector<uocr_b200_prefill_tile> order(h_tiles, h_tiles + n_tiles);
-    auto key_tiles = [window](const uocr_b200_prefill_tile& t) {
-        const int last = t.pos0 + t.rows - 1;
-        if (t.kind == 0) return last / kTcTile + 1;
-        const int first = t.pos0 - window + 1 > 0 ? t.pos0 - window + 1 : 0;
-        return 9 + last / kTcTile - first / kTcTile + 1;
-    };
-    std::stable_sort(order.begin(), order.end(),
-                     [&](const uocr_b200_prefill_tile& a, const uocr_b200_prefill_tile& b) { return key_tiles(a) > key_tiles(b); });
-    // pageable source: the copy has read `order` when the call returns
-    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, order.data(), sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
+    // pageable source: the copy has read the descriptors when the call returns
+    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, h_tiles, sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
                "tile descriptors H2D");
     PrefillParams pp{};
     pp.q = q;
@@ -940,6 +932,7 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     pp.table = pv.table;
     pp.d_prefill_len = d_prefill_len;
     pp.tiles = ws->tiles;
+    pp.order = ws->tile_order;
     pp.n_tiles = n_tiles;
     pp.table_stride = pv.table_stride;
     pp.num_blocks = pv.num_blocks;
@@ -970,7 +963,10 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
         maps.tk = maps.k;
         maps.tv = maps.v;
     }
-    // persistent grid: one CTA per SM walks (tile, head) items
+    // The prefix lengths live on the device, so the tiles are ordered there (most key tiles first); then the
+    // persistent grid: one CTA per SM walks (tile, head) items dealt from that order
+    rswa_prefill_order_kernel<<<1, 256, 0, st>>>(pp, ws->tile_order);
+    if (int rc = after_launch("prefill tile order")) return rc;
     const long long n_items = (long long)n_tiles * heads;
     const int grid = (int)std::min<long long>(n_items, di->sms);
     rswa_prefill_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, st>>>(pp, maps);

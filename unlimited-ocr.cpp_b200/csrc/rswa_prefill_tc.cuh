@@ -58,6 +58,7 @@ struct PrefillParams {
     const int32_t* table;
     const int* d_prefill_len;
     const PrefillTile* tiles;
+    const int* order;  // tile indices, most key tiles first (rswa_prefill_order_kernel)
     int table_stride, num_blocks, text_blocks;
     int n_tiles;
     int heads, kv_heads, group, window;
@@ -251,11 +252,31 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
                                                 float& alpha) {
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
+    // Of this thread's 64 keys the visible ones are [lo, hi).  A partly visible tile is handled in chunks of 16
+    // keys, classified for the whole warp: every lane sees the whole chunk (bit in `all`: no per-key tests), no
+    // lane sees any of it (bit in `none`: zeros, no exponentials), or mixed (per-key tests).  The rows of a warp
+    // are consecutive positions, so at most three of a causal or window edge's chunks are mixed.
+    const int lo = vlo - h * 64, hi = vhi - h * 64;
+    uint32_t all = 0xfu, none = 0u;
+    if (!FULL) {
+        all = 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            all |= (__all_sync(0xffffffffu, lo <= q * 16 && hi >= q * 16 + 16) ? 1u : 0u) << q;
+            none |= (__all_sync(0xffffffffu, hi <= q * 16 || lo >= q * 16 + 16) ? 1u : 0u) << q;
+        }
+    }
     float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 64; ++j) {
-        const int key = h * 64 + j;
-        if (FULL || (key >= vlo && key < vhi)) mx = fmaxf(mx, __uint_as_float(s[j]));
+    for (int q = 0; q < 4; ++q) {
+        if (FULL || ((all >> q) & 1u)) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(s[q * 16 + j]));
+        } else if (!((none >> q) & 1u)) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (q * 16 + j >= lo && q * 16 + j < hi) mx = fmaxf(mx, __uint_as_float(s[q * 16 + j]));
+        }
     }
     *my_max = mx;
     // also: both halves of S are in registers from here on, P may overwrite them
@@ -273,16 +294,29 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     for (int qq = 0; qq < 2; ++qq) {  // 32 keys at a time: their 16 hi words, then their 16 lo words, over their own columns
         uint32_t pk[32];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            float pr[2];
+        for (int c = 0; c < 2; ++c) {
+            const int q = qq * 2 + c;
+            if (FULL || ((all >> q) & 1u)) {
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int key = h * 64 + qq * 32 + 2 * e + u;
-                const bool valid = FULL || (key >= vlo && key < vhi);
-                pr[u] = valid ? tc_exp2(__uint_as_float(s[qq * 32 + 2 * e + u]) - m_safe) : 0.f;
-                lsum += pr[u];
+                for (int e = 0; e < 8; ++e) {
+                    const float p0 = tc_exp2(__uint_as_float(s[q * 16 + 2 * e]) - m_safe);
+                    const float p1 = tc_exp2(__uint_as_float(s[q * 16 + 2 * e + 1]) - m_safe);
+                    lsum += p0 + p1;
+                    tc_split2(p0, p1, pk[c * 8 + e], pk[16 + c * 8 + e]);
+                }
+            } else if ((none >> q) & 1u) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) pk[c * 8 + e] = pk[16 + c * 8 + e] = 0u;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int k0 = q * 16 + 2 * e;
+                    const float p0 = (k0 >= lo && k0 < hi) ? tc_exp2(__uint_as_float(s[k0]) - m_safe) : 0.f;
+                    const float p1 = (k0 + 1 >= lo && k0 + 1 < hi) ? tc_exp2(__uint_as_float(s[k0 + 1]) - m_safe) : 0.f;
+                    lsum += p0 + p1;
+                    tc_split2(p0, p1, pk[c * 8 + e], pk[16 + c * 8 + e]);
+                }
             }
-            tc_split2(pr[0], pr[1], pk[e], pk[16 + e]);
         }
         tc_st32(tS + h * 64 + qq * 32, pk);
     }
@@ -316,7 +350,48 @@ struct TcItem {
     bool valid;
 };
 
-// The j-th item of this CTA.  Items are numbered tile-major (the host orders the tiles longest first), heads
+// Key tiles the rows of query tile t can see: the fixed region (causal for vision rows), then, for text rows,
+// the text window.
+__device__ __forceinline__ void tc_tile_steps(const PrefillTile& t, int pfx, int window, int& n_prefix_tiles, int& text_tile0, int& n_steps) {
+    const int plim = t.kind == 0 ? min(t.pos0 + t.rows, pfx) : pfx;
+    n_prefix_tiles = (plim + kTcTile - 1) / kTcTile;
+    text_tile0 = 0;
+    int n_text_tiles = 0;
+    if (t.kind == 1) {
+        text_tile0 = max(0, t.pos0 - window + 1) / kTcTile;
+        n_text_tiles = (t.pos0 + t.rows - 1) / kTcTile - text_tile0 + 1;
+    }
+    n_steps = n_prefix_tiles + n_text_tiles;
+}
+
+// Orders the query tiles by their number of key tiles, most first (a counting sort in one CTA; the order within
+// one count is arbitrary).  The persistent grid deals (tile, head) items from this order.
+constexpr int kTcOrderBins = 256;
+__global__ void __launch_bounds__(256) rswa_prefill_order_kernel(const PrefillParams p, int* order) {
+    __shared__ int hist[kTcOrderBins];
+    auto steps_of = [&](int i) {
+        const PrefillTile t = p.tiles[i];
+        int a, b, n;
+        tc_tile_steps(t, max(__ldg(p.d_prefill_len + t.slot), 0), p.window, a, b, n);
+        return min(n, kTcOrderBins - 1);
+    };
+    for (int i = threadIdx.x; i < kTcOrderBins; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) atomicAdd(&hist[steps_of(i)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {  // first index of each count, largest count first
+        int at = 0;
+        for (int b = kTcOrderBins - 1; b >= 0; --b) {
+            const int n = hist[b];
+            hist[b] = at;
+            at += n;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) order[atomicAdd(&hist[steps_of(i)], 1)] = i;
+}
+
+// The j-th item of this CTA.  Items are numbered tile-major in the order of rswa_prefill_order_kernel, heads
 // innermost, and dealt to the CTAs in rounds that alternate direction, so that every CTA's items add up to
 // about the same number of key tiles.  Every role of the CTA walks the same sequence.
 __device__ __forceinline__ TcItem tc_load_item(const PrefillParams& p, uint32_t j) {
@@ -329,17 +404,9 @@ __device__ __forceinline__ TcItem tc_load_item(const PrefillParams& p, uint32_t 
     const int ti = (int)(k / p.heads);
     it.head = (int)(k - (long long)ti * p.heads);
     it.kvh = it.head / p.group;
-    it.t = p.tiles[ti];
+    it.t = p.tiles[__ldg(p.order + ti)];
     it.pfx = max(__ldg(p.d_prefill_len + it.t.slot), 0);
-    const int plim = it.t.kind == 0 ? min(it.t.pos0 + it.t.rows, it.pfx) : it.pfx;
-    it.n_prefix_tiles = (plim + kTcTile - 1) / kTcTile;
-    it.text_tile0 = 0;
-    int n_text_tiles = 0;
-    if (it.t.kind == 1) {
-        it.text_tile0 = max(0, it.t.pos0 - p.window + 1) / kTcTile;
-        n_text_tiles = (it.t.pos0 + it.t.rows - 1) / kTcTile - it.text_tile0 + 1;
-    }
-    it.n_steps = it.n_prefix_tiles + n_text_tiles;
+    tc_tile_steps(it.t, it.pfx, p.window, it.n_prefix_tiles, it.text_tile0, it.n_steps);
     return it;
 }
 
