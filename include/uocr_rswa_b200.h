@@ -306,10 +306,17 @@ UOCR_B200_API int uocr_b200_rswa_text_scatter_fill_paged(
  *           the semantics of uocr_b200_rswa_prefill_text_paged.
  * K/V must already be in the pools (uocr_b200_rswa_write_prefill_ragged_paged for the fixed
  * region, uocr_b200_rswa_text_scatter_paged for the text).  Same results as the CUDA-core entry
- * points within the attention tolerance.  The call sorts the tiles (longest first), copies them from
- * pageable host memory and encodes tensor maps on the host, so it cannot be part of a stream capture
- * (ragged prefill shapes change from call to call anyway); unwritten rows of the pools that fall
- * into a fetched block must hold finite values (they are masked, but a NaN times zero is a NaN). */
+ * points within the attention tolerance.  One persistent CTA per SM draws (tile, head) items from a
+ * plan: the tiles ordered by the number of key tiles their rows see, most first.  The plan is made
+ * on the device (the prefix lengths live there) by uocr_b200_rswa_prefill_plan_tc, or by this call
+ * itself when h_tiles is given; with h_tiles == NULL the call reuses the workspace's last plan, which
+ * must be for n_tiles tiles and this window and stays valid while the slots' prefix lengths are
+ * unchanged (the layers of one forward pass share one plan).  uocr_b200_workspace_prefill_plan_serial
+ * counts the plans made on a workspace, for callers that need to know theirs is still the last.
+ * Planning copies the tiles from pageable host memory and the call encodes tensor maps on the host,
+ * so neither can be part of a stream capture (ragged prefill shapes change from call to call
+ * anyway); unwritten rows of the pools that fall into a fetched block must hold finite values (they
+ * are masked, but a NaN times zero is a NaN). */
 typedef struct {
     int32_t row0;   /* first packed row of the tile */
     int32_t rows;   /* 1..128 */
@@ -322,6 +329,10 @@ UOCR_B200_API int uocr_b200_rswa_prefill_attention_tc(
     const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool, int text_blocks,
     const float* q, const int* d_prefill_len, const uocr_b200_prefill_tile* h_tiles, int n_tiles,
     int window, int heads, float* out, uocr_b200_workspace* ws, uocr_b200_stream_t stream);
+UOCR_B200_API int uocr_b200_rswa_prefill_plan_tc(const uocr_b200_prefill_tile* h_tiles, int n_tiles,
+                                                 const int* d_prefill_len, int window, uocr_b200_workspace* ws,
+                                                 uocr_b200_stream_t stream);
+UOCR_B200_API unsigned uocr_b200_workspace_prefill_plan_serial(const uocr_b200_workspace* ws);
 
 /* One decode step of one layer in a single launch: the batched ring append of
  * uocr::cuda::rswa_append_decode_batch followed by uocr::cuda::rswa_attention_batch (the pair issued

@@ -174,7 +174,17 @@ def test_prefill_tensor_core_bf16_output(orc, b):
     b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles, W, heads, out32, ws)
     ws.set_out_dtype(b.BF16)
     out16 = torch.full((P + T, heads * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-    b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles, W, heads, out16, ws)
+    serial = b.lib().uocr_b200_workspace_prefill_plan_serial(ws.h)
+    # the second call shares the first call's plan of the tiles
+    b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles, W, heads, out16, ws, reuse_plan=True)
+    assert b.lib().uocr_b200_workspace_prefill_plan_serial(ws.h) == serial
     a, c = out32.cpu().numpy(), out16.float().cpu().numpy()
     assert np.isfinite(a).all() and np.array_equal(c, synth.round_bf16(a))  # same kernel, same fp32 values, RNE
+    # a plan made on its own serves as well; without a matching plan the call is refused
+    assert b.prefill_plan_tc(tiles, pb.d_prefill, W, ws) == serial + 1
+    out16.fill_(float("nan"))
+    b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles, W, heads, out16, ws, reuse_plan=True)
+    assert np.array_equal(out16.float().cpu().numpy(), c)
+    with pytest.raises(b.Error):
+        b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles[:-1], W, heads, out16, ws, reuse_plan=True)
     assert ws.status() == 0

@@ -90,6 +90,8 @@ _SIGS = {
     "uocr_b200_rswa_text_scatter_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 4 + [_i, _vp, _vp]),
     "uocr_b200_rswa_text_scatter_fill_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 9 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_prefill_attention_tc": (_i, [C.POINTER(PagedKV), _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "uocr_b200_rswa_prefill_plan_tc": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
+    "uocr_b200_workspace_prefill_plan_serial": (C.c_uint, [_vp]),
     "uocr_b200_rswa_ring_fill_paged": (_i, [C.POINTER(PagedKV), _vp, _vp, _i] + [_vp] * 7 + [_i, _i, _vp, _vp]),
     "uocr_b200_rswa_decode_step_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 7 + [_i, _i, _i, _vp, _vp, _vp]),
     "uocr_b200_rswa_decode_step_rope_paged": (_i, [C.POINTER(PagedKV)] + [_vp] * 4 + [C.c_float] + [_vp] * 4 +
@@ -311,13 +313,23 @@ def text_scatter_fill_paged(layer, text_k, text_v, text_blocks, k, v, d_slots, d
                                                         stream_handle(stream)))
 
 
-def prefill_attention_tc(layer, text_k, text_v, text_blocks, q, d_prefill, tiles, window, heads, out, ws, stream=None):
-    """tiles: int32 numpy array [n, 6] = (row0, rows, slot, kind, pos0, block0) per query tile (host)."""
+def prefill_attention_tc(layer, text_k, text_v, text_blocks, q, d_prefill, tiles, window, heads, out, ws, stream=None,
+                         reuse_plan=False):
+    """tiles: int32 numpy array [n, 6] = (row0, rows, slot, kind, pos0, block0) per query tile (host).
+    reuse_plan: the workspace already holds the plan of exactly these tiles (prefill_plan_tc, or an earlier call)."""
     import numpy as np
     t = np.ascontiguousarray(tiles, dtype=np.int32)
     check(lib().uocr_b200_rswa_prefill_attention_tc(layer.ref(), _p(text_k), _p(text_v), text_blocks, _p(q),
-                                                     _p(d_prefill), t.ctypes.data, t.shape[0], window, heads, _p(out),
-                                                     ws.h, stream_handle(stream)))
+                                                     _p(d_prefill), None if reuse_plan else t.ctypes.data, t.shape[0], window,
+                                                     heads, _p(out), ws.h, stream_handle(stream)))
+
+
+def prefill_plan_tc(tiles, d_prefill, window, ws, stream=None):
+    """Uploads and orders the query tiles once; later prefill_attention_tc(..., reuse_plan=True) calls share the plan."""
+    import numpy as np
+    t = np.ascontiguousarray(tiles, dtype=np.int32)
+    check(lib().uocr_b200_rswa_prefill_plan_tc(t.ctypes.data, t.shape[0], _p(d_prefill), window, ws.h, stream_handle(stream)))
+    return lib().uocr_b200_workspace_prefill_plan_serial(ws.h)
 
 
 def make_prefill_tiles(requests):

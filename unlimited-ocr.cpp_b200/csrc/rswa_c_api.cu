@@ -104,7 +104,12 @@ struct uocr_b200_workspace {
     int pieces_max = 0;
     uint32_t wait_limit = kWaitLimit;  // polls a tile wait may take (uocr_b200_workspace_set_wait_limit)
     PrefillTile* tiles = nullptr;  // [max_rows] query-tile descriptors of the tensor-core prefill
-    int* tile_order = nullptr;     // [max_rows] their indices, most key tiles first
+    TcWork* tile_work = nullptr;   // [max_rows] the same tiles, most key tiles first, with their key-tile counts
+    int* item_counter = nullptr;   // items the persistent prefill grid has handed out beyond every CTA's first
+    int plan_tiles = 0;            // tiles of the plan in tile_work (0: none)
+    int plan_window = 0;
+    bool plan_any_text = false;
+    unsigned plan_serial = 0;      // plans made on this workspace so far
     int tiles_cap = 0;
     bool out_bf16 = false;  // attention results are written as bf16 instead of fp32
     bool timing = false;
@@ -151,7 +156,7 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     const size_t o_tiles = o_cnt + up(sizeof(int) * ((size_t)ws->pieces_max + 64));
     ws->tiles_cap = max_rows;
     const size_t o_order = o_tiles + up(sizeof(PrefillTile) * (size_t)ws->tiles_cap);
-    ws->bytes = o_order + up(sizeof(int) * (size_t)ws->tiles_cap);
+    ws->bytes = o_order + up(sizeof(TcWork) * (size_t)ws->tiles_cap) + 256;
     cudaError_t e = cudaMalloc(&ws->base, ws->bytes);
     if (e != cudaSuccess) {
         delete ws;
@@ -171,7 +176,8 @@ int uocr_b200_workspace_create(int max_rows, uocr_b200_workspace** out) {
     ws->counters = reinterpret_cast<int*>(ws->base + o_cnt);
     ws->planned_ctas = ws->counters + ws->pieces_max;
     ws->tiles = reinterpret_cast<PrefillTile*>(ws->base + o_tiles);
-    ws->tile_order = reinterpret_cast<int*>(ws->base + o_order);
+    ws->tile_work = reinterpret_cast<TcWork*>(ws->base + o_order);
+    ws->item_counter = reinterpret_cast<int*>(ws->base + o_order + up(sizeof(TcWork) * (size_t)ws->tiles_cap));
     *out = ws;
     return UOCR_B200_OK;
 }
@@ -891,6 +897,45 @@ static int make_kv_map(CUtensorMap* map, const void* pool, long rows) {
     return UOCR_B200_OK;
 }
 
+// Uploads the tile descriptors and orders them on the device (the prefix lengths live there).
+static int prefill_plan(const uocr_b200_prefill_tile* h_tiles, int n_tiles, const int* d_prefill_len, int window,
+                        uocr_b200_workspace* ws, cudaStream_t st, const char* who) {
+    if (!h_tiles || !d_prefill_len || !ws) return fail(UOCR_B200_ERR_INVALID, std::string(who) + ": null pointer");
+    if (n_tiles <= 0 || window <= 0) return fail(UOCR_B200_ERR_INVALID, std::string(who) + ": tile count and window must be positive");
+    if (n_tiles > ws->tiles_cap) return fail(UOCR_B200_ERR_WORKSPACE, std::string(who) + ": more tiles than the workspace holds");
+    bool any_text = false;
+    for (int i = 0; i < n_tiles; ++i) {
+        const uocr_b200_prefill_tile& t = h_tiles[i];
+        if (t.rows < 1 || t.rows > kTcTile || t.row0 < 0 || t.slot < 0 || t.pos0 < 0 || (t.kind != 0 && t.kind != 1))
+            return fail(UOCR_B200_ERR_INVALID, std::string(who) + ": bad tile descriptor");
+        any_text |= t.kind == 1;
+    }
+    static_assert(sizeof(uocr_b200_prefill_tile) == sizeof(PrefillTile), "tile descriptor layouts must match");
+    ws->plan_tiles = 0;
+    // pageable source: the copy has read the descriptors when the call returns
+    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, h_tiles, sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
+               "tile descriptors H2D");
+    PrefillParams pp{};
+    pp.tiles = ws->tiles;
+    pp.n_tiles = n_tiles;
+    pp.d_prefill_len = d_prefill_len;
+    pp.window = window;
+    rswa_prefill_order_kernel<<<1, 256, 0, st>>>(pp, ws->tile_work);
+    if (int rc = after_launch("prefill tile order")) return rc;
+    ws->plan_tiles = n_tiles;
+    ws->plan_window = window;
+    ws->plan_any_text = any_text;
+    ++ws->plan_serial;
+    return UOCR_B200_OK;
+}
+
+unsigned uocr_b200_workspace_prefill_plan_serial(const uocr_b200_workspace* ws) { return ws ? ws->plan_serial : 0u; }
+
+int uocr_b200_rswa_prefill_plan_tc(const uocr_b200_prefill_tile* h_tiles, int n_tiles, const int* d_prefill_len, int window,
+                                   uocr_b200_workspace* ws, uocr_b200_stream_t stream) {
+    return prefill_plan(h_tiles, n_tiles, d_prefill_len, window, ws, reinterpret_cast<cudaStream_t>(stream), "prefill_plan_tc");
+}
+
 int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void* text_k_pool, const void* text_v_pool,
                                         int text_blocks, const float* q, const int* d_prefill_len,
                                         const uocr_b200_prefill_tile* h_tiles, int n_tiles, int window, int heads,
@@ -900,27 +945,22 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     if (int rc = paged_view(kv, &pv)) return rc;
     if (kv->dtype != UOCR_B200_BF16 || kv->head_dim != kTcTile)
         return fail(UOCR_B200_ERR_UNSUPPORTED, "prefill_attention_tc: needs bf16 KV and head_dim 128");
-    if (!q || !out || !d_prefill_len || !h_tiles || !ws) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: null pointer");
+    if (!q || !out || !d_prefill_len || !ws) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: null pointer");
     if (!aligned16(q) || !aligned16(out)) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: q/out must be 16-byte aligned");
     if (heads <= 0 || heads % kv->kv_heads != 0) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: heads must be a multiple of kv_heads");
     if (window <= 0) return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: window must be positive");
-    if (n_tiles > ws->tiles_cap) return fail(UOCR_B200_ERR_WORKSPACE, "prefill_attention_tc: more tiles than the workspace holds");
-    bool any_text = false;
-    for (int i = 0; i < n_tiles; ++i) {
-        const uocr_b200_prefill_tile& t = h_tiles[i];
-        if (t.rows < 1 || t.rows > kTcTile || t.row0 < 0 || t.slot < 0 || t.pos0 < 0 || (t.kind != 0 && t.kind != 1))
-            return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: bad tile descriptor");
-        any_text |= t.kind == 1;
-    }
-    if (any_text && (!text_k_pool || !text_v_pool || text_blocks <= 0))
-        return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: text tiles need the text pool");
     const DeviceInfo* di = nullptr;
     if (int rc = device_info(&di)) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    static_assert(sizeof(uocr_b200_prefill_tile) == sizeof(PrefillTile), "tile descriptor layouts must match");
-    // pageable source: the copy has read the descriptors when the call returns
-    CHECK_CUDA(cudaMemcpyAsync(ws->tiles, h_tiles, sizeof(PrefillTile) * (size_t)n_tiles, cudaMemcpyHostToDevice, st),
-               "tile descriptors H2D");
+    if (h_tiles) {
+        if (int rc = prefill_plan(h_tiles, n_tiles, d_prefill_len, window, ws, st, "prefill_attention_tc")) return rc;
+    } else if (ws->plan_tiles != n_tiles || ws->plan_window != window) {
+        return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: no tiles given and the workspace holds no plan of this size and window");
+    }
+    if (ws->plan_any_text && (!text_k_pool || !text_v_pool || text_blocks <= 0))
+        return fail(UOCR_B200_ERR_INVALID, "prefill_attention_tc: text tiles need the text pool");
+    const bool any_text = ws->plan_any_text;
+    CHECK_CUDA(cudaMemsetAsync(ws->item_counter, 0, sizeof(int), st), "prefill item counter");
     PrefillParams pp{};
     pp.q = q;
     pp.out = out;
@@ -932,7 +972,8 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     pp.table = pv.table;
     pp.d_prefill_len = d_prefill_len;
     pp.tiles = ws->tiles;
-    pp.order = ws->tile_order;
+    pp.work = ws->tile_work;
+    pp.counter = ws->item_counter;
     pp.n_tiles = n_tiles;
     pp.table_stride = pv.table_stride;
     pp.num_blocks = pv.num_blocks;
@@ -963,10 +1004,7 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
         maps.tk = maps.k;
         maps.tv = maps.v;
     }
-    // The prefix lengths live on the device, so the tiles are ordered there (most key tiles first); then the
-    // persistent grid: one CTA per SM walks (tile, head) items dealt from that order
-    rswa_prefill_order_kernel<<<1, 256, 0, st>>>(pp, ws->tile_order);
-    if (int rc = after_launch("prefill tile order")) return rc;
+    // the persistent grid: one CTA per SM draws (tile, head) items in the plan's order
     const long long n_items = (long long)n_tiles * heads;
     const int grid = (int)std::min<long long>(n_items, di->sms);
     rswa_prefill_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, st>>>(pp, maps);

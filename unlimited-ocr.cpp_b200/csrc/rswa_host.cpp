@@ -897,6 +897,7 @@ struct PagedBatchKV::Impl {
     int* d_pf = nullptr;  // [v_slots nv][v_pos nv][t_slots nt][t_pos nt][t_block0 nt][t_len nt]
     int pf_cap = 0, pf_nv = 0, pf_nt = 0;
     std::vector<uocr_b200_prefill_tile> pf_tiles;
+    unsigned pf_plan_serial = 0;  // the workspace's plan count after this prefill's plan was made (0: not planned yet)
     int ws_rows = 0;
     // snapshot export: manifest entries written so far, per directory (tensor name -> "file/shape" json)
     std::map<std::string, std::map<std::string, std::string>> manifests;
@@ -1247,6 +1248,7 @@ int PagedBatchKV::plan_windowed_prefill(const std::vector<WindowedPrefill>& reqs
     int* t_b0 = t_pos + nt;
     int* t_len = t_b0 + nt;
     s.pf_tiles.clear();
+    s.pf_plan_serial = 0;
     auto add_tiles = [&](int row0, int n, int slot, int kind, int block0) {
         for (int a = 0; a < n; a += 128) s.pf_tiles.push_back({row0 + a, std::min(128, n - a), slot, kind, a, block0});
     };
@@ -1322,9 +1324,14 @@ void PagedBatchKV::windowed_prefill_layer(int layer, const float* q, const float
             abi_ok(uocr_b200_rswa_text_scatter_fill_paged(view, s.text_k, s.text_v, s.text_blocks, kt, vt, t_slots, t_pos, t_b0, t_len,
                                                           s.d_prefill, d_len(layer), d_ring_pos(layer), nt, s.cfg.window, s.ws, stream),
                    "windowed prefill: text scatter + ring fill");
-        abi_ok(uocr_b200_rswa_prefill_attention_tc(view, s.text_k, s.text_v, s.text_blocks, q, s.d_prefill, s.pf_tiles.data(),
-                                                   static_cast<int>(s.pf_tiles.size()), s.cfg.window, heads, out, s.ws, stream),
+        // the layers of one prefill share one plan of the query tiles (made by the first call, reused while it is
+        // still the workspace's last)
+        const bool planned = s.pf_plan_serial != 0 && s.pf_plan_serial == uocr_b200_workspace_prefill_plan_serial(s.ws);
+        abi_ok(uocr_b200_rswa_prefill_attention_tc(view, s.text_k, s.text_v, s.text_blocks, q, s.d_prefill,
+                                                   planned ? nullptr : s.pf_tiles.data(), static_cast<int>(s.pf_tiles.size()),
+                                                   s.cfg.window, heads, out, s.ws, stream),
                "windowed prefill: attention");
+        s.pf_plan_serial = uocr_b200_workspace_prefill_plan_serial(s.ws);
     } else {
         for (int a = 0; a < nv; a += s.ws_rows) {  // the split-KV scratch holds ws_rows query rows per call
             const int n = std::min(s.ws_rows, nv - a);

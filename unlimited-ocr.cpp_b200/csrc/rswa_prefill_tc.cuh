@@ -47,6 +47,7 @@ struct PrefillTile {
     int block0;  // kind 1: first block of the request's tokens in the text pool
 };
 
+struct TcWork;
 struct PrefillParams {
     const float* q;
     float* out;
@@ -58,7 +59,8 @@ struct PrefillParams {
     const int32_t* table;
     const int* d_prefill_len;
     const PrefillTile* tiles;
-    const int* order;  // tile indices, most key tiles first (rswa_prefill_order_kernel)
+    const struct TcWork* work;  // the tiles with their key-tile counts, most key tiles first (rswa_prefill_order_kernel)
+    int* counter;               // items handed out beyond every CTA's first (zero at launch)
     int table_stride, num_blocks, text_blocks;
     int n_tiles;
     int heads, kv_heads, group, window;
@@ -197,7 +199,7 @@ constexpr int kTcStages = 2;                                   // depth of the K
 constexpr uint32_t kTcStageBytes = 2 * kTcTileBytes;           // one K tile + one V tile
 constexpr uint32_t kTcQRowBytes = 528;                         // a staged fp32 row: 512 bytes + 16, so that row-owning and row-wide accesses are conflict-free
 constexpr uint32_t kTcQStageBytes = 128 * kTcQRowBytes;
-constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + kTcQStageBytes + 256 + kTcExchangeBytes + 1024;  // K/V ring, Q / output staging, barriers, exchange, alignment slack
+constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + kTcQStageBytes + 512 + 512 + kTcExchangeBytes + 1024;  // K/V ring, Q / output staging, barriers, item ring, exchange, alignment slack
 
 // 64 consecutive TMEM columns of this thread's lane into registers: two loads, one wait.  The wait
 // and the empty statement after it name the registers so that no use can be scheduled before them.
@@ -339,16 +341,26 @@ __device__ __forceinline__ void tc_rescale(uint32_t tO, float alpha) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// One work item of the persistent grid: a query tile and a head, with the key tiles its rows can see.
-struct TcItem {
+// A query tile with the key tiles its rows can see, as the ordering kernel leaves it for the persistent grid.
+struct TcWork {
     PrefillTile t;
-    int head, kvh;
     int pfx;             // the slot's fixed-region length
     int n_prefix_tiles;  // key tiles in the fixed region, then (text rows) in the text window from tile text_tile0
     int text_tile0;
     int n_steps;
+    int pad[2];
+};
+static_assert(sizeof(TcWork) == 48, "three 16-byte loads");
+
+// One work item of the persistent grid: a query tile and a head.
+struct TcItem {
+    PrefillTile t;
+    int head, kvh;
+    int pfx, n_prefix_tiles, text_tile0, n_steps;
     bool valid;
 };
+constexpr int kTcItemSlots = 8;  // items the CTA's scheduler may have published and not every role has read
+constexpr int kTcItemInts = 16;  // ints per published item
 
 // Key tiles the rows of query tile t can see: the fixed region (causal for vision rows), then, for text rows,
 // the text window.
@@ -365,19 +377,22 @@ __device__ __forceinline__ void tc_tile_steps(const PrefillTile& t, int pfx, int
 }
 
 // Orders the query tiles by their number of key tiles, most first (a counting sort in one CTA; the order within
-// one count is arbitrary).  The persistent grid deals (tile, head) items from this order.
+// one count is arbitrary), and leaves each with its counts in `work`.  The persistent grid hands out (tile, head)
+// items in this order, heads innermost: CTA c starts with item c, the counter (zero at launch) gives the rest.
 constexpr int kTcOrderBins = 256;
-__global__ void __launch_bounds__(256) rswa_prefill_order_kernel(const PrefillParams p, int* order) {
+__global__ void __launch_bounds__(256) rswa_prefill_order_kernel(const PrefillParams p, TcWork* work) {
     __shared__ int hist[kTcOrderBins];
-    auto steps_of = [&](int i) {
-        const PrefillTile t = p.tiles[i];
-        int a, b, n;
-        tc_tile_steps(t, max(__ldg(p.d_prefill_len + t.slot), 0), p.window, a, b, n);
-        return min(n, kTcOrderBins - 1);
+    auto work_of = [&](int i) {
+        TcWork w;
+        w.t = p.tiles[i];
+        w.pfx = max(__ldg(p.d_prefill_len + w.t.slot), 0);
+        tc_tile_steps(w.t, w.pfx, p.window, w.n_prefix_tiles, w.text_tile0, w.n_steps);
+        w.pad[0] = w.pad[1] = 0;
+        return w;
     };
     for (int i = threadIdx.x; i < kTcOrderBins; i += blockDim.x) hist[i] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) atomicAdd(&hist[steps_of(i)], 1);
+    for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) atomicAdd(&hist[min(work_of(i).n_steps, kTcOrderBins - 1)], 1);
     __syncthreads();
     if (threadIdx.x == 0) {  // first index of each count, largest count first
         int at = 0;
@@ -388,26 +403,10 @@ __global__ void __launch_bounds__(256) rswa_prefill_order_kernel(const PrefillPa
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) order[atomicAdd(&hist[steps_of(i)], 1)] = i;
-}
-
-// The j-th item of this CTA.  Items are numbered tile-major in the order of rswa_prefill_order_kernel, heads
-// innermost, and dealt to the CTAs in rounds that alternate direction, so that every CTA's items add up to
-// about the same number of key tiles.  Every role of the CTA walks the same sequence.
-__device__ __forceinline__ TcItem tc_load_item(const PrefillParams& p, uint32_t j) {
-    TcItem it;
-    const long long G = gridDim.x, c = blockIdx.x;
-    const long long k = (long long)j * G + ((j & 1u) ? G - 1 - c : c);
-    it.valid = k < (long long)p.n_tiles * p.heads;
-    it.n_steps = 0;
-    if (!it.valid) return it;
-    const int ti = (int)(k / p.heads);
-    it.head = (int)(k - (long long)ti * p.heads);
-    it.kvh = it.head / p.group;
-    it.t = p.tiles[__ldg(p.order + ti)];
-    it.pfx = max(__ldg(p.d_prefill_len + it.t.slot), 0);
-    tc_tile_steps(it.t, it.pfx, p.window, it.n_prefix_tiles, it.text_tile0, it.n_steps);
-    return it;
+    for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) {
+        const TcWork w = work_of(i);
+        work[atomicAdd(&hist[min(w.n_steps, kTcOrderBins - 1)], 1)] = w;
+    }
 }
 
 // Register budget of the roles (setmaxnreg): the kernel starts with 65536 / 512 = 128 registers per thread; the
@@ -424,9 +423,11 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     uint8_t* sQ = base + kTcStages * kTcStageBytes;    // fp32 query rows on their way to TMEM, then the output rows
     uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + kTcQStageBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 30);
-    float* xmax = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [tile parity][half][row]
+    int* item_ring = reinterpret_cast<int*>(bars + 64);                              // [kTcItemSlots][kTcItemInts]
+    float* xmax = reinterpret_cast<float*>(item_ring + kTcItemSlots * kTcItemInts);  // [tile parity][half][row]
     float* xsum = xmax + 2 * 2 * 128;                                                // [item parity][half][row]
     const uint32_t bar0 = smem_addr(bars);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Ring and S/P barriers are indexed by the parity of the CTA's running key-tile count g; their phase is (g >> 1) & 1.
     auto k_full = [&](uint32_t b) { return bar0 + (0 + b) * 8; };   // TMA bytes of K stage b have landed
     auto k_free = [&](uint32_t b) { return bar0 + (2 + b) * 8; };   // the S MMAs reading K stage b are done
@@ -446,8 +447,45 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     const uint32_t s_done = bar0 + 26 * 8, o_done = bar0 + 27 * 8;
     const uint32_t drained = bar0 + 24 * 8, drained2 = bar0 + 25 * 8; // the issuers' last instructions have completed
     auto pair_bar = [&](int quad) { return bar0 + (20 + quad) * 8; };  // the two softmax warps of a lane quadrant
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // The CTA's items come from a global counter: the K producer draws them two items ahead of its own loads and
+    // publishes each in a ring slot; every other role reads the slot when it gets to the item.  item_full: slot
+    // written; item_empty: every reading warp (8 softmax, 4 helper, V producer, the two issuers) has read it.
+    auto item_full = [&](uint32_t sl) { return bar0 + (32 + sl) * 8; };
+    auto item_empty = [&](uint32_t sl) { return bar0 + (40 + sl) * 8; };
+    constexpr uint32_t kItemReaders = 8 + 4 + 1 + 1 + 1;
+    auto read_slot = [&](uint32_t sl) {
+        const int* w = item_ring + sl * kTcItemInts;
+        TcItem it;
+        it.t.row0 = w[0]; it.t.rows = w[1]; it.t.slot = w[2]; it.t.kind = w[3]; it.t.pos0 = w[4]; it.t.block0 = w[5];
+        it.head = w[6]; it.pfx = w[7]; it.n_prefix_tiles = w[8]; it.text_tile0 = w[9]; it.n_steps = w[10];
+        it.valid = w[11] != 0;
+        it.kvh = it.head / p.group;
+        if (!it.valid) it.n_steps = 0;
+        return it;
+    };
+    auto no_item = [&]() {
+        TcItem it;
+        it.valid = false;
+        it.n_steps = 0;
+        it.t.rows = 0;
+        return it;
+    };
+    // the j-th item of this CTA, for a whole warp / for a single thread; invalid after the last one (or a wait that ran out)
+    auto get_item = [&](uint32_t j) {
+        const uint32_t sl = j % kTcItemSlots;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(item_full(sl), (j / kTcItemSlots) & 1u, p.status))) return no_item();
+        const TcItem it = read_slot(sl);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(item_empty(sl));
+        return it;
+    };
+    auto get_item_1 = [&](uint32_t j) {
+        const uint32_t sl = j % kTcItemSlots;
+        if (!mbar_wait_bounded(item_full(sl), (j / kTcItemSlots) & 1u, p.status)) return no_item();
+        const TcItem it = read_slot(sl);
+        mbar_arrive(item_empty(sl));
+        return it;
+    };
 
     if (tid == 0) {
 #pragma unroll
@@ -468,6 +506,11 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         mbar_init(o_done, 1);
         mbar_init(drained, 1);
         mbar_init(drained2, 1);
+#pragma unroll
+        for (int sl = 0; sl < kTcItemSlots; ++sl) {
+            mbar_init(item_full(sl), 1);
+            mbar_init(item_empty(sl), kItemReaders);
+        }
 #pragma unroll
         for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
         mbar_init_fence();
@@ -493,7 +536,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         uint32_t itc = 0;  // items this CTA has gone through
         uint32_t pp = 0;   // rendezvous of the warp pair so far
         bool ok = true;
-        for (TcItem cur = tc_load_item(p, 0); cur.valid && ok; cur = tc_load_item(p, ++itc)) {
+        for (TcItem cur = get_item(0); cur.valid && ok; cur = get_item(++itc)) {
             const PrefillTile& t = cur.t;
             const bool live = r < t.rows;
             const int i = t.pos0 + r;
@@ -584,8 +627,8 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         };
 
         uint32_t g = 0, m = 0;
-        TcItem cur = tc_load_item(p, 0);
-        TcItem nxt = tc_load_item(p, 1);
+        TcItem cur = get_item(0);
+        TcItem nxt = cur.valid ? get_item(1) : no_item();
         bool ok = true;
         if (cur.valid) {
             fetch_q(cur);
@@ -593,7 +636,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             if (ok) fetch_q(nxt);
         }
         while (cur.valid && ok) {
-            const TcItem nxt2 = tc_load_item(p, m + 2);
+            const TcItem nxt2 = nxt.valid ? get_item(m + 2) : no_item();
             // ---- the next item's Q, as soon as this item's last scores have left the tensor core ----------
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_done, m & 1u, p.status))) { ok = false; break; }
             if (nxt.valid) {
@@ -668,7 +711,53 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         const int text_rows = p.text_blocks * p.kv_heads * kBlockTokens;
         uint32_t g = 0, m = 0, issued = 0;
         bool ok = true;
-        for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+        // The K producer is also the CTA's scheduler (lane 0): item j of this CTA is the global item k_next -- the
+        // CTA's own index for its first, then whatever the counter gives -- written with its tile's data into ring
+        // slot j % kTcItemSlots.  The draw for the following item is started right away, its answer is only looked
+        // at when that item is published.
+        uint32_t pub = 0;
+        long long k_next = blockIdx.x;
+        bool more = true;
+        const long long n_items = (long long)p.n_tiles * p.heads;
+        auto publish_one = [&]() -> bool {  // lane 0 only
+            const uint32_t sl = pub % kTcItemSlots;
+            if (pub >= kTcItemSlots && !mbar_wait_bounded(item_empty(sl), ((pub / kTcItemSlots) - 1) & 1u, p.status)) return false;
+            int* w = item_ring + sl * kTcItemInts;
+            const bool valid = k_next < n_items;
+            if (valid) {
+                const int ti = (int)(k_next / p.heads);
+                const int4* src = reinterpret_cast<const int4*>(p.work + ti);
+                const int4 a = __ldg(src), b4 = __ldg(src + 1), c = __ldg(src + 2);
+                reinterpret_cast<int4*>(w)[0] = a;                                        // row0 rows slot kind
+                reinterpret_cast<int4*>(w)[1] = make_int4(b4.x, b4.y, (int)(k_next - (long long)ti * p.heads), b4.z);  // pos0 block0 head pfx
+                reinterpret_cast<int4*>(w)[2] = make_int4(b4.w, c.x, c.y, 1);             // n_prefix_tiles text_tile0 n_steps valid
+            } else {
+                w[11] = 0;
+                more = false;
+            }
+            mbar_arrive(item_full(sl));  // (release: the slot's contents are visible to whoever sees the phase)
+            ++pub;
+            if (valid) k_next = (long long)gridDim.x + atomicAdd(p.counter, 1);
+            return true;
+        };
+        if (!is_v) {
+            if (lane == 0) {
+                ok = publish_one();
+                if (ok && more) ok = publish_one();
+            }
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        for (;; ++m) {
+            TcItem it;
+            if (is_v) {
+                it = get_item(m);
+            } else {
+                // publish item m + 2, then read item m from its slot (published two rounds ago, or above)
+                if (lane == 0 && more) ok = publish_one();
+                ok = __all_sync(0xffffffffu, ok);
+                it = ok ? read_slot(m % kTcItemSlots) : no_item();
+            }
+            if (!it.valid || !ok) break;
             const int prefix_blocks = (it.pfx + kBlockTokens - 1) / kBlockTokens;
             for (int n = 0; n < it.n_steps; ++n) {
                 const uint32_t gn = g + n, b = gn & 1u;
@@ -718,7 +807,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 dK[j] = tc_smem_desc(smem_addr(sKV) + (uint32_t)((j >> 2) * kTcHalfBytes + (j & 3) * 32), 16, 1024);
             uint32_t g = 0, m = 0;
             bool ok = true;
-            for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+            for (TcItem it = get_item_1(0); it.valid && ok; it = get_item_1(++m)) {
                 if (!mbar_wait_bounded(q_full(m), (m >> 1) & 1u, p.status)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
                     const uint32_t gn = g + n, b = gn & 1u;
@@ -751,7 +840,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 dV[j] = tc_smem_desc(smem_addr(sKV) + kTcTileBytes + j * 2048, kTcHalfBytes, 1024);
             uint32_t g = 0, m = 0;
             bool ok = true;
-            for (TcItem it = tc_load_item(p, 0); it.valid && ok; it = tc_load_item(p, ++m)) {
+            for (TcItem it = get_item_1(0); it.valid && ok; it = get_item_1(++m)) {
                 // the item's first product overwrites the accumulator: the previous item's rows must have been read
                 if (m >= 1 && !mbar_wait_bounded(o_read, (m - 1) & 1u, p.status)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
