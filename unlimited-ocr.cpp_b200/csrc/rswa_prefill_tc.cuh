@@ -244,42 +244,27 @@ constexpr float kTcMaxSlack = 8.f;
 // One key tile of the online softmax for this thread: its row, its half (64 keys) of the tile.
 // Reads S once, agrees on the row maximum with the thread that owns the other half (shared-memory
 // exchange + a 64-thread rendezvous), writes P as bf16 pairs over its own 64 columns of the S buffer:
-// 32 words of hi pairs, then 32 words of lo pairs.  FULL: every key of the tile is visible to every row
-// of the warp.  m_ref is the reference the row's probabilities are scaled by; alpha is the factor the
-// row's accumulator and sum take when the reference moved (1 otherwise).  False if the rendezvous ran
-// out of time.
-template <bool FULL>
-__device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
+// 32 words of hi pairs, then 32 words of lo pairs.  full (the same for the whole warp): every key of the
+// tile is visible to every row of the warp; otherwise the scores of the keys outside [vlo, vhi) are
+// set to -inf first (their probabilities come out as zero), so that both cases run the same code.
+// m_ref is the reference the row's probabilities are scaled by; alpha is the factor the row's
+// accumulator and sum take when the reference moved (1 otherwise).  False if the rendezvous ran out
+// of time.
+__device__ __forceinline__ bool tc_softmax_half(bool full, uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
                                                 uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_ref, float& l_run,
                                                 float& alpha) {
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
-    // Of this thread's 64 keys the visible ones are [lo, hi).  A partly visible tile is handled in chunks of 16
-    // keys, classified for the whole warp: every lane sees the whole chunk (bit in `all`: no per-key tests), no
-    // lane sees any of it (bit in `none`: zeros, no exponentials), or mixed (per-key tests).  The rows of a warp
-    // are consecutive positions, so at most three of a causal or window edge's chunks are mixed.
-    const int lo = vlo - h * 64, hi = vhi - h * 64;
-    uint32_t all = 0xfu, none = 0u;
-    if (!FULL) {
-        all = 0u;
+    if (!full) {
+        const int lo = vlo - h * 64;                   // of this thread's 64 keys the visible ones are [lo, lo + span)
+        const unsigned span = (unsigned)max(vhi - vlo, 0);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            all |= (__all_sync(0xffffffffu, lo <= q * 16 && hi >= q * 16 + 16) ? 1u : 0u) << q;
-            none |= (__all_sync(0xffffffffu, hi <= q * 16 || lo >= q * 16 + 16) ? 1u : 0u) << q;
-        }
+        for (int j = 0; j < 64; ++j)
+            if ((unsigned)(j - lo) >= span) s[j] = 0xff800000u;  // -inf
     }
     float mx = -INFINITY;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (FULL || ((all >> q) & 1u)) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(s[q * 16 + j]));
-        } else if (!((none >> q) & 1u)) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (q * 16 + j >= lo && q * 16 + j < hi) mx = fmaxf(mx, __uint_as_float(s[q * 16 + j]));
-        }
-    }
+    for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(s[j]));
     *my_max = mx;
     // also: both halves of S are in registers from here on, P may overwrite them
     if (!pair_sync(pair_bar, pair_parity, status)) return false;
@@ -296,29 +281,11 @@ __device__ __forceinline__ bool tc_softmax_half(uint32_t tS, int h, int vlo, int
     for (int qq = 0; qq < 2; ++qq) {  // 32 keys at a time: their 16 hi words, then their 16 lo words, over their own columns
         uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const int q = qq * 2 + c;
-            if (FULL || ((all >> q) & 1u)) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float p0 = tc_exp2(__uint_as_float(s[q * 16 + 2 * e]) - m_safe);
-                    const float p1 = tc_exp2(__uint_as_float(s[q * 16 + 2 * e + 1]) - m_safe);
-                    lsum += p0 + p1;
-                    tc_split2(p0, p1, pk[c * 8 + e], pk[16 + c * 8 + e]);
-                }
-            } else if ((none >> q) & 1u) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) pk[c * 8 + e] = pk[16 + c * 8 + e] = 0u;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int k0 = q * 16 + 2 * e;
-                    const float p0 = (k0 >= lo && k0 < hi) ? tc_exp2(__uint_as_float(s[k0]) - m_safe) : 0.f;
-                    const float p1 = (k0 + 1 >= lo && k0 + 1 < hi) ? tc_exp2(__uint_as_float(s[k0 + 1]) - m_safe) : 0.f;
-                    lsum += p0 + p1;
-                    tc_split2(p0, p1, pk[c * 8 + e], pk[16 + c * 8 + e]);
-                }
-            }
+        for (int e = 0; e < 16; ++e) {
+            const float p0 = tc_exp2(__uint_as_float(s[qq * 32 + 2 * e]) - m_safe);
+            const float p1 = tc_exp2(__uint_as_float(s[qq * 32 + 2 * e + 1]) - m_safe);
+            lsum += p0 + p1;
+            tc_split2(p0, p1, pk[e], pk[16 + e]);
         }
         tc_st32(tS + h * 64 + qq * 32, pk);
     }
@@ -559,10 +526,8 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 float* my_max = xmax + (b * 2 + h) * 128 + r;
                 const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
                 float alpha = 1.f;
-                if (__all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile))
-                    ok = tc_softmax_half<true>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, m_ref, l_run, alpha);
-                else
-                    ok = tc_softmax_half<false>(tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, m_ref, l_run, alpha);
+                const bool full = __all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile);
+                ok = tc_softmax_half(full, tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, m_ref, l_run, alpha);
                 ++pp;
                 if (!ok) break;
                 // A row whose reference moved takes the factor on its accumulator before this tile's product is
