@@ -1,25 +1,37 @@
 // Ragged prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// One CTA owns one tile of up to 128 consecutive query rows of one request and one head, and walks
-// the 128-key tiles those rows can see: first the fixed (prefix) region through the block table,
-// then -- for text rows -- the sliding text window in the text pool.  The CTA is warp-specialised:
+// A work item is a tile of up to 128 consecutive query rows of one request and one head, with the
+// 128-key tiles those rows can see: first the fixed (prefix) region through the block table, then --
+// for text rows -- the sliding text window in the text pool.  One persistent CTA per SM draws items
+// from a global counter, longest first (rswa_prefill_order_kernel orders the tiles by their number of
+// key tiles), and keeps its pipeline running across items.  16 warps, warp-specialised, registers
+// re-split between the roles with setmaxnreg:
 //
-//   warps 8, 10  producers (K and V): per key tile, 16 tiled TMA loads each (one 16-token block half,
-//                SWIZZLE_128B) into two-deep K and V rings in shared memory; blocks the rows cannot
-//                see are fetched from an out-of-range coordinate, which fills zeros.  K runs further
-//                ahead than V: its stage is free as soon as the S product has read it
-//   warp 9       one thread issues the MMAs: S = Q K^T (tcgen05.mma kind::f16, M = N = 128, operands
-//                in shared memory, accumulator in TMEM) one tile ahead of the softmax, and
-//                O_tile = P V with P read straight from TMEM and V as the MN-major B operand
 //   warps 0-7    softmax: warp w owns rows 32*(w%4).. (its TMEM lane quadrant) and half w/4 of the
-//                keys of S and of the dims of O: tcgen05.ld of S, mask, row maximum agreed with the
-//                partner warp through shared memory, exp2-domain probabilities written over S in
-//                TMEM (tcgen05.st) as bf16 hi and lo pairs, and the previous tile's O_tile folded into
-//                a per-thread fp32 accumulator with the usual rescale while the tensor core works on
-//                the next products.  Q staging and the output rows go through shared memory so that
-//                global accesses are whole 512-byte rows
+//                keys of S: tcgen05.ld of S, scores of hidden keys set to -inf, row maximum agreed with
+//                the partner warp through shared memory, exp2-domain probabilities written over S in
+//                TMEM (tcgen05.st) as bf16 hi and lo pairs.  The accumulator O stays in TMEM across the
+//                item's key tiles; the reference the probabilities are scaled by only follows the row
+//                maximum in steps of 2^8, and a row whose reference moved rescales its accumulator row
+//                in place before the tile's product is added
+//   warps 8-11   helpers, thread r owning row r of a staging area: one bulk copy brings the fp32
+//                query row in, the thread splits it into the bf16 hi / lo operand in TMEM (as soon as
+//                the previous item's last scores have left the tensor core), later reads the finished
+//                accumulator row, normalises it, stages it and sends it off with one bulk store
+//   warp 12      K producer and the CTA's scheduler: per key tile 16 tiled TMA loads (one 16-token
+//                block half each, SWIZZLE_128B) into a two-deep ring; blocks the rows cannot see are
+//                fetched from an out-of-range coordinate, which fills zeros.  Lane 0 draws the items
+//                two ahead and publishes them in a shared-memory ring for every other role
+//   warp 14      V producer, the same loads for V
+//   warp 13      one thread issues S = Q K^T (tcgen05.mma kind::f16, M = N = 128, Q from TMEM, K from
+//                shared memory), up to two tiles ahead of the softmax
+//   warp 15      one thread issues O += P V (P from TMEM, V as the MN-major shared-memory operand)
 //
-// TMEM (512 columns): S/P double-buffered in [0,256), O_tile double-buffered in [256,512).
+// Two issuing threads because the tensor core takes one thread's instructions in order and every
+// barrier poll between two batches leaves its queue empty for a few hundred cycles: one thread's
+// polls are covered by the other's queued instructions.
+//
+// TMEM (512 columns): S/P double-buffered in [0,256), O in [256,384), Q hi / lo words in [384,512).
 //
 // The queries arrive in fp32 and the oracle computes in fp32, so Q and P are each fed to the tensor
 // cores as a bf16 pair (hi + lo): two MMAs per operand keep ~16 mantissa bits, which holds the
@@ -29,7 +41,9 @@
 // defines "prefix + last W tokens".
 //
 // Every wait is bounded; a wait that runs out sets a status bit, every role leaves its loop, the
-// copies and MMAs in flight are drained (bounded again) and the CTA frees its TMEM.
+// copies and MMAs in flight are drained (bounded again) and the CTA frees its TMEM.  A parity wait
+// only tells a barrier phase from its neighbours: every waiter here follows its barrier phase by
+// phase (per key tile, or per item on barriers of its own), never skipping one.
 #pragma once
 
 #include <cuda.h>  // CUtensorMap (type only; the encoder is fetched through the runtime)
@@ -74,14 +88,6 @@ constexpr uint32_t kTcColQ = 384;        // Q as bf16 pairs at 384 (hi words) an
 constexpr int kTcHalfBytes = 128 * 128;  // one 64-element-wide half of a 128x128 bf16 tile
 constexpr int kTcTileBytes = 2 * kTcHalfBytes;
 
-// Byte offset of 16-byte chunk `chunk` (0..15 across the 256-byte row) of row `row` inside a
-// 128 x 128 bf16 tile stored as two K-major / MN-major SWIZZLE_128B halves: rows of 128 bytes,
-// 8-row atoms of 1024 bytes, chunk index XORed with (row % 8).
-__device__ __forceinline__ uint32_t tc_tile_offset(int row, int chunk) {
-    const int half = chunk >> 3, c = chunk & 7;
-    return (uint32_t)(half * kTcHalfBytes + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4));
-}
-
 // Shared-memory matrix descriptor (SWIZZLE_128B, descriptor version 1).
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_byte_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -106,18 +112,8 @@ __device__ __forceinline__ uint32_t tc_instr_desc(bool b_mn_major) {
     return d;
 }
 
-// D[tmem_d] (+)= A * B with both operands in shared memory.  ACC false overwrites D.
-template <bool ACC>
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
-    if (ACC)
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
-    else
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc) : "memory");
-}
-
-// A operand from TMEM (lane = row, two bf16 per 32-bit column), B from shared memory.  acc == 0 overwrites D.
+// D[tmem_d] (+)= A * B: A operand from TMEM (lane = row, two bf16 per 32-bit column), B from shared memory.
+// acc == 0 overwrites D.
 __device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
@@ -225,12 +221,6 @@ __device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 
 // Bounded rendezvous of the 64 threads that share a TMEM lane quadrant (one mbarrier phase per call).
 __device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t parity, int* status) {
-    mbar_arrive(bar);
-    return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
-}
-
-// Bounded rendezvous of all softmax threads (one mbarrier phase per call).
-__device__ __forceinline__ bool softmax_sync(uint32_t bar, uint32_t parity, int* status) {
     mbar_arrive(bar);
     return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
 }
@@ -573,8 +563,8 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             const bool live = r < it.t.rows;
             const float s = p.scale_log2e;
             const float4* q4 = reinterpret_cast<const float4*>(my_row);
-#pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {  // 32 dims at a time: 16 hi words and 16 lo words
+#pragma unroll 1
+            for (int g4 = 0; g4 < 4; ++g4) {  // 32 dims at a time: 16 hi words and 16 lo words (rolled: this runs once per item)
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -591,32 +581,32 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             return true;
         };
 
-        uint32_t g = 0, m = 0;
-        TcItem cur = get_item(0);
-        TcItem nxt = cur.valid ? get_item(1) : no_item();
+        // Round m: the next item's Q into TMEM, item m's rows out, the query row of the item after next fetched.
+        // The first round (m = -1) has no current item: it only brings in Q of item 0 and fetches item 1's rows.
+        int m = -1;
+        TcItem cur = no_item();
+        TcItem nxt = get_item(0);
         bool ok = true;
-        if (cur.valid) {
-            fetch_q(cur);
-            ok = convert_q(cur, 0);
-            if (ok) fetch_q(nxt);
-        }
-        while (cur.valid && ok) {
-            const TcItem nxt2 = nxt.valid ? get_item(m + 2) : no_item();
+        fetch_q(nxt);
+        while (ok) {
+            const TcItem nxt2 = nxt.valid ? get_item((uint32_t)(m + 2)) : no_item();
             // ---- the next item's Q, as soon as this item's last scores have left the tensor core ----------
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_done, m & 1u, p.status))) { ok = false; break; }
+            if (cur.valid && !__all_sync(0xffffffffu, mbar_wait_bounded(s_done, (uint32_t)m & 1u, p.status))) { ok = false; break; }
             if (nxt.valid) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                ok = convert_q(nxt, m + 1);
+                ok = convert_q(nxt, (uint32_t)(m + 1));
                 if (!ok) break;
             }
+            if (cur.valid) {
             // ---- this item's row: accumulator / row sum -> staging area -> global -------------------------
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(l_ready(m), (m >> 1) & 1u, p.status))) { ok = false; break; }
-            const float l_tot = xsum[((m & 1u) * 2 + 0) * 128 + r] + xsum[((m & 1u) * 2 + 1) * 128 + r];
+            const uint32_t um = (uint32_t)m;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(l_ready(um), (um >> 1) & 1u, p.status))) { ok = false; break; }
+            const float l_tot = xsum[((um & 1u) * 2 + 0) * 128 + r] + xsum[((um & 1u) * 2 + 1) * 128 + r];
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_done, m & 1u, p.status))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_done, um & 1u, p.status))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll 1
+            for (int hh = 0; hh < 2; ++hh) {  // (rolled: once per item)
                 uint32_t o[64];
                 if (cur.n_steps > 0) {
                     tc_ld64(tmem + lane_base + kTcColO + hh * 64, o);
@@ -656,8 +646,9 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             // the row has been read out of the staging area: it takes the query row of the item after next
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            }
             fetch_q(nxt2);
-            g += cur.n_steps;
+            if (!nxt.valid) break;
             ++m;
             cur = nxt;
             nxt = nxt2;
@@ -705,20 +696,14 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             if (valid) k_next = (long long)gridDim.x + atomicAdd(p.counter, 1);
             return true;
         };
-        if (!is_v) {
-            if (lane == 0) {
-                ok = publish_one();
-                if (ok && more) ok = publish_one();
-            }
-            ok = __all_sync(0xffffffffu, ok);
-        }
         for (;; ++m) {
             TcItem it;
             if (is_v) {
                 it = get_item(m);
             } else {
-                // publish item m + 2, then read item m from its slot (published two rounds ago, or above)
-                if (lane == 0 && more) ok = publish_one();
+                // publish up to item m + 2, then read item m from its slot
+                if (lane == 0)
+                    while (ok && more && pub < m + 3) ok = publish_one();
                 ok = __all_sync(0xffffffffu, ok);
                 it = ok ? read_slot(m % kTcItemSlots) : no_item();
             }
@@ -766,6 +751,10 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         // from two threads, one's polls are covered by the other's queued instructions.
         if (lane == 0) {
             const uint32_t idesc_s = tc_instr_desc(false);
+            // Every operand descriptor is fixed for the CTA's lifetime except for the ring stage, which only
+            // moves the address field: build them once, so that one MMA costs the issuing thread one
+            // instruction and an add (the issue loops stay unrolled: rolled, with the descriptor arithmetic in
+            // the loop, the thread could not keep the tensor core's queue filled).
             uint64_t dK[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
