@@ -188,3 +188,65 @@ def test_prefill_tensor_core_bf16_output(orc, b):
     with pytest.raises(b.Error):
         b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, d(q), pb.d_prefill, tiles[:-1], W, heads, out16, ws, reuse_plan=True)
     assert ws.status() == 0
+
+
+def test_prefill_tensor_core_many_items_per_cta_against_cuda_core_path(orc, b):
+    # 12 requests with the benchmark's prefix lengths and prompts up to 1.5 windows: ~150 query tiles x 10 heads,
+    # i.e. ten items for every persistent CTA, drawn from the counter in longest-first order, with one plan of
+    # the tiles shared by two calls.  Too many rows for the scalar oracle; the reference here is the CUDA-core
+    # path on the same pools, which the cases above hold to the oracle (its own error is 1e-5).
+    import torch
+    W, heads, kvh, hd = 1024, 10, 10, 128
+    prefixes = [256, 656, 1056, 256, 656, 1056, 1056, 256, 656, 1056, 256, 656]
+    text_lens = [int(x) for x in synth.integers(909, 3, 64, 1536, (len(prefixes),))]
+    slots = len(prefixes)
+    pb = PagedBatch(orc, slots, 1, kvh, hd, W, b.BF16, prefixes, heads=heads, seed=909)
+    row = kvh * hd
+    pb.write_prefixes()
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    nv, nt = sum(prefixes), sum(text_lens)
+    ws = b.Workspace(nv + nt)
+    # vision rows
+    qv = d(synth.normal(909, 41, (nv, heads * hd)))
+    rs = d(np.concatenate([np.full(p, s) for s, p in enumerate(prefixes)]).astype(np.int32))
+    pos = d(np.concatenate([np.arange(p) for p in prefixes]).astype(np.int32))
+    ref_v = torch.full((nv, heads * hd), float("nan"), device="cuda")
+    for a in range(0, nv, 4096):
+        n = min(4096, nv - a)
+        b.attention_ragged_paged(pb.layer[0], qv[a:a + n], pb.d_prefill, rs[a:a + n], pos[a:a + n], n, heads, ref_v[a:a + n], ws)
+    # text rows
+    block0, nb = [], 0
+    for T in text_lens:
+        block0.append(nb)
+        nb += ceil_div(T, 16)
+    text_k = torch.zeros((nb, kvh, 16, hd), dtype=torch.bfloat16, device="cuda")
+    text_v = torch.zeros_like(text_k)
+    k = d(pb.rnd(synth.normal(909, 51, (nt, row))))
+    v = d(pb.rnd(synth.normal(909, 52, (nt, row))))
+    qt = d(synth.normal(909, 53, (nt, heads * hd)))
+    trs = d(np.concatenate([np.full(T, s) for s, T in enumerate(text_lens)]).astype(np.int32))
+    tpos = d(np.concatenate([np.arange(T) for T in text_lens]).astype(np.int32))
+    tb0 = d(np.concatenate([np.full(T, block0[s]) for s, T in enumerate(text_lens)]).astype(np.int32))
+    ref_t = torch.full((nt, heads * hd), float("nan"), device="cuda")
+    for a in range(0, nt, 4096):
+        n = min(4096, nt - a)
+        b.prefill_text_paged(pb.layer[0], text_k, text_v, nb, qt[a:a + n], k[a:a + n], v[a:a + n], pb.d_prefill, trs[a:a + n],
+                             tpos[a:a + n], tb0[a:a + n], n, W, heads, ref_t[a:a + n], ws)
+    # tensor-core path: vision and text tiles in ONE call, then once more on the same plan
+    reqs, at = [], 0
+    for s, p in enumerate(prefixes):
+        reqs.append((at, p, s, 0, 0, 0))
+        at += p
+    for s, T in enumerate(text_lens):
+        reqs.append((at, T, s, 1, 0, block0[s]))
+        at += T
+    tiles = b.make_prefill_tiles(reqs)
+    assert tiles.shape[0] * heads >= 8 * 148
+    q_all = torch.cat([qv, qt])
+    ref = torch.cat([ref_v, ref_t]).cpu().numpy()
+    assert np.isfinite(ref).all()
+    for reuse in (False, True):
+        out = torch.full((nv + nt, heads * hd), float("nan"), device="cuda")
+        b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, q_all, pb.d_prefill, tiles, W, heads, out, ws, reuse_plan=reuse)
+        assert_attention_close(out.cpu().numpy(), ref, 4e-4, 2e-4)  # two paths' errors: 1e-5 and 1e-4 against the oracle
+    assert ws.status() == 0
