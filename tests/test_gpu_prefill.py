@@ -250,3 +250,36 @@ def test_prefill_tensor_core_many_items_per_cta_against_cuda_core_path(orc, b):
         b.prefill_attention_tc(pb.layer[0], text_k, text_v, nb, q_all, pb.d_prefill, tiles, W, heads, out, ws, reuse_plan=reuse)
         assert_attention_close(out.cpu().numpy(), ref, 4e-4, 2e-4)  # two paths' errors: 1e-5 and 1e-4 against the oracle
     assert ws.status() == 0
+
+
+def test_prefill_tensor_core_items_without_key_tiles(orc, b):
+    # Query tiles of slots whose prefix length is zero on the device: their rows see no key and come out as
+    # zeros (the reference's empty attention), also when such an item follows an ordinary one on the same CTA
+    # (190 items for 148 CTAs, the empty ones last in the order).
+    import torch
+    W, heads, kvh, hd = 64, 10, 10, 128
+    prefixes = [128] * 16 + [0, 0, 0]
+    pb = PagedBatch(orc, len(prefixes), 1, kvh, hd, W, b.BF16, prefixes, heads=heads, seed=515)
+    pb.write_prefixes()
+    rows_of = [128] * 16 + [16, 128, 1]  # the packed batch claims vision rows for the empty slots too
+    n = sum(rows_of)
+    q = synth.normal(515, 41, (n, heads * hd))
+    out = torch.full((n, heads * hd), float("nan"), device="cuda")
+    reqs, at = [], 0
+    for s, r in enumerate(rows_of):
+        reqs.append((at, r, s, 0, 0, 0))
+        at += r
+    tiles = b.make_prefill_tiles(reqs)
+    assert tiles.shape[0] * heads > 148
+    ws = b.Workspace(n)
+    b.prefill_attention_tc(pb.layer[0], None, None, 0, torch.from_numpy(q).cuda(), pb.d_prefill, tiles, W, heads, out, ws)
+    got = out.cpu().numpy()
+    at = 0
+    for s, r in enumerate(rows_of):
+        if prefixes[s]:
+            want = pb.cache[s].attention(0, q[at:at + r], 0, heads, True)
+            assert_attention_close(got[at:at + r], want, *TC_TIGHT)
+        else:
+            assert not got[at:at + r].any()
+        at += r
+    assert ws.status() == 0
