@@ -152,6 +152,12 @@ def test_prefill_tensor_core_real_geometry(orc, b):
                      engine="tc")
 
 
+def test_prefill_tensor_core_grouped_heads(orc, b):
+    # six query heads on two KV heads (three query heads read each KV head's tiles), through both text paths
+    run_prefill_case(orc, b, b.BF16, 2, 128, 6, 48, prefixes=[150, 20, 0], text_lens=[70, 130, 49], seed=94, engine="tc")
+    run_prefill_case(orc, b, b.BF16, 2, 128, 6, 48, prefixes=[150, 20, 0], text_lens=[70, 130, 49], seed=95, engine="tc_fused")
+
+
 def test_prefill_tensor_core_bf16_output(orc, b):
     # the workspace's bf16 output option on the tcgen05 path: same rows as fp32, rounded to nearest even
     import torch
