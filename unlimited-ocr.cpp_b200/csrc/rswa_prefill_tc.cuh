@@ -646,6 +646,9 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             // the row has been read out of the staging area: it takes the query row of the item after next
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            } else {
+                // (first round) this thread's reads of its row in convert_q -> the bulk copy that overwrites it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             fetch_q(nxt2);
             if (!nxt.valid) break;
