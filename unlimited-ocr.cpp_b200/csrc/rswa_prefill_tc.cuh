@@ -246,11 +246,19 @@ __device__ __forceinline__ bool tc_softmax_half(bool full, uint32_t tS, int h, i
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
     if (!full) {
-        const int lo = vlo - h * 64;                   // of this thread's 64 keys the visible ones are [lo, lo + span)
-        const unsigned span = (unsigned)max(vhi - vlo, 0);
+        // Of this thread's 64 keys the visible ones are [lo, hi).  A causal edge only has an upper bound, a window
+        // edge only a lower one: each bound is applied only where some row of the warp needs it.
+        const int lo = vlo - h * 64, hi = vhi - h * 64;
+        if (__any_sync(0xffffffffu, hi < 64)) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-            if ((unsigned)(j - lo) >= span) s[j] = 0xff800000u;  // -inf
+            for (int j = 0; j < 64; ++j)
+                if (j >= hi) s[j] = 0xff800000u;  // -inf
+        }
+        if (__any_sync(0xffffffffu, lo > 0)) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+                if (j < lo) s[j] = 0xff800000u;
+        }
     }
     float mx = -INFINITY;
 #pragma unroll
