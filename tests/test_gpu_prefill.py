@@ -289,3 +289,36 @@ def test_prefill_tensor_core_items_without_key_tiles(orc, b):
             assert not got[at:at + r].any()
         at += r
     assert ws.status() == 0
+
+
+def test_prefill_tensor_core_waits_give_up_cleanly(orc, b):
+    # every wait of the tensor-core kernel is bounded: with a poll limit of zero each role gives up at its first
+    # wait, the copies already issued are seen to land, the kernel ends (nothing hangs, nothing faults) and the
+    # status word says the launch is void; the same workspace and plan then serve a correct launch
+    import torch
+    W, heads, kvh, hd = 64, 10, 10, 128
+    prefixes = [300, 150]
+    pb = PagedBatch(orc, len(prefixes), 1, kvh, hd, W, b.BF16, prefixes, heads=heads, seed=717)
+    pb.write_prefixes()
+    n = sum(prefixes)
+    q = synth.normal(717, 41, (n, heads * hd))
+    dq = torch.from_numpy(q).cuda()
+    tiles = b.make_prefill_tiles([(0, 300, 0, 0, 0, 0), (300, 150, 1, 0, 0, 0)])
+    ws = b.Workspace(n)
+    out = torch.full((n, heads * hd), float("nan"), device="cuda")
+    ws.set_wait_limit(0)
+    b.prefill_attention_tc(pb.layer[0], None, None, 0, dq, pb.d_prefill, tiles, W, heads, out, ws)  # void launch
+    torch.cuda.synchronize()
+    assert ws.status() & b.STATUS_WAIT_TIMEOUT
+    ws.set_wait_limit(1 << 22)
+    assert ws.status() == 0
+    for reuse in (True, False):
+        out.fill_(float("nan"))
+        b.prefill_attention_tc(pb.layer[0], None, None, 0, dq, pb.d_prefill, tiles, W, heads, out, ws, reuse_plan=reuse)
+        got = out.cpu().numpy()
+        at = 0
+        for s, p_ in enumerate(prefixes):
+            want = pb.cache[s].attention(0, q[at:at + p_], 0, heads, True)
+            assert_attention_close(got[at:at + p_], want, *TC_TIGHT)
+            at += p_
+    assert ws.status() == 0

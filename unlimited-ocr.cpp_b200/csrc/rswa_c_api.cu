@@ -984,6 +984,7 @@ int uocr_b200_rswa_prefill_attention_tc(const uocr_b200_paged_kv* kv, const void
     pp.window = window;
     pp.scale_log2e = (1.0f / std::sqrt(128.0f)) * 1.4426950408889634f;
     pp.status = ws->status;
+    pp.wait_limit = ws->wait_limit;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);

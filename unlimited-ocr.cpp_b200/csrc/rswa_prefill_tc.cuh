@@ -80,6 +80,8 @@ struct PrefillParams {
     int heads, kv_heads, group, window;
     float scale_log2e;
     int* status;
+    uint32_t wait_limit;  // polls a wait may take before the role gives up (kWaitLimit unless a test lowers it); the
+                          // drains of copies and MMAs in flight keep the full limit
 };
 
 constexpr int kTcTile = 128;             // queries per CTA, keys per step, head_dim
@@ -220,9 +222,9 @@ __device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 }
 
 // Bounded rendezvous of the 64 threads that share a TMEM lane quadrant (one mbarrier phase per call).
-__device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t parity, int* status) {
+__device__ __forceinline__ bool pair_sync(uint32_t bar, uint32_t parity, int* status, uint32_t limit) {
     mbar_arrive(bar);
-    return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
+    return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status, limit));
 }
 
 // How far a row's maximum may rise above the reference its probabilities are scaled by before the
@@ -241,8 +243,8 @@ constexpr float kTcMaxSlack = 8.f;
 // accumulator and sum take when the reference moved (1 otherwise).  False if the rendezvous ran out
 // of time.
 __device__ __forceinline__ bool tc_softmax_half(bool full, uint32_t tS, int h, int vlo, int vhi, float* my_max, const float* other_max,
-                                                uint32_t pair_bar, uint32_t pair_parity, int* status, float& m_ref, float& l_run,
-                                                float& alpha) {
+                                                uint32_t pair_bar, uint32_t pair_parity, int* status, uint32_t wait_limit,
+                                                float& m_ref, float& l_run, float& alpha) {
     uint32_t s[64];
     tc_ld64(tS + h * 64, s);
     if (!full) {
@@ -265,7 +267,7 @@ __device__ __forceinline__ bool tc_softmax_half(bool full, uint32_t tS, int h, i
     for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(s[j]));
     *my_max = mx;
     // also: both halves of S are in registers from here on, P may overwrite them
-    if (!pair_sync(pair_bar, pair_parity, status)) return false;
+    if (!pair_sync(pair_bar, pair_parity, status, wait_limit)) return false;
     // both threads of the row see the same two maxima and take the same decision
     const float m_tile = fmaxf(mx, *other_max);
     alpha = 1.f;
@@ -438,7 +440,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     // the j-th item of this CTA, for a whole warp / for a single thread; invalid after the last one (or a wait that ran out)
     auto get_item = [&](uint32_t j) {
         const uint32_t sl = j % kTcItemSlots;
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(item_full(sl), (j / kTcItemSlots) & 1u, p.status))) return no_item();
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(item_full(sl), (j / kTcItemSlots) & 1u, p.status, p.wait_limit))) return no_item();
         const TcItem it = read_slot(sl);
         __syncwarp();
         if (lane == 0) mbar_arrive(item_empty(sl));
@@ -446,7 +448,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
     };
     auto get_item_1 = [&](uint32_t j) {
         const uint32_t sl = j % kTcItemSlots;
-        if (!mbar_wait_bounded(item_full(sl), (j / kTcItemSlots) & 1u, p.status)) return no_item();
+        if (!mbar_wait_bounded(item_full(sl), (j / kTcItemSlots) & 1u, p.status, p.wait_limit)) return no_item();
         const TcItem it = read_slot(sl);
         mbar_arrive(item_empty(sl));
         return it;
@@ -509,7 +511,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             const int tlo = max(0, i - p.window + 1);
             const int thi = (live && t.kind == 1) ? i + 1 : 0;                           // text tokens [tlo, thi)
             // Q of this item is in TMEM: the helpers have also taken the sums of the item before last out of xsum
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_full(itc), (itc >> 1) & 1u, p.status))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_full(itc), (itc >> 1) & 1u, p.status, p.wait_limit))) { ok = false; break; }
             float m_ref = -INFINITY, l_run = 0.f;
             for (int n = 0; n < cur.n_steps; ++n) {
                 const uint32_t gn = g + n, b = gn & 1u, par = (gn >> 1) & 1u;
@@ -518,21 +520,21 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
                 const int vlo = text ? tlo - t0 : -(1 << 30);
                 const int vhi = (text ? thi : phi) - t0;
                 // warp-uniform outcome: the TMEM instructions below need the whole warp
-                if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(s_full(b), par, p.status, p.wait_limit))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tS = tmem + lane_base + b * 128;
                 float* my_max = xmax + (b * 2 + h) * 128 + r;
                 const float* other_max = xmax + (b * 2 + (h ^ 1)) * 128 + r;
                 float alpha = 1.f;
                 const bool full = __all_sync(0xffffffffu, vlo <= 0 && vhi >= kTcTile);
-                ok = tc_softmax_half(full, tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, m_ref, l_run, alpha);
+                ok = tc_softmax_half(full, tS, h, vlo, vhi, my_max, other_max, pair_bar(quad), pp & 1u, p.status, p.wait_limit, m_ref, l_run, alpha);
                 ++pp;
                 if (!ok) break;
                 // A row whose reference moved takes the factor on its accumulator before this tile's product is
                 // added: the previous product must have landed, and this tile's P is only announced afterwards.
                 if (n >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
                     const uint32_t gk = gn - 1;
-                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(gk & 1u), (gk >> 1) & 1u, p.status))) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_full(gk & 1u), (gk >> 1) & 1u, p.status, p.wait_limit))) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     tc_rescale(tO, alpha);
                 }
@@ -556,8 +558,10 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         uint8_t* my_row = sQ + (size_t)r * kTcQRowBytes;
         const uint32_t my_row_s = smem_addr(my_row);
+        uint32_t fetched = 0;  // query-row fetches so far (phases of q_landed begun)
         auto fetch_q = [&](const TcItem& it) {  // this thread's share of the arrivals on q_landed, with its row's bytes
             if (!it.valid) return;
+            ++fetched;
             if (r < it.t.rows) {
                 mbar_arrive_expect_tx(q_landed, 512u);
                 bulk_copy_g2s(my_row_s, p.q + ((size_t)(it.t.row0 + r) * p.heads + it.head) * kTcTile, 512u, q_landed);
@@ -567,7 +571,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         };
         // Q row of item m -> TMEM (lane = row, column c of a 64-column block = dims 2c, 2c+1; hi words, then lo words)
         auto convert_q = [&](const TcItem& it, uint32_t m) -> bool {
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_landed, m & 1u, p.status))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_landed, m & 1u, p.status, p.wait_limit))) return false;
             const bool live = r < it.t.rows;
             const float s = p.scale_log2e;
             const float4* q4 = reinterpret_cast<const float4*>(my_row);
@@ -599,7 +603,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         while (ok) {
             const TcItem nxt2 = nxt.valid ? get_item((uint32_t)(m + 2)) : no_item();
             // ---- the next item's Q, as soon as this item's last scores have left the tensor core ----------
-            if (cur.valid && !__all_sync(0xffffffffu, mbar_wait_bounded(s_done, (uint32_t)m & 1u, p.status))) { ok = false; break; }
+            if (cur.valid && !__all_sync(0xffffffffu, mbar_wait_bounded(s_done, (uint32_t)m & 1u, p.status, p.wait_limit))) { ok = false; break; }
             if (nxt.valid) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 ok = convert_q(nxt, (uint32_t)(m + 1));
@@ -608,10 +612,10 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             if (cur.valid) {
             // ---- this item's row: accumulator / row sum -> staging area -> global -------------------------
             const uint32_t um = (uint32_t)m;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(l_ready(um), (um >> 1) & 1u, p.status))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(l_ready(um), (um >> 1) & 1u, p.status, p.wait_limit))) { ok = false; break; }
             const float l_tot = xsum[((um & 1u) * 2 + 0) * 128 + r] + xsum[((um & 1u) * 2 + 1) * 128 + r];
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_done, um & 1u, p.status))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(o_done, um & 1u, p.status, p.wait_limit))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int hh = 0; hh < 2; ++hh) {  // (rolled: once per item)
@@ -664,6 +668,8 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             cur = nxt;
             nxt = nxt2;
         }
+        // after a wait that ran out a fetched query row may still be on its way into the staging area: see it land
+        if (!ok && fetched > 0) mbar_wait_bounded(q_landed, (fetched - 1) & 1u, nullptr);
         // the output rows are written before the kernel ends
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
@@ -688,7 +694,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
         const long long n_items = (long long)p.n_tiles * p.heads;
         auto publish_one = [&]() -> bool {  // lane 0 only
             const uint32_t sl = pub % kTcItemSlots;
-            if (pub >= kTcItemSlots && !mbar_wait_bounded(item_empty(sl), ((pub / kTcItemSlots) - 1) & 1u, p.status)) return false;
+            if (pub >= kTcItemSlots && !mbar_wait_bounded(item_empty(sl), ((pub / kTcItemSlots) - 1) & 1u, p.status, p.wait_limit)) return false;
             int* w = item_ring + sl * kTcItemInts;
             const bool valid = k_next < n_items;
             if (valid) {
@@ -723,7 +729,7 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             for (int n = 0; n < it.n_steps; ++n) {
                 const uint32_t gn = g + n, b = gn & 1u;
                 const uint32_t full = is_v ? v_full(b) : k_full(b), freed = is_v ? v_free(b) : k_free(b);
-                if (gn >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(freed, ((gn >> 1) - 1) & 1u, p.status))) { ok = false; break; }
+                if (gn >= 2 && !__all_sync(0xffffffffu, mbar_wait_bounded(freed, ((gn >> 1) - 1) & 1u, p.status, p.wait_limit))) { ok = false; break; }
                 const bool text = n >= it.n_prefix_tiles;
                 const int t0 = text ? (it.text_tile0 + n - it.n_prefix_tiles) * kTcTile : n * kTcTile;
                 const int idx = t0 / kBlockTokens + blk_i;  // block index within the request's region
@@ -773,12 +779,12 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             uint32_t g = 0, m = 0;
             bool ok = true;
             for (TcItem it = get_item_1(0); it.valid && ok; it = get_item_1(++m)) {
-                if (!mbar_wait_bounded(q_full(m), (m >> 1) & 1u, p.status)) { ok = false; break; }
+                if (!mbar_wait_bounded(q_full(m), (m >> 1) & 1u, p.status, p.wait_limit)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
                     const uint32_t gn = g + n, b = gn & 1u;
-                    if (!mbar_wait_bounded(k_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    if (!mbar_wait_bounded(k_full(b), (gn >> 1) & 1u, p.status, p.wait_limit)) { ok = false; break; }
                     // S buffer b held P of the tile two back: the product that read it must have completed
-                    if (gn >= 2 && !mbar_wait_bounded(o_full(b), ((gn >> 1) - 1) & 1u, p.status)) { ok = false; break; }
+                    if (gn >= 2 && !mbar_wait_bounded(o_full(b), ((gn >> 1) - 1) & 1u, p.status, p.wait_limit)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t stage = (uint64_t)(b * (kTcStageBytes >> 4));  // address field counts 16-byte units
                     const uint32_t tS = tmem + b * 128;
@@ -807,11 +813,11 @@ rswa_prefill_tc_kernel(const PrefillParams p, const __grid_constant__ PrefillMap
             bool ok = true;
             for (TcItem it = get_item_1(0); it.valid && ok; it = get_item_1(++m)) {
                 // the item's first product overwrites the accumulator: the previous item's rows must have been read
-                if (m >= 1 && !mbar_wait_bounded(o_read, (m - 1) & 1u, p.status)) { ok = false; break; }
+                if (m >= 1 && !mbar_wait_bounded(o_read, (m - 1) & 1u, p.status, p.wait_limit)) { ok = false; break; }
                 for (int n = 0; n < it.n_steps; ++n) {
                     const uint32_t gn = g + n, b = gn & 1u;
-                    if (!mbar_wait_bounded(v_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
-                    if (!mbar_wait_bounded(p_full(b), (gn >> 1) & 1u, p.status)) { ok = false; break; }
+                    if (!mbar_wait_bounded(v_full(b), (gn >> 1) & 1u, p.status, p.wait_limit)) { ok = false; break; }
+                    if (!mbar_wait_bounded(p_full(b), (gn >> 1) & 1u, p.status, p.wait_limit)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t stage = (uint64_t)(b * (kTcStageBytes >> 4));
                     const uint32_t tP = tmem + b * 128, tO = tmem + kTcColO;
