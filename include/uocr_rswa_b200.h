@@ -96,7 +96,9 @@ UOCR_B200_API int uocr_b200_workspace_set_out_dtype(uocr_b200_workspace* ws, int
  * scratch counters the abandoned launch left half-way); the warp lets its copies in flight land and
  * leaves, the kernel ends normally and the results of that launch are void.  Lowering the limit is
  * a diagnostic aid: 0 makes every wait give up at once, which exercises exactly that path without
- * hanging anything.  Applies to the split-KV attention kernels launched with this workspace. */
+ * hanging anything.  Applies to the split-KV attention kernels and to the tensor-core prefill
+ * kernel launched with this workspace (there every role of the CTA gives up at its first wait; the
+ * waits that see issued copies and tensor-core instructions through keep the full limit). */
 UOCR_B200_API int uocr_b200_workspace_set_wait_limit(uocr_b200_workspace* ws, unsigned polls);
 
 /* Opt-in launch overlap for uocr_b200_rswa_decode_step_paged calls that use this workspace.  When
