@@ -196,15 +196,17 @@ def test_prefill_tensor_core_bf16_output(orc, b):
     assert ws.status() == 0
 
 
-def test_prefill_tensor_core_many_items_per_cta_against_cuda_core_path(orc, b):
+@pytest.mark.parametrize("W,t_max", [(1024, 1536), (4096, 6000)])
+def test_prefill_tensor_core_many_items_per_cta_against_cuda_core_path(orc, b, W, t_max):
     # 12 requests with the benchmark's prefix lengths and prompts up to 1.5 windows: ~150 query tiles x 10 heads,
     # i.e. ten items for every persistent CTA, drawn from the counter in longest-first order, with one plan of
     # the tiles shared by two calls.  Too many rows for the scalar oracle; the reference here is the CUDA-core
     # path on the same pools, which the cases above hold to the oracle (its own error is 1e-5).
+    # The second case has windows of 4096 and prompts up to 6000: items of up to 42 key tiles.
     import torch
-    W, heads, kvh, hd = 1024, 10, 10, 128
+    heads, kvh, hd = 10, 10, 128
     prefixes = [256, 656, 1056, 256, 656, 1056, 1056, 256, 656, 1056, 256, 656]
-    text_lens = [int(x) for x in synth.integers(909, 3, 64, 1536, (len(prefixes),))]
+    text_lens = [int(x) for x in synth.integers(909 + W, 3, 64, t_max, (len(prefixes),))]
     slots = len(prefixes)
     pb = PagedBatch(orc, slots, 1, kvh, hd, W, b.BF16, prefixes, heads=heads, seed=909)
     row = kvh * hd
